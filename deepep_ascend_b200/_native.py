@@ -1,0 +1,104 @@
+"""Builds and loads the native extension (C++ runtime + sm_100a kernels).
+
+The extension is built ahead of time into ``deepep_ascend_b200/_ext`` (in-tree, next to the sources) with
+``nvcc -gencode arch=compute_100a,code=sm_100a``; importing the package only loads the shared object.  If the
+object is missing and ``nvcc`` is available it is built on first use.  There is no runtime JIT of kernels:
+shapes are runtime arguments (the reference compiles each shape with nvcc at run time, csrc/jit/compiler.hpp:22-267).
+"""
+import glob
+import importlib.util
+import os
+import sys
+import threading
+from typing import Optional
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+_CSRC = os.path.join(_PKG_DIR, 'csrc')
+_EXT_DIR = os.path.join(_PKG_DIR, '_ext')
+_NAME = 'deepep_b200_C'
+_lock = threading.Lock()
+_module = None
+
+NVCC_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-std=c++17', '-lineinfo',
+              '--expt-relaxed-constexpr', '-Xptxas', '-v']
+CXX_FLAGS = ['-O2', '-std=c++17']
+
+
+def sources():
+    srcs = [os.path.join(_CSRC, 'python_api.cpp')]
+    srcs += sorted(glob.glob(os.path.join(_CSRC, 'kernels', '*.cu')))
+    return srcs
+
+
+def extra_include_paths():
+    """CUTLASS / CuTe headers vendored in site-packages (used by the tcgen05 GEMM kernels for descriptor
+    layouts only)."""
+    paths = [_CSRC]
+    for p in sys.path:
+        cand = os.path.join(p, 'flashinfer', 'data', 'cutlass', 'include')
+        if os.path.isdir(cand):
+            paths.append(cand)
+            break
+    return paths
+
+
+def shared_object() -> Optional[str]:
+    hits = glob.glob(os.path.join(_EXT_DIR, _NAME + '*.so'))
+    return hits[0] if hits else None
+
+
+def build(verbose: bool = False):
+    """Compile every source for sm_100a into ``_ext/`` (incremental through ninja) and load the result."""
+    global _module
+    from torch.utils import cpp_extension
+    os.makedirs(_EXT_DIR, exist_ok=True)
+    os.environ.setdefault('MAX_JOBS', str(os.cpu_count() or 4))
+    with _lock:
+        _module = cpp_extension.load(
+            name=_NAME, sources=sources(), extra_cflags=CXX_FLAGS, extra_cuda_cflags=NVCC_FLAGS,
+            extra_include_paths=extra_include_paths(), extra_ldflags=['-lcuda'],
+            build_directory=_EXT_DIR, verbose=verbose, with_cuda=True)
+    return _module
+
+
+def _stale(so: str) -> bool:
+    so_time = os.path.getmtime(so)
+    for root, _, files in os.walk(_CSRC):
+        for f in files:
+            if os.path.getmtime(os.path.join(root, f)) > so_time:
+                return True
+    return False
+
+
+def load(required: bool = True):
+    """Return the extension module; build it if it is missing or older than its sources and nvcc exists.
+    With ``required=False`` returns ``None`` instead of raising (CPU-only use of the package)."""
+    global _module
+    if _module is not None:
+        return _module
+    import torch  # noqa: F401  (the extension links against libtorch)
+    so = shared_object()
+    from torch.utils.cpp_extension import CUDA_HOME
+    have_nvcc = CUDA_HOME is not None and os.path.exists(os.path.join(CUDA_HOME, 'bin', 'nvcc'))
+    try:
+        if so is not None and not (have_nvcc and _stale(so) and os.environ.get('EP_NO_REBUILD', '0') != '1'):
+            with _lock:
+                spec = importlib.util.spec_from_file_location(_NAME, so)
+                mod = importlib.util.module_from_spec(spec)
+                spec.loader.exec_module(mod)
+                _module = mod
+            return _module
+        if have_nvcc:
+            return build()
+    except Exception:
+        if required:
+            raise
+        return None
+    if required:
+        raise ImportError('deepep_ascend_b200: native extension is not built and nvcc is not available; '
+                          'run `python -c "import __graft_entry__ as g; g.build()"` on a machine with CUDA 12.9')
+    return None
+
+
+def is_available() -> bool:
+    return load(required=False) is not None

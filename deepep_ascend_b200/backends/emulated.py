@@ -1,0 +1,70 @@
+"""Several virtual ranks on ONE GPU in one process.
+
+Kernels of different ranks wait on one another, so they can never be separate launches on one device.  Here every
+collective call of the virtual ranks is issued as ONE cooperative launch whose ``blockIdx.y`` selects the rank;
+each virtual rank has its own symmetric buffer and the peer tables point at the other ranks' buffers.  The device
+code is exactly the code that runs with one process per GPU, which makes this the way to test the multi-rank
+protocol (layout exchange, peer stores, peer pulls, barriers) on a single GPU.
+"""
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..buffers.elastic import ElasticBuffer
+
+
+class EmulatedWorld:
+    def __init__(self, num_ranks: int, **buffer_kwargs):
+        self.num_ranks = num_ranks
+        self.buffers: List[ElasticBuffer] = [
+            ElasticBuffer(None, _virtual=(r, num_ranks), **buffer_kwargs) for r in range(num_ranks)]
+        self._C = self.buffers[0]._C
+        self._C.ElasticBuffer.link_local([b.core for b in self.buffers])
+        torch.cuda.synchronize()
+
+    @property
+    def cores(self):
+        return [b.core for b in self.buffers]
+
+    def max_sms_per_rank(self) -> int:
+        """All virtual ranks' CTAs must be co-resident: one CTA per SM."""
+        return max(1, torch.cuda.get_device_properties('cuda').multi_processor_count // self.num_ranks)
+
+    def dispatch(self, xs: Sequence, topk_idxs: Sequence[Optional[torch.Tensor]], topk_weights: Sequence[Optional[torch.Tensor]],
+                 num_experts: int, num_sms: int = 0, expert_alignment: int = 1, do_expand: bool = False,
+                 do_cpu_sync: bool = True, handles: Optional[Sequence] = None, stats: Optional[Sequence] = None,
+                 use_tma_aligned_col_major_sf: bool = False, do_zero_padding: bool = False):
+        """Per-rank lists in, per-rank list of ``(recv_x, recv_topk_idx, recv_topk_weights, handle)`` out."""
+        num_sms = min(num_sms or 8, self.max_sms_per_rank())
+        states = []
+        for r, b in enumerate(self.buffers):
+            h = handles[r] if handles is not None else None
+            states.append(b._prepare_dispatch(
+                xs[r], None if h is not None else topk_idxs[r], topk_weights[r], stats[r] if stats is not None else None,
+                num_experts, b.num_max_tokens_per_rank, expert_alignment, num_sms, h, True,
+                do_cpu_sync and h is None, do_expand if h is None else h.do_expand, use_tma_aligned_col_major_sf))
+        self._C.ElasticBuffer.dispatch_group(self.cores, [s.call for s in states], num_sms)
+        return [b._finish_dispatch(s, do_zero_padding) for b, s in zip(self.buffers, states)]
+
+    def combine(self, xs: Sequence[torch.Tensor], handles: Sequence, topk_weights: Optional[Sequence] = None,
+                bias0: Optional[Sequence] = None, bias1: Optional[Sequence] = None, weighted: bool = False, num_sms: int = 0):
+        """Per-rank list of ``(combined_x, combined_topk_weights)``."""
+        num_sms = min(num_sms or 8, self.max_sms_per_rank())
+        calls, outs = [], []
+        for r, b in enumerate(self.buffers):
+            call, out, out_w = b._prepare_combine(
+                xs[r], handles[r], topk_weights[r] if topk_weights is not None else None,
+                bias0[r] if bias0 is not None else None, bias1[r] if bias1 is not None else None, weighted)
+            calls.append(call)
+            outs.append((out, out_w))
+        self._C.ElasticBuffer.combine_group(self.cores, calls, num_sms)
+        return outs
+
+    def barrier(self) -> None:
+        self._C.ElasticBuffer.barrier_group(self.cores)
+
+    def destroy(self) -> None:
+        torch.cuda.synchronize()
+        for b in self.buffers:
+            b.core.destroy()
+            b._destroyed = True

@@ -1,0 +1,156 @@
+// Host-visible contract of the CUDA kernels: limits, status words, per-rank context and the argument structs
+// of every launcher.  Plain C++ (no torch, no CUDA headers beyond the runtime API) so that host-only unit
+// tests can include it.
+#pragma once
+#include <cuda_runtime_api.h>
+#include <stdint.h>
+
+#define EP_MAX_RANKS 8
+#define EP_MAX_EXPERTS 1024
+#define EP_MAX_TOPK 16
+#define EP_MAX_CTAS 160
+#define EP_MAX_TILE_FLAGS 16384
+#define EP_WORKSPACE_BYTES (4u << 20)
+#define EP_BUFFER_ALIGNMENT (2u << 20)
+
+// One independent sequence of collective calls per channel (own epoch, own barrier counters), so that e.g.
+// a low-latency step on one stream never aliases an all-gather session on another.
+enum EpChannel {
+    EP_CH_DISPATCH = 0,
+    EP_CH_COMBINE = 1,
+    EP_CH_BARRIER = 2,
+    EP_CH_LL_DISPATCH = 3,
+    EP_CH_LL_COMBINE = 4,
+    EP_CH_AGRS = 5,
+    EP_CH_PP = 6,
+    EP_CH_ENGRAM = 7,
+    EP_CH_GEMM = 8,
+    EP_CH_FUSED = 9,
+    EP_NUM_CHANNELS = 12
+};
+
+// Status block (uint64 words in pinned, device-mapped host memory).
+enum EpStatusWord {
+    EP_STATUS_CODE = 0,
+    EP_STATUS_PHASE = 1,
+    EP_STATUS_PEER = 2,
+    EP_STATUS_EXPECTED = 3,
+    EP_STATUS_OBSERVED = 4,
+    EP_STATUS_RANK = 5,
+    EP_STATUS_NUM_RECV = 8,        // epoch-tagged: rows received by the last dispatch
+    EP_STATUS_NUM_EXPANDED = 9,    // epoch-tagged: rows of the expand layout
+    EP_STATUS_EXPERT_BASE = 16,    // epoch-tagged per-local-expert counts follow
+    EP_STATUS_WORDS = 16 + EP_MAX_EXPERTS
+};
+
+enum EpError { EP_OK = 0, EP_ERR_TIMEOUT = 1, EP_ERR_BOUNDS = 2, EP_ERR_PROTOCOL = 3 };
+
+// Where a wait gave up (EP_STATUS_PHASE).
+enum EpPhase {
+    EP_PH_GRID_SYNC = 1,
+    EP_PH_XGPU_BARRIER = 2,
+    EP_PH_COUNT_EXCHANGE = 3,
+    EP_PH_DISPATCH_LOAD = 4,
+    EP_PH_DISPATCH_DONE = 5,
+    EP_PH_COMBINE_ENTRY = 6,
+    EP_PH_COMBINE_LOAD = 7,
+    EP_PH_COMBINE_EXIT = 8,
+    EP_PH_LL_RECV_COUNT = 9,
+    EP_PH_LL_COMBINE_FLAG = 10,
+    EP_PH_TEST_FLAG = 11,
+    EP_PH_PP = 12,
+    EP_PH_TILE_FLAG = 13,
+    EP_PH_GEMM_PIPE = 14
+};
+
+struct RankCtx {
+    int rank;
+    int num_ranks;
+    uint8_t* peer_base[EP_MAX_RANKS];   // every rank's symmetric buffer as mapped here; [rank] is local
+    uint64_t* status;                   // device pointer of this rank's status block
+    uint64_t timeout_ns;
+};
+
+struct DispatchArgs {
+    RankCtx ctx;
+    // inputs
+    const void* x;                 // [T, H] bf16, or e4m3 when x_is_fp8
+    const float* sf;               // [T, H/128] fp32 scales of pre-quantized input, else null
+    const void* topk_idx;          // [T, K] int64 or int32
+    const float* topk_weights;     // [T, K] or null
+    int num_tokens, hidden, num_topk, num_experts;
+    int idx_is_64;
+    int x_is_fp8;                  // input already e4m3
+    int quantize;                  // bf16 in, e4m3 + 1x128 scales out (fused cast)
+    int do_expand;
+    int expert_alignment;
+    int cached;                    // reuse lane_src / plan of an earlier call
+    int num_max_tokens;            // per rank; src_token_global_idx = rank * num_max_tokens + t
+    // handle tensors (local)
+    int32_t* lane_src;             // [T, K]
+    int32_t* plan;                 // [T, K]
+    int32_t* psum_rank;            // [R]
+    int32_t* psum_expert;          // [E_local]
+    int32_t* recv_per_expert;      // [E_local]
+    int32_t* stats;                // [E_local] cumulative, or null
+    // receive regions: byte offsets inside every rank's symmetric buffer
+    uint64_t off_recv_x, off_recv_sf, off_recv_idx, off_recv_w, off_recv_meta;
+    int64_t sf_stride_row, sf_stride_col;   // element strides of the receiver's scale tensor
+    int recv_capacity_rows;
+};
+
+struct CombineArgs {
+    RankCtx ctx;
+    uint64_t off_x;                // combine input rows [rows, H] bf16 inside every rank's symmetric buffer
+    uint64_t off_w;                // optional weights to carry back (fp32), 0 when unused
+    int w_cols;                    // K (non-expand) or 1 (expand)
+    const int32_t* plan;           // [T, K]
+    const int32_t* lane_src;       // [T, K]
+    const float* mul_weights;      // [T, K] multiply rows by these (weighted reduce), or null
+    const void* bias0;             // [T, H] bf16 or null
+    const void* bias1;
+    void* out;                     // [T, H] bf16
+    float* out_w;                  // [T, K] or null
+    int num_tokens, hidden, num_topk;
+};
+
+struct LayoutArgs {
+    const void* topk_idx;
+    int idx_is_64;
+    int num_tokens, num_topk, num_experts, num_ranks;
+    int32_t* num_tokens_per_rank;     // [R]
+    int32_t* num_tokens_per_expert;   // [E]
+    uint8_t* is_token_in_rank;        // [T, R] bool
+};
+
+struct QuantArgs {
+    const void* x;        // [T, H] bf16
+    void* q;              // [T, H] e4m3
+    float* sf;            // [T, H/128] fp32 (or packed UE8M0 int32 [T, ceil(H/512)])
+    int num_tokens, hidden;
+    int round_scale, use_ue8m0;
+    int64_t sf_stride_row, sf_stride_col;
+};
+
+namespace ep {
+
+struct LaunchShape {
+    int num_ctas;
+    int num_warps;
+    int smem_bytes;
+};
+
+// Every launcher takes `n` argument structs: n == 1 is the production path (this process drives one GPU);
+// n > 1 runs n virtual ranks that all live on the current device as ONE cooperative launch (gridDim.y = n),
+// which is how the multi-rank protocol is exercised on a single GPU.
+cudaError_t launch_dispatch(const DispatchArgs* args, int n, int num_sms, cudaStream_t stream);
+cudaError_t launch_combine(const CombineArgs* args, int n, int num_sms, cudaStream_t stream);
+cudaError_t launch_barrier(const RankCtx* ctxs, int n, cudaStream_t stream);
+cudaError_t launch_wait_flag_test(const RankCtx* ctxs, int n, uint64_t expected, cudaStream_t stream);
+cudaError_t launch_layout(const LayoutArgs& args, cudaStream_t stream);
+cudaError_t launch_quant(const QuantArgs& args, cudaStream_t stream);
+
+LaunchShape dispatch_launch_shape(const DispatchArgs& a, int num_sms);
+LaunchShape combine_launch_shape(const CombineArgs& a, int num_sms);
+
+}  // namespace ep

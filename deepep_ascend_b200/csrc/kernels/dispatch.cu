@@ -1,0 +1,548 @@
+// Expert-parallel dispatch for one NVLink domain, as ONE kernel per call:
+//
+//   1. layout   - every CTA counts, for its slice of tokens, the rows it will send to each rank (a token
+//                 counts once per rank) and the selections of each expert;
+//   2. exchange - CTA 0 publishes this rank's totals into every peer's workspace as epoch-tagged words and
+//                 every CTA waits for all ranks' totals (this is also the entry barrier: a peer's totals
+//                 arrive only once the peer has entered the same call);
+//   3. assign   - prefix sums turn the counts into FINAL row numbers in the receivers' output tensors, in
+//                 (source rank, token) order, so the result is deterministic and needs no second pass;
+//   4. scatter  - per token: TMA bulk load into shared memory, optional fused bf16 -> e4m3 cast with 1x128
+//                 scales, then one bulk store per destination rank straight into that rank's recv_x through
+//                 its peer mapping, plus small direct stores for scales / expert ids / weights / metadata;
+//   5. finish   - drain the bulk stores, grid barrier, cross-GPU arrival signal, wait for all peers' signals.
+//
+// Parity: does the work of dispatch_impl + dispatch_copy_epilogue_impl
+// (deep_ep/include/deep_ep/impls/dispatch.cuh:17-409, dispatch_copy_epilogue.cuh:11-323) and of the fused
+// FP8 cast of the legacy low-latency kernel (csrc/kernels/legacy/internode_ll.cu:212-250).
+#include "common.cuh"
+
+namespace ep {
+
+namespace {
+
+constexpr int kDispatchMaxWarps = 12;
+constexpr int kDispatchSmemBudget = 220 * 1024;
+
+struct DispatchSmemPlan {
+    int off_peer;       // uint8_t* [EP_MAX_RANKS]
+    int off_tot;        // uint32 [E]   expert totals over sources
+    int off_before;     // uint32 [E]   selections from lower source ranks
+    int off_start;      // uint32 [E]   first row of each expert at its rank
+    int off_wc_rank;    // uint32 [W][R]
+    int off_wc_expert;  // uint32 [W][E]
+    int off_bar;        // uint64 [W][2]
+    int off_sf;         // float  [W][2][G]
+    int off_stage;      // per warp: stage buffers
+    int in_bytes, out_bytes, n_in, n_out, warp_stage_bytes;
+    int total;
+};
+
+__host__ __device__ inline int align_int(int x, int a) { return (x + a - 1) / a * a; }
+
+__host__ __device__ inline DispatchSmemPlan make_smem_plan(const DispatchArgs& a, int num_warps) {
+    DispatchSmemPlan p;
+    const int E = a.num_experts, R = a.ctx.num_ranks;
+    const int G = (a.hidden + 127) / 128;
+    int off = 0;
+    p.off_peer = off;       off += EP_MAX_RANKS * 8;
+    p.off_tot = off;        off += align_int(E * 4, 16);
+    p.off_before = off;     off += align_int(E * 4, 16);
+    p.off_start = off;      off += align_int(E * 4, 16);
+    p.off_wc_rank = off;    off += align_int(num_warps * R * 4, 16);
+    p.off_wc_expert = off;  off += align_int(num_warps * E * 4, 16);
+    p.off_bar = off;        off += num_warps * 2 * 8;
+    p.off_sf = off;         off += align_int(num_warps * 2 * G * 4, 16);
+    off = align_int(off, 128);
+    p.off_stage = off;
+    const int in_row = a.hidden * (a.x_is_fp8 ? 1 : 2);
+    p.in_bytes = align_int(in_row, 128);
+    if (a.quantize) {
+        p.out_bytes = align_int(a.hidden, 128);
+        p.n_in = 1;
+        p.n_out = 2;
+    } else {
+        p.out_bytes = 0;
+        p.n_in = 2;
+        p.n_out = 0;
+    }
+    p.warp_stage_bytes = p.n_in * p.in_bytes + p.n_out * p.out_bytes;
+    p.total = off + num_warps * p.warp_stage_bytes;
+    return p;
+}
+
+__device__ __forceinline__ int load_idx(const DispatchArgs& a, int t, int k) {
+    const int64_t i = static_cast<int64_t>(t) * a.num_topk + k;
+    return a.idx_is_64 ? static_cast<int>(__ldg(reinterpret_cast<const long long*>(a.topk_idx) + i))
+                       : __ldg(reinterpret_cast<const int*>(a.topk_idx) + i);
+}
+
+struct Slice {
+    int begin, end;
+};
+
+// Contiguous token slice of (cta, warp); warp slices are multiples of the tokens handled per layout step.
+__device__ __forceinline__ Slice warp_slice(int T, int K, int num_warps, int warp) {
+    const int chunk = (T + gridDim.x - 1) / gridDim.x;
+    const int cta_begin = min(T, static_cast<int>(blockIdx.x) * chunk);
+    const int cta_end = min(T, cta_begin + chunk);
+    const int tps = 32 / K;
+    int sub = (chunk + num_warps - 1) / num_warps;
+    sub = (sub + tps - 1) / tps * tps;
+    Slice s;
+    s.begin = min(cta_end, cta_begin + warp * sub);
+    s.end = min(cta_end, s.begin + sub);
+    return s;
+}
+
+// One pass over the warp's tokens, `32 / K` tokens per step with lane = (token_in_step, top-k lane).
+// kAssign == false: count into the warp's private counters.
+// kAssign == true : the counters hold the first row for this warp; hand out rows in (token, lane) order.
+template <bool kAssign>
+__device__ __forceinline__ void layout_pass(const DispatchArgs& a, Slice sl, uint32_t* wc_rank, uint32_t* wc_expert) {
+    const int K = a.num_topk, R = a.ctx.num_ranks, E = a.num_experts, El = E / R;
+    const int lane = ptx::lane_id();
+    const int tps = 32 / K;
+    const int ts = lane / K, k = lane - ts * K;
+    const uint32_t lt = ptx::lanemask_lt();
+    for (int t0 = sl.begin; t0 < sl.end; t0 += tps) {
+        const int t = t0 + ts;
+        const bool active = ts < tps && t < sl.end;
+        const int e = active ? load_idx(a, t, k) : -1;
+        const bool valid = e >= 0 && e < E;
+        const int r = valid ? e / El : -1;
+        const uint32_t peers_tr = __match_any_sync(0xffffffffu, valid ? (ts * EP_MAX_RANKS + r) : (1024 + lane));
+        const int master = 31 - __clz(peers_tr);
+        const bool is_last = valid && lane == master;
+        if (!kAssign) {
+            if (valid) atomicAdd(&wc_expert[e], 1u);
+            if (is_last) atomicAdd(&wc_rank[r], 1u);
+        } else {
+            int packed;
+            if (a.do_expand) {
+                const uint32_t peers = __match_any_sync(0xffffffffu, valid ? e : (0x10000 + lane));
+                const int leader = __ffs(peers) - 1;
+                uint32_t old = 0;
+                if (valid && lane == leader) {
+                    old = wc_expert[e];
+                    wc_expert[e] = old + __popc(peers);
+                }
+                old = __shfl_sync(0xffffffffu, old, leader);
+                const uint32_t row = old + __popc(peers & lt);
+                packed = valid ? static_cast<int>((static_cast<uint32_t>(r) << 24) | row) : -1;
+                if (active) {
+                    a.lane_src[static_cast<int64_t>(t) * K + k] = packed;
+                    a.plan[static_cast<int64_t>(t) * K + k] = packed;
+                }
+            } else {
+                const uint32_t peers = __match_any_sync(0xffffffffu, is_last ? r : (1024 + lane));
+                const int leader = __ffs(peers) - 1;
+                uint32_t old = 0;
+                if (is_last && lane == leader) {
+                    old = wc_rank[r];
+                    wc_rank[r] = old + __popc(peers);
+                }
+                old = __shfl_sync(0xffffffffu, old, leader);
+                uint32_t row = old + __popc(peers & lt);
+                row = __shfl_sync(0xffffffffu, row, master);
+                packed = valid ? static_cast<int>((static_cast<uint32_t>(r) << 24) | row) : -1;
+                if (active) {
+                    a.lane_src[static_cast<int64_t>(t) * K + k] = packed;
+                    a.plan[static_cast<int64_t>(t) * K + k] = is_last ? packed : -1;
+                }
+            }
+            __syncwarp();
+        }
+    }
+    __syncwarp();
+}
+
+__device__ __forceinline__ uint32_t count_of(uint64_t word) { return static_cast<uint32_t>(word & 0xffffffffull); }
+
+// bf16 row in shared memory -> e4m3 row + one fp32 scale per 128 channels.
+// q = x * (448 / max(amax, 1e-4)) rounded to nearest even, scale = max(amax, 1e-4) / 448.
+__device__ __forceinline__ void quantize_row(const uint8_t* in, uint8_t* out, float* sf, int H) {
+    const int lane = ptx::lane_id();
+    const int iters = (H + 255) / 256;
+    for (int i = 0; i < iters; ++i) {
+        const int elem = (i * 32 + lane) * 8;
+        const bool in_range = elem < H;
+        float v[8];
+        if (in_range) {
+            const int4 raw = *reinterpret_cast<const int4*>(in + elem * 2);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h[j]);
+                v[2 * j] = f.x;
+                v[2 * j + 1] = f.y;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.f;
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        amax = fmaxf(ptx::warp_max_16(amax), 1e-4f);
+        const float scale = __fdiv_rn(448.f, amax);
+        if (in_range) {
+            uint32_t packed[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j] * scale, v[4 * j + 1] * scale),
+                                                              __NV_SATFINITE, __NV_E4M3);
+                const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                    make_float2(v[4 * j + 2] * scale, v[4 * j + 3] * scale), __NV_SATFINITE, __NV_E4M3);
+                packed[j] = lo | (hi << 16);
+            }
+            *reinterpret_cast<uint2*>(out + elem) = make_uint2(packed[0], packed[1]);
+            if ((lane & 15) == 0) sf[elem / 128] = __fdiv_rn(amax, 448.f);
+        }
+    }
+}
+
+template <bool kQuant>
+__device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const RankCtx& ctx = a.ctx;
+    Workspace* ws = local_ws(ctx);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int num_warps = blockDim.x >> 5, nthreads = blockDim.x;
+    const int cta = blockIdx.x, num_ctas = gridDim.x;
+    const int R = ctx.num_ranks, me = ctx.rank, E = a.num_experts, El = E / R, K = a.num_topk, T = a.num_tokens;
+    const int G = (a.hidden + 127) / 128;
+    const DispatchSmemPlan sp = make_smem_plan(a, num_warps);
+
+    uint8_t** s_peer = reinterpret_cast<uint8_t**>(smem + sp.off_peer);
+    uint32_t* s_tot = reinterpret_cast<uint32_t*>(smem + sp.off_tot);
+    uint32_t* s_before = reinterpret_cast<uint32_t*>(smem + sp.off_before);
+    uint32_t* s_start = reinterpret_cast<uint32_t*>(smem + sp.off_start);
+    uint32_t* s_wc_rank = reinterpret_cast<uint32_t*>(smem + sp.off_wc_rank);
+    uint32_t* s_wc_expert = reinterpret_cast<uint32_t*>(smem + sp.off_wc_expert);
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + sp.off_bar) + warp * 2;
+    float* s_sf = reinterpret_cast<float*>(smem + sp.off_sf) + warp * 2 * G;
+    uint8_t* s_stage = smem + sp.off_stage + warp * sp.warp_stage_bytes;
+
+    const uint64_t epoch = ws->epoch[EP_CH_DISPATCH] + 1;
+    if (tid < EP_MAX_RANKS) s_peer[tid] = tid < R ? ctx.peer_base[tid] : nullptr;
+    if (lane == 0) {
+        ptx::mbar_init(&s_bar[0], 1);
+        ptx::mbar_init(&s_bar[1], 1);
+    }
+    ptx::mbar_fence_init();
+    for (int i = tid; i < num_warps * R; i += nthreads) s_wc_rank[i] = 0;
+    for (int i = tid; i < num_warps * E; i += nthreads) s_wc_expert[i] = 0;
+    __syncthreads();
+    ptx::fence_proxy_async_smem();
+
+    const Slice sl = warp_slice(T, K, num_warps, warp);
+    bool alive = !is_aborted(ws);
+
+    if (!a.cached) {
+        // ---------------------------------------------------------------- 1. layout (counts)
+        layout_pass<false>(a, sl, s_wc_rank + warp * R, s_wc_expert + warp * E);
+        __syncthreads();
+        for (int i = tid; i < E + R; i += nthreads) {
+            uint32_t tot = 0;
+            if (i < E) {
+                for (int w = 0; w < num_warps; ++w) tot += s_wc_expert[w * E + i];
+                __stcg(&ws->cta_expert_count[cta][i], tot);
+            } else {
+                for (int w = 0; w < num_warps; ++w) tot += s_wc_rank[w * R + (i - E)];
+                __stcg(&ws->cta_rank_count[cta][i - E], tot);
+            }
+        }
+        alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && alive;
+
+        // ---------------------------------------------------------------- 2. exchange
+        if (alive && cta == 0) {
+            for (int i = tid; i < E + R; i += nthreads) {
+                uint32_t tot = 0;
+                for (int c = 0; c < num_ctas; ++c)
+                    tot += i < E ? __ldcg(&ws->cta_expert_count[c][i]) : __ldcg(&ws->cta_rank_count[c][i - E]);
+                const uint64_t word = tag_value(epoch, tot);
+                for (int p = 0; p < R; ++p) {
+                    Workspace* pws = reinterpret_cast<Workspace*>(s_peer[p]);
+                    ptx::st_relaxed_sys(i < E ? &pws->disp_expert_count[me][i] : &pws->disp_rank_count[me][i - E],
+                                        word);
+                }
+            }
+        }
+        const bool need_experts = a.do_expand || cta == 0;
+        int ok = alive ? 1 : 0;
+        if (alive) {
+            for (int i = tid; i < R * R && ok; i += nthreads) {
+                const uint64_t* slot = &ws->disp_rank_count[i / R][i % R];
+                ok = bounded_wait(
+                    ctx, ws, EP_PH_COUNT_EXCHANGE, i / R, epoch,
+                    [&] { return tag_matches(ptx::ld_relaxed_sys(slot), epoch); },
+                    [&] { return ptx::ld_relaxed_sys(slot); });
+            }
+            if (need_experts) {
+                for (int i = tid; i < R * E && ok; i += nthreads) {
+                    const uint64_t* slot = &ws->disp_expert_count[i / E][i % E];
+                    ok = bounded_wait(
+                        ctx, ws, EP_PH_COUNT_EXCHANGE, i / E, epoch,
+                        [&] { return tag_matches(ptx::ld_relaxed_sys(slot), epoch); },
+                        [&] { return ptx::ld_relaxed_sys(slot); });
+                }
+            }
+        }
+        alive = __syncthreads_and(ok) != 0;
+
+        // ---------------------------------------------------------------- 3. assign: counts -> first rows
+        if (alive) {
+            if (!a.do_expand && tid < R) {
+                const int d = tid;
+                uint32_t running = 0;
+                for (int s = 0; s < me; ++s) running += count_of(ptx::ld_relaxed_sys(&ws->disp_rank_count[s][d]));
+                for (int c = 0; c < cta; ++c) running += __ldcg(&ws->cta_rank_count[c][d]);
+                for (int w = 0; w < num_warps; ++w) {
+                    const uint32_t n = s_wc_rank[w * R + d];
+                    s_wc_rank[w * R + d] = running;
+                    running += n;
+                }
+            }
+            if (need_experts) {
+                for (int e = tid; e < E; e += nthreads) {
+                    uint32_t tot = 0, before = 0;
+                    for (int s = 0; s < R; ++s) {
+                        const uint32_t n = count_of(ptx::ld_relaxed_sys(&ws->disp_expert_count[s][e]));
+                        tot += n;
+                        if (s < me) before += n;
+                    }
+                    s_tot[e] = tot;
+                    s_before[e] = before;
+                }
+                __syncthreads();
+                if (tid < R) {
+                    const uint32_t A = max(1, a.expert_alignment);
+                    uint32_t end = 0;
+                    for (int j = 0; j < El; ++j) {
+                        const uint32_t start = (end + A - 1) / A * A;
+                        s_start[tid * El + j] = start;
+                        end = start + s_tot[tid * El + j];
+                    }
+                }
+                __syncthreads();
+                if (a.do_expand) {
+                    for (int e = tid; e < E; e += nthreads) {
+                        uint32_t running = s_start[e] + s_before[e];
+                        for (int c = 0; c < cta; ++c) running += __ldcg(&ws->cta_expert_count[c][e]);
+                        for (int w = 0; w < num_warps; ++w) {
+                            const uint32_t n = s_wc_expert[w * E + e];
+                            s_wc_expert[w * E + e] = running;
+                            running += n;
+                        }
+                    }
+                }
+                if (cta == 0) {
+                    // what this rank receives: handle tensors + host-visible counters
+                    volatile uint64_t* st = ctx.status;
+                    const uint32_t A = max(1, a.expert_alignment);
+                    for (int j = tid; j < El; j += nthreads) {
+                        const uint32_t n = s_tot[me * El + j];
+                        a.recv_per_expert[j] = n;
+                        if (a.stats != nullptr) a.stats[j] += n;
+                        st[EP_STATUS_EXPERT_BASE + j] = tag_value(epoch, n);
+                    }
+                    if (tid == 0) {
+                        uint32_t psum = 0;
+                        for (int s = 0; s < R; ++s) {
+                            psum += count_of(ptx::ld_relaxed_sys(&ws->disp_rank_count[s][me]));
+                            a.psum_rank[s] = psum;
+                        }
+                        uint32_t acc = 0, end = 0;
+                        for (int j = 0; j < El; ++j) {
+                            const uint32_t n = s_tot[me * El + j];
+                            if (a.do_expand) {
+                                end = s_start[me * El + j] + n;
+                                a.psum_expert[j] = end;
+                            } else {
+                                acc += (n + A - 1) / A * A;
+                                a.psum_expert[j] = acc;
+                            }
+                        }
+                        st[EP_STATUS_NUM_EXPANDED] = tag_value(epoch, a.do_expand ? (end + A - 1) / A * A : 0);
+                        st[EP_STATUS_NUM_RECV] = tag_value(epoch, psum);
+                        __threadfence_system();
+                    }
+                }
+            }
+            __syncthreads();
+            layout_pass<true>(a, sl, s_wc_rank + warp * R, s_wc_expert + warp * E);
+        }
+    } else {
+        // cached layout: only the entry barrier (receivers must be done with the previous contents)
+        if (cta == 0) alive = xgpu_barrier(ctx, ws, EP_CH_DISPATCH, EP_PH_XGPU_BARRIER) && alive;
+        alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && alive;
+    }
+
+    // -------------------------------------------------------------------- 4. scatter
+    if (alive) {
+        const int in_row = a.hidden * (a.x_is_fp8 ? 1 : 2);
+        const int out_row = kQuant ? a.hidden : in_row;
+        const int idx_bytes = a.idx_is_64 ? 8 : 4;
+        const bool has_sf = kQuant || a.sf != nullptr;
+        uint8_t* in_stage = s_stage;
+        uint8_t* out_stage = s_stage + sp.n_in * sp.in_bytes;
+        const uint8_t* xb = reinterpret_cast<const uint8_t*>(a.x);
+        const int count = sl.end - sl.begin;
+        if (count > 0 && lane == 0) {
+            ptx::mbar_arrive_expect_tx(&s_bar[0], in_row);
+            ptx::bulk_load(in_stage, xb + static_cast<int64_t>(sl.begin) * in_row, in_row, &s_bar[0]);
+        }
+        for (int n = 0; n < count && alive; ++n) {
+            const int t = sl.begin + n;
+            const int st = kQuant ? 0 : (n & 1);
+            const uint32_t parity = kQuant ? (n & 1) : ((n >> 1) & 1);
+            int e_k = -1, plan_k = -1;
+            float w_k = 0.f;
+            if (lane < K) {
+                e_k = load_idx(a, t, lane);
+                plan_k = a.plan[static_cast<int64_t>(t) * K + lane];
+                if (a.topk_weights != nullptr) w_k = __ldg(a.topk_weights + static_cast<int64_t>(t) * K + lane);
+            }
+            float* sf_cur = s_sf + (n & 1) * G;
+            if (!kQuant && has_sf)
+                for (int j = lane; j < G; j += 32) sf_cur[j] = __ldg(a.sf + static_cast<int64_t>(t) * G + j);
+            alive = mbar_wait_bounded(ctx, ws, &s_bar[st], parity, EP_PH_DISPATCH_LOAD);
+            if (!alive) break;
+            const uint8_t* src_smem;
+            if (kQuant) {
+                // the out stage about to be overwritten was read by the stores of token n-2
+                ptx::bulk_wait_read<1>();
+                __syncwarp();
+                uint8_t* o = out_stage + (n & 1) * sp.out_bytes;
+                quantize_row(in_stage, o, sf_cur, a.hidden);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (n + 1 < count && lane == 0) {
+                    ptx::mbar_arrive_expect_tx(&s_bar[0], in_row);
+                    ptx::bulk_load(in_stage, xb + static_cast<int64_t>(t + 1) * in_row, in_row, &s_bar[0]);
+                }
+                src_smem = o;
+            } else {
+                src_smem = in_stage + st * sp.in_bytes;
+                __syncwarp();
+            }
+            // one bulk store per destination row, issued by the lane that owns the plan entry
+            if (plan_k >= 0) {
+                const int d = plan_k >> 24, row = plan_k & 0xffffff;
+                if (row < a.recv_capacity_rows) {
+                    ptx::bulk_store(s_peer[d] + a.off_recv_x + static_cast<int64_t>(row) * out_row, src_smem, out_row);
+                } else {
+                    report_failure(ctx, ws, EP_ERR_BOUNDS, EP_PH_DISPATCH_LOAD, d, a.recv_capacity_rows, row);
+                    plan_k = -1;
+                }
+            }
+            ptx::bulk_commit();
+            // small per-row pieces go out as plain peer stores
+            uint32_t sends = __ballot_sync(0xffffffffu, plan_k >= 0);
+            while (sends) {
+                const int k = __ffs(sends) - 1;
+                sends &= sends - 1;
+                const int p = __shfl_sync(0xffffffffu, plan_k, k);
+                const int d = p >> 24;
+                const int64_t row = p & 0xffffff;
+                uint8_t* base = s_peer[d];
+                if (has_sf) {
+                    float* dst = reinterpret_cast<float*>(base + a.off_recv_sf);
+                    for (int j = lane; j < G; j += 32) dst[row * a.sf_stride_row + j * a.sf_stride_col] = sf_cur[j];
+                }
+                if (a.do_expand) {
+                    const float w = __shfl_sync(0xffffffffu, w_k, k);
+                    if (lane == 0) {
+                        if (a.topk_weights != nullptr) reinterpret_cast<float*>(base + a.off_recv_w)[row] = w;
+                        reinterpret_cast<int2*>(base + a.off_recv_meta)[row] = make_int2(me * a.num_max_tokens + t, me * K + k);
+                    }
+                } else {
+                    if (lane < K) {
+                        const int lo = d * El;
+                        const int local = (e_k >= lo && e_k < lo + El) ? e_k - lo : -1;
+                        uint8_t* ip = base + a.off_recv_idx + (row * K + lane) * idx_bytes;
+                        if (a.idx_is_64) *reinterpret_cast<long long*>(ip) = local;
+                        else *reinterpret_cast<int*>(ip) = local;
+                        if (a.topk_weights != nullptr) reinterpret_cast<float*>(base + a.off_recv_w)[row * K + lane] = w_k;
+                    }
+                    if (lane == 0)
+                        reinterpret_cast<int2*>(base + a.off_recv_meta)[row] = make_int2(me * a.num_max_tokens + t, me * K + k);
+                }
+            }
+            if (!kQuant) {
+                // the other stage was read by the stores of token n-1: free it, then prefetch token n+1
+                ptx::bulk_wait_read<1>();
+                __syncwarp();
+                if (n + 1 < count && lane == 0) {
+                    ptx::mbar_arrive_expect_tx(&s_bar[st ^ 1], in_row);
+                    ptx::bulk_load(in_stage + (st ^ 1) * sp.in_bytes, xb + static_cast<int64_t>(t + 1) * in_row, in_row,
+                                   &s_bar[st ^ 1]);
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------------ 5. finish
+    ptx::bulk_commit();
+    ptx::bulk_wait<0>();
+    __threadfence_system();
+    const bool cta_ok = __syncthreads_and(alive ? 1 : 0) != 0;
+    alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && cta_ok;
+    if (cta == 0) {
+        if (alive) alive = xgpu_barrier(ctx, ws, EP_CH_DISPATCH, EP_PH_DISPATCH_DONE);
+        if (tid == 0) ws->epoch[EP_CH_DISPATCH] = epoch;
+    }
+}
+
+template <bool kQuant>
+__global__ void __launch_bounds__(kDispatchMaxWarps * 32, 1) dispatch_kernel(const __grid_constant__ DispatchArgs args) {
+    dispatch_body<kQuant>(args);
+}
+
+// n virtual ranks on one device: blockIdx.y selects the rank
+template <bool kQuant>
+__global__ void __launch_bounds__(kDispatchMaxWarps * 32, 1) dispatch_kernel_multi(const DispatchArgs* args) {
+    dispatch_body<kQuant>(args[blockIdx.y]);
+}
+
+}  // namespace
+
+LaunchShape dispatch_launch_shape(const DispatchArgs& a, int num_sms) {
+    LaunchShape s;
+    s.num_ctas = num_sms < 1 ? 1 : (num_sms > EP_MAX_CTAS ? EP_MAX_CTAS : num_sms);
+    // as many warps (each with its own staging ring) as fit in shared memory; the token-per-step layout
+    // needs at least one warp
+    s.num_warps = kDispatchMaxWarps;
+    while (s.num_warps > 1 && make_smem_plan(a, s.num_warps).total > kDispatchSmemBudget) --s.num_warps;
+    s.smem_bytes = make_smem_plan(a, s.num_warps).total;
+    return s;
+}
+
+cudaError_t launch_dispatch(const DispatchArgs* args, int n, int num_sms, cudaStream_t stream) {
+    const DispatchArgs& a0 = args[0];
+    const LaunchShape shape = dispatch_launch_shape(a0, num_sms);
+    if (shape.smem_bytes > 227 * 1024) return cudaErrorInvalidValue;
+    const void* fn;
+    if (n == 1) fn = a0.quantize ? (const void*)dispatch_kernel<true> : (const void*)dispatch_kernel<false>;
+    else fn = a0.quantize ? (const void*)dispatch_kernel_multi<true> : (const void*)dispatch_kernel_multi<false>;
+    cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, shape.smem_bytes);
+    if (err != cudaSuccess) return err;
+    dim3 grid(shape.num_ctas, n, 1), block(shape.num_warps * 32, 1, 1);
+    if (n == 1) {
+        void* params[] = {const_cast<DispatchArgs*>(&a0)};
+        return cudaLaunchCooperativeKernel(fn, grid, block, params, shape.smem_bytes, stream);
+    }
+    DispatchArgs* dev = nullptr;
+    err = cudaMallocAsync(reinterpret_cast<void**>(&dev), sizeof(DispatchArgs) * n, stream);
+    if (err != cudaSuccess) return err;
+    err = cudaMemcpyAsync(dev, args, sizeof(DispatchArgs) * n, cudaMemcpyHostToDevice, stream);
+    if (err == cudaSuccess) {
+        void* params[] = {&dev};
+        err = cudaLaunchCooperativeKernel(fn, grid, block, params, shape.smem_bytes, stream);
+    }
+    cudaFreeAsync(dev, stream);
+    return err;
+}
+
+}  // namespace ep

@@ -1,0 +1,179 @@
+// Small stand-alone kernels: the cross-GPU barrier, a bounded-wait self test, the routing-layout kernel behind
+// get_dispatch_layout, and a stand-alone bf16 -> e4m3 (1x128 scales) cast.
+// Parity: barrier_impl (deep_ep/include/deep_ep/impls/barrier.cuh:11-40), get_dispatch_layout
+// (csrc/kernels/legacy/layout.cu:10-150), per_token_cast_to_fp8 (deep_ep/utils/math.py:30-39).
+#include "common.cuh"
+
+namespace ep {
+
+namespace {
+
+__device__ __forceinline__ void barrier_body(const RankCtx& ctx) {
+    Workspace* ws = local_ws(ctx);
+    if (is_aborted(ws)) return;
+    xgpu_barrier(ctx, ws, EP_CH_BARRIER, EP_PH_XGPU_BARRIER);
+    if (threadIdx.x == 0) ws->epoch[EP_CH_BARRIER] += 1;
+}
+__global__ void barrier_kernel(const __grid_constant__ RankCtx ctx) { barrier_body(ctx); }
+__global__ void barrier_kernel_multi(const RankCtx* ctxs) { barrier_body(ctxs[blockIdx.y]); }
+
+// Waits (bounded) until tile_flags[0] of the local workspace reaches `expected`.  Nothing in the library sets
+// that word, so with a short limit this exercises the timeout -> status -> abort path without any fault.
+__device__ __forceinline__ void wait_flag_body(const RankCtx& ctx, uint64_t expected) {
+    Workspace* ws = local_ws(ctx);
+    const uint64_t* flag = &ws->tile_flags[0];
+    if (threadIdx.x == 0)
+        bounded_wait(
+            ctx, ws, EP_PH_TEST_FLAG, ctx.rank, expected, [&] { return ptx::ld_acquire_sys(flag) >= expected; },
+            [&] { return ptx::ld_relaxed_sys(flag); });
+}
+__global__ void wait_flag_kernel(const __grid_constant__ RankCtx ctx, uint64_t expected) { wait_flag_body(ctx, expected); }
+__global__ void wait_flag_kernel_multi(const RankCtx* ctxs, uint64_t expected) { wait_flag_body(ctxs[blockIdx.y], expected); }
+
+// One thread per token; block-level shared histograms, then one global atomic per (block, bin).
+__global__ void layout_kernel(const LayoutArgs a) {
+    extern __shared__ uint32_t hist[];   // [E + R]
+    const int E = a.num_experts, R = a.num_ranks, K = a.num_topk, El = E / R;
+    for (int i = threadIdx.x; i < E + R; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < a.num_tokens) {
+        uint32_t rank_mask = 0;
+        for (int k = 0; k < K; ++k) {
+            const int64_t i = static_cast<int64_t>(t) * K + k;
+            const int e = a.idx_is_64 ? static_cast<int>(reinterpret_cast<const long long*>(a.topk_idx)[i])
+                                      : reinterpret_cast<const int*>(a.topk_idx)[i];
+            if (e >= 0 && e < E) {
+                atomicAdd(&hist[e], 1u);
+                rank_mask |= 1u << (e / El);
+            }
+        }
+        for (int r = 0; r < R; ++r) {
+            const bool in = (rank_mask >> r) & 1u;
+            a.is_token_in_rank[static_cast<int64_t>(t) * R + r] = in;
+            if (in) atomicAdd(&hist[E + r], 1u);
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < E + R; i += blockDim.x) {
+        const uint32_t n = hist[i];
+        if (n == 0) continue;
+        if (i < E) atomicAdd(reinterpret_cast<unsigned int*>(a.num_tokens_per_expert) + i, n);
+        else atomicAdd(reinterpret_cast<unsigned int*>(a.num_tokens_per_rank) + (i - E), n);
+    }
+}
+
+// One warp per token row; 16 lanes share one 128-channel scale.
+__global__ void quant_kernel(const QuantArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= a.num_tokens) return;
+    const int H = a.hidden;
+    const uint8_t* in = reinterpret_cast<const uint8_t*>(a.x) + static_cast<int64_t>(t) * H * 2;
+    uint8_t* out = reinterpret_cast<uint8_t*>(a.q) + static_cast<int64_t>(t) * H;
+    const int iters = (H + 255) / 256;
+    for (int i = 0; i < iters; ++i) {
+        const int elem = (i * 32 + lane) * 8;
+        const bool in_range = elem < H;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = 0.f;
+        if (in_range) {
+            const int4 raw = ptx::ld_nc_v4(in + elem * 2);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h[j]);
+                v[2 * j] = f.x;
+                v[2 * j + 1] = f.y;
+            }
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        amax = fmaxf(ptx::warp_max_16(amax), 1e-4f);
+        float scale, sf;
+        if (a.round_scale || a.use_ue8m0) {
+            // dequantization factor rounded up to a power of two
+            const float raw = __fdiv_rn(amax, 448.f);
+            const int exp = static_cast<int>((__float_as_uint(raw) >> 23) & 0xff) + ((__float_as_uint(raw) & 0x7fffff) ? 1 : 0);
+            sf = __uint_as_float(static_cast<uint32_t>(exp) << 23);
+            scale = __uint_as_float(static_cast<uint32_t>(254 - exp) << 23);
+        } else {
+            scale = __fdiv_rn(448.f, amax);
+            sf = __fdiv_rn(amax, 448.f);
+        }
+        if (in_range) {
+            uint32_t packed[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j] * scale, v[4 * j + 1] * scale),
+                                                              __NV_SATFINITE, __NV_E4M3);
+                const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                    make_float2(v[4 * j + 2] * scale, v[4 * j + 3] * scale), __NV_SATFINITE, __NV_E4M3);
+                packed[j] = lo | (hi << 16);
+            }
+            *reinterpret_cast<uint2*>(out + elem) = make_uint2(packed[0], packed[1]);
+            if ((lane & 15) == 0) {
+                const int g = elem / 128;
+                if (a.use_ue8m0) {
+                    uint8_t* p = reinterpret_cast<uint8_t*>(a.sf) + (static_cast<int64_t>(t) * a.sf_stride_row + (g / 4) * a.sf_stride_col) * 4 + (g & 3);
+                    *p = static_cast<uint8_t>(__float_as_uint(sf) >> 23);
+                } else {
+                    a.sf[static_cast<int64_t>(t) * a.sf_stride_row + g * a.sf_stride_col] = sf;
+                }
+            }
+        }
+    }
+}
+
+template <typename T>
+cudaError_t launch_small(const void* single, const void* multi, const T* items, int n, dim3 block, cudaStream_t stream,
+                         uint64_t extra, bool has_extra) {
+    if (n == 1) {
+        void* params[] = {const_cast<T*>(items), &extra};
+        return cudaLaunchKernel(single, dim3(1, 1, 1), block, params, 0, stream);
+    }
+    T* dev = nullptr;
+    cudaError_t err = cudaMallocAsync(reinterpret_cast<void**>(&dev), sizeof(T) * n, stream);
+    if (err != cudaSuccess) return err;
+    err = cudaMemcpyAsync(dev, items, sizeof(T) * n, cudaMemcpyHostToDevice, stream);
+    if (err == cudaSuccess) {
+        void* params[] = {&dev, &extra};
+        // the n single-CTA virtual ranks wait on one another: cooperative launch keeps them co-resident
+        err = cudaLaunchCooperativeKernel(multi, dim3(1, n, 1), block, params, 0, stream);
+    }
+    cudaFreeAsync(dev, stream);
+    (void)has_extra;
+    return err;
+}
+
+}  // namespace
+
+cudaError_t launch_barrier(const RankCtx* ctxs, int n, cudaStream_t stream) {
+    return launch_small<RankCtx>((const void*)barrier_kernel, (const void*)barrier_kernel_multi, ctxs, n, dim3(32, 1, 1),
+                                 stream, 0, false);
+}
+
+cudaError_t launch_wait_flag_test(const RankCtx* ctxs, int n, uint64_t expected, cudaStream_t stream) {
+    return launch_small<RankCtx>((const void*)wait_flag_kernel, (const void*)wait_flag_kernel_multi, ctxs, n,
+                                 dim3(32, 1, 1), stream, expected, true);
+}
+
+cudaError_t launch_layout(const LayoutArgs& a, cudaStream_t stream) {
+    const int threads = 256;
+    const int blocks = (a.num_tokens + threads - 1) / threads;
+    if (blocks == 0) return cudaSuccess;
+    layout_kernel<<<blocks, threads, (a.num_experts + a.num_ranks) * sizeof(uint32_t), stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_quant(const QuantArgs& a, cudaStream_t stream) {
+    const int warps = 8;
+    const int blocks = (a.num_tokens + warps - 1) / warps;
+    if (blocks == 0) return cudaSuccess;
+    quant_kernel<<<blocks, warps * 32, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace ep

@@ -1,0 +1,179 @@
+// Python bindings of the native runtime (module `_C`).
+// Parity: csrc/python_api.cpp:1-54, csrc/elastic/binding.hpp:9-44 of the reference.
+#include <torch/extension.h>
+
+#include "kernels/api.h"
+#include "runtime/coordinator.hpp"
+#include "runtime/elastic_buffer.hpp"
+#include "runtime/layout.hpp"
+
+namespace py = pybind11;
+using namespace ep_host;
+
+namespace {
+
+std::vector<at::Tensor> get_dispatch_layout(const at::Tensor& topk_idx, int64_t num_experts, int64_t num_ranks) {
+    TORCH_CHECK(topk_idx.is_cuda() && topk_idx.is_contiguous() && topk_idx.dim() == 2, "topk_idx must be contiguous [T, K]");
+    TORCH_CHECK(topk_idx.scalar_type() == at::kLong || topk_idx.scalar_type() == at::kInt, "topk_idx must be int64 or int32");
+    TORCH_CHECK(num_experts % num_ranks == 0 && num_ranks <= 32, "bad expert / rank counts");
+    auto iopts = topk_idx.options().dtype(at::kInt);
+    at::Tensor per_rank = at::zeros({num_ranks}, iopts);
+    at::Tensor per_expert = at::zeros({num_experts}, iopts);
+    at::Tensor in_rank = at::empty({topk_idx.size(0), num_ranks}, topk_idx.options().dtype(at::kBool));
+    LayoutArgs a{};
+    a.topk_idx = topk_idx.data_ptr();
+    a.idx_is_64 = topk_idx.scalar_type() == at::kLong;
+    a.num_tokens = static_cast<int>(topk_idx.size(0));
+    a.num_topk = static_cast<int>(topk_idx.size(1));
+    a.num_experts = static_cast<int>(num_experts);
+    a.num_ranks = static_cast<int>(num_ranks);
+    a.num_tokens_per_rank = per_rank.data_ptr<int32_t>();
+    a.num_tokens_per_expert = per_expert.data_ptr<int32_t>();
+    a.is_token_in_rank = reinterpret_cast<uint8_t*>(in_rank.data_ptr());
+    cuda_check(ep::launch_layout(a, at::cuda::getCurrentCUDAStream()), "layout launch");
+    return {per_rank, per_expert, in_rank};
+}
+
+// bf16 [T, H] -> (e4m3 [T, H], scales).  Scales are fp32 [T, ceil(H/128)] or, with use_ue8m0, int32
+// [T, ceil(H/512)] holding four power-of-two exponents each.
+std::vector<at::Tensor> per_token_cast_to_fp8(const at::Tensor& x, bool round_scale, bool use_ue8m0) {
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 2 && x.scalar_type() == at::kBFloat16, "x must be contiguous bf16 [T, H]");
+    const int64_t T = x.size(0), H = x.size(1);
+    TORCH_CHECK(H % 16 == 0, "hidden must be a multiple of 16");
+    const int64_t G = (H + 127) / 128;
+    at::Tensor q = at::empty({T, H}, x.options().dtype(at::kFloat8_e4m3fn));
+    at::Tensor sf = use_ue8m0 ? at::zeros({T, (G + 3) / 4}, x.options().dtype(at::kInt)) : at::empty({T, G}, x.options().dtype(at::kFloat));
+    QuantArgs a{};
+    a.x = x.data_ptr();
+    a.q = q.data_ptr();
+    a.sf = reinterpret_cast<float*>(sf.data_ptr());
+    a.num_tokens = static_cast<int>(T);
+    a.hidden = static_cast<int>(H);
+    a.round_scale = round_scale;
+    a.use_ue8m0 = use_ue8m0;
+    a.sf_stride_row = sf.size(1);
+    a.sf_stride_col = 1;
+    cuda_check(ep::launch_quant(a, at::cuda::getCurrentCUDAStream()), "quant launch");
+    return {q, sf};
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.doc() = "Blackwell-native expert-parallel communication runtime";
+    m.def("get_platform", [] { return std::string("cuda-sm100a"); });
+    m.def("get_elastic_buffer_alignment", [] { return static_cast<int64_t>(EP_BUFFER_ALIGNMENT); });
+    m.def("get_workspace_bytes", [] { return static_cast<int64_t>(EP_WORKSPACE_BYTES); });
+    m.attr("MAX_RANKS") = EP_MAX_RANKS;
+    m.attr("MAX_EXPERTS") = EP_MAX_EXPERTS;
+    m.attr("MAX_TOPK") = EP_MAX_TOPK;
+
+    py::register_exception<BufferError>(m, "BufferError", PyExc_RuntimeError);
+
+    py::class_<MoeShape>(m, "MoeShape")
+        .def(py::init<>())
+        .def_readwrite("num_ranks", &MoeShape::num_ranks)
+        .def_readwrite("num_max_tokens_per_rank", &MoeShape::num_max_tokens_per_rank)
+        .def_readwrite("hidden", &MoeShape::hidden)
+        .def_readwrite("num_topk", &MoeShape::num_topk)
+        .def_readwrite("num_experts_hint", &MoeShape::num_experts_hint)
+        .def_readwrite("expert_alignment", &MoeShape::expert_alignment)
+        .def_readwrite("use_fp8_dispatch", &MoeShape::use_fp8_dispatch)
+        .def_readwrite("enable_expand", &MoeShape::enable_expand)
+        .def_readwrite("num_recv_slots", &MoeShape::num_recv_slots);
+    py::class_<RecvSlot>(m, "RecvSlot")
+        .def_readonly("x", &RecvSlot::x)
+        .def_readonly("sf", &RecvSlot::sf)
+        .def_readonly("idx", &RecvSlot::idx)
+        .def_readonly("w", &RecvSlot::w)
+        .def_readonly("meta", &RecvSlot::meta);
+    py::class_<RegionLayout>(m, "RegionLayout")
+        .def_readonly("capacity_rows", &RegionLayout::capacity_rows)
+        .def_readonly("x_row_bytes", &RegionLayout::x_row_bytes)
+        .def_readonly("sf_cols", &RegionLayout::sf_cols)
+        .def_readonly("num_recv_slots", &RegionLayout::num_recv_slots)
+        .def("slot", [](const RegionLayout& r, int i) {
+            TORCH_CHECK(i >= 0 && i < r.num_recv_slots, "slot index out of range");
+            return r.slots[i];
+        })
+        .def_readonly("combine_x", &RegionLayout::combine_x)
+        .def_readonly("combine_w", &RegionLayout::combine_w)
+        .def_readonly("extra", &RegionLayout::extra)
+        .def_readonly("moe_bytes", &RegionLayout::moe_bytes);
+    m.def("plan_regions", &plan_regions);
+    m.def("calculate_elastic_buffer_size", [](const MoeShape& s) { return plan_regions(s).moe_bytes; });
+
+    py::class_<DispatchCall>(m, "DispatchCall")
+        .def(py::init<>())
+        .def_readwrite("x", &DispatchCall::x)
+        .def_readwrite("sf", &DispatchCall::sf)
+        .def_readwrite("topk_idx", &DispatchCall::topk_idx)
+        .def_readwrite("topk_weights", &DispatchCall::topk_weights)
+        .def_readwrite("stats", &DispatchCall::stats)
+        .def_readwrite("lane_src", &DispatchCall::lane_src)
+        .def_readwrite("plan", &DispatchCall::plan)
+        .def_readwrite("psum_rank", &DispatchCall::psum_rank)
+        .def_readwrite("psum_expert", &DispatchCall::psum_expert)
+        .def_readwrite("recv_per_expert", &DispatchCall::recv_per_expert)
+        .def_readwrite("num_experts", &DispatchCall::num_experts)
+        .def_readwrite("expert_alignment", &DispatchCall::expert_alignment)
+        .def_readwrite("num_max_tokens", &DispatchCall::num_max_tokens)
+        .def_readwrite("quantize", &DispatchCall::quantize)
+        .def_readwrite("do_expand", &DispatchCall::do_expand)
+        .def_readwrite("cached", &DispatchCall::cached)
+        .def_readwrite("off_recv_x", &DispatchCall::off_recv_x)
+        .def_readwrite("off_recv_sf", &DispatchCall::off_recv_sf)
+        .def_readwrite("off_recv_idx", &DispatchCall::off_recv_idx)
+        .def_readwrite("off_recv_w", &DispatchCall::off_recv_w)
+        .def_readwrite("off_recv_meta", &DispatchCall::off_recv_meta)
+        .def_readwrite("sf_stride_row", &DispatchCall::sf_stride_row)
+        .def_readwrite("sf_stride_col", &DispatchCall::sf_stride_col)
+        .def_readwrite("recv_capacity_rows", &DispatchCall::recv_capacity_rows);
+    py::class_<CombineCall>(m, "CombineCall")
+        .def(py::init<>())
+        .def_readwrite("off_x", &CombineCall::off_x)
+        .def_readwrite("off_w", &CombineCall::off_w)
+        .def_readwrite("w_cols", &CombineCall::w_cols)
+        .def_readwrite("plan", &CombineCall::plan)
+        .def_readwrite("lane_src", &CombineCall::lane_src)
+        .def_readwrite("mul_weights", &CombineCall::mul_weights)
+        .def_readwrite("bias0", &CombineCall::bias0)
+        .def_readwrite("bias1", &CombineCall::bias1)
+        .def_readwrite("out", &CombineCall::out)
+        .def_readwrite("out_w", &CombineCall::out_w)
+        .def_readwrite("hidden", &CombineCall::hidden);
+
+    py::class_<ElasticBufferCore>(m, "ElasticBuffer")
+        .def(py::init<int, int, int64_t, double, double>(), py::arg("rank"), py::arg("num_ranks"), py::arg("num_bytes"),
+             py::arg("gpu_timeout_secs") = 100.0, py::arg("cpu_timeout_secs") = 300.0)
+        .def("get_local_ipc_handle", &ElasticBufferCore::get_local_ipc_handle)
+        .def("open_peers", [](ElasticBufferCore& b, const std::vector<py::bytes>& handles) {
+            std::vector<std::string> hs;
+            for (const auto& h : handles) hs.push_back(static_cast<std::string>(h));
+            b.open_peers(hs);
+        })
+        .def_static("link_local", &ElasticBufferCore::link_local)
+        .def("destroy", &ElasticBufferCore::destroy)
+        .def("rank", &ElasticBufferCore::rank)
+        .def("num_ranks", &ElasticBufferCore::num_ranks)
+        .def("num_bytes", &ElasticBufferCore::num_bytes)
+        .def("state", &ElasticBufferCore::state)
+        .def("generation", &ElasticBufferCore::generation)
+        .def("set_gpu_timeout", &ElasticBufferCore::set_gpu_timeout)
+        .def("view", &ElasticBufferCore::view)
+        .def("read_status", &ElasticBufferCore::read_status)
+        .def("check_status", &ElasticBufferCore::check_status)
+        .def("wait_recv_counts", &ElasticBufferCore::wait_recv_counts)
+        .def("dispatch", &ElasticBufferCore::dispatch)
+        .def("combine", &ElasticBufferCore::combine)
+        .def("barrier", &ElasticBufferCore::barrier)
+        .def("wait_flag_test", &ElasticBufferCore::wait_flag_test)
+        .def_static("dispatch_group", &ElasticBufferCore::dispatch_group)
+        .def_static("combine_group", &ElasticBufferCore::combine_group)
+        .def_static("barrier_group", &ElasticBufferCore::barrier_group)
+        .def_static("wait_flag_test_group", &ElasticBufferCore::wait_flag_test_group);
+
+    m.def("get_dispatch_layout", &get_dispatch_layout);
+    m.def("per_token_cast_to_fp8", &per_token_cast_to_fp8, py::arg("x"), py::arg("round_scale") = false,
+          py::arg("use_ue8m0") = false);
+}

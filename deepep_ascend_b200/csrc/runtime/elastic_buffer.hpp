@@ -1,0 +1,367 @@
+// Native core of ElasticBuffer: owns the symmetric memory, the status block and the operation coordinator,
+// validates every call, fills the kernel argument structs and launches on the current CUDA stream.  The
+// Python class of the same name adds process-group plumbing, stream/event control and handle objects.
+//
+// Every operation exists in two forms: a method (this process drives one GPU) and a static `*_group` function
+// that takes the cores of several virtual ranks living on ONE device and runs them as a single cooperative
+// launch, which is how the multi-rank protocols are tested on a single GPU.
+// Parity: csrc/elastic/buffer.hpp:19-1346 (deep_ep::elastic::ElasticBuffer).
+#pragma once
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/extension.h>
+
+#include <chrono>
+#include <memory>
+#include <optional>
+#include <thread>
+#include <vector>
+
+#include "../kernels/api.h"
+#include "coordinator.hpp"
+#include "layout.hpp"
+#include "symmetric.hpp"
+
+namespace ep_host {
+
+using OptTensor = std::optional<at::Tensor>;
+
+struct DispatchCall {
+    at::Tensor x;                  // [T, H] bf16 or float8_e4m3fn
+    OptTensor sf;                  // [T, H/128] fp32 when x is fp8
+    OptTensor topk_idx;            // [T, K] int64 / int32 (absent with a cached layout)
+    OptTensor topk_weights;        // [T, K] fp32
+    OptTensor stats;               // [E_local] int32 cumulative counters
+    at::Tensor lane_src, plan;     // [T, K] int32 handle tensors (outputs, or inputs when cached)
+    at::Tensor psum_rank, psum_expert, recv_per_expert;   // int32 handle tensors
+    int64_t num_experts = 0;
+    int64_t expert_alignment = 1;
+    int64_t num_max_tokens = 0;
+    bool quantize = false;
+    bool do_expand = false;
+    bool cached = false;
+    int64_t off_recv_x = 0, off_recv_sf = 0, off_recv_idx = 0, off_recv_w = 0, off_recv_meta = 0;
+    int64_t sf_stride_row = 0, sf_stride_col = 1;
+    int64_t recv_capacity_rows = 0;
+};
+
+struct CombineCall {
+    int64_t off_x = 0, off_w = 0;
+    int64_t w_cols = 0;
+    at::Tensor plan, lane_src;     // [T, K] int32
+    OptTensor mul_weights;         // [T, K] fp32
+    OptTensor bias0, bias1;        // [T, H] bf16
+    at::Tensor out;                // [T, H] bf16
+    OptTensor out_w;               // [T, K] fp32
+    int64_t hidden = 0;
+};
+
+class ElasticBufferCore {
+public:
+    ElasticBufferCore(int rank, int num_ranks, int64_t num_bytes, double gpu_timeout_secs, double cpu_timeout_secs)
+        : mem_(std::make_unique<SymmetricMemory>(rank, num_ranks, num_bytes)),
+          gpu_timeout_ns_(static_cast<uint64_t>(gpu_timeout_secs * 1e9)),
+          cpu_timeout_secs_(cpu_timeout_secs) {}
+
+    ~ElasticBufferCore() {
+        if (!mem_->released()) destroy();
+    }
+
+    // ------------------------------------------------------------------ set-up / tear-down
+    py::bytes get_local_ipc_handle() const { return py::bytes(mem_->export_handle()); }
+    void open_peers(const std::vector<std::string>& handles) { mem_->open_peers(handles); }
+    static void link_local(const std::vector<ElasticBufferCore*>& group) {
+        std::vector<SymmetricMemory*> mems;
+        for (auto* g : group) mems.push_back(g->mem_.get());
+        SymmetricMemory::link_local(mems);
+    }
+    void destroy() {
+        if (!coord_.begin_destroy()) return;
+        cudaDeviceSynchronize();
+        coord_.end_destroy(mem_->release());
+    }
+
+    int rank() const { return mem_->rank(); }
+    int num_ranks() const { return mem_->num_ranks(); }
+    int64_t num_bytes() const { return mem_->bytes(); }
+    std::string state() const { return to_string(coord_.state()); }
+    uint64_t generation() const { return coord_.generation(); }
+    void set_gpu_timeout(double secs) { gpu_timeout_ns_ = static_cast<uint64_t>(secs * 1e9); }
+
+    // a tensor that aliases [offset, offset + bytes) of the local symmetric buffer
+    at::Tensor view(int64_t offset, std::vector<int64_t> sizes, std::vector<int64_t> strides, at::ScalarType dtype) const {
+        int64_t max_index = 0;
+        for (size_t i = 0; i < sizes.size(); ++i) {
+            if (sizes[i] == 0) { max_index = -1; break; }
+            max_index += (sizes[i] - 1) * strides[i];
+        }
+        const int64_t end = offset + (max_index + 1) * static_cast<int64_t>(c10::elementSize(dtype));
+        TORCH_CHECK(offset >= static_cast<int64_t>(EP_WORKSPACE_BYTES) && end <= mem_->bytes(),
+                    "view [", offset, ", ", end, ") is outside the data area of the symmetric buffer");
+        auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, mem_->device());
+        return at::from_blob(mem_->local() + offset, sizes, strides, [](void*) {}, opts);
+    }
+
+    // ------------------------------------------------------------------ status
+    // (code, phase, peer, expected, observed, rank)
+    std::vector<int64_t> read_status() const {
+        const volatile uint64_t* st = mem_->status();
+        return {static_cast<int64_t>(st[EP_STATUS_CODE]), static_cast<int64_t>(st[EP_STATUS_PHASE]),
+                static_cast<int64_t>(st[EP_STATUS_PEER]), static_cast<int64_t>(st[EP_STATUS_EXPECTED]),
+                static_cast<int64_t>(st[EP_STATUS_OBSERVED]), static_cast<int64_t>(st[EP_STATUS_RANK])};
+    }
+    // throws (and poisons the buffer) if any kernel reported a failed wait
+    void check_status() {
+        const volatile uint64_t* st = mem_->status();
+        if (st[EP_STATUS_CODE] != EP_OK) {
+            const std::string msg = describe_status(st);
+            coord_.poison(msg);
+            throw BufferError(msg);
+        }
+    }
+
+    // Host side of do_cpu_sync: spin on the mapped counters of dispatch number `epoch` (1-based).
+    // -> [num_recv, num_expanded, count of local expert 0, 1, ...]
+    std::vector<int64_t> wait_recv_counts(int64_t num_local_experts) {
+        const volatile uint64_t* st = mem_->status();
+        const uint64_t epoch = dispatch_epoch_ & 0xffffffffull;
+        const auto t0 = std::chrono::steady_clock::now();
+        std::vector<int64_t> out(2 + num_local_experts);
+        py::gil_scoped_release release;
+        auto ready = [&](uint64_t w) { return (w >> 32) == epoch; };
+        while (true) {
+            bool all = ready(st[EP_STATUS_NUM_RECV]) && ready(st[EP_STATUS_NUM_EXPANDED]);
+            for (int64_t j = 0; all && j < num_local_experts; ++j) all = ready(st[EP_STATUS_EXPERT_BASE + j]);
+            if (all) break;
+            if (st[EP_STATUS_CODE] != EP_OK) {
+                const std::string msg = describe_status(st);
+                coord_.poison(msg);
+                throw BufferError(msg);
+            }
+            const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+            if (waited > cpu_timeout_secs_) {
+                coord_.poison("host timed out waiting for receive counts");
+                throw BufferError("host timed out waiting for the receive counts of dispatch " + std::to_string(dispatch_epoch_));
+            }
+            std::this_thread::yield();
+        }
+        out[0] = static_cast<int64_t>(st[EP_STATUS_NUM_RECV] & 0xffffffffull);
+        out[1] = static_cast<int64_t>(st[EP_STATUS_NUM_EXPANDED] & 0xffffffffull);
+        for (int64_t j = 0; j < num_local_experts; ++j)
+            out[2 + j] = static_cast<int64_t>(st[EP_STATUS_EXPERT_BASE + j] & 0xffffffffull);
+        return out;
+    }
+
+    // ------------------------------------------------------------------ operations
+    void dispatch(const DispatchCall& call, int num_sms) { dispatch_group({this}, {call}, num_sms); }
+    void combine(const CombineCall& call, int num_sms) { combine_group({this}, {call}, num_sms); }
+    void barrier() { barrier_group({this}); }
+    void wait_flag_test(int64_t expected) { wait_flag_test_group({this}, expected); }
+
+    static void dispatch_group(const std::vector<ElasticBufferCore*>& group, const std::vector<DispatchCall>& calls,
+                               int num_sms) {
+        TORCH_CHECK(group.size() == calls.size() && !group.empty(), "one call per buffer is required");
+        std::vector<std::unique_ptr<OperationScope>> scopes;
+        std::vector<DispatchArgs> args(group.size());
+        for (size_t i = 0; i < group.size(); ++i) {
+            group[i]->check_status();
+            scopes.push_back(std::make_unique<OperationScope>(group[i]->coord_, "dispatch"));
+            args[i] = group[i]->make_dispatch_args(calls[i]);
+            TORCH_CHECK(args[i].quantize == args[0].quantize && args[i].hidden == args[0].hidden &&
+                            args[i].num_experts == args[0].num_experts && args[i].num_topk == args[0].num_topk &&
+                            args[i].x_is_fp8 == args[0].x_is_fp8,
+                        "all virtual ranks must use the same dispatch configuration");
+        }
+        auto stream = at::cuda::getCurrentCUDAStream();
+        cuda_check(ep::launch_dispatch(args.data(), static_cast<int>(args.size()), num_sms, stream), "dispatch launch");
+        for (size_t i = 0; i < group.size(); ++i) {
+            group[i]->dispatch_epoch_ += 1;
+            scopes[i]->commit();
+        }
+    }
+
+    static void combine_group(const std::vector<ElasticBufferCore*>& group, const std::vector<CombineCall>& calls,
+                              int num_sms) {
+        TORCH_CHECK(group.size() == calls.size() && !group.empty(), "one call per buffer is required");
+        std::vector<std::unique_ptr<OperationScope>> scopes;
+        std::vector<CombineArgs> args(group.size());
+        for (size_t i = 0; i < group.size(); ++i) {
+            group[i]->check_status();
+            scopes.push_back(std::make_unique<OperationScope>(group[i]->coord_, "combine"));
+            args[i] = group[i]->make_combine_args(calls[i]);
+            TORCH_CHECK(args[i].hidden == args[0].hidden && args[i].num_topk == args[0].num_topk,
+                        "all virtual ranks must use the same combine configuration");
+        }
+        auto stream = at::cuda::getCurrentCUDAStream();
+        cuda_check(ep::launch_combine(args.data(), static_cast<int>(args.size()), num_sms, stream), "combine launch");
+        for (auto& s : scopes) s->commit();
+    }
+
+    static void barrier_group(const std::vector<ElasticBufferCore*>& group) {
+        std::vector<std::unique_ptr<OperationScope>> scopes;
+        std::vector<RankCtx> ctxs;
+        for (auto* g : group) {
+            g->check_status();
+            scopes.push_back(std::make_unique<OperationScope>(g->coord_, "barrier"));
+            ctxs.push_back(g->ctx());
+        }
+        cuda_check(ep::launch_barrier(ctxs.data(), static_cast<int>(ctxs.size()), at::cuda::getCurrentCUDAStream()),
+                   "barrier launch");
+        for (auto& s : scopes) s->commit();
+    }
+
+    // Launches a kernel that waits (bounded by the GPU timeout) for a flag nothing sets; used to test that a
+    // failed wait ends in a status record and a poisoned buffer instead of a trap or a hang.
+    static void wait_flag_test_group(const std::vector<ElasticBufferCore*>& group, int64_t expected) {
+        std::vector<RankCtx> ctxs;
+        for (auto* g : group) ctxs.push_back(g->ctx());
+        cuda_check(ep::launch_wait_flag_test(ctxs.data(), static_cast<int>(ctxs.size()), static_cast<uint64_t>(expected),
+                                             at::cuda::getCurrentCUDAStream()),
+                   "wait-flag launch");
+    }
+
+    RankCtx ctx() const { return mem_->ctx(gpu_timeout_ns_); }
+    OperationCoordinator& coordinator() { return coord_; }
+    SymmetricMemory& memory() { return *mem_; }
+
+private:
+    static const void* ptr_or_null(const OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+
+    void check_region(int64_t off, int64_t bytes, const char* what) const {
+        TORCH_CHECK(off >= static_cast<int64_t>(EP_WORKSPACE_BYTES) && off % 16 == 0 && off + bytes <= mem_->bytes(), what,
+                    " region [", off, ", ", off + bytes, ") does not fit the symmetric buffer of ", mem_->bytes(), " bytes");
+    }
+
+    DispatchArgs make_dispatch_args(const DispatchCall& c) const {
+        DispatchArgs a{};
+        a.ctx = ctx();
+        const int R = a.ctx.num_ranks;
+        TORCH_CHECK(c.x.is_cuda() && c.x.dim() == 2 && c.x.is_contiguous(), "x must be a contiguous [T, H] CUDA tensor");
+        const bool fp8 = c.x.scalar_type() == at::kFloat8_e4m3fn;
+        TORCH_CHECK(fp8 || c.x.scalar_type() == at::kBFloat16, "x must be bf16 or float8_e4m3fn");
+        const int64_t T = c.x.size(0), H = c.x.size(1);
+        TORCH_CHECK(T <= c.num_max_tokens, "num_tokens exceeds num_max_tokens_per_rank");
+        TORCH_CHECK((H * c.x.element_size()) % 16 == 0 && H % 16 == 0, "hidden bytes must be a multiple of 16");
+        TORCH_CHECK(reinterpret_cast<uintptr_t>(c.x.data_ptr()) % 16 == 0, "x must be 16-byte aligned");
+        TORCH_CHECK(!(c.quantize && fp8), "fused quantization takes bf16 input");
+        const int64_t G = (H + 127) / 128;
+        if (fp8) {
+            TORCH_CHECK(c.sf.has_value() && c.sf->scalar_type() == at::kFloat && c.sf->is_contiguous() &&
+                            c.sf->dim() == 2 && c.sf->size(0) == T && c.sf->size(1) == G,
+                        "fp8 input needs contiguous fp32 scales [T, ceil(H/128)]");
+        }
+        TORCH_CHECK(c.num_experts > 0 && c.num_experts % R == 0 && c.num_experts <= EP_MAX_EXPERTS,
+                    "num_experts must be a positive multiple of the rank count (at most ", EP_MAX_EXPERTS, ")");
+        TORCH_CHECK(!c.do_expand || c.expert_alignment >= 1, "bad expert alignment");
+        const at::Tensor& plan = c.plan;
+        TORCH_CHECK(plan.scalar_type() == at::kInt && plan.is_contiguous() && plan.dim() == 2 && plan.size(0) == T,
+                    "plan must be int32 [T, K]");
+        const int64_t K = plan.size(1);
+        TORCH_CHECK(K >= 1 && K <= EP_MAX_TOPK, "num_topk out of range");
+        TORCH_CHECK(c.lane_src.scalar_type() == at::kInt && c.lane_src.is_contiguous() && c.lane_src.sizes() == plan.sizes(),
+                    "lane_src must match plan");
+        TORCH_CHECK(c.topk_idx.has_value(), "topk_idx is required (a cached layout passes the handle's copy)");
+        {
+            const auto& idx = *c.topk_idx;
+            TORCH_CHECK(idx.is_contiguous() && idx.dim() == 2 && idx.size(0) == T && idx.size(1) == K &&
+                            (idx.scalar_type() == at::kLong || idx.scalar_type() == at::kInt),
+                        "topk_idx must be contiguous int64/int32 [T, K]");
+            a.topk_idx = idx.data_ptr();
+            a.idx_is_64 = idx.scalar_type() == at::kLong;
+        }
+        if (c.topk_weights.has_value()) {
+            TORCH_CHECK(c.topk_weights->scalar_type() == at::kFloat && c.topk_weights->is_contiguous() &&
+                            c.topk_weights->size(0) == T && c.topk_weights->size(1) == K,
+                        "topk_weights must be contiguous fp32 [T, K]");
+        }
+        const int64_t El = c.num_experts / R;
+        TORCH_CHECK(c.psum_rank.numel() == R && c.psum_expert.numel() == El && c.recv_per_expert.numel() == El,
+                    "handle tensors have the wrong size");
+        if (c.stats.has_value()) TORCH_CHECK(c.stats->scalar_type() == at::kInt && c.stats->numel() == El, "bad stats tensor");
+        const int64_t out_row = (c.quantize || fp8) ? H : H * 2;
+        const int64_t cap = c.recv_capacity_rows;
+        TORCH_CHECK(cap > 0 && cap < (1 << 24), "bad receive capacity");
+        check_region(c.off_recv_x, cap * out_row, "recv_x");
+        if (c.quantize || fp8) check_region(c.off_recv_sf, cap * G * 4, "recv_sf");
+        if (!c.do_expand) check_region(c.off_recv_idx, cap * K * 8, "recv_topk_idx");
+        check_region(c.off_recv_w, cap * (c.do_expand ? 1 : K) * 4, "recv_topk_weights");
+        check_region(c.off_recv_meta, cap * 8, "recv_src_metadata");
+
+        a.x = c.x.data_ptr();
+        a.sf = fp8 ? c.sf->data_ptr<float>() : nullptr;
+        a.topk_weights = c.topk_weights.has_value() ? c.topk_weights->data_ptr<float>() : nullptr;
+        a.num_tokens = static_cast<int>(T);
+        a.hidden = static_cast<int>(H);
+        a.num_topk = static_cast<int>(K);
+        a.num_experts = static_cast<int>(c.num_experts);
+        a.x_is_fp8 = fp8;
+        a.quantize = c.quantize;
+        a.do_expand = c.do_expand;
+        a.expert_alignment = static_cast<int>(c.expert_alignment);
+        a.cached = c.cached;
+        a.num_max_tokens = static_cast<int>(c.num_max_tokens);
+        a.lane_src = c.lane_src.data_ptr<int32_t>();
+        a.plan = c.plan.data_ptr<int32_t>();
+        a.psum_rank = c.psum_rank.data_ptr<int32_t>();
+        a.psum_expert = c.psum_expert.data_ptr<int32_t>();
+        a.recv_per_expert = c.recv_per_expert.data_ptr<int32_t>();
+        a.stats = c.stats.has_value() ? c.stats->data_ptr<int32_t>() : nullptr;
+        a.off_recv_x = c.off_recv_x;
+        a.off_recv_sf = c.off_recv_sf;
+        a.off_recv_idx = c.off_recv_idx;
+        a.off_recv_w = c.off_recv_w;
+        a.off_recv_meta = c.off_recv_meta;
+        a.sf_stride_row = c.sf_stride_row;
+        a.sf_stride_col = c.sf_stride_col;
+        a.recv_capacity_rows = static_cast<int>(cap);
+        return a;
+    }
+
+    CombineArgs make_combine_args(const CombineCall& c) const {
+        CombineArgs a{};
+        a.ctx = ctx();
+        TORCH_CHECK(c.plan.scalar_type() == at::kInt && c.plan.is_contiguous() && c.plan.dim() == 2, "plan must be int32 [T, K]");
+        const int64_t T = c.plan.size(0), K = c.plan.size(1), H = c.hidden;
+        TORCH_CHECK(K >= 1 && K <= EP_MAX_TOPK && H > 0 && (H * 2) % 16 == 0, "bad combine shape");
+        TORCH_CHECK(c.out.scalar_type() == at::kBFloat16 && c.out.is_contiguous() && c.out.size(0) == T && c.out.size(1) == H,
+                    "out must be contiguous bf16 [T, H]");
+        for (const OptTensor* b : {&c.bias0, &c.bias1})
+            if (b->has_value())
+                TORCH_CHECK((*b)->scalar_type() == at::kBFloat16 && (*b)->is_contiguous() && (*b)->sizes() == c.out.sizes(),
+                            "bias must be contiguous bf16 [T, H]");
+        TORCH_CHECK(c.off_x >= static_cast<int64_t>(EP_WORKSPACE_BYTES) && c.off_x % 16 == 0 && c.off_x < mem_->bytes(),
+                    "combine input offset outside the symmetric buffer");
+        if (c.out_w.has_value()) {
+            TORCH_CHECK(c.out_w->scalar_type() == at::kFloat && c.out_w->is_contiguous() && c.out_w->numel() == T * K &&
+                            c.off_w >= static_cast<int64_t>(EP_WORKSPACE_BYTES) && c.w_cols >= 1,
+                        "bad weight transport arguments");
+            TORCH_CHECK(c.lane_src.scalar_type() == at::kInt && c.lane_src.is_contiguous() && c.lane_src.sizes() == c.plan.sizes(),
+                        "lane_src must match plan");
+        }
+        if (c.mul_weights.has_value())
+            TORCH_CHECK(c.mul_weights->scalar_type() == at::kFloat && c.mul_weights->is_contiguous() &&
+                            c.mul_weights->numel() == T * K, "mul_weights must be contiguous fp32 [T, K]");
+        a.off_x = c.off_x;
+        a.off_w = c.off_w;
+        a.w_cols = static_cast<int>(c.w_cols);
+        a.plan = c.plan.data_ptr<int32_t>();
+        a.lane_src = c.out_w.has_value() ? c.lane_src.data_ptr<int32_t>() : nullptr;
+        a.mul_weights = c.mul_weights.has_value() ? c.mul_weights->data_ptr<float>() : nullptr;
+        a.bias0 = ptr_or_null(c.bias0);
+        a.bias1 = ptr_or_null(c.bias1);
+        a.out = c.out.data_ptr();
+        a.out_w = c.out_w.has_value() ? c.out_w->data_ptr<float>() : nullptr;
+        a.num_tokens = static_cast<int>(T);
+        a.hidden = static_cast<int>(H);
+        a.num_topk = static_cast<int>(K);
+        return a;
+    }
+
+    std::unique_ptr<SymmetricMemory> mem_;
+    OperationCoordinator coord_;
+    uint64_t gpu_timeout_ns_;
+    double cpu_timeout_secs_;
+    uint64_t dispatch_epoch_ = 0;
+};
+
+}  // namespace ep_host
