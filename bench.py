@@ -1,0 +1,256 @@
+"""Headline benchmark: expert-parallel dispatch + combine at the DeepSeek-V3 shape.
+
+One step = one ``ElasticBuffer.dispatch`` (bf16 tokens in, FP8 e4m3 + 1x128 scales out, cast fused into the NVLink
+scatter) followed by one ``ElasticBuffer.combine`` (bf16 pull + fp32 reduce) of 8192 tokens per rank, hidden 7168,
+top-8 of 256 experts.  Bandwidth is the reference's "logical bandwidth": received rows x bytes per row, local-rank
+rows included (reference: tests/elastic/test_ep.py:444-451, 523-550, README.md:53).
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 20 --warmup 5
+
+Rank 0 prints ONE JSON line.  ``--impl reference`` is the arm for the unmodified reference build.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+# published reference numbers on SM100, EP8, 64 SMs (reference README.md:50): 726 GB/s dispatch, 740 GB/s combine
+REF_DISPATCH_GBS, REF_COMBINE_GBS = 726.0, 740.0
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument('--gpus', type=int, default=1)
+    p.add_argument('--steps', type=int, default=20)
+    p.add_argument('--warmup', type=int, default=5)
+    p.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    p.add_argument('--tokens', type=int, default=8192)
+    p.add_argument('--hidden', type=int, default=7168)
+    p.add_argument('--experts', type=int, default=256)
+    p.add_argument('--topk', type=int, default=8)
+    p.add_argument('--num-sms', type=int, default=int(os.environ.get('EP_BENCH_NUM_SMS', '64')))
+    p.add_argument('--combine-sms', type=int, default=0)
+    p.add_argument('--no-e2e', action='store_true')
+    p.add_argument('--sweep-sms', default='', help='comma separated SM counts: print one extra JSON line per count')
+    return p.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of this process's GPU with nvidia-smi while the timed region runs."""
+
+    QUERY = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
+             'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+             'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, device_index: int):
+        self.rows, self.proc, self.device_index = [], None, device_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.QUERY}', '--format=csv,noheader,nounits',
+                                          '-i', str(self.device_index), '-lms', '100'],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(',')])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace('.', '').isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace('.', '').isdigit()]
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        reasons = sorted({n for r in self.rows if len(r) >= 7 for n, v in zip(names, r[3:7]) if v == 'Active'})
+        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': max(mx) if mx else None,
+                'reasons': reasons, 'samples': len(sm)}
+
+
+def reference_arm(args):
+    """The reference needs NCCL >= 2.30.4 (Gin device API), NVSHMEM's IBGDA headers (infiniband/mlx5dv.h) and the
+    fmt submodule; its offline install into baseline/_ref fails at compile time on this image, so there is no
+    reference build to run."""
+    ref_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'baseline', '_ref')
+    why = 'reference build failed offline: needs NCCL>=2.30.4 Gin API (image has 2.28.9), infiniband/mlx5dv.h and third-party/fmt'
+    if os.path.isdir(os.path.join(ref_dir, 'deep_ep')):
+        sys.path.insert(0, ref_dir)
+        try:
+            import deep_ep  # noqa: F401
+            why = 'reference imported but its EPv2 kernels need the NCCL Gin device API at run time, absent from NCCL 2.28.9'
+        except Exception as e:  # pragma: no cover
+            why = f'reference import failed: {type(e).__name__}: {str(e)[:120]}'
+    if int(os.environ.get('RANK', '0')) == 0:
+        print(json.dumps({'impl': 'reference', 'unavailable': why}), flush=True)
+    return 0
+
+
+def main():
+    args = parse_args()
+    if args.impl == 'reference':
+        return reference_arm(args)
+    import torch
+    import torch.distributed as dist
+    from deepep_ascend_b200 import ElasticBuffer
+    from deepep_ascend_b200.utils.testing import flush_l2_cache
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    assert world == args.gpus, f'--gpus {args.gpus} needs {args.gpus} ranks (launch with torch.distributed.run), got {world}'
+    torch.cuda.set_device(local_rank)
+    group = None
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', local_rank))
+        group = dist.new_group(list(range(world)))
+
+    T, H, E, K = args.tokens, args.hidden, args.experts, args.topk
+    G = (H + 127) // 128
+    buf = ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=True,
+                        prefer_overlap_with_compute=False, num_gpu_timeout_secs=20, num_cpu_timeout_secs=60)
+
+    # synthetic routed tokens: x ~ N(0,1) bf16, top-8 of N(0,1) logits with softmax weights; pinned host copies
+    gen = torch.Generator().manual_seed(1234 + rank)
+    x_host = torch.randn(T, H, generator=gen).bfloat16().pin_memory()
+    logits = torch.randn(T, E, generator=gen)
+    w_host, idx_host = torch.softmax(logits, dim=-1).topk(K, dim=-1)
+    w_host, idx_host = w_host.contiguous().pin_memory(), idx_host.contiguous().pin_memory()
+    x, idx, w = x_host.cuda(), idx_host.cuda(), w_host.cuda()
+    h2d_bytes = x_host.numel() * 2 + idx_host.numel() * 8 + w_host.numel() * 4
+
+    def gpu_barrier():
+        if world > 1:
+            buf.barrier(use_comm_stream=False)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(group=group)
+        torch.cuda.synchronize()
+
+    def run(num_sms, combine_sms, steps, warmup):
+        handle = None
+        times = []
+        for i in range(warmup + steps):
+            timed = i >= warmup
+            if i == warmup:
+                sync_all()
+            flush_l2_cache()
+            gpu_barrier()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record()
+            recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x, idx, w, num_experts=E, num_sms=num_sms)
+            ev[1].record()
+            y = buf.get_combine_buffer(handle)
+            if i == 0:
+                y.normal_()
+            flush_l2_cache()
+            gpu_barrier()
+            ev[2].record()
+            out, _, _ = buf.combine(y, handle, num_sms=combine_sms or num_sms)
+            ev[3].record()
+            if timed:
+                times.append(ev)
+        sync_all()
+        buf.check_status()
+        t = torch.tensor([[e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3])] for e in times], dtype=torch.float64, device='cuda')
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return t.mean(dim=0).tolist(), handle
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    wall0 = time.perf_counter()
+    (t_disp, t_comb), handle = run(args.num_sms, args.combine_sms, args.steps, args.warmup)
+    wall = time.perf_counter() - wall0
+    clocks = sampler.stop() if rank == 0 else None
+
+    rows = torch.tensor([handle.num_recv_tokens], dtype=torch.float64, device='cuda')
+    rows_min = rows.clone()
+    if world > 1:
+        dist.all_reduce(rows, op=dist.ReduceOp.SUM, group=group)
+        dist.all_reduce(rows_min, op=dist.ReduceOp.MIN, group=group)
+    rows_total, rows_min = float(rows.item()), float(rows_min.item())
+    disp_row_bytes = H + G * 4 + K * 8 + K * 4
+    comb_row_bytes = H * 2 + K * 4
+    disp_gbs = rows_total / world * disp_row_bytes / (t_disp * 1e-3) / 1e9
+    comb_gbs = rows_total / world * comb_row_bytes / (t_comb * 1e-3) / 1e9
+    ms_per_step = t_disp + t_comb
+    value = rows_total * (disp_row_bytes + comb_row_bytes) / (ms_per_step * 1e-3) / 1e9
+    ref_per_gpu = (disp_row_bytes + comb_row_bytes) / (disp_row_bytes / REF_DISPATCH_GBS + comb_row_bytes / REF_COMBINE_GBS)
+
+    sweep = {}
+    for s in [int(v) for v in args.sweep_sms.split(',') if v]:
+        (td, tc), _ = run(s, s, max(3, args.steps // 2), 3)
+        sweep[str(s)] = {'dispatch_ms': td, 'combine_ms': tc,
+                         'dispatch_gbs_per_gpu': rows_total / world * disp_row_bytes / (td * 1e-3) / 1e9,
+                         'combine_gbs_per_gpu': rows_total / world * comb_row_bytes / (tc * 1e-3) / 1e9}
+
+    e2e = None
+    if not args.no_e2e:
+        # end to end through the public API: every step copies its inputs from pinned host memory, runs
+        # dispatch + combine, and reads one fp32 checksum of the combined tokens back to the host
+        steps = max(3, min(args.steps, 10))
+        x_d, idx_d, w_d = torch.empty_like(x), torch.empty_like(idx), torch.empty_like(w)
+        checksum = 0.0
+        for i in range(3 + steps):
+            if i == 3:
+                sync_all()
+                t0 = time.perf_counter()
+            x_d.copy_(x_host, non_blocking=True)
+            idx_d.copy_(idx_host, non_blocking=True)
+            w_d.copy_(w_host, non_blocking=True)
+            _, _, _, hd, _ = buf.dispatch(x_d, idx_d, w_d, num_experts=E, num_sms=args.num_sms)
+            out, _, _ = buf.combine(buf.get_combine_buffer(hd), hd, num_sms=args.combine_sms or args.num_sms)
+            checksum = float(out.sum(dtype=torch.float32).item())
+        torch.cuda.synchronize()
+        dt = torch.tensor([(time.perf_counter() - t0) / steps], dtype=torch.float64, device='cuda')
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX, group=group)
+        e2e = {'value': rows_total * (disp_row_bytes + comb_row_bytes) / float(dt.item()) / 1e9, 'unit': 'GB/s',
+               'ms_per_step': float(dt.item()) * 1e3, 'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': 4,
+               'checksum_finite': checksum == checksum}
+
+    if rank == 0:
+        line = {
+            'metric': 'ep_dispatch_combine_logical_bandwidth', 'value': value, 'unit': 'GB/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True,
+            'scaling': 'weak', 'vs_baseline': value / world / ref_per_gpu, 'dtype': 'fp8_e4m3 dispatch (fused cast from bf16) + bf16 combine',
+            'data': 'synthetic', 'impl': 'ours',
+            'config': {'model': 'DeepSeek-V3 MoE routing shape', 'global_batch': T * world, 'seq_len': 1,
+                       'tokens_per_rank': T, 'hidden': H, 'num_experts': E, 'num_topk': K, 'parallelism': f'ep{world}',
+                       'num_sms_dispatch': args.num_sms, 'num_sms_combine': args.combine_sms or args.num_sms,
+                       'l2': 'flushed (256 MB write) before every timed kernel', 'timing': 'CUDA events per kernel, max over ranks, mean over steps',
+                       'baseline': f'{ref_per_gpu:.1f} GB/s per GPU = published 726 (dispatch) / 740 (combine) GB/s at EP8, 64 SMs'},
+            'dispatch_ms': t_disp, 'combine_ms': t_comb, 'dispatch_gbs_per_gpu': disp_gbs, 'combine_gbs_per_gpu': comb_gbs,
+            'dispatch_vs_ref': disp_gbs / REF_DISPATCH_GBS, 'combine_vs_ref': comb_gbs / REF_COMBINE_GBS,
+            'recv_rows_total': rows_total, 'recv_rows_min_rank': rows_min, 'wall_s_timed_run': wall,
+            'clocks': clocks, 'e2e': e2e, 'gpu_launches': args.steps * (2 + (2 if world > 1 else 0)),
+        }
+        if sweep:
+            line['sm_sweep'] = sweep
+        print(json.dumps(line), flush=True)
+    buf.destroy()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == '__main__':
+    sys.exit(main())

@@ -58,16 +58,31 @@ def build(verbose: bool = False):
             name=_NAME, sources=sources(), extra_cflags=CXX_FLAGS, extra_cuda_cflags=NVCC_FLAGS,
             extra_include_paths=extra_include_paths(), extra_ldflags=['-lcuda'],
             build_directory=_EXT_DIR, verbose=verbose, with_cuda=True)
+        with open(os.path.join(_EXT_DIR, 'sources.sha256'), 'w') as fh:
+            fh.write(_source_digest())
     return _module
 
 
+def _source_digest() -> str:
+    import hashlib
+    h = hashlib.sha256()
+    for root, dirs, files in os.walk(_CSRC):
+        dirs.sort()
+        for f in sorted(files):
+            h.update(f.encode())
+            with open(os.path.join(root, f), 'rb') as fh:
+                h.update(fh.read())
+    return h.hexdigest()
+
+
 def _stale(so: str) -> bool:
-    so_time = os.path.getmtime(so)
-    for root, _, files in os.walk(_CSRC):
-        for f in files:
-            if os.path.getmtime(os.path.join(root, f)) > so_time:
-                return True
-    return False
+    """The shared object is stale when the digest recorded at build time differs from the sources'
+    (file times do not survive copying the tree to another machine)."""
+    stamp = os.path.join(_EXT_DIR, 'sources.sha256')
+    if not os.path.exists(stamp):
+        return True
+    with open(stamp) as fh:
+        return fh.read().strip() != _source_digest()
 
 
 def load(required: bool = True):
