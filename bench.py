@@ -44,41 +44,54 @@ def parse_args():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of this process's GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and throttle reasons of this process's GPU through NVML (read-only queries) in a
+    background thread while the timed region runs."""
 
-    QUERY = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
-             'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
-             'clocks_event_reasons.sw_power_cap')
-
-    def __init__(self, device_index: int):
-        self.rows, self.proc, self.device_index = [], None, device_index
+    def __init__(self, device_index: int, period_s: float = 0.1):
+        self.device_index, self.period_s = device_index, period_s
+        self.samples, self._stop, self._thread, self._h, self._nvml = [], threading.Event(), None, None, None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.QUERY}', '--format=csv,noheader,nounits',
-                                          '-i', str(self.device_index), '-lms', '100'],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get('CUDA_VISIBLE_DEVICES')
+            index = int(visible.split(',')[self.device_index]) if visible and visible.split(',')[0].isdigit() else self.device_index
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self._nvml = pynvml
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
         except Exception:
-            self.proc = None
+            self._nvml = None
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(',')])
-
-    def stop(self):
-        if self.proc is not None:
-            self.proc.terminate()
+    def _loop(self):
+        n = self._nvml
+        while not self._stop.is_set():
             try:
-                self.proc.wait(timeout=5)
+                self.samples.append((n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM),
+                                     n.nvmlDeviceGetMaxClockInfo(self._h, n.NVML_CLOCK_SM),
+                                     n.nvmlDeviceGetCurrentClocksEventReasons(self._h),
+                                     n.nvmlDeviceGetPowerUsage(self._h) / 1000.0))
             except Exception:
                 pass
-        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace('.', '').isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace('.', '').isdigit()]
-        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
-        reasons = sorted({n for r in self.rows if len(r) >= 7 for n, v in zip(names, r[3:7]) if v == 'Active'})
-        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': max(mx) if mx else None,
-                'reasons': reasons, 'samples': len(sm)}
+            self._stop.wait(self.period_s)
+
+    def mark(self):
+        """Samples taken before this call (warm-up) are dropped from the summary."""
+        self.samples = []
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        if self._nvml is None or not self.samples:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
+        n = self._nvml
+        bits = {'hw_slowdown': n.nvmlClocksEventReasonHwSlowdown, 'hw_thermal_slowdown': n.nvmlClocksEventReasonHwThermalSlowdown,
+                'sw_thermal_slowdown': n.nvmlClocksEventReasonSwThermalSlowdown, 'sw_power_cap': n.nvmlClocksEventReasonSwPowerCap}
+        reasons = sorted({name for s in self.samples for name, bit in bits.items() if s[2] & bit})
+        return {'sm_mhz': statistics.median(s[0] for s in self.samples), 'sm_max_mhz': max(s[1] for s in self.samples),
+                'reasons': reasons, 'samples': len(self.samples), 'power_w_max': max(s[3] for s in self.samples)}
 
 
 def reference_arm(args):
@@ -150,11 +163,13 @@ def main():
             timed = i >= warmup
             if i == warmup:
                 sync_all()
+                sampler.mark()
             flush_l2_cache()
             gpu_barrier()
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
             ev[0].record()
-            recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x, idx, w, num_experts=E, num_sms=num_sms)
+            # no host sync inside the timed kernels: outputs get their worst-case size and the host runs ahead
+            recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x, idx, w, num_experts=E, num_sms=num_sms, do_cpu_sync=False)
             ev[1].record()
             y = buf.get_combine_buffer(handle)
             if i == 0:
@@ -171,17 +186,17 @@ def main():
         t = torch.tensor([[e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3])] for e in times], dtype=torch.float64, device='cuda')
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
-        return t.mean(dim=0).tolist(), handle
+        return t.mean(dim=0).tolist(), t.median(dim=0).values.tolist(), handle
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     wall0 = time.perf_counter()
-    (t_disp, t_comb), handle = run(args.num_sms, args.combine_sms, args.steps, args.warmup)
+    (t_disp, t_comb), (t_disp_med, t_comb_med), handle = run(args.num_sms, args.combine_sms, args.steps, args.warmup)
     wall = time.perf_counter() - wall0
     clocks = sampler.stop() if rank == 0 else None
 
-    rows = torch.tensor([handle.num_recv_tokens], dtype=torch.float64, device='cuda')
+    rows = handle.psum_num_recv_tokens_per_scaleup_rank[-1:].to(torch.float64)
     rows_min = rows.clone()
     if world > 1:
         dist.all_reduce(rows, op=dist.ReduceOp.SUM, group=group)
@@ -197,7 +212,7 @@ def main():
 
     sweep = {}
     for s in [int(v) for v in args.sweep_sms.split(',') if v]:
-        (td, tc), _ = run(s, s, max(3, args.steps // 2), 3)
+        (td, tc), _, _ = run(s, s, max(3, args.steps // 2), 3)
         sweep[str(s)] = {'dispatch_ms': td, 'combine_ms': tc,
                          'dispatch_gbs_per_gpu': rows_total / world * disp_row_bytes / (td * 1e-3) / 1e9,
                          'combine_gbs_per_gpu': rows_total / world * comb_row_bytes / (tc * 1e-3) / 1e9}
@@ -238,7 +253,7 @@ def main():
                        'num_sms_dispatch': args.num_sms, 'num_sms_combine': args.combine_sms or args.num_sms,
                        'l2': 'flushed (256 MB write) before every timed kernel', 'timing': 'CUDA events per kernel, max over ranks, mean over steps',
                        'baseline': f'{ref_per_gpu:.1f} GB/s per GPU = published 726 (dispatch) / 740 (combine) GB/s at EP8, 64 SMs'},
-            'dispatch_ms': t_disp, 'combine_ms': t_comb, 'dispatch_gbs_per_gpu': disp_gbs, 'combine_gbs_per_gpu': comb_gbs,
+            'dispatch_ms': t_disp, 'combine_ms': t_comb, 'dispatch_ms_median': t_disp_med, 'combine_ms_median': t_comb_med, 'dispatch_gbs_per_gpu': disp_gbs, 'combine_gbs_per_gpu': comb_gbs,
             'dispatch_vs_ref': disp_gbs / REF_DISPATCH_GBS, 'combine_vs_ref': comb_gbs / REF_COMBINE_GBS,
             'recv_rows_total': rows_total, 'recv_rows_min_rank': rows_min, 'wall_s_timed_run': wall,
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': args.steps * (2 + (2 if world > 1 else 0)),

@@ -185,7 +185,8 @@ __device__ __forceinline__ void quantize_row(const uint8_t* in, uint8_t* out, fl
 #pragma unroll
         for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
         amax = fmaxf(ptx::warp_max_16(amax), 1e-4f);
-        const float scale = __fdiv_rn(448.f, amax);
+        // 448 * (1 / amax), each step correctly rounded: bit-identical to the PyTorch expression `448.0 / amax`
+        const float scale = __fmul_rn(448.f, __frcp_rn(amax));
         if (in_range) {
             uint32_t packed[2];
 #pragma unroll

@@ -100,7 +100,7 @@ __global__ void quant_kernel(const QuantArgs a) {
             sf = __uint_as_float(static_cast<uint32_t>(exp) << 23);
             scale = __uint_as_float(static_cast<uint32_t>(254 - exp) << 23);
         } else {
-            scale = __fdiv_rn(448.f, amax);
+            scale = __fmul_rn(448.f, __frcp_rn(amax));   // what PyTorch computes for `448.0 / amax`
             sf = __fdiv_rn(amax, 448.f);
         }
         if (in_range) {
