@@ -53,6 +53,11 @@ def build(verbose: bool = False):
     from torch.utils import cpp_extension
     os.makedirs(_EXT_DIR, exist_ok=True)
     os.environ.setdefault('MAX_JOBS', str(os.cpu_count() or 4))
+    # Link with the distribution's g++: a toolchain whose libstdc++.so is missing falls back to the static
+    # archive, and a second private copy of libstdc++ inside the extension breaks iostreams at run time.
+    for var, path in (('CXX', '/usr/bin/g++'), ('CC', '/usr/bin/gcc')):
+        if os.path.exists(path):
+            os.environ[var] = path
     with _lock:
         _module = cpp_extension.load(
             name=_NAME, sources=sources(), extra_cflags=CXX_FLAGS, extra_cuda_cflags=NVCC_FLAGS,

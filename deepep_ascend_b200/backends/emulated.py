@@ -60,6 +60,36 @@ class EmulatedWorld:
         self._C.ElasticBuffer.combine_group(self.cores, calls, num_sms)
         return outs
 
+    def low_latency_dispatch(self, xs, topk_idxs, num_max_tokens: int, num_experts: int, use_fp8: bool = True,
+                             round_scale: bool = False, use_ue8m0: bool = False, num_sms: int = 0, stats=None,
+                             split_phases: bool = False):
+        """Per-rank list of ``(recv_x | (recv_x, scales), recv_count, handle)``.  ``split_phases`` launches the
+        send and the receive half separately, as the hook mode does."""
+        num_sms = min(num_sms or 8, self.max_sms_per_rank())
+        prepared = [b._ll_prepare_dispatch(xs[r], topk_idxs[r], num_max_tokens, num_experts,
+                                           stats[r] if stats is not None else None, None, use_fp8, round_scale, use_ue8m0, 3)
+                    for r, b in enumerate(self.buffers)]
+        calls = [c for c, _ in prepared]
+        for phases in ((1, 2) if split_phases else (3,)):
+            for c in calls:
+                c.phases = phases
+            self._C.ll_dispatch_group(self.cores, calls, num_sms)
+        outs = []
+        for (c, sf), x in zip(prepared, xs):
+            handle = (c.packed_src_info, c.layout_range, num_max_tokens, x.shape[1], num_experts)
+            outs.append(((c.packed_x, sf) if use_fp8 else c.packed_x, c.packed_count, handle))
+        return outs
+
+    def low_latency_combine(self, xs, topk_idxs, topk_weights, handles, num_sms: int = 0, split_phases: bool = False):
+        num_sms = min(num_sms or 8, self.max_sms_per_rank())
+        calls = [b._ll_prepare_combine(xs[r], topk_idxs[r], topk_weights[r], handles[r], None, None, 3)
+                 for r, b in enumerate(self.buffers)]
+        for phases in ((1, 2) if split_phases else (3,)):
+            for c in calls:
+                c.phases = phases
+            self._C.ll_combine_group(self.cores, calls, num_sms)
+        return [c.out for c in calls]
+
     def barrier(self) -> None:
         self._C.ElasticBuffer.barrier_group(self.cores)
 

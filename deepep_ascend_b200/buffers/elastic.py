@@ -22,6 +22,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import layout_ref
+from .low_latency import LowLatencyMixin
 from ..utils.comm import all_gather_object
 from ..utils.event import EventHandle, EventOverlap
 from ..utils.math import align
@@ -103,7 +104,7 @@ class _DispatchState:
                  'keep_alive', 'do_handle_copy')
 
 
-class ElasticBuffer:
+class ElasticBuffer(LowLatencyMixin):
     """Symmetric communication buffer for one expert-parallel group (one process per GPU, or CPU ranks on gloo).
 
     Arguments follow deep_ep (deep_ep/buffers/elastic.py:331-349).  ``num_bytes`` overrides the size derived
@@ -118,8 +119,12 @@ class ElasticBuffer:
                  prefer_overlap_with_compute: bool = True, sl_idx: int = 3, num_allocated_qps: int = 0,
                  num_cpu_timeout_secs: float = 300, num_gpu_timeout_secs: float = 100, explicitly_destroy: bool = False,
                  enable_expand: bool = False, num_experts: int = 0, expert_alignment: int = 1, num_recv_slots: int = 2,
-                 extra_bytes: int = 0, zero_copy: bool = True, _virtual: Optional[Tuple[int, int]] = None):
+                 extra_bytes: int = 0, zero_copy: bool = True, low_latency_shrink: bool = False,
+                 _virtual: Optional[Tuple[int, int]] = None):
         self.group = group
+        self._virtual = _virtual
+        self.low_latency_shrink = low_latency_shrink
+        self._ll = None
         if _virtual is not None:
             self.rank_idx, self.num_ranks = _virtual
         else:
@@ -170,6 +175,7 @@ class ElasticBuffer:
         self.num_bytes = total
         self.extra_offset = align(self.regions.extra, 1024)
         self.extra_bytes = total - self.extra_offset
+        self._extra_cursor = self.extra_offset
         if os.environ.get('EP_BUFFER_DEBUG'):
             print(f'[EP rank {self.rank_idx}] symmetric buffer {total / 2**20:.1f} MiB '
                   f'(MoE regions {moe_bytes / 2**20:.1f} MiB, capacity {self.regions.capacity_rows} rows, '
@@ -184,6 +190,17 @@ class ElasticBuffer:
             if group is not None and self.num_ranks > 1:
                 dist.barrier(group=group)
         self.comm_stream = _get_comm_stream()
+
+    # ------------------------------------------------------------------------------------------ extra region
+    def reserve(self, num_bytes: int, alignment: int = 1024) -> int:
+        """Carve ``num_bytes`` out of the region behind the MoE buffers (``extra_bytes`` at construction) and
+        return its byte offset.  Every rank must make the same sequence of calls."""
+        off = align(self._extra_cursor, alignment)
+        if off + num_bytes > self.num_bytes:
+            raise RuntimeError(f'symmetric buffer too small: need {num_bytes} more bytes behind offset {off} of '
+                               f'{self.num_bytes}; pass a larger `extra_bytes`')
+        self._extra_cursor = off + num_bytes
+        return off
 
     # ------------------------------------------------------------------------------------------ life cycle
     def destroy(self) -> None:

@@ -154,3 +154,49 @@ LaunchShape dispatch_launch_shape(const DispatchArgs& a, int num_sms);
 LaunchShape combine_launch_shape(const CombineArgs& a, int num_sms);
 
 }  // namespace ep
+
+// ------------------------------------------------------------------------------------------------ low latency
+enum { EP_LL_SEND = 1, EP_LL_RECV = 2 };
+
+struct LLDispatchArgs {
+    RankCtx ctx;
+    const void* x;               // [T, H] bf16
+    const void* topk_idx;        // [T, K]
+    int idx_is_64;
+    int num_tokens, hidden, num_topk, num_experts, num_max_tokens;
+    int use_fp8, round_scale, use_ue8m0;
+    int phases;                  // EP_LL_SEND | EP_LL_RECV
+    uint64_t off_slab[2];        // per buffer set: [E_local][R][M] messages inside every rank's symmetric buffer
+    int msg_bytes;               // 16-byte header + payload (+ scales), multiple of 16
+    void* packed_x;              // [E_local, R*M, H] e4m3 or bf16
+    void* packed_sf;             // fp32 [E_local, G, R*M] (column-major per expert) or int32 [E_local, G/4, R*M]
+    int32_t* packed_src_info;    // [E_local, R*M]: (lane << 20) | source token
+    int64_t* layout_range;       // [E_local, R]: (begin << 32) | count
+    int32_t* packed_count;       // [E_local]
+    int32_t* stats;              // [E_local] cumulative or null
+    int64_t* wait_stats;         // [R] accumulated wait ns per source rank, or null
+    int32_t* mask;               // [R] ranks to ignore (shrink mode) or null
+    int shrink;                  // a source that never arrives is masked instead of poisoning the buffer
+};
+
+struct LLCombineArgs {
+    RankCtx ctx;
+    const void* x;               // [E_local, R*M, H] bf16
+    const void* topk_idx;        // [T, K]
+    int idx_is_64;
+    const float* topk_weights;   // [T, K]
+    const int32_t* src_info;     // [E_local, R*M]
+    const int64_t* layout_range; // [E_local, R]
+    int num_tokens, hidden, num_topk, num_experts, num_max_tokens;
+    int phases;
+    uint64_t off_slab[2];        // per buffer set: [M * K][H] bf16 rows inside every rank's symmetric buffer
+    void* out;                   // [T, H] bf16
+    int64_t* wait_stats;
+    int32_t* mask;
+    int shrink;
+};
+
+namespace ep {
+cudaError_t launch_ll_dispatch(const LLDispatchArgs* args, int n, int num_sms, cudaStream_t stream);
+cudaError_t launch_ll_combine(const LLCombineArgs* args, int n, int num_sms, cudaStream_t stream);
+}  // namespace ep

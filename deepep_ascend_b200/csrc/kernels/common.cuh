@@ -59,16 +59,18 @@ __device__ __forceinline__ bool is_aborted(Workspace* ws) {
 // First error wins; later ones only keep the abort flag up.
 static __device__ __noinline__ void report_failure(const RankCtx& ctx, Workspace* ws, uint32_t code, uint32_t phase,
                                             int peer, uint64_t expected, uint64_t observed) {
-    unsigned long long* st = reinterpret_cast<unsigned long long*>(ctx.status);
-    if (atomicCAS_system(st + EP_STATUS_CODE, 0ull, static_cast<unsigned long long>(code)) == 0ull) {
+    // the abort flag lives in device memory, so the race for "first" needs no atomics on host memory
+    if (atomicCAS(&ws->abort_flag, 0u, 1u) == 0u) {
+        volatile uint64_t* st = ctx.status;
         st[EP_STATUS_PHASE] = phase;
-        st[EP_STATUS_PEER] = static_cast<unsigned long long>(static_cast<long long>(peer));
+        st[EP_STATUS_PEER] = static_cast<uint64_t>(static_cast<int64_t>(peer));
         st[EP_STATUS_EXPECTED] = expected;
         st[EP_STATUS_OBSERVED] = observed;
         st[EP_STATUS_RANK] = ctx.rank;
         __threadfence_system();
+        st[EP_STATUS_CODE] = code;
+        __threadfence_system();
     }
-    atomicExch(&ws->abort_flag, 1u);
     __threadfence();
 }
 
@@ -143,6 +145,7 @@ __device__ __forceinline__ bool xgpu_barrier(const RankCtx& ctx, Workspace* ws, 
 }
 
 __device__ __forceinline__ uint64_t tag_value(uint64_t epoch, uint32_t value) { return (epoch << 32) | value; }
+__device__ __forceinline__ uint32_t count_low32(uint64_t word) { return static_cast<uint32_t>(word & 0xffffffffull); }
 __device__ __forceinline__ bool tag_matches(uint64_t word, uint64_t epoch) {
     return (word >> 32) == (epoch & 0xffffffffull);
 }

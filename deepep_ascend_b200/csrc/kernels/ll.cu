@@ -1,0 +1,434 @@
+// Low-latency dispatch / combine for decode-sized batches (graph-capturable: no host sync, no allocation, all
+// protocol state lives in device memory and is epoch-tagged so nothing has to be cleaned between calls).
+//
+// Dispatch:  SEND  - one token per CTA iteration: all warps cast the token bf16 -> e4m3 (1x128 scales; fp32,
+//                    power-of-two or UE8M0) into a message {16 B header, payload, scales} in shared memory, then
+//                    warp k claims a slot for expert topk[k] and bulk-stores the message into the slab
+//                    [local expert][source rank][slot] of the expert's rank through its peer mapping;
+//                    after a grid barrier the per-expert counts go out as epoch-tagged words.
+//            RECV  - one CTA per local expert: wait for every source's count, then pack the messages into
+//                    [local expert, ranks * max_tokens, hidden] (+ column-major scales, source info, ranges).
+// Combine:   SEND  - one CTA per local expert: every packed row is bulk-copied into the slot
+//                    [source token][top-k lane] of the token's home rank; then one epoch-tagged flag per rank pair.
+//            RECV  - wait for all ranks' flags, then out[t] = sum_k w[t,k] * slot[t,k] in fp32 -> bf16.
+// SEND and RECV can be launched separately (phases argument) so that no SM is held while data is in flight.
+//
+// Parity: csrc/kernels/legacy/internode_ll.cu:128-554 (dispatch) and 714-1238 (combine) of the reference.
+#include "common.cuh"
+
+namespace ep {
+
+namespace {
+
+constexpr int kLLThreads = 512;
+constexpr int kLLWarps = kLLThreads / 32;
+constexpr int kLLCombineSmemBudget = 200 * 1024;
+
+// warps of a CTA that stage combine rows (two bf16 rows of shared memory each)
+__host__ __device__ inline int ll_combine_send_warps(int hidden) {
+    const int w = (kLLCombineSmemBudget - 1024) / (2 * hidden * 2);
+    return w < 1 ? 1 : (w > kLLWarps ? kLLWarps : w);
+}
+
+__device__ __forceinline__ int ll_load_idx(const void* p, int is64, int64_t i) {
+    return is64 ? static_cast<int>(__ldg(reinterpret_cast<const long long*>(p) + i)) : __ldg(reinterpret_cast<const int*>(p) + i);
+}
+
+__device__ __forceinline__ bool rank_masked(const int32_t* mask, int r) {
+    return mask != nullptr && *reinterpret_cast<const volatile int32_t*>(mask + r) != 0;
+}
+
+// 8 bf16 values held by each lane -> 8 e4m3 bytes + the dequantization scale of the lane's 128-channel group
+__device__ __forceinline__ uint2 cast_8(const float (&v)[8], int round_scale, float& sf) {
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    amax = fmaxf(ptx::warp_max_16(amax), 1e-4f);
+    float scale;
+    if (round_scale) {
+        const float raw = __fdiv_rn(amax, 448.f);
+        const int exp = static_cast<int>((__float_as_uint(raw) >> 23) & 0xff) + ((__float_as_uint(raw) & 0x7fffff) ? 1 : 0);
+        sf = __uint_as_float(static_cast<uint32_t>(exp) << 23);
+        scale = __uint_as_float(static_cast<uint32_t>(254 - exp) << 23);
+    } else {
+        scale = __fmul_rn(448.f, __frcp_rn(amax));
+        sf = __fdiv_rn(amax, 448.f);
+    }
+    uint32_t packed[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j] * scale, v[4 * j + 1] * scale), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j + 2] * scale, v[4 * j + 3] * scale), __NV_SATFINITE, __NV_E4M3);
+        packed[j] = lo | (hi << 16);
+    }
+    return make_uint2(packed[0], packed[1]);
+}
+
+__device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const RankCtx& ctx = a.ctx;
+    Workspace* ws = local_ws(ctx);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int R = ctx.num_ranks, me = ctx.rank, E = a.num_experts, El = E / R, K = a.num_topk, H = a.hidden;
+    const int M = a.num_max_tokens, G = (H + 127) / 128;
+    const uint64_t epoch = ws->epoch[EP_CH_LL_DISPATCH] + 1;
+    const int set = static_cast<int>(epoch & 1);
+    const int payload = a.use_fp8 ? H : 2 * H;
+    __shared__ uint8_t* s_peer[EP_MAX_RANKS];
+    __shared__ uint32_t s_count[EP_MAX_RANKS], s_begin[EP_MAX_RANKS];
+    if (tid < EP_MAX_RANKS) s_peer[tid] = tid < R ? ctx.peer_base[tid] : nullptr;
+    __syncthreads();
+    bool alive = !is_aborted(ws);
+    uint32_t* slot_counter = ws->ll_counters[0];
+
+    if (a.phases & EP_LL_SEND) {
+        if (blockIdx.x == 0)
+            for (int j = tid; j < El; j += blockDim.x) a.packed_count[j] = 0;
+        const uint8_t* xb = reinterpret_cast<const uint8_t*>(a.x);
+        int n = 0;
+        for (int t = blockIdx.x; t < a.num_tokens; t += gridDim.x, ++n) {
+            uint8_t* msg = smem + (n & 1) * a.msg_bytes;
+            // the message buffer about to be rewritten was the source of the stores issued two tokens ago
+            ptx::bulk_wait_read<1>();
+            __syncthreads();
+            if (a.use_fp8) {
+                float* sf_out = reinterpret_cast<float*>(msg + 16 + H);
+                for (int i = warp; i * 256 < H; i += kLLWarps) {
+                    const int elem = (i * 32 + lane) * 8;
+                    float v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+                    if (elem < H) {
+                        const int4 raw = ptx::ld_nc_v4(xb + (static_cast<int64_t>(t) * H + elem) * 2);
+                        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 f = __bfloat1622float2(h[j]);
+                            v[2 * j] = f.x;
+                            v[2 * j + 1] = f.y;
+                        }
+                    }
+                    float sf;
+                    const uint2 q = cast_8(v, a.round_scale | a.use_ue8m0, sf);
+                    if (elem < H) {
+                        *reinterpret_cast<uint2*>(msg + 16 + elem) = q;
+                        if ((lane & 15) == 0) sf_out[elem / 128] = sf;
+                    }
+                }
+            } else {
+                for (int off = tid * 16; off < payload; off += blockDim.x * 16)
+                    *reinterpret_cast<int4*>(msg + 16 + off) = ptx::ld_nc_v4(xb + static_cast<int64_t>(t) * payload + off);
+            }
+            ptx::fence_proxy_async_smem();
+            __syncthreads();
+            if (warp < K && lane == 0) {
+                const int e = ll_load_idx(a.topk_idx, a.idx_is_64, static_cast<int64_t>(t) * K + warp);
+                if (e >= 0 && e < E && !rank_masked(a.mask, e / El)) {
+                    const uint32_t slot = atomicAdd(&slot_counter[e], 1u);
+                    if (slot < static_cast<uint32_t>(M)) {
+                        uint8_t* dst = s_peer[e / El] + a.off_slab[set] +
+                                       ((static_cast<int64_t>(e % El) * R + me) * M + slot) * a.msg_bytes;
+                        // header word 1 carries the top-k lane; it differs per destination, so it goes out as a
+                        // separate 16-byte store after the bulk copy of the shared message body
+                        ptx::bulk_store(dst + 16, msg + 16, a.msg_bytes - 16);
+                        *reinterpret_cast<int4*>(dst) = make_int4(t, warp, 0, 0);
+                    } else {
+                        report_failure(ctx, ws, EP_ERR_BOUNDS, EP_PH_LL_RECV_COUNT, e / El, M, slot);
+                    }
+                }
+                ptx::bulk_commit();
+            }
+        }
+        ptx::bulk_commit();
+        ptx::bulk_wait<0>();
+        __threadfence_system();
+        alive = grid_sync(ctx, ws, EP_CH_LL_DISPATCH, EP_PH_GRID_SYNC) && alive;
+        // publish how many messages every expert got from this rank (a tagged zero means "none")
+        if (alive) {
+            for (int e = blockIdx.x * blockDim.x + tid; e < E; e += gridDim.x * blockDim.x) {
+                const uint32_t n_sent = min(__ldcg(&slot_counter[e]), static_cast<uint32_t>(M));
+                __stcg(&slot_counter[e], 0u);
+                if (!rank_masked(a.mask, e / El)) {
+                    Workspace* pws = reinterpret_cast<Workspace*>(s_peer[e / El]);
+                    ptx::st_release_sys(&pws->ll_signal[0][(e % El) * R + me], tag_value(epoch, n_sent));
+                }
+            }
+        }
+    }
+
+    if (a.phases & EP_LL_RECV) {
+        const uint8_t* slab = s_peer[me] + a.off_slab[set];
+        const int64_t rows_per_expert = static_cast<int64_t>(R) * M;
+        for (int j = blockIdx.x; j < El && alive; j += gridDim.x) {
+            __syncthreads();
+            int ok = 1;
+            if (tid < R) {
+                const int src = tid;
+                uint32_t n_recv = 0;
+                if (!rank_masked(a.mask, src)) {
+                    const uint64_t* sig = &ws->ll_signal[0][j * R + src];
+                    const uint64_t t0 = globaltimer_ns();
+                    if (a.shrink) {
+                        // shrink mode: a source that stays silent is masked out instead of failing the call
+                        bool got = false;
+                        while (!(got = tag_matches(ptx::ld_acquire_sys(sig), epoch)))
+                            if (globaltimer_ns() - t0 > ctx.timeout_ns) break;
+                        if (!got) atomicExch(a.mask + src, 1);
+                        else n_recv = count_low32(ptx::ld_relaxed_sys(sig));
+                    } else {
+                        ok = bounded_wait(
+                            ctx, ws, EP_PH_LL_RECV_COUNT, src, epoch, [&] { return tag_matches(ptx::ld_acquire_sys(sig), epoch); },
+                            [&] { return ptx::ld_relaxed_sys(sig); });
+                        if (ok) n_recv = count_low32(ptx::ld_relaxed_sys(sig));
+                    }
+                    if (a.wait_stats != nullptr && j == static_cast<int>(blockIdx.x))
+                        atomicAdd(reinterpret_cast<unsigned long long*>(a.wait_stats + src), globaltimer_ns() - t0);
+                }
+                s_count[src] = n_recv;
+            }
+            alive = __syncthreads_and(ok) != 0;
+            if (!alive) break;
+            if (tid == 0) {
+                uint32_t begin = 0;
+                for (int s = 0; s < R; ++s) {
+                    s_begin[s] = begin;
+                    a.layout_range[j * R + s] = (static_cast<int64_t>(begin) << 32) | s_count[s];
+                    begin += s_count[s];
+                }
+                a.packed_count[j] = begin;
+                if (a.stats != nullptr) a.stats[j] += begin;
+            }
+            __syncthreads();
+            // one warp per message
+            for (int s = 0; s < R; ++s) {
+                const uint32_t cnt = s_count[s], begin = s_begin[s];
+                for (uint32_t i = warp; i < cnt; i += kLLWarps) {
+                    const uint8_t* m = slab + ((static_cast<int64_t>(j) * R + s) * M + i) * a.msg_bytes;
+                    const int64_t pos = static_cast<int64_t>(j) * rows_per_expert + begin + i;
+                    const int4 hdr = __ldcg(reinterpret_cast<const int4*>(m));
+                    if (lane == 0) a.packed_src_info[pos] = (hdr.y << 20) | hdr.x;
+                    uint8_t* out = reinterpret_cast<uint8_t*>(a.packed_x) + pos * payload;
+                    for (int off = lane * 16; off < payload; off += 32 * 16)
+                        *reinterpret_cast<int4*>(out + off) = __ldcg(reinterpret_cast<const int4*>(m + 16 + off));
+                    if (a.use_fp8) {
+                        const float* sf = reinterpret_cast<const float*>(m + 16 + H);
+                        if (a.use_ue8m0) {
+                            // four exponents per int32, groups along the slow axis: [E_local, ceil(G/4), R*M]
+                            uint8_t* dst = reinterpret_cast<uint8_t*>(a.packed_sf);
+                            const int64_t G4 = (G + 3) / 4;
+                            for (int g = lane; g < G; g += 32)
+                                dst[((static_cast<int64_t>(j) * G4 + g / 4) * rows_per_expert + begin + i) * 4 + (g & 3)] =
+                                    static_cast<uint8_t>(__float_as_uint(sf[g]) >> 23);
+                        } else {
+                            float* dst = reinterpret_cast<float*>(a.packed_sf);
+                            for (int g = lane; g < G; g += 32)
+                                dst[(static_cast<int64_t>(j) * G + g) * rows_per_expert + begin + i] = sf[g];
+                        }
+                    }
+                }
+            }
+        }
+        const bool cta_ok = __syncthreads_and(alive ? 1 : 0) != 0;
+        alive = grid_sync(ctx, ws, EP_CH_LL_DISPATCH, EP_PH_GRID_SYNC) && cta_ok;
+        if (blockIdx.x == 0 && tid == 0) ws->epoch[EP_CH_LL_DISPATCH] = epoch;
+    }
+}
+
+
+__device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const RankCtx& ctx = a.ctx;
+    Workspace* ws = local_ws(ctx);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int R = ctx.num_ranks, me = ctx.rank, E = a.num_experts, El = E / R, K = a.num_topk, H = a.hidden;
+    const int M = a.num_max_tokens;
+    const int row_bytes = 2 * H;
+    const uint64_t epoch = ws->epoch[EP_CH_LL_COMBINE] + 1;
+    const int set = static_cast<int>(epoch & 1);
+    __shared__ uint8_t* s_peer[EP_MAX_RANKS];
+    __shared__ uint32_t s_count[EP_MAX_RANKS], s_begin[EP_MAX_RANKS + 1];
+    if (tid < EP_MAX_RANKS) s_peer[tid] = tid < R ? ctx.peer_base[tid] : nullptr;
+    // per warp: two staging rows and two mbarriers
+    const int send_warps = ll_combine_send_warps(H);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * 2;
+    uint8_t* stage = smem + 1024 + static_cast<size_t>(warp < send_warps ? warp : 0) * 2 * row_bytes;
+    if (lane == 0) {
+        ptx::mbar_init(&bars[0], 1);
+        ptx::mbar_init(&bars[1], 1);
+    }
+    ptx::mbar_fence_init();
+    __syncthreads();
+    ptx::fence_proxy_async_smem();
+    bool alive = !is_aborted(ws);
+
+    if (a.phases & EP_LL_SEND) {
+        const uint8_t* xb = reinterpret_cast<const uint8_t*>(a.x);
+        const int64_t rows_per_expert = static_cast<int64_t>(R) * M;
+        uint32_t n_loaded = 0;   // loads issued by this warp so far (selects stage and mbarrier parity)
+        for (int j = blockIdx.x; j < El && alive; j += gridDim.x) {
+            __syncthreads();
+            if (tid < R) {
+                const int64_t lr = a.layout_range[j * R + tid];
+                s_count[tid] = static_cast<uint32_t>(lr & 0xffffffffll);
+                s_begin[tid] = static_cast<uint32_t>(lr >> 32);
+            }
+            __syncthreads();
+            for (int s = 0; s < R && alive; ++s) {
+                if (rank_masked(a.mask, s)) continue;
+                const uint32_t cnt = s_count[s], begin = s_begin[s];
+                for (uint32_t i = warp; warp < send_warps && i < cnt && alive; i += send_warps) {
+                    const int64_t pos = static_cast<int64_t>(j) * rows_per_expert + begin + i;
+                    const int info = a.src_info[pos];
+                    const int t = info & 0xfffff, k = info >> 20;
+                    const int st = n_loaded & 1;
+                    // the stage was the source of the store issued two rows ago
+                    ptx::bulk_wait_read<1>();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::mbar_arrive_expect_tx(&bars[st], row_bytes);
+                        ptx::bulk_load(stage + st * row_bytes, xb + pos * row_bytes, row_bytes, &bars[st]);
+                    }
+                    alive = mbar_wait_bounded(ctx, ws, &bars[st], (n_loaded >> 1) & 1, EP_PH_COMBINE_LOAD);
+                    ++n_loaded;
+                    if (!alive) break;
+                    if (lane == 0) {
+                        uint8_t* dst = s_peer[s] + a.off_slab[set] + (static_cast<int64_t>(t) * K + k) * row_bytes;
+                        ptx::bulk_store(dst, stage + st * row_bytes, row_bytes);
+                    }
+                    ptx::bulk_commit();
+                }
+            }
+        }
+        ptx::bulk_commit();
+        ptx::bulk_wait<0>();
+        __threadfence_system();
+        const bool cta_ok = __syncthreads_and(alive ? 1 : 0) != 0;
+        alive = grid_sync(ctx, ws, EP_CH_LL_COMBINE, EP_PH_GRID_SYNC) && cta_ok;
+        if (alive && blockIdx.x == 0 && tid < R && !rank_masked(a.mask, tid)) {
+            Workspace* pws = reinterpret_cast<Workspace*>(s_peer[tid]);
+            ptx::st_release_sys(&pws->ll_signal[1][me], tag_value(epoch, 1));
+        }
+    }
+
+    if (a.phases & EP_LL_RECV) {
+        int ok = alive ? 1 : 0;
+        if (alive && tid < R && !rank_masked(a.mask, tid)) {
+            const uint64_t* sig = &ws->ll_signal[1][tid];
+            const uint64_t t0 = globaltimer_ns();
+            if (a.shrink) {
+                bool got = false;
+                while (!(got = tag_matches(ptx::ld_acquire_sys(sig), epoch)))
+                    if (globaltimer_ns() - t0 > ctx.timeout_ns) break;
+                if (!got) atomicExch(a.mask + tid, 1);
+            } else {
+                ok = bounded_wait(
+                    ctx, ws, EP_PH_LL_COMBINE_FLAG, tid, epoch, [&] { return tag_matches(ptx::ld_acquire_sys(sig), epoch); },
+                    [&] { return ptx::ld_relaxed_sys(sig); });
+            }
+            if (a.wait_stats != nullptr && blockIdx.x == 0)
+                atomicAdd(reinterpret_cast<unsigned long long*>(a.wait_stats + tid), globaltimer_ns() - t0);
+        }
+        alive = __syncthreads_and(ok) != 0;
+        if (alive) {
+            // out[t] = sum_k w[t, k] * slot[t, k]; work item = (token, 4 KB column chunk), one warp each
+            const uint8_t* slab = s_peer[me] + a.off_slab[set];
+            constexpr int kChunk = 32 * 16 * 8;
+            const int num_chunks = (row_bytes + kChunk - 1) / kChunk;
+            const int64_t items = static_cast<int64_t>(a.num_tokens) * num_chunks;
+            for (int64_t it = static_cast<int64_t>(blockIdx.x) * kLLWarps + warp; it < items; it += static_cast<int64_t>(gridDim.x) * kLLWarps) {
+                const int t = static_cast<int>(it / num_chunks), c = static_cast<int>(it % num_chunks);
+                const int bytes = min(kChunk, row_bytes - c * kChunk);
+                int e_k = -1;
+                float w_k = 0.f;
+                if (lane < K) {
+                    e_k = ll_load_idx(a.topk_idx, a.idx_is_64, static_cast<int64_t>(t) * K + lane);
+                    w_k = __ldg(a.topk_weights + static_cast<int64_t>(t) * K + lane);
+                    if (e_k >= 0 && rank_masked(a.mask, e_k / El)) e_k = -1;
+                }
+                float acc[64];
+#pragma unroll
+                for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+                const uint32_t srcs = __ballot_sync(0xffffffffu, e_k >= 0 && e_k < E);
+                for (int k = 0; k < K; ++k) {
+                    if (!((srcs >> k) & 1u)) continue;
+                    const float w = __shfl_sync(0xffffffffu, w_k, k);
+                    const uint8_t* row = slab + (static_cast<int64_t>(t) * K + k) * row_bytes + static_cast<int64_t>(c) * kChunk;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int off = (u * 32 + lane) * 16;
+                        if (off < bytes) {
+                            const int4 raw = __ldcg(reinterpret_cast<const int4*>(row + off));
+                            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float2 f = __bfloat1622float2(h[q]);
+                                acc[u * 8 + 2 * q] = fmaf(w, f.x, acc[u * 8 + 2 * q]);
+                                acc[u * 8 + 2 * q + 1] = fmaf(w, f.y, acc[u * 8 + 2 * q + 1]);
+                            }
+                        }
+                    }
+                }
+                uint8_t* out = reinterpret_cast<uint8_t*>(a.out) + static_cast<int64_t>(t) * row_bytes + static_cast<int64_t>(c) * kChunk;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int off = (u * 32 + lane) * 16;
+                    if (off < bytes) {
+                        int4 raw;
+                        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(acc[u * 8 + 2 * q], acc[u * 8 + 2 * q + 1]);
+                        *reinterpret_cast<int4*>(out + off) = raw;
+                    }
+                }
+            }
+        }
+        const bool cta_ok = __syncthreads_and(alive ? 1 : 0) != 0;
+        grid_sync(ctx, ws, EP_CH_LL_COMBINE, EP_PH_GRID_SYNC);
+        (void)cta_ok;
+        if (blockIdx.x == 0 && tid == 0) ws->epoch[EP_CH_LL_COMBINE] = epoch;
+    }
+}
+
+__global__ void __launch_bounds__(kLLThreads, 1) ll_dispatch_kernel(const __grid_constant__ LLDispatchArgs a) { ll_dispatch_body(a); }
+__global__ void __launch_bounds__(kLLThreads, 1) ll_dispatch_kernel_multi(const LLDispatchArgs* a) { ll_dispatch_body(a[blockIdx.y]); }
+__global__ void __launch_bounds__(kLLThreads, 1) ll_combine_kernel(const __grid_constant__ LLCombineArgs a) { ll_combine_body(a); }
+__global__ void __launch_bounds__(kLLThreads, 1) ll_combine_kernel_multi(const LLCombineArgs* a) { ll_combine_body(a[blockIdx.y]); }
+
+template <typename Args>
+cudaError_t launch_ll(const void* single, const void* multi, const Args* args, int n, int num_sms, int smem, cudaStream_t stream) {
+    const void* fn = n == 1 ? single : multi;
+    cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return err;
+    const int ctas = num_sms < 1 ? 1 : (num_sms > EP_MAX_CTAS ? EP_MAX_CTAS : num_sms);
+    dim3 grid(ctas, n, 1), block(kLLThreads, 1, 1);
+    if (n == 1) {
+        void* params[] = {const_cast<Args*>(args)};
+        return cudaLaunchCooperativeKernel(fn, grid, block, params, smem, stream);
+    }
+    Args* dev = nullptr;
+    err = cudaMallocAsync(reinterpret_cast<void**>(&dev), sizeof(Args) * n, stream);
+    if (err != cudaSuccess) return err;
+    err = cudaMemcpyAsync(dev, args, sizeof(Args) * n, cudaMemcpyHostToDevice, stream);
+    if (err == cudaSuccess) {
+        void* params[] = {&dev};
+        err = cudaLaunchCooperativeKernel(fn, grid, block, params, smem, stream);
+    }
+    cudaFreeAsync(dev, stream);
+    return err;
+}
+
+}  // namespace
+
+cudaError_t launch_ll_dispatch(const LLDispatchArgs* args, int n, int num_sms, cudaStream_t stream) {
+    const int smem = 2 * args[0].msg_bytes;
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    return launch_ll<LLDispatchArgs>((const void*)ll_dispatch_kernel, (const void*)ll_dispatch_kernel_multi, args, n, num_sms, smem, stream);
+}
+
+cudaError_t launch_ll_combine(const LLCombineArgs* args, int n, int num_sms, cudaStream_t stream) {
+    const int smem = 1024 + ll_combine_send_warps(args[0].hidden) * 2 * args[0].hidden * 2;
+    if (smem > 227 * 1024) return cudaErrorInvalidValue;
+    return launch_ll<LLCombineArgs>((const void*)ll_combine_kernel, (const void*)ll_combine_kernel_multi, args, n, num_sms, smem, stream);
+}
+
+}  // namespace ep

@@ -6,6 +6,11 @@
 #include "runtime/coordinator.hpp"
 #include "runtime/elastic_buffer.hpp"
 #include "runtime/layout.hpp"
+#include "runtime/low_latency.hpp"
+
+#include <execinfo.h>
+#include <signal.h>
+#include <unistd.h>
 
 namespace py = pybind11;
 using namespace ep_host;
@@ -55,6 +60,15 @@ std::vector<at::Tensor> per_token_cast_to_fp8(const at::Tensor& x, bool round_sc
     a.sf_stride_col = 1;
     cuda_check(ep::launch_quant(a, at::cuda::getCurrentCUDAStream()), "quant launch");
     return {q, sf};
+}
+
+// Debug aid: print the native call stack when the process receives SIGSEGV, then re-raise.
+void segv_backtrace_handler(int sig) {
+    void* frames[64];
+    const int n = backtrace(frames, 64);
+    backtrace_symbols_fd(frames, n, STDERR_FILENO);
+    signal(sig, SIG_DFL);
+    raise(sig);
 }
 
 }  // namespace
@@ -173,6 +187,50 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_static("barrier_group", &ElasticBufferCore::barrier_group)
         .def_static("wait_flag_test_group", &ElasticBufferCore::wait_flag_test_group);
 
+    py::class_<LLDispatchCall>(m, "LLDispatchCall")
+        .def(py::init<>())
+        .def_readwrite("x", &LLDispatchCall::x)
+        .def_readwrite("topk_idx", &LLDispatchCall::topk_idx)
+        .def_readwrite("num_experts", &LLDispatchCall::num_experts)
+        .def_readwrite("num_max_tokens", &LLDispatchCall::num_max_tokens)
+        .def_readwrite("use_fp8", &LLDispatchCall::use_fp8)
+        .def_readwrite("round_scale", &LLDispatchCall::round_scale)
+        .def_readwrite("use_ue8m0", &LLDispatchCall::use_ue8m0)
+        .def_readwrite("phases", &LLDispatchCall::phases)
+        .def_readwrite("off_slab0", &LLDispatchCall::off_slab0)
+        .def_readwrite("off_slab1", &LLDispatchCall::off_slab1)
+        .def_readwrite("msg_bytes", &LLDispatchCall::msg_bytes)
+        .def_readwrite("packed_x", &LLDispatchCall::packed_x)
+        .def_readwrite("packed_sf", &LLDispatchCall::packed_sf)
+        .def_readwrite("packed_src_info", &LLDispatchCall::packed_src_info)
+        .def_readwrite("layout_range", &LLDispatchCall::layout_range)
+        .def_readwrite("packed_count", &LLDispatchCall::packed_count)
+        .def_readwrite("stats", &LLDispatchCall::stats)
+        .def_readwrite("wait_stats", &LLDispatchCall::wait_stats)
+        .def_readwrite("mask", &LLDispatchCall::mask)
+        .def_readwrite("shrink", &LLDispatchCall::shrink);
+    py::class_<LLCombineCall>(m, "LLCombineCall")
+        .def(py::init<>())
+        .def_readwrite("x", &LLCombineCall::x)
+        .def_readwrite("topk_idx", &LLCombineCall::topk_idx)
+        .def_readwrite("topk_weights", &LLCombineCall::topk_weights)
+        .def_readwrite("src_info", &LLCombineCall::src_info)
+        .def_readwrite("layout_range", &LLCombineCall::layout_range)
+        .def_readwrite("out", &LLCombineCall::out)
+        .def_readwrite("num_experts", &LLCombineCall::num_experts)
+        .def_readwrite("num_max_tokens", &LLCombineCall::num_max_tokens)
+        .def_readwrite("phases", &LLCombineCall::phases)
+        .def_readwrite("off_slab0", &LLCombineCall::off_slab0)
+        .def_readwrite("off_slab1", &LLCombineCall::off_slab1)
+        .def_readwrite("wait_stats", &LLCombineCall::wait_stats)
+        .def_readwrite("mask", &LLCombineCall::mask)
+        .def_readwrite("shrink", &LLCombineCall::shrink);
+    m.def("ll_dispatch_group", &ll_dispatch_group);
+    m.def("ll_combine_group", &ll_combine_group);
+    m.def("ll_message_bytes", &ll_message_bytes);
+    m.def("get_low_latency_rdma_size_hint", &ll_size_hint, py::arg("num_max_dispatch_tokens_per_rank"), py::arg("hidden"),
+          py::arg("num_ranks"), py::arg("num_experts"), py::arg("num_topk") = 8);
+    m.def("install_segv_backtrace", [] { signal(SIGSEGV, segv_backtrace_handler); });
     m.def("get_dispatch_layout", &get_dispatch_layout);
     m.def("per_token_cast_to_fp8", &per_token_cast_to_fp8, py::arg("x"), py::arg("round_scale") = false,
           py::arg("use_ue8m0") = false);

@@ -164,8 +164,8 @@ public:
         std::vector<std::unique_ptr<OperationScope>> scopes;
         std::vector<DispatchArgs> args(group.size());
         for (size_t i = 0; i < group.size(); ++i) {
-            group[i]->check_status();
             scopes.push_back(std::make_unique<OperationScope>(group[i]->coord_, "dispatch"));
+            group[i]->check_status();
             args[i] = group[i]->make_dispatch_args(calls[i]);
             TORCH_CHECK(args[i].quantize == args[0].quantize && args[i].hidden == args[0].hidden &&
                             args[i].num_experts == args[0].num_experts && args[i].num_topk == args[0].num_topk &&
@@ -186,8 +186,8 @@ public:
         std::vector<std::unique_ptr<OperationScope>> scopes;
         std::vector<CombineArgs> args(group.size());
         for (size_t i = 0; i < group.size(); ++i) {
-            group[i]->check_status();
             scopes.push_back(std::make_unique<OperationScope>(group[i]->coord_, "combine"));
+            group[i]->check_status();
             args[i] = group[i]->make_combine_args(calls[i]);
             TORCH_CHECK(args[i].hidden == args[0].hidden && args[i].num_topk == args[0].num_topk,
                         "all virtual ranks must use the same combine configuration");
@@ -201,8 +201,8 @@ public:
         std::vector<std::unique_ptr<OperationScope>> scopes;
         std::vector<RankCtx> ctxs;
         for (auto* g : group) {
-            g->check_status();
             scopes.push_back(std::make_unique<OperationScope>(g->coord_, "barrier"));
+            g->check_status();
             ctxs.push_back(g->ctx());
         }
         cuda_check(ep::launch_barrier(ctxs.data(), static_cast<int>(ctxs.size()), at::cuda::getCurrentCUDAStream()),
