@@ -11,22 +11,48 @@
 // Parity: does the work of combine_impl + combine_reduce_epilogue_impl
 // (deep_ep/include/deep_ep/impls/combine.cuh:15-243, combine_reduce_epilogue.cuh:12-143) plus the weighted
 // reduction of the legacy low-latency combine (csrc/kernels/legacy/internode_ll.cu:1033-1136).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ep {
 
 namespace {
 
-constexpr int kCombineMaxWarps = 12;
-constexpr int kCombineSlots = 2;
-constexpr int kCombineSmemBudget = 216 * 1024;
+constexpr int kCombineMaxWarps = 16;
+constexpr int kCombineMaxRing = 32;              // chunk buffers (and mbarriers) per warp
+constexpr int kCombineSmemBudget = 208 * 1024;
 
 template <int kUnroll>
 struct CombineCfg {
     static constexpr int kChunkBytes = 32 * 16 * kUnroll;
 };
 
-__host__ __device__ inline int combine_slot_bytes(int K, int chunk_bytes) { return K * chunk_bytes; }
+// Shared-memory plan: [peer table | mbarriers W x ring | chunk buffers W x ring]
+struct CombineSmemPlan {
+    int num_warps, ring, off_bar, off_data, total;
+};
+__host__ __device__ inline CombineSmemPlan combine_smem_plan(int chunk_bytes, int num_warps) {
+    CombineSmemPlan p;
+    p.num_warps = num_warps;
+    p.off_bar = 128;
+    p.off_data = 128 + num_warps * kCombineMaxRing * 8;
+    p.off_data = (p.off_data + 1023) / 1024 * 1024;
+    int ring = (kCombineSmemBudget - p.off_data) / (num_warps * chunk_bytes);
+    p.ring = ring > kCombineMaxRing ? kCombineMaxRing : ring;
+    p.total = p.off_data + num_warps * p.ring * chunk_bytes;
+    return p;
+}
+
+// Cursor over the flattened sequence of (work item, source) pairs of one warp.  Lane k holds plan[t][k] of the
+// cursor's item; `pending` has one bit per source that is still to be visited, lowest lane first.
+struct PullCursor {
+    int token;           // >= num_tokens when exhausted
+    int chunk;
+    int plan_k;
+    uint32_t sources;    // lanes of the token's plan that hold a row
+    uint32_t pending;    // sources of the current chunk not visited yet
+};
 
 template <int kUnroll>
 __device__ __forceinline__ void combine_body(const CombineArgs& a) {
@@ -39,14 +65,16 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
     const int K = a.num_topk, T = a.num_tokens;
     const int row_bytes = a.hidden * 2;
     const int num_chunks = (row_bytes + kChunk - 1) / kChunk;
+    const CombineSmemPlan sp = combine_smem_plan(kChunk, num_warps);
+    const int ring = sp.ring;
 
     uint8_t** s_peer = reinterpret_cast<uint8_t**>(smem);
-    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + EP_MAX_RANKS * 8) + warp * kCombineSlots;
-    uint8_t* s_data = smem + 1024 + static_cast<size_t>(warp) * kCombineSlots * combine_slot_bytes(K, kChunk);
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + sp.off_bar) + warp * kCombineMaxRing;
+    uint8_t* s_data = smem + sp.off_data + static_cast<size_t>(warp) * ring * kChunk;
 
     if (tid < EP_MAX_RANKS) s_peer[tid] = tid < ctx.num_ranks ? ctx.peer_base[tid] : nullptr;
     if (lane == 0)
-        for (int s = 0; s < kCombineSlots; ++s) ptx::mbar_init(&s_bar[s], 1);
+        for (int b = 0; b < ring; ++b) ptx::mbar_init(&s_bar[b], 1);
     ptx::mbar_fence_init();
     __syncthreads();
     ptx::fence_proxy_async_smem();
@@ -56,54 +84,64 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
     if (blockIdx.x == 0) alive = xgpu_barrier(ctx, ws, EP_CH_COMBINE, EP_PH_COMBINE_ENTRY) && alive;
     alive = grid_sync(ctx, ws, EP_CH_COMBINE, EP_PH_GRID_SYNC) && alive;
 
-    const int64_t num_items = static_cast<int64_t>(T) * num_chunks;
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * num_warps;
-    const int64_t first = static_cast<int64_t>(blockIdx.x) * num_warps + warp;
+    // a warp owns tokens first, first + stride, ... and walks the column chunks of each token in order, so the
+    // plan row of a token is read once
+    const int stride = static_cast<int>(gridDim.x) * num_warps;
+    const int first = static_cast<int>(blockIdx.x) * num_warps + warp;
 
-    // issue the loads of item `it` into slot `slot`; returns this lane's plan entry for the item
-    auto issue = [&](int64_t it, int slot) -> int {
-        const int t = static_cast<int>(it / num_chunks), c = static_cast<int>(it % num_chunks);
-        const int p = lane < K ? a.plan[static_cast<int64_t>(t) * K + lane] : -1;
-        const int bytes = min(kChunk, row_bytes - c * kChunk);
-        const uint32_t srcs = __ballot_sync(0xffffffffu, p >= 0);
-        // always arrive (with 0 bytes for an item without sources) so the slot's phase advances once per item
-        if (lane == 0) ptx::mbar_arrive_expect_tx(&s_bar[slot], __popc(srcs) * bytes);
-        __syncwarp();
-        if (p >= 0) {
-            const uint8_t* src = s_peer[p >> 24] + a.off_x + static_cast<int64_t>(p & 0xffffff) * row_bytes +
-                                 static_cast<int64_t>(c) * kChunk;
-            ptx::bulk_load(s_data + (slot * K + lane) * kChunk, src, bytes, &s_bar[slot]);
+    auto load_token = [&](PullCursor& c) {
+        c.chunk = 0;
+        c.plan_k = -1;
+        c.sources = 0;
+        if (c.token < T) {
+            c.plan_k = lane < K ? a.plan[static_cast<int64_t>(c.token) * K + lane] : -1;
+            c.sources = __ballot_sync(0xffffffffu, c.plan_k >= 0);
         }
-        return p;
+        c.pending = c.sources;
+    };
+    auto next_chunk = [&](PullCursor& c) {
+        if (++c.chunk == num_chunks) {
+            c.token += stride;
+            load_token(c);
+        } else {
+            c.pending = c.sources;
+        }
     };
 
     if (alive) {
-        int plan_q[kCombineSlots];   // this lane's plan entry of the item held by each slot
-#pragma unroll
-        for (int s = 0; s < kCombineSlots - 1; ++s) {
-            const int64_t it = first + s * stride;
-            plan_q[s] = it < num_items ? issue(it, s) : -1;
-        }
-        int64_t n = 0;
-        for (int64_t it = first; it < num_items && alive; it += stride, ++n) {
-            const int slot = static_cast<int>(n % kCombineSlots);
-            const uint32_t parity = static_cast<uint32_t>((n / kCombineSlots) & 1);
-            // prefetch the item that is kSlots-1 ahead into the slot that was consumed last iteration
-            {
-                const int64_t ahead = it + (kCombineSlots - 1) * stride;
-                const int aslot = static_cast<int>((n + kCombineSlots - 1) % kCombineSlots);
-                const int p = ahead < num_items ? issue(ahead, aslot) : -1;
-#pragma unroll
-                for (int s = 0; s < kCombineSlots; ++s)
-                    if (s == aslot) plan_q[s] = p;
+        PullCursor prod{first, 0, -1, 0, 0}, cons{first, 0, -1, 0, 0};
+        load_token(prod);
+        load_token(cons);
+        uint32_t issued = 0, consumed = 0;   // loads issued / consumed by this warp; buffer = counter % ring
+
+        // issue loads in sequence order until the ring is full or the warp's work is exhausted
+        auto issue_ahead = [&]() {
+            while (issued - consumed < static_cast<uint32_t>(ring) && prod.token < T) {
+                if (prod.pending == 0) {
+                    next_chunk(prod);
+                    continue;
+                }
+                const int k = __ffs(prod.pending) - 1;
+                prod.pending &= prod.pending - 1;
+                const int p = __shfl_sync(0xffffffffu, prod.plan_k, k);
+                if (lane == 0) {
+                    const int c = prod.chunk;
+                    const int bytes = min(kChunk, row_bytes - c * kChunk);
+                    const int b = issued % ring;
+                    const uint8_t* src = s_peer[p >> 24] + a.off_x + static_cast<int64_t>(p & 0xffffff) * row_bytes +
+                                         static_cast<int64_t>(c) * kChunk;
+                    ptx::mbar_arrive_expect_tx(&s_bar[b], bytes);
+                    ptx::bulk_load(s_data + b * kChunk, src, bytes, &s_bar[b]);
+                }
+                ++issued;
             }
-            int plan_k = -1;
-#pragma unroll
-            for (int s = 0; s < kCombineSlots; ++s)
-                if (s == slot) plan_k = plan_q[s];
-            const int t = static_cast<int>(it / num_chunks), c = static_cast<int>(it % num_chunks);
+        };
+
+        for (; cons.token < T && alive; next_chunk(cons)) {
+            const int t = cons.token, c = cons.chunk;
             const int bytes = min(kChunk, row_bytes - c * kChunk);
             const int col0 = c * kChunk;   // byte offset inside the row
+            issue_ahead();
 
             float acc[kUnroll * 8];
 #pragma unroll
@@ -142,13 +180,16 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
             float mul_k = 1.f;
             if (a.mul_weights != nullptr && lane < K) mul_k = __ldg(a.mul_weights + static_cast<int64_t>(t) * K + lane);
 
-            const uint32_t srcs = __ballot_sync(0xffffffffu, plan_k >= 0);
-            alive = mbar_wait_bounded(ctx, ws, &s_bar[slot], parity, EP_PH_COMBINE_LOAD);
-            if (!alive) break;
-            for (int k = 0; k < K; ++k) {
-                if (!((srcs >> k) & 1u)) continue;
+            // sources in top-k lane order; each one sits in the next ring buffer
+            uint32_t srcs = cons.pending;
+            while (srcs != 0 && alive) {
+                const int k = __ffs(srcs) - 1;
+                srcs &= srcs - 1;
+                const int b = consumed % ring;
+                alive = mbar_wait_bounded(ctx, ws, &s_bar[b], (consumed / ring) & 1, EP_PH_COMBINE_LOAD);
+                if (!alive) break;
                 const float w = __shfl_sync(0xffffffffu, mul_k, k);
-                const uint8_t* buf = s_data + (slot * K + k) * kChunk;
+                const uint8_t* buf = s_data + b * kChunk;
 #pragma unroll
                 for (int u = 0; u < kUnroll; ++u) {
                     const int off = (u * 32 + lane) * 16;
@@ -163,7 +204,13 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
                         }
                     }
                 }
+                // the buffer may be refilled once every lane has read it
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                ++consumed;
+                issue_ahead();
             }
+            if (!alive) break;
             uint8_t* out = reinterpret_cast<uint8_t*>(a.out) + static_cast<int64_t>(t) * row_bytes + col0;
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
@@ -176,8 +223,14 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
                     ptx::st_na_v4(out + off, raw);
                 }
             }
-            ptx::fence_proxy_async_smem();
-            __syncwarp();   // every lane is done with this slot before the next iteration refills it
+        }
+        // loads still in flight belong to nobody once the loop was left early: wait for them (bounded) so that
+        // no copy lands in shared memory after the CTA has exited
+        while (consumed < issued) {
+            if (!bounded_wait(ctx, ws, EP_PH_COMBINE_LOAD, -1, consumed,
+                              [&] { return ptx::mbar_try_wait(&s_bar[consumed % ring], (consumed / ring) & 1); }, [&] { return 0ull; }))
+                break;
+            ++consumed;
         }
     }
 
@@ -199,8 +252,18 @@ __global__ void __launch_bounds__(kCombineMaxWarps * 32, 1) combine_kernel_multi
     combine_body<kUnroll>(args[blockIdx.y]);
 }
 
+inline int env_int(const char* name, int fallback) {
+    const char* v = std::getenv(name);
+    return v != nullptr && *v != 0 ? std::atoi(v) : fallback;
+}
+
+// column chunk = 512 B x unroll; EP_COMBINE_UNROLL overrides the choice when the row divides evenly
 inline int pick_unroll(const CombineArgs& a) {
     const int row_bytes = a.hidden * 2;
+    const int forced = env_int("EP_COMBINE_UNROLL", 0);
+    if ((forced == 7 || forced == 4 || forced == 2 || forced == 1) && row_bytes % (512 * forced) == 0) return forced;
+    // larger chunks amortise the per-chunk bookkeeping: 3584 B when the row divides evenly (hidden 7168), else 2048 B
+    if (row_bytes % 3584 == 0) return 7;
     return row_bytes % 2048 == 0 ? 4 : (row_bytes % 1024 == 0 ? 2 : (row_bytes >= 2048 ? 4 : 1));
 }
 
@@ -209,11 +272,11 @@ inline int pick_unroll(const CombineArgs& a) {
 LaunchShape combine_launch_shape(const CombineArgs& a, int num_sms) {
     LaunchShape s;
     s.num_ctas = num_sms < 1 ? 1 : (num_sms > EP_MAX_CTAS ? EP_MAX_CTAS : num_sms);
-    const int chunk = 512 * pick_unroll(a);
-    const int per_warp = kCombineSlots * combine_slot_bytes(a.num_topk, chunk);
-    s.num_warps = kCombineMaxWarps;
-    while (s.num_warps > 1 && 1024 + s.num_warps * per_warp > kCombineSmemBudget) --s.num_warps;
-    s.smem_bytes = 1024 + s.num_warps * per_warp;
+    int warps = env_int("EP_COMBINE_WARPS", 12);
+    warps = warps < 1 ? 1 : (warps > kCombineMaxWarps ? kCombineMaxWarps : warps);
+    const CombineSmemPlan p = combine_smem_plan(512 * pick_unroll(a), warps);
+    s.num_warps = p.num_warps;
+    s.smem_bytes = p.total;
     return s;
 }
 
@@ -224,10 +287,11 @@ cudaError_t launch_combine(const CombineArgs* args, int n, int num_sms, cudaStre
     const int unroll = pick_unroll(a0);
     const void* fn;
     if (n == 1)
-        fn = unroll == 4 ? (const void*)combine_kernel<4> : unroll == 2 ? (const void*)combine_kernel<2> : (const void*)combine_kernel<1>;
+        fn = unroll == 7 ? (const void*)combine_kernel<7> : unroll == 4 ? (const void*)combine_kernel<4>
+             : unroll == 2 ? (const void*)combine_kernel<2> : (const void*)combine_kernel<1>;
     else
-        fn = unroll == 4 ? (const void*)combine_kernel_multi<4>
-                         : unroll == 2 ? (const void*)combine_kernel_multi<2> : (const void*)combine_kernel_multi<1>;
+        fn = unroll == 7 ? (const void*)combine_kernel_multi<7> : unroll == 4 ? (const void*)combine_kernel_multi<4>
+             : unroll == 2 ? (const void*)combine_kernel_multi<2> : (const void*)combine_kernel_multi<1>;
     cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, shape.smem_bytes);
     if (err != cudaSuccess) return err;
     dim3 grid(shape.num_ctas, n, 1), block(shape.num_warps * 32, 1, 1);

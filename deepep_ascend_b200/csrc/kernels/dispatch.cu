@@ -15,6 +15,8 @@
 // Parity: does the work of dispatch_impl + dispatch_copy_epilogue_impl
 // (deep_ep/include/deep_ep/impls/dispatch.cuh:17-409, dispatch_copy_epilogue.cuh:11-323) and of the fused
 // FP8 cast of the legacy low-latency kernel (csrc/kernels/legacy/internode_ll.cu:212-250).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ep {
@@ -31,7 +33,7 @@ struct DispatchSmemPlan {
     int off_start;      // uint32 [E]   first row of each expert at its rank
     int off_wc_rank;    // uint32 [W][R]
     int off_wc_expert;  // uint32 [W][E]
-    int off_bar;        // uint64 [W][2]
+    int off_bar;        // uint64 [W][3]
     int off_sf;         // float  [W][2][G]
     int off_stage;      // per warp: stage buffers
     int in_bytes, out_bytes, n_in, n_out, warp_stage_bytes;
@@ -51,19 +53,22 @@ __host__ __device__ inline DispatchSmemPlan make_smem_plan(const DispatchArgs& a
     p.off_start = off;      off += align_int(E * 4, 16);
     p.off_wc_rank = off;    off += align_int(num_warps * R * 4, 16);
     p.off_wc_expert = off;  off += align_int(num_warps * E * 4, 16);
-    p.off_bar = off;        off += num_warps * 2 * 8;
+    p.off_bar = off;        off += num_warps * 3 * 8;
     p.off_sf = off;         off += align_int(num_warps * 2 * G * 4, 16);
     off = align_int(off, 128);
     p.off_stage = off;
     const int in_row = a.hidden * (a.x_is_fp8 ? 1 : 2);
     p.in_bytes = align_int(in_row, 128);
     if (a.quantize) {
+        // the cast reads global memory directly; two output stages (the stores of token n-1 may still be
+        // reading while token n is cast)
         p.out_bytes = align_int(a.hidden, 128);
-        p.n_in = 1;
+        p.n_in = 0;
         p.n_out = 2;
     } else {
+        // the input stage is also the store source: three stages keep one load and one store in flight
         p.out_bytes = 0;
-        p.n_in = 2;
+        p.n_in = 3;
         p.n_out = 0;
     }
     p.warp_stage_bytes = p.n_in * p.in_bytes + p.n_out * p.out_bytes;
@@ -159,27 +164,38 @@ __device__ __forceinline__ void layout_pass(const DispatchArgs& a, Slice sl, uin
 
 __device__ __forceinline__ uint32_t count_of(uint64_t word) { return static_cast<uint32_t>(word & 0xffffffffull); }
 
-// bf16 row in shared memory -> e4m3 row + one fp32 scale per 128 channels.
+// Fused cast: a row is processed in register batches of kCastSteps x 256 channels.  All 16-byte loads of a batch
+// are issued back to back straight from global memory, the next batch is requested before the current one is
+// converted, and the unrolled conversions of a batch are independent of one another, so neither the memory
+// latency nor the shuffle / reciprocal latency chains of one 128-channel group are exposed.
 // q = x * (448 / max(amax, 1e-4)) rounded to nearest even, scale = max(amax, 1e-4) / 448.
-__device__ __forceinline__ void quantize_row(const uint8_t* in, uint8_t* out, float* sf, int H) {
+constexpr int kCastSteps = 7;
+
+struct RowBatch {
+    int4 v[kCastSteps];
+};
+
+__device__ __forceinline__ void load_batch(RowBatch& b, const uint8_t* row, int H, int batch) {
     const int lane = ptx::lane_id();
-    const int iters = (H + 255) / 256;
-    for (int i = 0; i < iters; ++i) {
-        const int elem = (i * 32 + lane) * 8;
-        const bool in_range = elem < H;
+#pragma unroll
+    for (int i = 0; i < kCastSteps; ++i) {
+        const int elem = ((batch * kCastSteps + i) * 32 + lane) * 8;
+        b.v[i] = elem < H ? ptx::ld_nc_v4(row + elem * 2) : make_int4(0, 0, 0, 0);
+    }
+}
+
+__device__ __forceinline__ void cast_batch(const RowBatch& b, uint8_t* out, float* sf, int H, int batch) {
+    const int lane = ptx::lane_id();
+#pragma unroll
+    for (int i = 0; i < kCastSteps; ++i) {
+        const int elem = ((batch * kCastSteps + i) * 32 + lane) * 8;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&b.v[i]);
         float v[8];
-        if (in_range) {
-            const int4 raw = *reinterpret_cast<const int4*>(in + elem * 2);
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __bfloat1622float2(h[j]);
-                v[2 * j] = f.x;
-                v[2 * j + 1] = f.y;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = 0.f;
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            v[2 * j] = f.x;
+            v[2 * j + 1] = f.y;
         }
         float amax = 0.f;
 #pragma unroll
@@ -187,7 +203,7 @@ __device__ __forceinline__ void quantize_row(const uint8_t* in, uint8_t* out, fl
         amax = fmaxf(ptx::warp_max_16(amax), 1e-4f);
         // 448 * (1 / amax), each step correctly rounded: bit-identical to the PyTorch expression `448.0 / amax`
         const float scale = __fmul_rn(448.f, __frcp_rn(amax));
-        if (in_range) {
+        if (elem < H) {
             uint32_t packed[2];
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
@@ -221,7 +237,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
     uint32_t* s_start = reinterpret_cast<uint32_t*>(smem + sp.off_start);
     uint32_t* s_wc_rank = reinterpret_cast<uint32_t*>(smem + sp.off_wc_rank);
     uint32_t* s_wc_expert = reinterpret_cast<uint32_t*>(smem + sp.off_wc_expert);
-    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + sp.off_bar) + warp * 2;
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + sp.off_bar) + warp * 3;
     float* s_sf = reinterpret_cast<float*>(smem + sp.off_sf) + warp * 2 * G;
     uint8_t* s_stage = smem + sp.off_stage + warp * sp.warp_stage_bytes;
 
@@ -230,6 +246,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
     if (lane == 0) {
         ptx::mbar_init(&s_bar[0], 1);
         ptx::mbar_init(&s_bar[1], 1);
+        ptx::mbar_init(&s_bar[2], 1);
     }
     ptx::mbar_fence_init();
     for (int i = tid; i < num_warps * R; i += nthreads) s_wc_rank[i] = 0;
@@ -390,14 +407,29 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
         uint8_t* out_stage = s_stage + sp.n_in * sp.in_bytes;
         const uint8_t* xb = reinterpret_cast<const uint8_t*>(a.x);
         const int count = sl.end - sl.begin;
-        if (count > 0 && lane == 0) {
+        const int S_in = kQuant ? 1 : sp.n_in;
+        const int num_batches = ((a.hidden + 255) / 256 + kCastSteps - 1) / kCastSteps;
+        RowBatch cur;
+        if (kQuant) {
+            if (count > 0) load_batch(cur, xb + static_cast<int64_t>(sl.begin) * in_row, a.hidden, 0);
+        } else if (count > 0 && lane == 0) {
             ptx::mbar_arrive_expect_tx(&s_bar[0], in_row);
             ptx::bulk_load(in_stage, xb + static_cast<int64_t>(sl.begin) * in_row, in_row, &s_bar[0]);
         }
         for (int n = 0; n < count && alive; ++n) {
             const int t = sl.begin + n;
-            const int st = kQuant ? 0 : (n & 1);
-            const uint32_t parity = kQuant ? (n & 1) : ((n >> 1) & 1);
+            const int st = n % S_in;
+            const uint32_t parity = (n / S_in) & 1;
+            if (!kQuant) {
+                // prefetch token n+1; its stage was the source of the bulk stores of token n-2
+                ptx::bulk_wait_read<1>();
+                __syncwarp();
+                if (n + 1 < count && lane == 0) {
+                    const int ns = (n + 1) % S_in;
+                    ptx::mbar_arrive_expect_tx(&s_bar[ns], in_row);
+                    ptx::bulk_load(in_stage + ns * sp.in_bytes, xb + static_cast<int64_t>(t + 1) * in_row, in_row, &s_bar[ns]);
+                }
+            }
             int e_k = -1, plan_k = -1;
             float w_k = 0.f;
             if (lane < K) {
@@ -408,23 +440,26 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
             float* sf_cur = s_sf + (n & 1) * G;
             if (!kQuant && has_sf)
                 for (int j = lane; j < G; j += 32) sf_cur[j] = __ldg(a.sf + static_cast<int64_t>(t) * G + j);
-            alive = mbar_wait_bounded(ctx, ws, &s_bar[st], parity, EP_PH_DISPATCH_LOAD);
-            if (!alive) break;
             const uint8_t* src_smem;
             if (kQuant) {
                 // the out stage about to be overwritten was read by the stores of token n-2
                 ptx::bulk_wait_read<1>();
                 __syncwarp();
                 uint8_t* o = out_stage + (n & 1) * sp.out_bytes;
-                quantize_row(in_stage, o, sf_cur, a.hidden);
+                const uint8_t* row = xb + static_cast<int64_t>(t) * in_row;
+                for (int b = 0; b < num_batches; ++b) {
+                    RowBatch nxt;
+                    if (b + 1 < num_batches) load_batch(nxt, row, a.hidden, b + 1);
+                    else if (n + 1 < count) load_batch(nxt, row + in_row, a.hidden, 0);   // first batch of the next token
+                    cast_batch(cur, o, sf_cur, a.hidden, b);
+                    cur = nxt;
+                }
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
-                if (n + 1 < count && lane == 0) {
-                    ptx::mbar_arrive_expect_tx(&s_bar[0], in_row);
-                    ptx::bulk_load(in_stage, xb + static_cast<int64_t>(t + 1) * in_row, in_row, &s_bar[0]);
-                }
                 src_smem = o;
             } else {
+                alive = mbar_wait_bounded(ctx, ws, &s_bar[st], parity, EP_PH_DISPATCH_LOAD);
+                if (!alive) break;
                 src_smem = in_stage + st * sp.in_bytes;
                 __syncwarp();
             }
@@ -471,16 +506,6 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                         reinterpret_cast<int2*>(base + a.off_recv_meta)[row] = make_int2(me * a.num_max_tokens + t, me * K + k);
                 }
             }
-            if (!kQuant) {
-                // the other stage was read by the stores of token n-1: free it, then prefetch token n+1
-                ptx::bulk_wait_read<1>();
-                __syncwarp();
-                if (n + 1 < count && lane == 0) {
-                    ptx::mbar_arrive_expect_tx(&s_bar[st ^ 1], in_row);
-                    ptx::bulk_load(in_stage + (st ^ 1) * sp.in_bytes, xb + static_cast<int64_t>(t + 1) * in_row, in_row,
-                                   &s_bar[st ^ 1]);
-                }
-            }
         }
     }
 
@@ -514,7 +539,9 @@ LaunchShape dispatch_launch_shape(const DispatchArgs& a, int num_sms) {
     s.num_ctas = num_sms < 1 ? 1 : (num_sms > EP_MAX_CTAS ? EP_MAX_CTAS : num_sms);
     // as many warps (each with its own staging ring) as fit in shared memory; the token-per-step layout
     // needs at least one warp
+    const char* forced = std::getenv("EP_DISPATCH_WARPS");
     s.num_warps = kDispatchMaxWarps;
+    if (forced != nullptr && std::atoi(forced) >= 1 && std::atoi(forced) <= kDispatchMaxWarps) s.num_warps = std::atoi(forced);
     while (s.num_warps > 1 && make_smem_plan(a, s.num_warps).total > kDispatchSmemBudget) --s.num_warps;
     s.smem_bytes = make_smem_plan(a, s.num_warps).total;
     return s;
