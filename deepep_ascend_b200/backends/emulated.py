@@ -90,6 +90,72 @@ class EmulatedWorld:
             self._C.ll_combine_group(self.cores, calls, num_sms)
         return [c.out for c in calls]
 
+    def agrs_set_config(self, num_max_session_bytes: int, num_max_agrs_per_session: int = 32) -> None:
+        for b in self.buffers:
+            b.agrs_set_config(num_max_session_bytes, num_max_agrs_per_session)
+
+    def create_agrs_session(self) -> None:
+        for b in self.buffers:
+            b.create_agrs_session()
+
+    def destroy_agrs_session(self) -> None:
+        self._C.ElasticBuffer.barrier_group(self.cores, self._C.CH_AGRS)
+        for b in self.buffers:
+            b._agrs['open'] = False
+
+    def all_gather(self, tensors: Sequence[torch.Tensor]):
+        """tensors[r] is rank r's contribution -> per-rank ``[num_ranks, *shape]`` views."""
+        from ..buffers.collectives import _contiguous_strides
+        outs = []
+        for r, b in enumerate(self.buffers):
+            t = tensors[r].contiguous()
+            off, nbytes = b._agrs_alloc(t.shape, t.dtype)
+            for peer in range(self.num_ranks):
+                b.core.peer_copy(peer, off + r * nbytes, t)
+            shape = [self.num_ranks] + list(t.shape)
+            outs.append(b.core.view(off, shape, list(_contiguous_strides(shape)), t.dtype))
+        self._C.ElasticBuffer.barrier_group(self.cores, self._C.CH_AGRS)
+        return outs
+
+    def reduce_scatter(self, tensors: Sequence[torch.Tensor]):
+        """tensors[r] is rank r's ``[num_ranks, *shape]`` input -> per-rank reduced ``[*shape]``."""
+        from ..buffers.collectives import _contiguous_strides
+        views = []
+        for r, b in enumerate(self.buffers):
+            t = tensors[r].contiguous()
+            shape = list(t.shape[1:])
+            off, nbytes = b._agrs_alloc(shape, t.dtype)
+            for peer in range(self.num_ranks):
+                b.core.peer_copy(peer, off + r * nbytes, t[peer])
+            sshape = [self.num_ranks] + shape
+            views.append((b.core.view(off, sshape, list(_contiguous_strides(sshape)), t.dtype), shape, t))
+        self._C.ElasticBuffer.barrier_group(self.cores, self._C.CH_AGRS)
+        outs = []
+        for slots, shape, t in views:
+            out = torch.empty(shape, dtype=t.dtype, device=t.device)
+            self._C.reduce_slots(slots, out)
+            outs.append(out)
+        return outs
+
+    def engram_write(self, storages: Sequence[torch.Tensor]) -> None:
+        from ..utils.math import align
+        self._C.ElasticBuffer.barrier_group(self.cores, self._C.CH_ENGRAM)
+        for b, st in zip(self.buffers, storages):
+            st = st.contiguous()
+            N, H = st.shape
+            entry = H * st.element_size()
+            if b._engram is None:
+                b._engram = {'offset': b.reserve(align(N * entry, 1024)), 'N': N, 'H': H, 'dtype': st.dtype, 'entry': entry}
+            b.core.view(b._engram['offset'], [N, H], [H, 1], st.dtype).copy_(st)
+        self._C.ElasticBuffer.barrier_group(self.cores, self._C.CH_ENGRAM)
+
+    def engram_fetch(self, indices: Sequence[torch.Tensor], num_sms: int = 4):
+        e = self.buffers[0]._engram
+        idx = [i.contiguous().to(torch.int32) for i in indices]
+        outs = [torch.empty((i.shape[0], i.shape[1] * e['H']), dtype=e['dtype'], device=i.device) for i in idx]
+        self._C.ElasticBuffer.engram_fetch_group(self.cores, [i.view(-1) for i in idx], outs, e['N'], e['entry'], e['offset'], num_sms)
+        return outs
+
     def barrier(self) -> None:
         self._C.ElasticBuffer.barrier_group(self.cores)
 

@@ -1,0 +1,211 @@
+"""The non-MoE collectives of ``ElasticBuffer``: all-gather / reduce-scatter sessions on the copy engines,
+pipeline-parallel send / recv, context-parallel KV gather and Engram remote fetch.
+
+* AG / RS sessions (parity: csrc/elastic/buffer.hpp:379-526, deep_ep/buffers/elastic.py:1154-1251; reduce-scatter
+  has no counterpart in the reference, whose README lists it as on-going): data moves with peer
+  ``cudaMemcpyAsync`` on the copy engines, one per peer; completion is a 32-thread signal kernel over NVLink, so
+  no SM is busy while the bytes move.
+* PP (parity: csrc/elastic/buffer.hpp:329-377): ring-neighbour send / recv on NCCL point-to-point, on a side
+  stream so that it overlaps with compute.
+* Engram (parity: csrc/elastic/buffer.hpp:212-327): every rank publishes a table of fixed-size entries in its
+  symmetric buffer; ``engram_fetch`` pulls arbitrary entries from their owners with TMA loads over NVLink.
+"""
+import math
+from typing import Callable, List, Optional, Sequence, Tuple, Union
+
+import torch
+import torch.distributed as dist
+
+from ..utils.math import align
+
+
+class CollectivesMixin:
+    """Mixed into ``ElasticBuffer``; uses ``self.core``, ``self.reserve``, ``self.comm_stream``."""
+
+    _agrs = None
+    _pp = None
+    _engram = None
+
+    # ------------------------------------------------------------------------------------------ AG / RS sessions
+    def agrs_set_config(self, num_max_session_bytes: int, num_max_agrs_per_session: int = 32) -> None:
+        """Reserve the gather region: ``num_max_session_bytes`` is the sum over the tensors of one session of
+        ``align(num_ranks * tensor_bytes, 32)``."""
+        assert num_max_agrs_per_session <= 32
+        assert self._agrs is None or not self._agrs['open'], 'destroy the open session first'
+        self._agrs = {'offset': self.reserve(align(num_max_session_bytes, 1024)), 'bytes': num_max_session_bytes,
+                      'cursor': 0, 'open': False, 'count': 0, 'max': num_max_agrs_per_session, 'inplace': {}}
+
+    def create_agrs_session(self) -> None:
+        assert self._agrs is not None, 'call agrs_set_config first'
+        assert not self._agrs['open'], 'one session at a time'
+        self._agrs.update(open=True, cursor=0, count=0, inplace={})
+
+    def destroy_agrs_session(self) -> None:
+        """All ranks must be done reading the gathered tensors before the region is recycled."""
+        assert self._agrs is not None and self._agrs['open']
+        self.comm_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.comm_stream):
+            self.core.barrier(self._C.CH_AGRS)
+        torch.cuda.current_stream().wait_stream(self.comm_stream)
+        self._agrs['open'] = False
+
+    def _agrs_alloc(self, shape: Sequence[int], dtype: torch.dtype) -> Tuple[int, int]:
+        a = self._agrs
+        assert a is not None and a['open'], 'no open AG/RS session'
+        assert a['count'] < a['max'], 'too many collectives in this session'
+        nbytes = math.prod(shape) * dtype.itemsize
+        total = align(self.num_ranks * nbytes, 32)
+        assert a['cursor'] + total <= a['bytes'], 'session region exhausted: raise num_max_session_bytes'
+        off = a['offset'] + a['cursor']
+        a['cursor'] += total
+        a['count'] += 1
+        return off, nbytes
+
+    def agrs_get_inplace_tensor(self, shape: Sequence[int], dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """This rank's slice inside the next gather slot: a producer that writes its result here saves the
+        local copy of ``all_gather``."""
+        off, nbytes = self._agrs_alloc(shape, dtype)
+        t = self.core.view(off + self.rank_idx * nbytes, list(shape), list(_contiguous_strides(shape)), dtype)
+        self._agrs['inplace'][t.data_ptr()] = (off, nbytes)
+        return t
+
+    def all_gather(self, tensors: Union[torch.Tensor, Sequence[torch.Tensor]]) -> Tuple[Union[torch.Tensor, List[torch.Tensor]], Callable]:
+        """Gather ``t`` (or each tensor of a list) from all ranks -> ``([num_ranks, *shape] view(s), wait)``.
+        ``wait()`` makes the current stream wait for the gathered data."""
+        single = isinstance(tensors, torch.Tensor)
+        ts = [tensors] if single else list(tensors)
+        self.comm_stream.wait_stream(torch.cuda.current_stream())
+        outs = []
+        with torch.cuda.stream(self.comm_stream):
+            for t in ts:
+                t = t.contiguous()
+                if t.data_ptr() in self._agrs['inplace']:
+                    off, nbytes = self._agrs['inplace'].pop(t.data_ptr())
+                    skip_local = True
+                else:
+                    off, nbytes = self._agrs_alloc(t.shape, t.dtype)
+                    skip_local = False
+                for step in range(self.num_ranks):
+                    peer = (self.rank_idx + step) % self.num_ranks     # stagger the destinations
+                    if peer == self.rank_idx and skip_local:
+                        continue
+                    self.core.peer_copy(peer, off + self.rank_idx * nbytes, t)
+                shape = [self.num_ranks] + list(t.shape)
+                outs.append(self.core.view(off, shape, list(_contiguous_strides(shape)), t.dtype))
+            self.core.barrier(self._C.CH_AGRS)
+        event = torch.cuda.Event()
+        event.record(self.comm_stream)
+
+        def wait() -> None:
+            torch.cuda.current_stream().wait_event(event)
+        return (outs[0] if single else outs), wait
+
+    def reduce_scatter(self, tensor: torch.Tensor) -> Tuple[torch.Tensor, Callable]:
+        """``tensor [num_ranks, *shape]`` (bf16 or fp32): rank ``r`` receives ``sum over ranks of tensor[r]``
+        accumulated in fp32 in rank order.  Slices travel on the copy engines; the sum is one local kernel.
+        -> ``(out [*shape], wait)``."""
+        assert tensor.shape[0] == self.num_ranks and tensor.dtype in (torch.bfloat16, torch.float32)
+        tensor = tensor.contiguous()
+        shape = list(tensor.shape[1:])
+        self.comm_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.comm_stream):
+            off, nbytes = self._agrs_alloc(shape, tensor.dtype)
+            for step in range(self.num_ranks):
+                peer = (self.rank_idx + step) % self.num_ranks
+                self.core.peer_copy(peer, off + self.rank_idx * nbytes, tensor[peer])
+            self.core.barrier(self._C.CH_AGRS)
+            slots_shape = [self.num_ranks] + shape
+            slots = self.core.view(off, slots_shape, list(_contiguous_strides(slots_shape)), tensor.dtype)
+            out = torch.empty(shape, dtype=tensor.dtype, device=tensor.device)
+            self._C.reduce_slots(slots, out)
+        event = torch.cuda.Event()
+        event.record(self.comm_stream)
+
+        def wait() -> None:
+            torch.cuda.current_stream().wait_event(event)
+        return out, wait
+
+    def cp_all_gather_kv(self, k: torch.Tensor, v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, Callable]:
+        """Context parallelism helper: gather the K and V shards of every rank with zero SMs (inside an open
+        AG/RS session).  -> ``(k_all [ranks, ...], v_all [ranks, ...], wait)``."""
+        (k_all, v_all), wait = self.all_gather([k, v])
+        return k_all, v_all, wait
+
+    # ------------------------------------------------------------------------------------------ pipeline parallel
+    def pp_set_config(self, num_max_tensor_bytes: int, num_max_inflight_tensors: int) -> None:
+        """Ring neighbours and the side stream for pipeline send / recv."""
+        self._pp = {'prev': (self.rank_idx - 1) % self.num_ranks, 'next': (self.rank_idx + 1) % self.num_ranks,
+                    'max_bytes': num_max_tensor_bytes, 'inflight': num_max_inflight_tensors,
+                    'stream': torch.cuda.Stream(), 'pending': []}
+
+    def _pp_check(self, t: torch.Tensor, peer: int) -> None:
+        assert self._pp is not None, 'call pp_set_config first'
+        assert peer in (self._pp['prev'], self._pp['next']), 'pipeline peers are the ring neighbours'
+        assert t.numel() * t.element_size() <= self._pp['max_bytes'], 'tensor exceeds num_max_tensor_bytes'
+        if len(self._pp['pending']) >= 2 * self._pp['inflight']:
+            self._pp['pending'].pop(0).wait()
+
+    def pp_send(self, t: torch.Tensor, dst_rank_idx: int) -> None:
+        """Send ``t`` to a ring neighbour; ordered after the current stream's work, executed on the side stream."""
+        self._pp_check(t, dst_rank_idx)
+        s = self._pp['stream']
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            t.record_stream(s)
+            self._pp['pending'].append(dist.isend(t.contiguous(), dist.get_global_rank(self.group, dst_rank_idx), group=self.group))
+
+    def pp_recv(self, t: torch.Tensor, src_rank_idx: int) -> None:
+        """Receive into ``t`` from a ring neighbour; the current stream waits for the data."""
+        self._pp_check(t, src_rank_idx)
+        s = self._pp['stream']
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            work = dist.irecv(t, dist.get_global_rank(self.group, src_rank_idx), group=self.group)
+            work.wait()
+        torch.cuda.current_stream().wait_stream(s)
+
+    # ------------------------------------------------------------------------------------------ Engram
+    def engram_write(self, storage: torch.Tensor, sf: Optional[torch.Tensor] = None) -> None:
+        """Publish this rank's table ``storage [N, H]`` (bf16 or fp8); scale factors stay local."""
+        storage = storage.contiguous()
+        N, H = storage.shape
+        entry = H * storage.element_size()
+        assert entry % 16 == 0
+        if self._engram is None:
+            self._engram = {'offset': self.reserve(align(N * entry, 1024)), 'N': N, 'H': H, 'dtype': storage.dtype, 'entry': entry}
+        e = self._engram
+        assert (N, H, storage.dtype) == (e['N'], e['H'], e['dtype']), 'the Engram table shape is fixed per buffer'
+        e['sf'] = sf
+        self.comm_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.comm_stream):
+            self.core.barrier(self._C.CH_ENGRAM)       # nobody is still fetching the old table
+            self.core.view(e['offset'], [N, H], [H, 1], storage.dtype).copy_(storage)
+            self.core.barrier(self._C.CH_ENGRAM)       # every table is in place
+        torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    def engram_fetch(self, indices: torch.Tensor, num_qps: int = 0, use_tma_aligned_col_major_sf: bool = False, num_sms: int = 16):
+        """``indices int32 [T, n]`` of global entry ids (owner = id // N) -> hook; ``hook()`` waits and returns
+        ``(fetched [T, n * H], fetched_sf | None)``."""
+        e = self._engram
+        assert e is not None, 'call engram_write first'
+        idx = indices.contiguous().to(torch.int32)
+        T, n = idx.shape
+        out = torch.empty((T, n * e['H']), dtype=e['dtype'], device=idx.device)
+        self.comm_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.comm_stream):
+            self._C.ElasticBuffer.engram_fetch_group([self.core], [idx.view(-1)], [out], e['N'], e['entry'], e['offset'], num_sms)
+        event = torch.cuda.Event()
+        event.record(self.comm_stream)
+
+        def hook():
+            torch.cuda.current_stream().wait_event(event)
+            return out, None
+        return hook
+
+
+def _contiguous_strides(shape: Sequence[int]) -> Tuple[int, ...]:
+    strides, acc = [], 1
+    for s in reversed(list(shape)):
+        strides.append(acc)
+        acc *= max(1, s)
+    return tuple(reversed(strides))

@@ -23,6 +23,7 @@ import torch.distributed as dist
 
 from ..ops import layout_ref
 from .low_latency import LowLatencyMixin
+from .collectives import CollectivesMixin
 from ..utils.comm import all_gather_object
 from ..utils.event import EventHandle, EventOverlap
 from ..utils.math import align
@@ -104,7 +105,7 @@ class _DispatchState:
                  'keep_alive', 'do_handle_copy')
 
 
-class ElasticBuffer(LowLatencyMixin):
+class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
     """Symmetric communication buffer for one expert-parallel group (one process per GPU, or CPU ranks on gloo).
 
     Arguments follow deep_ep (deep_ep/buffers/elastic.py:331-349).  ``num_bytes`` overrides the size derived
@@ -125,6 +126,8 @@ class ElasticBuffer(LowLatencyMixin):
         self._virtual = _virtual
         self.low_latency_shrink = low_latency_shrink
         self._ll = None
+        self._agrs = self._pp = self._engram = None
+        self.profile = None
         if _virtual is not None:
             self.rank_idx, self.num_ranks = _virtual
         else:
@@ -422,6 +425,9 @@ class ElasticBuffer(LowLatencyMixin):
         G = (H + 127) // 128
         call.sf_stride_row, call.sf_stride_col = (1, cap) if col_major_sf else (G, 1)
         call.recv_capacity_rows = cap
+        if self.profile is not None:
+            call.prof = self.profile['dispatch']
+            call.skip_side_stores = bool(int(os.environ.get('EP_PROFILE_SKIP_SIDE_STORES', '0')))
 
         st = _DispatchState()
         st.call, st.T, st.H, st.K, st.E = call, T, H, K, num_experts
@@ -543,6 +549,8 @@ class ElasticBuffer(LowLatencyMixin):
         call.plan = handle.plan
         call.lane_src = handle.dst_buffer_slot_idx
         call.hidden = H
+        if self.profile is not None:
+            call.prof = self.profile['combine']
         T, K = handle.plan.shape
         out = torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
         call.out = out
@@ -595,6 +603,22 @@ class ElasticBuffer(LowLatencyMixin):
     def capture(self) -> EventHandle:
         """An event on the current stream, usable as ``previous_event``."""
         return EventHandle(torch.cuda.current_stream() if not self.is_cpu else None)
+
+    # ------------------------------------------------------------------------------------------ profiling
+    def enable_profiling(self, enabled: bool = True) -> None:
+        """Make dispatch / combine record device-side phase timestamps (ns, CTA 0 of this rank); read them with
+        :meth:`phase_times`.  Dispatch: start, counted, exchanged, assigned, scattered, grid drained, peers done.
+        Combine: start, entry barrier, pulled, grid drained, exit barrier."""
+        self.profile = {k: torch.zeros(8, dtype=torch.int64, device='cuda') for k in ('dispatch', 'combine')} if enabled else None
+
+    def phase_times(self) -> dict:
+        """Microseconds spent in each phase of the last dispatch and combine."""
+        torch.cuda.synchronize()
+        d, c = self.profile['dispatch'].tolist(), self.profile['combine'].tolist()
+        names_d = ['layout_count', 'count_exchange', 'assign_rows', 'scatter', 'grid_drain', 'peer_done']
+        names_c = ['entry_barrier', 'pull_reduce', 'grid_drain', 'exit_barrier']
+        return {'dispatch': {n: (d[i + 1] - d[i]) / 1e3 for i, n in enumerate(names_d) if d[i + 1] and d[i]},
+                'combine': {n: (c[i + 1] - c[i]) / 1e3 for i, n in enumerate(names_c) if c[i + 1] and c[i]}}
 
     # ------------------------------------------------------------------------------------------ failures
     def check_status(self) -> None:

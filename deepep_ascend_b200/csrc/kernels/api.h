@@ -97,6 +97,8 @@ struct DispatchArgs {
     uint64_t off_recv_x, off_recv_sf, off_recv_idx, off_recv_w, off_recv_meta;
     int64_t sf_stride_row, sf_stride_col;   // element strides of the receiver's scale tensor
     int recv_capacity_rows;
+    uint64_t* prof;                // optional [8] phase timestamps (ns) written by CTA 0, or null
+    int skip_side_stores;          // profiling only: leave out the per-row scale / index / weight / metadata stores
 };
 
 struct CombineArgs {
@@ -112,6 +114,7 @@ struct CombineArgs {
     void* out;                     // [T, H] bf16
     float* out_w;                  // [T, K] or null
     int num_tokens, hidden, num_topk;
+    uint64_t* prof;                // optional [8] phase timestamps (ns) written by CTA 0, or null
 };
 
 struct LayoutArgs {
@@ -145,7 +148,7 @@ struct LaunchShape {
 // which is how the multi-rank protocol is exercised on a single GPU.
 cudaError_t launch_dispatch(const DispatchArgs* args, int n, int num_sms, cudaStream_t stream);
 cudaError_t launch_combine(const CombineArgs* args, int n, int num_sms, cudaStream_t stream);
-cudaError_t launch_barrier(const RankCtx* ctxs, int n, cudaStream_t stream);
+cudaError_t launch_barrier(const RankCtx* ctxs, int n, int channel, cudaStream_t stream);
 cudaError_t launch_wait_flag_test(const RankCtx* ctxs, int n, uint64_t expected, cudaStream_t stream);
 cudaError_t launch_layout(const LayoutArgs& args, cudaStream_t stream);
 cudaError_t launch_quant(const QuantArgs& args, cudaStream_t stream);
@@ -199,4 +202,29 @@ struct LLCombineArgs {
 namespace ep {
 cudaError_t launch_ll_dispatch(const LLDispatchArgs* args, int n, int num_sms, cudaStream_t stream);
 cudaError_t launch_ll_combine(const LLCombineArgs* args, int n, int num_sms, cudaStream_t stream);
+}  // namespace ep
+
+// ------------------------------------------------------------------------------------------------ Engram fetch
+struct EngramFetchArgs {
+    RankCtx ctx;
+    const int32_t* indices;      // [num_fetches] global entry ids; owner rank = id / entries_per_rank
+    int num_fetches;
+    int entries_per_rank;
+    int entry_bytes;             // multiple of 16
+    uint64_t off_storage;        // storage region inside every rank's symmetric buffer
+    void* out;                   // [num_fetches, entry_bytes]
+};
+
+// ------------------------------------------------------------------------------------------------ local reduce
+struct ReduceSlotsArgs {
+    const void* slots;           // [num_slots, n] bf16 / fp32
+    void* out;                   // [n]
+    int64_t n;
+    int num_slots;
+    int is_bf16;
+};
+
+namespace ep {
+cudaError_t launch_engram_fetch(const EngramFetchArgs* args, int n, int num_sms, cudaStream_t stream);
+cudaError_t launch_reduce_slots(const ReduceSlotsArgs& args, cudaStream_t stream);
 }  // namespace ep

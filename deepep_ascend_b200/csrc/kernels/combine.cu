@@ -79,10 +79,15 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
     __syncthreads();
     ptx::fence_proxy_async_smem();
 
+    auto stamp = [&](int i) {
+        if (a.prof != nullptr && blockIdx.x == 0 && tid == 0) a.prof[i] = globaltimer_ns();
+    };
+    stamp(0);
     // every rank's input rows must be in place before anyone pulls
     bool alive = !is_aborted(ws);
     if (blockIdx.x == 0) alive = xgpu_barrier(ctx, ws, EP_CH_COMBINE, EP_PH_COMBINE_ENTRY) && alive;
     alive = grid_sync(ctx, ws, EP_CH_COMBINE, EP_PH_GRID_SYNC) && alive;
+    stamp(1);
 
     // a warp owns tokens first, first + stride, ... and walks the column chunks of each token in order, so the
     // plan row of a token is read once
@@ -234,11 +239,14 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
         }
     }
 
+    stamp(2);
     // nobody may overwrite its input rows until every rank has finished pulling
     const bool cta_ok = __syncthreads_and(alive ? 1 : 0) != 0;
     alive = grid_sync(ctx, ws, EP_CH_COMBINE, EP_PH_GRID_SYNC) && cta_ok;
+    stamp(3);
     if (blockIdx.x == 0) {
         if (alive) xgpu_barrier(ctx, ws, EP_CH_COMBINE, EP_PH_COMBINE_EXIT);
+        stamp(4);
         if (tid == 0) ws->epoch[EP_CH_COMBINE] += 1;
     }
 }

@@ -256,6 +256,10 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
 
     const Slice sl = warp_slice(T, K, num_warps, warp);
     bool alive = !is_aborted(ws);
+    auto stamp = [&](int i) {
+        if (a.prof != nullptr && cta == 0 && tid == 0) a.prof[i] = globaltimer_ns();
+    };
+    stamp(0);
 
     if (!a.cached) {
         // ---------------------------------------------------------------- 1. layout (counts)
@@ -272,6 +276,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
             }
         }
         alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && alive;
+        stamp(1);
 
         // ---------------------------------------------------------------- 2. exchange
         if (alive && cta == 0) {
@@ -308,6 +313,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
             }
         }
         alive = __syncthreads_and(ok) != 0;
+        stamp(2);
 
         // ---------------------------------------------------------------- 3. assign: counts -> first rows
         if (alive) {
@@ -397,6 +403,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
         alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && alive;
     }
 
+    stamp(3);
     // -------------------------------------------------------------------- 4. scatter
     if (alive) {
         const int in_row = a.hidden * (a.x_is_fp8 ? 1 : 2);
@@ -476,6 +483,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
             ptx::bulk_commit();
             // small per-row pieces go out as plain peer stores
             uint32_t sends = __ballot_sync(0xffffffffu, plan_k >= 0);
+            if (a.skip_side_stores) sends = 0;
             while (sends) {
                 const int k = __ffs(sends) - 1;
                 sends &= sends - 1;
@@ -513,10 +521,13 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
     ptx::bulk_commit();
     ptx::bulk_wait<0>();
     __threadfence_system();
+    stamp(4);
     const bool cta_ok = __syncthreads_and(alive ? 1 : 0) != 0;
     alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && cta_ok;
+    stamp(5);
     if (cta == 0) {
         if (alive) alive = xgpu_barrier(ctx, ws, EP_CH_DISPATCH, EP_PH_DISPATCH_DONE);
+        stamp(6);
         if (tid == 0) ws->epoch[EP_CH_DISPATCH] = epoch;
     }
 }

@@ -8,14 +8,14 @@ namespace ep {
 
 namespace {
 
-__device__ __forceinline__ void barrier_body(const RankCtx& ctx) {
+__device__ __forceinline__ void barrier_body(const RankCtx& ctx, int channel) {
     Workspace* ws = local_ws(ctx);
     if (is_aborted(ws)) return;
-    xgpu_barrier(ctx, ws, EP_CH_BARRIER, EP_PH_XGPU_BARRIER);
-    if (threadIdx.x == 0) ws->epoch[EP_CH_BARRIER] += 1;
+    xgpu_barrier(ctx, ws, channel, EP_PH_XGPU_BARRIER);
+    if (threadIdx.x == 0) ws->epoch[channel] += 1;
 }
-__global__ void barrier_kernel(const __grid_constant__ RankCtx ctx) { barrier_body(ctx); }
-__global__ void barrier_kernel_multi(const RankCtx* ctxs) { barrier_body(ctxs[blockIdx.y]); }
+__global__ void barrier_kernel(const __grid_constant__ RankCtx ctx, uint64_t channel) { barrier_body(ctx, static_cast<int>(channel)); }
+__global__ void barrier_kernel_multi(const RankCtx* ctxs, uint64_t channel) { barrier_body(ctxs[blockIdx.y], static_cast<int>(channel)); }
 
 // Waits (bounded) until tile_flags[0] of the local workspace reaches `expected`.  Nothing in the library sets
 // that word, so with a short limit this exercises the timeout -> status -> abort path without any fault.
@@ -127,6 +127,66 @@ __global__ void quant_kernel(const QuantArgs a) {
     }
 }
 
+// Engram fetch: one warp per requested entry; the entry is pulled from its owner's storage (TMA bulk load through
+// the peer mapping, no multicast) into shared memory and bulk-stored into the local output row.
+__device__ __forceinline__ void engram_fetch_body(const EngramFetchArgs& a) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const RankCtx& ctx = a.ctx;
+    Workspace* ws = local_ws(ctx);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, num_warps = blockDim.x >> 5;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * 2;
+    const int stage_bytes = (a.entry_bytes + 127) / 128 * 128;
+    uint8_t* stage = smem + 1024 + static_cast<size_t>(warp) * 2 * stage_bytes;
+    if (lane == 0) {
+        ptx::mbar_init(&bars[0], 1);
+        ptx::mbar_init(&bars[1], 1);
+    }
+    ptx::mbar_fence_init();
+    __syncthreads();
+    ptx::fence_proxy_async_smem();
+    bool alive = !is_aborted(ws);
+    uint32_t n = 0;
+    for (int i = blockIdx.x * num_warps + warp; i < a.num_fetches && alive; i += gridDim.x * num_warps, ++n) {
+        const int id = a.indices[i];
+        const int owner = id / a.entries_per_rank, local = id - owner * a.entries_per_rank;
+        const int st = n & 1;
+        ptx::bulk_wait_read<1>();   // the stage was the source of the store issued two entries ago
+        __syncwarp();
+        if (owner < 0 || owner >= ctx.num_ranks) {
+            if (lane == 0) report_failure(ctx, ws, EP_ERR_BOUNDS, EP_PH_TILE_FLAG, owner, ctx.num_ranks, id);
+            alive = false;
+            break;
+        }
+        if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(&bars[st], a.entry_bytes);
+            ptx::bulk_load(stage + st * stage_bytes,
+                           ctx.peer_base[owner] + a.off_storage + static_cast<int64_t>(local) * a.entry_bytes, a.entry_bytes, &bars[st]);
+        }
+        alive = mbar_wait_bounded(ctx, ws, &bars[st], (n >> 1) & 1, EP_PH_COMBINE_LOAD);
+        if (!alive) break;
+        if (lane == 0)
+            ptx::bulk_store(reinterpret_cast<uint8_t*>(a.out) + static_cast<int64_t>(i) * a.entry_bytes, stage + st * stage_bytes, a.entry_bytes);
+        ptx::bulk_commit();
+    }
+    ptx::bulk_commit();
+    ptx::bulk_wait<0>();
+}
+__global__ void engram_fetch_kernel(const __grid_constant__ EngramFetchArgs a) { engram_fetch_body(a); }
+__global__ void engram_fetch_kernel_multi(const EngramFetchArgs* a) { engram_fetch_body(a[blockIdx.y]); }
+
+// out[i] = sum over slots of slots[s][i], accumulated in fp32 in slot order
+__global__ void reduce_slots_kernel(const ReduceSlotsArgs a) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < a.n; i += stride) {
+        float acc = 0.f;
+        for (int s = 0; s < a.num_slots; ++s)
+            acc += a.is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.slots)[s * a.n + i])
+                             : reinterpret_cast<const float*>(a.slots)[s * a.n + i];
+        if (a.is_bf16) reinterpret_cast<__nv_bfloat16*>(a.out)[i] = __float2bfloat16_rn(acc);
+        else reinterpret_cast<float*>(a.out)[i] = acc;
+    }
+}
+
 template <typename T>
 cudaError_t launch_small(const void* single, const void* multi, const T* items, int n, dim3 block, cudaStream_t stream,
                          uint64_t extra, bool has_extra) {
@@ -150,14 +210,49 @@ cudaError_t launch_small(const void* single, const void* multi, const T* items, 
 
 }  // namespace
 
-cudaError_t launch_barrier(const RankCtx* ctxs, int n, cudaStream_t stream) {
+cudaError_t launch_barrier(const RankCtx* ctxs, int n, int channel, cudaStream_t stream) {
+    if (channel < 0 || channel >= EP_NUM_CHANNELS) return cudaErrorInvalidValue;
     return launch_small<RankCtx>((const void*)barrier_kernel, (const void*)barrier_kernel_multi, ctxs, n, dim3(32, 1, 1),
-                                 stream, 0, false);
+                                 stream, static_cast<uint64_t>(channel), true);
 }
 
 cudaError_t launch_wait_flag_test(const RankCtx* ctxs, int n, uint64_t expected, cudaStream_t stream) {
     return launch_small<RankCtx>((const void*)wait_flag_kernel, (const void*)wait_flag_kernel_multi, ctxs, n,
                                  dim3(32, 1, 1), stream, expected, true);
+}
+
+cudaError_t launch_engram_fetch(const EngramFetchArgs* args, int n, int num_sms, cudaStream_t stream) {
+    const int warps = 4;
+    const int stage_bytes = (args[0].entry_bytes + 127) / 128 * 128;
+    const int smem = 1024 + warps * 2 * stage_bytes;
+    if (smem > 200 * 1024 || args[0].entry_bytes % 16 != 0) return cudaErrorInvalidValue;
+    const void* fn = n == 1 ? (const void*)engram_fetch_kernel : (const void*)engram_fetch_kernel_multi;
+    cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return err;
+    dim3 grid(num_sms < 1 ? 1 : num_sms, n, 1), block(warps * 32, 1, 1);
+    if (n == 1) {
+        void* params[] = {const_cast<EngramFetchArgs*>(args)};
+        return cudaLaunchKernel(fn, grid, block, params, smem, stream);
+    }
+    EngramFetchArgs* dev = nullptr;
+    err = cudaMallocAsync(reinterpret_cast<void**>(&dev), sizeof(EngramFetchArgs) * n, stream);
+    if (err != cudaSuccess) return err;
+    err = cudaMemcpyAsync(dev, args, sizeof(EngramFetchArgs) * n, cudaMemcpyHostToDevice, stream);
+    if (err == cudaSuccess) {
+        void* params[] = {&dev};
+        err = cudaLaunchKernel(fn, grid, block, params, smem, stream);
+    }
+    cudaFreeAsync(dev, stream);
+    return err;
+}
+
+cudaError_t launch_reduce_slots(const ReduceSlotsArgs& a, cudaStream_t stream) {
+    if (a.n == 0) return cudaSuccess;
+    const int threads = 256;
+    const int64_t want = (a.n + threads - 1) / threads;
+    const int blocks = static_cast<int>(want < 148 * 8 ? want : 148 * 8);
+    reduce_slots_kernel<<<blocks, threads, 0, stream>>>(a);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_layout(const LayoutArgs& a, cudaStream_t stream) {

@@ -142,7 +142,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("off_recv_meta", &DispatchCall::off_recv_meta)
         .def_readwrite("sf_stride_row", &DispatchCall::sf_stride_row)
         .def_readwrite("sf_stride_col", &DispatchCall::sf_stride_col)
-        .def_readwrite("recv_capacity_rows", &DispatchCall::recv_capacity_rows);
+        .def_readwrite("recv_capacity_rows", &DispatchCall::recv_capacity_rows)
+        .def_readwrite("prof", &DispatchCall::prof)
+        .def_readwrite("skip_side_stores", &DispatchCall::skip_side_stores);
     py::class_<CombineCall>(m, "CombineCall")
         .def(py::init<>())
         .def_readwrite("off_x", &CombineCall::off_x)
@@ -155,7 +157,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("bias1", &CombineCall::bias1)
         .def_readwrite("out", &CombineCall::out)
         .def_readwrite("out_w", &CombineCall::out_w)
-        .def_readwrite("hidden", &CombineCall::hidden);
+        .def_readwrite("hidden", &CombineCall::hidden)
+        .def_readwrite("prof", &CombineCall::prof);
 
     py::class_<ElasticBufferCore>(m, "ElasticBuffer")
         .def(py::init<int, int, int64_t, double, double>(), py::arg("rank"), py::arg("num_ranks"), py::arg("num_bytes"),
@@ -180,11 +183,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("wait_recv_counts", &ElasticBufferCore::wait_recv_counts)
         .def("dispatch", &ElasticBufferCore::dispatch)
         .def("combine", &ElasticBufferCore::combine)
-        .def("barrier", &ElasticBufferCore::barrier)
+        .def("barrier", &ElasticBufferCore::barrier, py::arg("channel") = static_cast<int>(EP_CH_BARRIER))
+        .def("peer_copy", &ElasticBufferCore::peer_copy)
+        .def_static("engram_fetch_group", &ElasticBufferCore::engram_fetch_group)
         .def("wait_flag_test", &ElasticBufferCore::wait_flag_test)
         .def_static("dispatch_group", &ElasticBufferCore::dispatch_group)
         .def_static("combine_group", &ElasticBufferCore::combine_group)
-        .def_static("barrier_group", &ElasticBufferCore::barrier_group)
+        .def_static("barrier_group", &ElasticBufferCore::barrier_group, py::arg("group"), py::arg("channel") = static_cast<int>(EP_CH_BARRIER))
         .def_static("wait_flag_test_group", &ElasticBufferCore::wait_flag_test_group);
 
     py::class_<LLDispatchCall>(m, "LLDispatchCall")
@@ -230,6 +235,23 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("ll_message_bytes", &ll_message_bytes);
     m.def("get_low_latency_rdma_size_hint", &ll_size_hint, py::arg("num_max_dispatch_tokens_per_rank"), py::arg("hidden"),
           py::arg("num_ranks"), py::arg("num_experts"), py::arg("num_topk") = 8);
+    m.def("reduce_slots", [](const at::Tensor& slots, at::Tensor out) {
+        TORCH_CHECK(slots.is_cuda() && slots.is_contiguous() && out.is_contiguous() && slots.dim() >= 1 &&
+                        slots.scalar_type() == out.scalar_type() && slots.numel() == slots.size(0) * out.numel(),
+                    "slots must be [num_slots, ...] matching out");
+        TORCH_CHECK(slots.scalar_type() == at::kBFloat16 || slots.scalar_type() == at::kFloat, "bf16 or fp32 only");
+        ReduceSlotsArgs a{};
+        a.slots = slots.data_ptr();
+        a.out = out.data_ptr();
+        a.n = out.numel();
+        a.num_slots = static_cast<int>(slots.size(0));
+        a.is_bf16 = slots.scalar_type() == at::kBFloat16;
+        cuda_check(ep::launch_reduce_slots(a, at::cuda::getCurrentCUDAStream()), "reduce launch");
+    });
+    m.attr("CH_BARRIER") = static_cast<int>(EP_CH_BARRIER);
+    m.attr("CH_AGRS") = static_cast<int>(EP_CH_AGRS);
+    m.attr("CH_PP") = static_cast<int>(EP_CH_PP);
+    m.attr("CH_ENGRAM") = static_cast<int>(EP_CH_ENGRAM);
     m.def("install_segv_backtrace", [] { signal(SIGSEGV, segv_backtrace_handler); });
     m.def("get_dispatch_layout", &get_dispatch_layout);
     m.def("per_token_cast_to_fp8", &per_token_cast_to_fp8, py::arg("x"), py::arg("round_scale") = false,

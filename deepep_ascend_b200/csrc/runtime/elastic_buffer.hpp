@@ -43,6 +43,8 @@ struct DispatchCall {
     int64_t off_recv_x = 0, off_recv_sf = 0, off_recv_idx = 0, off_recv_w = 0, off_recv_meta = 0;
     int64_t sf_stride_row = 0, sf_stride_col = 1;
     int64_t recv_capacity_rows = 0;
+    OptTensor prof;               // int64 [8]: phase timestamps of CTA 0 (profiling)
+    bool skip_side_stores = false;
 };
 
 struct CombineCall {
@@ -54,6 +56,7 @@ struct CombineCall {
     at::Tensor out;                // [T, H] bf16
     OptTensor out_w;               // [T, K] fp32
     int64_t hidden = 0;
+    OptTensor prof;                // int64 [8]: phase timestamps of CTA 0 (profiling)
 };
 
 class ElasticBufferCore {
@@ -155,7 +158,7 @@ public:
     // ------------------------------------------------------------------ operations
     void dispatch(const DispatchCall& call, int num_sms) { dispatch_group({this}, {call}, num_sms); }
     void combine(const CombineCall& call, int num_sms) { combine_group({this}, {call}, num_sms); }
-    void barrier() { barrier_group({this}); }
+    void barrier(int channel) { barrier_group({this}, channel); }
     void wait_flag_test(int64_t expected) { wait_flag_test_group({this}, expected); }
 
     static void dispatch_group(const std::vector<ElasticBufferCore*>& group, const std::vector<DispatchCall>& calls,
@@ -197,7 +200,7 @@ public:
         for (auto& s : scopes) s->commit();
     }
 
-    static void barrier_group(const std::vector<ElasticBufferCore*>& group) {
+    static void barrier_group(const std::vector<ElasticBufferCore*>& group, int channel) {
         std::vector<std::unique_ptr<OperationScope>> scopes;
         std::vector<RankCtx> ctxs;
         for (auto* g : group) {
@@ -205,7 +208,7 @@ public:
             g->check_status();
             ctxs.push_back(g->ctx());
         }
-        cuda_check(ep::launch_barrier(ctxs.data(), static_cast<int>(ctxs.size()), at::cuda::getCurrentCUDAStream()),
+        cuda_check(ep::launch_barrier(ctxs.data(), static_cast<int>(ctxs.size()), channel, at::cuda::getCurrentCUDAStream()),
                    "barrier launch");
         for (auto& s : scopes) s->commit();
     }
@@ -218,6 +221,45 @@ public:
         cuda_check(ep::launch_wait_flag_test(ctxs.data(), static_cast<int>(ctxs.size()), static_cast<uint64_t>(expected),
                                              at::cuda::getCurrentCUDAStream()),
                    "wait-flag launch");
+    }
+
+    // Copy-engine push of a contiguous tensor into `dst_rank`'s symmetric buffer at `dst_offset` (stream ordered).
+    void peer_copy(int dst_rank, int64_t dst_offset, const at::Tensor& src) {
+        TORCH_CHECK(src.is_cuda() && src.is_contiguous(), "src must be a contiguous CUDA tensor");
+        const int64_t bytes = src.numel() * src.element_size();
+        TORCH_CHECK(dst_rank >= 0 && dst_rank < num_ranks(), "bad destination rank");
+        check_region(dst_offset, bytes, "peer copy");
+        const RankCtx c = ctx();
+        if (bytes == 0) return;
+        cuda_check(cudaMemcpyAsync(c.peer_base[dst_rank] + dst_offset, src.data_ptr(), static_cast<size_t>(bytes),
+                                   cudaMemcpyDeviceToDevice, at::cuda::getCurrentCUDAStream()),
+                   "peer cudaMemcpyAsync");
+    }
+
+    // Engram: pull `indices.numel()` entries of `entry_bytes` from their owners' storage regions into `out`.
+    static void engram_fetch_group(const std::vector<ElasticBufferCore*>& group, const std::vector<at::Tensor>& indices,
+                                   const std::vector<at::Tensor>& outs, int64_t entries_per_rank, int64_t entry_bytes,
+                                   int64_t off_storage, int num_sms) {
+        std::vector<EngramFetchArgs> args(group.size());
+        for (size_t i = 0; i < group.size(); ++i) {
+            group[i]->check_status();
+            const at::Tensor& idx = indices[i];
+            TORCH_CHECK(idx.is_cuda() && idx.is_contiguous() && idx.scalar_type() == at::kInt, "indices must be contiguous int32");
+            TORCH_CHECK(outs[i].is_contiguous() && outs[i].numel() * outs[i].element_size() == idx.numel() * entry_bytes,
+                        "output has the wrong size");
+            group[i]->check_region(off_storage, entries_per_rank * entry_bytes, "engram storage");
+            EngramFetchArgs a{};
+            a.ctx = group[i]->ctx();
+            a.indices = idx.data_ptr<int32_t>();
+            a.num_fetches = static_cast<int>(idx.numel());
+            a.entries_per_rank = static_cast<int>(entries_per_rank);
+            a.entry_bytes = static_cast<int>(entry_bytes);
+            a.off_storage = off_storage;
+            a.out = outs[i].data_ptr();
+            args[i] = a;
+        }
+        cuda_check(ep::launch_engram_fetch(args.data(), static_cast<int>(args.size()), num_sms, at::cuda::getCurrentCUDAStream()),
+                   "engram fetch launch");
     }
 
     RankCtx ctx() const { return mem_->ctx(gpu_timeout_ns_); }
@@ -314,6 +356,11 @@ private:
         a.sf_stride_row = c.sf_stride_row;
         a.sf_stride_col = c.sf_stride_col;
         a.recv_capacity_rows = static_cast<int>(cap);
+        if (c.prof.has_value()) {
+            TORCH_CHECK(c.prof->scalar_type() == at::kLong && c.prof->numel() >= 8 && c.prof->is_cuda(), "prof must be int64 [8] on the GPU");
+            a.prof = reinterpret_cast<uint64_t*>(c.prof->data_ptr<int64_t>());
+        }
+        a.skip_side_stores = c.skip_side_stores;
         return a;
     }
 
@@ -354,6 +401,10 @@ private:
         a.num_tokens = static_cast<int>(T);
         a.hidden = static_cast<int>(H);
         a.num_topk = static_cast<int>(K);
+        if (c.prof.has_value()) {
+            TORCH_CHECK(c.prof->scalar_type() == at::kLong && c.prof->numel() >= 8 && c.prof->is_cuda(), "prof must be int64 [8] on the GPU");
+            a.prof = reinterpret_cast<uint64_t*>(c.prof->data_ptr<int64_t>());
+        }
         return a;
     }
 

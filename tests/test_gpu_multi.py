@@ -67,3 +67,98 @@ def test_multi_process_dispatch_combine(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f'needs {world} GPUs')
     mp.spawn(_worker, args=(world, _free_port()), nprocs=world, join=True)
+
+
+def _worker_misc(rank: int, world: int, port: int):
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    try:
+        import deepep_ascend_b200 as ep
+        from deepep_ascend_b200.utils.math import per_token_cast_back
+        group = dist.new_group(list(range(world)))
+        M, H, E, K = 64, 2048, 8 * world, 4
+        extra = ep.ElasticBuffer.get_low_latency_size_hint(M, H, world, E, K) + (96 << 20)
+        buf = ep.ElasticBuffer(group, num_max_tokens_per_rank=256, hidden=H, num_topk=K, extra_bytes=extra,
+                               num_gpu_timeout_secs=10, num_cpu_timeout_secs=30)
+        # ---- all-gather / reduce-scatter session
+        buf.agrs_set_config(64 << 20)
+        buf.create_agrs_session()
+        x = torch.full((300, 40), float(rank + 1), device='cuda', dtype=torch.bfloat16)
+        inplace = buf.agrs_get_inplace_tensor((16, 8), torch.float32)
+        inplace.fill_(rank + 0.5)
+        (g1, g2), wait = buf.all_gather([x, inplace])
+        wait()
+        for r in range(world):
+            assert bool((g1[r] == r + 1).all()) and bool((g2[r] == r + 0.5).all())
+        rs_in = torch.randn(world, 1000, device='cuda', generator=torch.Generator('cuda').manual_seed(rank)).bfloat16()
+        out, wait = buf.reduce_scatter(rs_in)
+        wait()
+        gathered = [torch.empty_like(rs_in) for _ in range(world)]
+        dist.all_gather(gathered, rs_in, group=group)
+        acc = torch.zeros(1000, device='cuda')
+        for s in range(world):
+            acc += gathered[s][rank].float()
+        assert torch.equal(out, acc.bfloat16())
+        buf.destroy_agrs_session()
+        # ---- pipeline send / recv around the ring
+        buf.pp_set_config(1 << 20, 4)
+        nxt, prv = (rank + 1) % world, (rank - 1) % world
+        send = torch.full((1024,), float(rank), device='cuda')
+        recv = torch.empty_like(send)
+        if rank % 2 == 0:
+            buf.pp_send(send, nxt)
+            buf.pp_recv(recv, prv)
+        else:
+            buf.pp_recv(recv, prv)
+            buf.pp_send(send, nxt)
+        torch.cuda.synchronize()
+        assert bool((recv == prv).all())
+        # ---- Engram
+        table = torch.full((100, 256), float(rank), device='cuda', dtype=torch.bfloat16) + torch.arange(100, device='cuda').unsqueeze(1).bfloat16()
+        buf.engram_write(table)
+        idx = torch.randint(0, 100 * world, (50, 2), device='cuda', dtype=torch.int32)
+        fetched, _ = buf.engram_fetch(idx)()
+        want = (idx // 100).float().unsqueeze(-1) + (idx % 100).float().unsqueeze(-1)
+        assert torch.equal(fetched.view(50, 2, 256).float(), want.expand(50, 2, 256).bfloat16().float())
+        # ---- low latency (also in hook mode) and its use through the legacy API names
+        torch.manual_seed(rank)
+        xt = torch.randn(M - rank, H, device='cuda').bfloat16()
+        w, idx2 = torch.softmax(torch.randn(M - rank, E, device='cuda'), -1).topk(K, -1)
+        for hook_mode in (False, True):
+            (rx, rsf), count, handle, _, hook = buf.low_latency_dispatch(xt, idx2, M, E, return_recv_hook=hook_mode)
+            if hook_mode:
+                hook()
+            y = torch.zeros(rx.shape, dtype=torch.bfloat16, device='cuda')
+            for j in range(E // world):
+                n = int(count[j])
+                y[j, :n] = per_token_cast_back(rx[j, :n], rsf[j, :n])
+            out, _, hook = buf.low_latency_combine(y, idx2, w, handle, return_recv_hook=hook_mode)
+            if hook_mode:
+                hook()
+            torch.cuda.synchronize()
+            want = xt.float() * w.sum(-1, keepdim=True)
+            assert float((out.float() - want).abs().max()) < 0.3
+        buf.check_status()
+        buf.destroy()
+        # ---- first-generation API
+        legacy = ep.Buffer(group, num_nvl_bytes=0)
+        xt = torch.randn(128, 1024, device='cuda').bfloat16()
+        w, idx3 = torch.softmax(torch.randn(128, E, device='cuda'), -1).topk(K, -1)
+        per_rank, _, per_expert, in_rank, _ = legacy.get_dispatch_layout(idx3, E)
+        rx, ridx, rw, per_expert_list, h, _ = legacy.dispatch(xt, topk_idx=idx3, topk_weights=w, num_tokens_per_rank=per_rank,
+                                                              is_token_in_rank=in_rank, num_tokens_per_expert=per_expert)
+        assert sum(per_expert_list) == int((ridx >= 0).sum())
+        cx, cw, _ = legacy.combine(rx, h, topk_weights=rw)
+        hits = in_rank.sum(dim=1, keepdim=True).float()
+        assert float((cx.float() - xt.float() * hits).abs().max()) < 0.13 and torch.equal(cw, w)
+        legacy.destroy()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('world', [2, 8])
+def test_multi_process_collectives_ll_legacy(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f'needs {world} GPUs')
+    mp.spawn(_worker_misc, args=(world, _free_port()), nprocs=world, join=True)
