@@ -228,7 +228,8 @@ public:
         TORCH_CHECK(src.is_cuda() && src.is_contiguous(), "src must be a contiguous CUDA tensor");
         const int64_t bytes = src.numel() * src.element_size();
         TORCH_CHECK(dst_rank >= 0 && dst_rank < num_ranks(), "bad destination rank");
-        check_region(dst_offset, bytes, "peer copy");
+        TORCH_CHECK(dst_offset >= static_cast<int64_t>(EP_WORKSPACE_BYTES) && dst_offset + bytes <= mem_->bytes(),
+                    "peer copy [", dst_offset, ", ", dst_offset + bytes, ") is outside the symmetric buffer");
         const RankCtx c = ctx();
         if (bytes == 0) return;
         cuda_check(cudaMemcpyAsync(c.peer_base[dst_rank] + dst_offset, src.data_ptr(), static_cast<size_t>(bytes),
