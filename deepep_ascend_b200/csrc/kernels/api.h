@@ -228,3 +228,30 @@ namespace ep {
 cudaError_t launch_engram_fetch(const EngramFetchArgs* args, int n, int num_sms, cudaStream_t stream);
 cudaError_t launch_reduce_slots(const ReduceSlotsArgs& args, cudaStream_t stream);
 }  // namespace ep
+
+// ------------------------------------------------------------------------------------------------ tcgen05 GEMM
+// C[M, N] (bf16) = A[M, K] * B[g][N, K]^T, both operands K-major.  bf16 inputs, or e4m3 inputs with fp32 block
+// scales (A: one per row and 128 channels; B: one per 128 x 128 block).  With `tile_group` the M dimension is
+// a concatenation of 128-row tiles, each using the weights of one group (expert); -1 skips a tile.
+struct GemmArgs {
+    const void* a;
+    const void* b;
+    void* c;
+    int M, N, K;
+    int num_groups;
+    int is_fp8;
+    int64_t lda, ldb, ldc;            // row strides in elements
+    const float* sfa;                 // fp8: scale of (row, k block) at sfa[row * sfa_stride_row + kb * sfa_stride_kb]
+    int64_t sfa_stride_row, sfa_stride_kb;
+    const float* sfb;                 // fp8: [num_groups, ceil(N/128), ceil(K/128)] contiguous
+    const int32_t* tile_group;        // [ceil(M/128)] or null (single group 0)
+    int* error;                       // device int set to non-zero if a pipeline wait ran out
+    // fused collectives (null / 0 when unused)
+    const uint64_t* a_ready_flags;    // all-gather fused into the loads: rows of M tile t may be read once
+    uint64_t a_ready_value;           //   a_ready_flags[a_flag_of_tile[t]] >= a_ready_value
+    const int32_t* a_flag_of_tile;
+};
+
+namespace ep {
+cudaError_t launch_gemm(const GemmArgs& args, int num_sms, cudaStream_t stream);
+}  // namespace ep

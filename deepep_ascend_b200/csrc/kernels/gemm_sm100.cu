@@ -1,0 +1,331 @@
+// Persistent tcgen05 GEMM for sm_100a: C[M, N] (bf16) = A[M, K] * B[g][N, K]^T.
+//
+//   warp 0   : TMA producer - 2-D tiled loads of 128 x 128-byte A and B tiles (128B swizzle) into a ring of
+//              shared-memory stages, completion counted on mbarriers; optionally waits for an "A rows are ready"
+//              flag per M tile (all-gather fused into the loads)
+//   warp 1   : MMA issuer   - one elected thread issues tcgen05.mma (kind::f16 for bf16, kind::f8f6f4 for e4m3)
+//              with fp32 accumulators in tensor memory; tcgen05.commit releases stages and publishes accumulators
+//   warps 2-5: epilogue     - tcgen05.ld the accumulator (each warp its 32 TMEM lanes), scale / convert, store bf16
+//
+// bf16 operands: one accumulator per output tile, two TMEM buffers so the epilogue of tile i overlaps the MMAs of
+// tile i+1.  e4m3 operands with fp32 block scales (A: per row x 128 channels, B: per 128 x 128 block): every
+// 128-channel block is accumulated into its own TMEM buffer and promoted into fp32 registers with its scale by
+// the epilogue warps (two buffers, so promotion of block j overlaps the MMAs of block j+1).
+// Grouped (MoE) use: `tile_group[m_tile]` selects the expert whose weights multiply that 128-row tile.
+// Every pipeline wait is bounded; on expiry the kernel raises `*error`, leaves its loops and frees its TMEM.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "api.h"
+#include "gemm_sm100.cuh"
+
+namespace ep {
+
+namespace {
+
+constexpr int kBlockM = 128, kBlockN = 128, kTileBytes = 128 * 128;   // one operand tile: 128 rows x 128 bytes
+constexpr int kStages = 6;
+constexpr int kGemmThreads = 192;
+constexpr int kTmemColumns = 256;   // two accumulator buffers of kBlockN fp32 columns
+constexpr uint64_t kWaitLimitNs = 4ull * 1000 * 1000 * 1000;
+
+struct GemmSmem {
+    uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
+    uint32_t tmem_base;
+    int failed;
+};
+constexpr int kGemmSmemBytes = 2 * kStages * kTileBytes + 1024;
+
+__device__ __forceinline__ uint64_t gemm_timer() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// bounded mbarrier wait; returns false (and raises the failure flags) when the limit runs out
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, GemmSmem* sm, int* error, int code) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = gemm_timer();
+    uint32_t spins = 0;
+    while (!ptx::mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0u) {
+            if (*reinterpret_cast<volatile int*>(&sm->failed)) return false;
+            if (gemm_timer() - t0 > kWaitLimitNs) {
+                sm->failed = code;
+                if (error != nullptr) atomicCAS(error, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+struct PipeState {
+    int stage = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance() {
+        if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+        }
+    }
+};
+
+template <bool kFp8>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* s_a = smem;
+    uint8_t* s_b = smem + kStages * kTileBytes;
+    GemmSmem* sm = reinterpret_cast<GemmSmem*>(smem + 2 * kStages * kTileBytes);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kBlockK = kFp8 ? 128 : 64;          // elements per 128-byte row
+    constexpr int kUmmaK = kFp8 ? 32 : 16;            // elements per tcgen05.mma (32 bytes of K)
+    constexpr uint32_t kIdesc = umma::make_instr_desc(kBlockM, kBlockN, kFp8 ? umma::kFormatE4M3 : umma::kFormatBF16);
+    const int num_m = (g.M + kBlockM - 1) / kBlockM, num_n = (g.N + kBlockN - 1) / kBlockN;
+    const int num_k = (g.K + kBlockK - 1) / kBlockK;
+    const int num_tiles = num_m * num_n;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStages; ++i) {
+            ptx::mbar_init(&sm->full[i], 1);
+            ptx::mbar_init(&sm->empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(&sm->tmem_full[i], 1);
+            ptx::mbar_init(&sm->tmem_empty[i], 4);
+        }
+        sm->failed = 0;
+        ptx::mbar_fence_init();
+        umma::prefetch_tensormap(&map_a);
+        umma::prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) {
+        umma::tmem_alloc(&sm->tmem_base, kTmemColumns);
+        umma::tmem_relinquish();
+    }
+    umma::fence_before_thread_sync();
+    __syncthreads();
+    umma::fence_after_thread_sync();
+    const uint32_t tmem_base = sm->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            PipeState p;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m_blk = tile / num_n, n_blk = tile % num_n;
+                const int grp = g.tile_group != nullptr ? g.tile_group[m_blk] : 0;
+                if (grp < 0) continue;
+                if (g.a_ready_flags != nullptr) {
+                    // rows of this M tile arrive from another rank: wait (bounded) for their flag
+                    const uint64_t* flag = g.a_ready_flags + (g.a_flag_of_tile != nullptr ? g.a_flag_of_tile[m_blk] : m_blk);
+                    const uint64_t t0 = gemm_timer();
+                    while (ptx::ld_acquire_sys(flag) < g.a_ready_value) {
+                        if (gemm_timer() - t0 > kWaitLimitNs || *reinterpret_cast<volatile int*>(&sm->failed)) {
+                            sm->failed = 3;
+                            if (g.error != nullptr) atomicCAS(g.error, 0, 3);
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok) break;
+                }
+                for (int kb = 0; kb < num_k && ok; ++kb) {
+                    ok = wait_bar(&sm->empty[p.stage], p.phase ^ 1, sm, g.error, 1);
+                    if (!ok) break;
+                    ptx::mbar_arrive_expect_tx(&sm->full[p.stage], 2 * kTileBytes);
+                    umma::tma_load_2d(s_a + p.stage * kTileBytes, &map_a, kb * kBlockK, m_blk * kBlockM, &sm->full[p.stage]);
+                    umma::tma_load_2d(s_b + p.stage * kTileBytes, &map_b, kb * kBlockK, grp * g.N + n_blk * kBlockN, &sm->full[p.stage]);
+                    p.advance();
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            PipeState p;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m_blk = tile / num_n;
+                const int grp = g.tile_group != nullptr ? g.tile_group[m_blk] : 0;
+                if (grp < 0) continue;
+                if (!kFp8) {
+                    ok = wait_bar(&sm->tmem_empty[acc], acc_phase ^ 1, sm, g.error, 2);
+                    if (!ok) break;
+                    umma::fence_after_thread_sync();
+                }
+                for (int kb = 0; kb < num_k && ok; ++kb) {
+                    if (kFp8) {
+                        ok = wait_bar(&sm->tmem_empty[acc], acc_phase ^ 1, sm, g.error, 2);
+                        if (!ok) break;
+                    }
+                    ok = wait_bar(&sm->full[p.stage], p.phase, sm, g.error, 4);
+                    if (!ok) break;
+                    umma::fence_after_thread_sync();
+                    const uint64_t desc_a = umma::make_smem_desc_sw128(s_a + p.stage * kTileBytes);
+                    const uint64_t desc_b = umma::make_smem_desc_sw128(s_b + p.stage * kTileBytes);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                        const uint32_t accumulate = kFp8 ? (k != 0) : ((kb | k) != 0);
+                        umma::mma_ss<kFp8>(tmem_base + acc * kBlockN, umma::advance_desc_k(desc_a, k * 32), umma::advance_desc_k(desc_b, k * 32),
+                                           kIdesc, accumulate);
+                    }
+                    umma::mma_commit(&sm->empty[p.stage]);       // the stage may be refilled once these MMAs are done
+                    p.advance();
+                    if (kFp8) {
+                        umma::mma_commit(&sm->tmem_full[acc]);   // one 128-channel block is ready for promotion
+                        if ((acc ^= 1) == 0) acc_phase ^= 1;
+                    }
+                }
+                if (!kFp8 && ok) {
+                    umma::mma_commit(&sm->tmem_full[acc]);
+                    if ((acc ^= 1) == 0) acc_phase ^= 1;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps, 32 TMEM lanes each)
+        const int quad = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        uint8_t* cb = reinterpret_cast<uint8_t*>(g.c);
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int m_blk = tile / num_n, n_blk = tile % num_n;
+            const int grp = g.tile_group != nullptr ? g.tile_group[m_blk] : 0;
+            if (grp < 0) continue;
+            const int row = m_blk * kBlockM + quad * 32 + lane;
+            const int n0 = n_blk * kBlockN;
+            const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+            if (!kFp8) {
+                ok = wait_bar(&sm->tmem_full[acc], acc_phase, sm, g.error, 5);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                umma::fence_after_thread_sync();
+#pragma unroll
+                for (int c = 0; c < kBlockN / 32; ++c) {
+                    uint32_t r[32];
+                    umma::tmem_ld_32x32(tmem_base + lane_addr + acc * kBlockN + c * 32, r);
+                    umma::tmem_ld_wait();
+                    if (row < g.M) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const int col = n0 + c * 32 + v * 8;
+                            if (col + 8 <= g.N) {
+                                int4 out;
+                                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    h[j] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+                                *reinterpret_cast<int4*>(cb + (static_cast<int64_t>(row) * g.ldc + col) * 2) = out;
+                            }
+                        }
+                    }
+                }
+                umma::fence_before_thread_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
+                if ((acc ^= 1) == 0) acc_phase ^= 1;
+            } else {
+                float sum[kBlockN];
+#pragma unroll
+                for (int i = 0; i < kBlockN; ++i) sum[i] = 0.f;
+                const int num_kb_sf = (g.K + 127) / 128, num_nb_sf = (g.N + 127) / 128;
+                const float* sfb = g.sfb + (static_cast<int64_t>(grp) * num_nb_sf + n_blk) * num_kb_sf;
+                for (int kb = 0; kb < num_k && ok; ++kb) {
+                    const float scale = (row < g.M ? __ldg(g.sfa + row * g.sfa_stride_row + kb * g.sfa_stride_kb) : 0.f) * __ldg(sfb + kb);
+                    ok = wait_bar(&sm->tmem_full[acc], acc_phase, sm, g.error, 5);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    umma::fence_after_thread_sync();
+#pragma unroll
+                    for (int c = 0; c < kBlockN / 32; ++c) {
+                        uint32_t r[32];
+                        umma::tmem_ld_32x32(tmem_base + lane_addr + acc * kBlockN + c * 32, r);
+                        umma::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) sum[c * 32 + i] = fmaf(scale, __uint_as_float(r[i]), sum[c * 32 + i]);
+                    }
+                    umma::fence_before_thread_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
+                    if ((acc ^= 1) == 0) acc_phase ^= 1;
+                }
+                if (ok && row < g.M) {
+#pragma unroll
+                    for (int v = 0; v < kBlockN / 8; ++v) {
+                        const int col = n0 + v * 8;
+                        if (col + 8 <= g.N) {
+                            int4 out;
+                            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(sum[v * 8 + 2 * j], sum[v * 8 + 2 * j + 1]);
+                            *reinterpret_cast<int4*>(cb + (static_cast<int64_t>(row) * g.ldc + col) * 2) = out;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    umma::fence_before_thread_sync();
+    __syncthreads();
+    if (warp == 1) umma::tmem_dealloc(tmem_base, kTmemColumns);
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// K-major [rows, K] operand, box = 128 rows x 128 bytes, 128B swizzle, out-of-range elements read as zero
+bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld_elems, bool fp8) {
+    EncodeTiledFn encode = get_encode_fn();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems * (fp8 ? 1 : 2))};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(fp8 ? 128 : 64), 128};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    return encode(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                  elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+cudaError_t launch_gemm(const GemmArgs& g, int num_sms, cudaStream_t stream) {
+    if (g.M <= 0 || g.N <= 0 || g.K <= 0) return cudaSuccess;
+    const int elem = g.is_fp8 ? 1 : 2;
+    if ((g.lda * elem) % 16 != 0 || (g.ldb * elem) % 16 != 0 || g.ldc % 8 != 0 || g.N % 8 != 0) return cudaErrorInvalidValue;
+    if (reinterpret_cast<uintptr_t>(g.a) % 16 != 0 || reinterpret_cast<uintptr_t>(g.b) % 16 != 0 || reinterpret_cast<uintptr_t>(g.c) % 16 != 0)
+        return cudaErrorInvalidValue;
+    CUtensorMap map_a, map_b;
+    if (!make_operand_map(&map_a, g.a, g.M, g.K, g.lda, g.is_fp8) ||
+        !make_operand_map(&map_b, g.b, static_cast<int64_t>(g.num_groups) * g.N, g.K, g.ldb, g.is_fp8))
+        return cudaErrorInvalidValue;
+    const void* fn = g.is_fp8 ? (const void*)gemm_kernel<true> : (const void*)gemm_kernel<false>;
+    cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    if (err != cudaSuccess) return err;
+    const int num_tiles = ((g.M + kBlockM - 1) / kBlockM) * ((g.N + kBlockN - 1) / kBlockN);
+    int ctas = num_sms < 1 ? 1 : num_sms;
+    if (ctas > num_tiles) ctas = num_tiles;
+    void* params[] = {&map_a, &map_b, const_cast<GemmArgs*>(&g)};
+    return cudaLaunchKernel(fn, dim3(ctas, 1, 1), dim3(kGemmThreads, 1, 1), params, kGemmSmemBytes, stream);
+}
+
+}  // namespace ep

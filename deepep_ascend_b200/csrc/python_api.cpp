@@ -62,6 +62,67 @@ std::vector<at::Tensor> per_token_cast_to_fp8(const at::Tensor& x, bool round_sc
     return {q, sf};
 }
 
+// Device int that the GEMM kernels raise when one of their bounded pipeline waits runs out (one per device).
+at::Tensor& gemm_error_flag(int device) {
+    static std::vector<at::Tensor> flags(64);
+    if (!flags[device].defined()) flags[device] = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+    return flags[device];
+}
+
+// C[M, N] (bf16) = A[M, K] @ B[g][N, K]^T on the tcgen05 tensor cores.  bf16 operands, or float8_e4m3fn operands
+// with fp32 block scales (sfa [M, ceil(K/128)] any strides, sfb [G, ceil(N/128), ceil(K/128)] contiguous).
+// `tile_group` int32 [ceil(M/128)]: weights group of every 128-row tile (-1 = skip the tile).
+at::Tensor gemm_nt(const at::Tensor& a, const at::Tensor& b, const std::optional<at::Tensor>& sfa, const std::optional<at::Tensor>& sfb,
+                   const std::optional<at::Tensor>& tile_group, const std::optional<at::Tensor>& out, int64_t num_sms,
+                   const std::optional<at::Tensor>& a_ready_flags, int64_t a_ready_value, const std::optional<at::Tensor>& a_flag_of_tile) {
+    TORCH_CHECK(a.is_cuda() && a.dim() == 2 && a.stride(1) == 1, "A must be [M, K] with contiguous rows");
+    TORCH_CHECK(b.is_cuda() && (b.dim() == 2 || b.dim() == 3) && b.is_contiguous(), "B must be contiguous [N, K] or [G, N, K]");
+    const bool fp8 = a.scalar_type() == at::kFloat8_e4m3fn;
+    TORCH_CHECK(fp8 || a.scalar_type() == at::kBFloat16, "A must be bf16 or float8_e4m3fn");
+    TORCH_CHECK(b.scalar_type() == a.scalar_type(), "A and B must have the same dtype");
+    const int64_t M = a.size(0), K = a.size(1), G = b.dim() == 3 ? b.size(0) : 1, N = b.size(-2);
+    TORCH_CHECK(b.size(-1) == K, "K mismatch");
+    at::Tensor c = out.has_value() ? *out : at::empty({M, N}, a.options().dtype(at::kBFloat16));
+    TORCH_CHECK(c.scalar_type() == at::kBFloat16 && c.dim() == 2 && c.size(0) == M && c.size(1) == N && c.stride(1) == 1, "bad output");
+    GemmArgs g{};
+    g.a = a.data_ptr();
+    g.b = b.data_ptr();
+    g.c = c.data_ptr();
+    g.M = static_cast<int>(M);
+    g.N = static_cast<int>(N);
+    g.K = static_cast<int>(K);
+    g.num_groups = static_cast<int>(G);
+    g.is_fp8 = fp8;
+    g.lda = a.stride(0);
+    g.ldb = K;
+    g.ldc = c.stride(0);
+    if (fp8) {
+        TORCH_CHECK(sfa.has_value() && sfb.has_value(), "fp8 operands need scale tensors");
+        TORCH_CHECK(sfa->scalar_type() == at::kFloat && sfa->dim() == 2 && sfa->size(0) >= M && sfa->size(1) == (K + 127) / 128, "bad sfa");
+        TORCH_CHECK(sfb->scalar_type() == at::kFloat && sfb->is_contiguous() && sfb->numel() == G * ((N + 127) / 128) * ((K + 127) / 128), "bad sfb");
+        g.sfa = sfa->data_ptr<float>();
+        g.sfa_stride_row = sfa->stride(0);
+        g.sfa_stride_kb = sfa->stride(1);
+        g.sfb = sfb->data_ptr<float>();
+    }
+    if (tile_group.has_value()) {
+        TORCH_CHECK(tile_group->scalar_type() == at::kInt && tile_group->is_contiguous() && tile_group->numel() >= (M + 127) / 128, "bad tile_group");
+        g.tile_group = tile_group->data_ptr<int32_t>();
+    } else {
+        TORCH_CHECK(G == 1, "several weight groups need tile_group");
+    }
+    if (a_ready_flags.has_value()) {
+        TORCH_CHECK(a_ready_flags->scalar_type() == at::kLong, "flags must be int64");
+        g.a_ready_flags = reinterpret_cast<const uint64_t*>(a_ready_flags->data_ptr<int64_t>());
+        g.a_ready_value = static_cast<uint64_t>(a_ready_value);
+        if (a_flag_of_tile.has_value()) g.a_flag_of_tile = a_flag_of_tile->data_ptr<int32_t>();
+    }
+    g.error = gemm_error_flag(a.get_device()).data_ptr<int>();
+    const int sms = num_sms > 0 ? static_cast<int>(num_sms) : at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    cuda_check(ep::launch_gemm(g, sms, at::cuda::getCurrentCUDAStream()), "tcgen05 GEMM launch");
+    return c;
+}
+
 // Debug aid: print the native call stack when the process receives SIGSEGV, then re-raise.
 void segv_backtrace_handler(int sig) {
     void* frames[64];
@@ -252,6 +313,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.attr("CH_AGRS") = static_cast<int>(EP_CH_AGRS);
     m.attr("CH_PP") = static_cast<int>(EP_CH_PP);
     m.attr("CH_ENGRAM") = static_cast<int>(EP_CH_ENGRAM);
+    m.def("gemm_nt", &gemm_nt, py::arg("a"), py::arg("b"), py::arg("sfa") = py::none(), py::arg("sfb") = py::none(),
+          py::arg("tile_group") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0, py::arg("a_ready_flags") = py::none(),
+          py::arg("a_ready_value") = 0, py::arg("a_flag_of_tile") = py::none());
+    m.def("gemm_error", [](int device) { return gemm_error_flag(device).item<int>(); });
     m.def("install_segv_backtrace", [] { signal(SIGSEGV, segv_backtrace_handler); });
     m.def("get_dispatch_layout", &get_dispatch_layout);
     m.def("per_token_cast_to_fp8", &per_token_cast_to_fp8, py::arg("x"), py::arg("round_scale") = false,
