@@ -326,7 +326,7 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
                  previous_event_before_epilogue: Optional[EventHandle] = None, async_with_compute_stream: bool = False,
                  allocate_on_comm_stream: bool = False, handle: Optional[EPHandle] = None, do_handle_copy: bool = True,
                  do_cpu_sync: Optional[bool] = None, do_expand: bool = False, do_zero_padding: bool = False,
-                 use_tma_aligned_col_major_sf: bool = False):
+                 use_tma_aligned_col_major_sf: bool = False, fused_fp8_cast: Optional[bool] = None):
         """Send every token to the ranks that own its selected experts.
 
         Returns ``(recv_x | (recv_x, recv_sf), recv_topk_idx, recv_topk_weights, handle, event)`` with the
@@ -336,7 +336,8 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         ``recv_topk_weights`` is 1-D.  With ``do_cpu_sync`` (default unless a cached ``handle`` is passed) the
         tensors have the exact number of rows; otherwise they have the worst-case size and
         ``handle.psum_num_recv_tokens_per_scaleup_rank[-1]`` holds the valid row count on the device.
-        With ``use_fp8_dispatch`` and bf16 input the e4m3 cast is fused into the kernel.
+        With ``use_fp8_dispatch`` (or ``fused_fp8_cast=True`` for this call) and bf16 input the e4m3 cast is fused into
+        the kernel; ``fused_fp8_cast=False`` sends bf16 rows even on an FP8 buffer (backward passes).
         """
         assert not self._destroyed
         assert not do_zero_padding or do_expand, '`do_zero_padding` requires `do_expand`'
@@ -364,7 +365,7 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         with torch.cuda.stream(self.comm_stream):
             st = self._prepare_dispatch(x, topk_idx, topk_weights, cumulative_local_expert_recv_stats, num_experts,
                                         num_max_tokens_per_rank, expert_alignment, num_sms, handle, do_handle_copy,
-                                        do_cpu_sync, do_expand, use_tma_aligned_col_major_sf)
+                                        do_cpu_sync, do_expand, use_tma_aligned_col_major_sf, fused_fp8_cast)
             self.core.dispatch(st.call, num_sms)
             out = self._finish_dispatch(st, do_zero_padding)
         event = self._stream_epilogue(async_with_compute_stream, out)
@@ -376,7 +377,7 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         return slot
 
     def _prepare_dispatch(self, x, topk_idx, topk_weights, stats, num_experts, num_max_tokens, alignment, num_sms, handle,
-                          do_handle_copy, do_cpu_sync, do_expand, col_major_sf) -> _DispatchState:
+                          do_handle_copy, do_cpu_sync, do_expand, col_major_sf, fused_fp8_cast=None) -> _DispatchState:
         C = self._C
         x_in, sf_in = x if isinstance(x, tuple) else (x, None)
         T, H = x_in.shape
@@ -385,7 +386,9 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         assert idx.dtype in (torch.int64, torch.int32)
         K = idx.shape[1]
         R, El = self.num_ranks, num_experts // self.num_ranks
-        quantize = self.use_fp8_dispatch and x_in.dtype == torch.bfloat16
+        quantize = (self.use_fp8_dispatch if fused_fp8_cast is None else fused_fp8_cast) and x_in.dtype == torch.bfloat16
+        assert H * (1 if quantize or x_in.dtype == torch.float8_e4m3fn else 2) <= self.regions.x_row_bytes, \
+            'rows are wider than the receive regions: size the buffer with use_fp8_dispatch=False for bf16 rows'
         fp8_out = quantize or x_in.dtype == torch.float8_e4m3fn
         assert H <= self.hidden or self.hidden == 0, 'hidden exceeds what the buffer was sized for'
         assert not do_expand or self.enable_expand, 'construct the buffer with enable_expand=True for the expand layout'

@@ -255,3 +255,19 @@ struct GemmArgs {
 namespace ep {
 cudaError_t launch_gemm(const GemmArgs& args, int num_sms, cudaStream_t stream);
 }  // namespace ep
+
+// ------------------------------------------------------------------------------------------------ MoE helpers
+// h [rows, 2 * I] bf16 (gate | up) -> act = silu(gate) * up, cast to e4m3 with one fp32 scale per (row, 128 channels)
+struct SwigluQuantArgs {
+    const void* h;          // [rows, 2 * inter] bf16, row stride ldh elements
+    int64_t ldh;
+    void* q;                // [rows, inter] e4m3
+    float* sf;              // scale of (row, block) at sf[row * sf_stride_row + blk * sf_stride_col]
+    int64_t sf_stride_row, sf_stride_col;
+    void* act_bf16;         // optional [rows, inter] bf16 copy of the activation (kept for the backward pass), or null
+    int rows, inter;
+};
+
+namespace ep {
+cudaError_t launch_swiglu_quant(const SwigluQuantArgs& args, cudaStream_t stream);
+}  // namespace ep

@@ -123,6 +123,29 @@ at::Tensor gemm_nt(const at::Tensor& a, const at::Tensor& b, const std::optional
     return c;
 }
 
+// h [rows, 2I] bf16 (gate | up) -> (e4m3 [rows, I], fp32 scales [rows, I/128], optional bf16 activation)
+std::vector<at::Tensor> swiglu_quant(const at::Tensor& h, bool keep_bf16) {
+    TORCH_CHECK(h.is_cuda() && h.dim() == 2 && h.stride(1) == 1 && h.scalar_type() == at::kBFloat16 && h.size(1) % 32 == 0,
+                "h must be bf16 [rows, 2 * I] with contiguous rows and I a multiple of 16");
+    const int64_t rows = h.size(0), I = h.size(1) / 2;
+    at::Tensor q = at::empty({rows, I}, h.options().dtype(at::kFloat8_e4m3fn));
+    at::Tensor sf = at::empty({rows, (I + 127) / 128}, h.options().dtype(at::kFloat));
+    at::Tensor act = keep_bf16 ? at::empty({rows, I}, h.options()) : at::Tensor();
+    SwigluQuantArgs a{};
+    a.h = h.data_ptr();
+    a.ldh = h.stride(0);
+    a.q = q.data_ptr();
+    a.sf = sf.data_ptr<float>();
+    a.sf_stride_row = sf.stride(0);
+    a.sf_stride_col = 1;
+    a.act_bf16 = keep_bf16 ? act.data_ptr() : nullptr;
+    a.rows = static_cast<int>(rows);
+    a.inter = static_cast<int>(I);
+    cuda_check(ep::launch_swiglu_quant(a, at::cuda::getCurrentCUDAStream()), "swiglu launch");
+    if (keep_bf16) return {q, sf, act};
+    return {q, sf};
+}
+
 // Debug aid: print the native call stack when the process receives SIGSEGV, then re-raise.
 void segv_backtrace_handler(int sig) {
     void* frames[64];
@@ -316,6 +339,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_nt", &gemm_nt, py::arg("a"), py::arg("b"), py::arg("sfa") = py::none(), py::arg("sfb") = py::none(),
           py::arg("tile_group") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0, py::arg("a_ready_flags") = py::none(),
           py::arg("a_ready_value") = 0, py::arg("a_flag_of_tile") = py::none());
+    m.def("swiglu_quant", &swiglu_quant, py::arg("h"), py::arg("keep_bf16") = false);
     m.def("gemm_error", [](int device) { return gemm_error_flag(device).item<int>(); });
     m.def("install_segv_backtrace", [] { signal(SIGSEGV, segv_backtrace_handler); });
     m.def("get_dispatch_layout", &get_dispatch_layout);

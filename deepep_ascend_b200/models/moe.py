@@ -1,0 +1,140 @@
+"""Expert-parallel MoE feed-forward layer built from this library's own kernels:
+
+    dispatch (expand layout, bf16 -> e4m3 cast fused into the NVLink scatter)
+      -> grouped block-scaled FP8 GEMM on tcgen05 (gate | up projection)
+      -> SwiGLU fused with the e4m3 cast of the next GEMM's input
+      -> grouped block-scaled FP8 GEMM (down projection) writing straight into the combine input region
+      -> combine (pull + top-k-weighted fp32 reduction in one kernel)
+
+and its backward pass, in which the gradients travel the same routes in reverse (the backward of combine is a
+cached dispatch, the backward of dispatch is a combine).  The reference library stops at dispatch / combine and
+leaves the layer to the caller (its README shows this data flow for DeepSeek-V3 style training, README.md:227-273).
+"""
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from ..buffers.elastic import ElasticBuffer
+from ..ops import gemm as G
+from ..utils.math import per_token_cast_back
+
+
+class _MoEFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, topk_weights, w13, w2, layer, topk_idx):
+        buf: ElasticBuffer = layer.buffer
+        E = layer.num_experts
+        (rx, rsf), _, recv_w, handle, _ = buf.dispatch(x, topk_idx, topk_weights, num_experts=E, do_expand=True,
+                                                      expert_alignment=G.BLOCK_M, fused_fp8_cast=True, num_sms=layer.num_sms)
+        rows = handle.num_rows
+        tile_group, valid_row = G.expert_tile_groups(handle.psum_num_recv_tokens_per_expert, rows)
+        q13, s13, q2, s2 = layer.fp8_weights()
+        h = G.grouped_gemm_nt(rx, q13, tile_group, sfa=rsf, sfb=s13)                       # [rows, 2I]
+        a2, sf2, act = G.swiglu_quant(h, keep_bf16=True)
+        y = buf.get_combine_buffer(handle)
+        G.grouped_gemm_nt(a2, q2, tile_group, out=y, sfa=sf2, sfb=s2)                      # [rows, H] in the combine region
+        out, _, _ = buf.combine(y, handle, weighted=True, num_sms=layer.num_sms)
+        ctx.layer, ctx.handle = layer, handle
+        ctx.save_for_backward(rx, rsf, recv_w, h, act, y.clone(), tile_group, valid_row, w13, w2)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        layer, handle = ctx.layer, ctx.handle
+        buf: ElasticBuffer = layer.buffer
+        rx, rsf, recv_w, h, act, y, tile_group, valid_row, w13, w2 = ctx.saved_tensors
+        I = act.shape[1]
+        El = w13.shape[0]
+        # backward of the weighted combine: every expert row receives its token's gradient
+        g_rows, _, _, _, _ = buf.dispatch(d_out.contiguous(), handle=handle, fused_fp8_cast=False, num_sms=layer.num_sms)
+        g_rows = torch.where(valid_row.unsqueeze(1), g_rows, torch.zeros_like(g_rows))
+        d_w_rows = (g_rows.float() * y.float()).sum(dim=1)                                  # d loss / d weight of each row
+        dy = (g_rows.float() * recv_w.unsqueeze(1)).to(torch.bfloat16)
+        # down projection
+        w2_t, w13_t = layer.transposed_weights()
+        d_act = G.grouped_gemm_nt(dy, w2_t, tile_group)                                     # [rows, I]
+        d_act = torch.where(valid_row.unsqueeze(1), d_act, torch.zeros_like(d_act))
+        gate, up = h[:, :I].float(), h[:, I:].float()
+        sig = torch.sigmoid(gate)
+        d_up = d_act.float() * gate * sig
+        d_gate = d_act.float() * up * sig * (1 + gate * (1 - sig))
+        dh = torch.cat([d_gate, d_up], dim=1).to(torch.bfloat16)
+        dh = torch.where(valid_row.unsqueeze(1), dh, torch.zeros_like(dh))
+        # up projection: the gradient rows go into the combine region and travel home (backward of dispatch)
+        d_recv = buf.get_combine_buffer(handle)
+        G.grouped_gemm_nt(dh, w13_t, tile_group, out=d_recv)
+        dx, d_topk_w, _ = buf.combine(d_recv, handle, topk_weights=d_w_rows, num_sms=layer.num_sms)
+        # weight gradients, one expert segment at a time (K = rows of the segment)
+        x_rows = per_token_cast_back(rx, rsf.contiguous() if rsf.stride(1) != 1 else rsf)
+        x_rows = torch.where(valid_row.unsqueeze(1), x_rows, torch.zeros_like(x_rows))
+        act_m = torch.where(valid_row.unsqueeze(1), act, torch.zeros_like(act))
+        d_w13, d_w2 = torch.zeros_like(w13), torch.zeros_like(w2)
+        ends = handle.psum_num_recv_tokens_per_expert.tolist()
+        start = 0
+        for e in range(El):
+            stop = (ends[e] + G.BLOCK_M - 1) // G.BLOCK_M * G.BLOCK_M
+            if ends[e] > start:
+                seg = slice(start, stop)
+                d_w2[e] = G.gemm_nt(dy[seg].t().contiguous(), act_m[seg].t().contiguous())
+                d_w13[e] = G.gemm_nt(dh[seg].t().contiguous(), x_rows[seg].t().contiguous())
+            start = stop
+        return dx, d_topk_w, d_w13, d_w2, None, None
+
+
+class FusedMoE(nn.Module):
+    """SwiGLU expert FFN sharded over an expert-parallel group.
+
+    ``w13 [E_local, 2 * intermediate, hidden]`` (gate rows then up rows) and ``w2 [E_local, hidden, intermediate]`` are
+    bf16 master weights; the forward pass runs on e4m3 copies with 128 x 128 block scales that are refreshed
+    whenever the master weights change.  ``forward(x [T, hidden] bf16, topk_idx [T, K], topk_weights [T, K] fp32)``
+    returns ``sum_k w_k * FFN_{e_k}(x)`` as bf16 ``[T, hidden]``.
+    """
+
+    def __init__(self, buffer: ElasticBuffer, num_experts: int, hidden: int, intermediate: int, init_std: float = 0.02,
+                 num_sms: int = 0, device='cuda'):
+        super().__init__()
+        assert num_experts % buffer.num_ranks == 0 and hidden % 128 == 0 and intermediate % 128 == 0
+        assert buffer.enable_expand, 'construct the buffer with enable_expand=True, expert_alignment=128'
+        self.buffer, self.num_experts, self.hidden, self.intermediate = buffer, num_experts, hidden, intermediate
+        self.num_sms = num_sms
+        el = num_experts // buffer.num_ranks
+        self.w13 = nn.Parameter((torch.randn(el, 2 * intermediate, hidden, device=device) * init_std).bfloat16())
+        self.w2 = nn.Parameter((torch.randn(el, hidden, intermediate, device=device) * init_std).bfloat16())
+        self._fp8 = None
+        self._t = None
+
+    def _versions(self):
+        return (self.w13._version, self.w2._version, self.w13.data_ptr(), self.w2.data_ptr())
+
+    def fp8_weights(self):
+        if self._fp8 is None or self._fp8[0] != self._versions():
+            q13, s13 = G.quantize_weight_blocks(self.w13.detach().float())
+            q2, s2 = G.quantize_weight_blocks(self.w2.detach().float())
+            self._fp8 = (self._versions(), (q13, s13, q2, s2))
+        return self._fp8[1]
+
+    def transposed_weights(self):
+        if self._t is None or self._t[0] != self._versions():
+            self._t = (self._versions(), (self.w2.detach().transpose(1, 2).contiguous(), self.w13.detach().transpose(1, 2).contiguous()))
+        return self._t[1]
+
+    def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+        return _MoEFunction.apply(x, topk_weights, self.w13, self.w2, self, topk_idx)
+
+
+def moe_reference(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, w13_all: torch.Tensor,
+                  w2_all: torch.Tensor) -> torch.Tensor:
+    """Plain PyTorch fp32 statement of the layer with ALL experts' weights on one device (for tests)."""
+    T, H = x.shape
+    I = w2_all.shape[2]
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    for k in range(topk_idx.shape[1]):
+        for e in topk_idx[:, k].unique().tolist():
+            if e < 0:
+                continue
+            m = topk_idx[:, k] == e
+            h = x[m].float() @ w13_all[e].float().t()
+            act = torch.nn.functional.silu(h[:, :I]) * h[:, I:]
+            out[m] += topk_weights[m, k].unsqueeze(1) * (act @ w2_all[e].float().t())
+    return out

@@ -1,0 +1,62 @@
+"""Python front end of the tcgen05 GEMM kernels (``csrc/kernels/gemm_sm100.cu``) and of the small MoE helpers.
+
+No counterpart in the reference, which contains no tensor-core code; these kernels exist for the fused MoE layer
+and for the all-gather / reduce-scatter fused GEMMs.
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _native
+
+BLOCK_M = 128   # rows of one output tile; expert segments of the grouped GEMM are aligned to it
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, num_sms: int = 0) -> torch.Tensor:
+    """``a [M, K] @ b [N, K]^T -> bf16 [M, N]`` (bf16 operands, fp32 accumulation in tensor memory)."""
+    return _native.load().gemm_nt(a, b, None, None, None, out, num_sms)
+
+
+def grouped_gemm_nt(a: torch.Tensor, b: torch.Tensor, tile_group: torch.Tensor, out: Optional[torch.Tensor] = None,
+                    sfa: Optional[torch.Tensor] = None, sfb: Optional[torch.Tensor] = None, num_sms: int = 0) -> torch.Tensor:
+    """Every 128-row tile ``t`` of ``a`` is multiplied by ``b[tile_group[t]]`` (``-1`` skips the tile).  bf16 operands,
+    or e4m3 operands with ``sfa [M, K/128]`` and ``sfb [G, N/128, K/128]`` fp32 block scales."""
+    return _native.load().gemm_nt(a, b, sfa, sfb, tile_group, out, num_sms)
+
+
+def quantize_weight_blocks(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``w [G, N, K]`` -> (e4m3 ``[G, N, K]``, fp32 scales ``[G, ceil(N/128), ceil(K/128)]``), one scale per
+    128 x 128 block (the weight format of DeepSeek-V3 style FP8 training)."""
+    G, N, K = w.shape
+    nb, kb = (N + 127) // 128, (K + 127) // 128
+    wp = torch.zeros(G, nb * 128, kb * 128, device=w.device, dtype=torch.float32)
+    wp[:, :N, :K] = w
+    blocks = wp.view(G, nb, 128, kb, 128)
+    amax = blocks.abs().amax(dim=(2, 4)).clamp(1e-4)
+    q = (blocks * (448.0 / amax)[:, :, None, :, None]).to(torch.float8_e4m3fn).view(G, nb * 128, kb * 128)[:, :N, :K].contiguous()
+    return q, (amax / 448.0).contiguous()
+
+
+def expert_tile_groups(psum_expert_ends: torch.Tensor, num_rows: int, alignment: int = BLOCK_M) -> Tuple[torch.Tensor, torch.Tensor]:
+    """From the expand-layout segment ends of ``EPHandle.psum_num_recv_tokens_per_expert`` (segment ``i`` starts at
+    ``align(end[i-1], alignment)``) -> (``tile_group int32 [ceil(num_rows / 128)]`` with -1 for tiles that hold no
+    token, ``valid_row bool [num_rows]``).  Stays on the device: no host synchronisation."""
+    assert alignment % BLOCK_M == 0, 'expert segments must start on a tile boundary'
+    ends = psum_expert_ends.to(torch.int64)
+    aligned_ends = (ends + alignment - 1) // alignment * alignment
+    starts = torch.cat([torch.zeros(1, dtype=torch.int64, device=ends.device), aligned_ends[:-1]])
+    num_tiles = (num_rows + BLOCK_M - 1) // BLOCK_M
+    tile_start = torch.arange(num_tiles, device=ends.device, dtype=torch.int64) * BLOCK_M
+    grp = torch.searchsorted(aligned_ends, tile_start, right=True)
+    grp_c = grp.clamp_max(ends.numel() - 1)
+    has_rows = (grp < ends.numel()) & (tile_start < ends[grp_c]) & (tile_start >= starts[grp_c])
+    tile_group = torch.where(has_rows, grp_c, torch.full_like(grp_c, -1)).to(torch.int32)
+    rows = torch.arange(num_rows, device=ends.device, dtype=torch.int64)
+    rgrp = torch.searchsorted(aligned_ends, rows, right=True).clamp_max(ends.numel() - 1)
+    valid_row = (rows >= starts[rgrp]) & (rows < ends[rgrp])
+    return tile_group.contiguous(), valid_row
+
+
+def swiglu_quant(h: torch.Tensor, keep_bf16: bool = False):
+    """``h [rows, 2I]`` bf16 (gate | up) -> ``(e4m3 [rows, I], scales [rows, I/128][, bf16 activation])``."""
+    return _native.load().swiglu_quant(h, keep_bf16)
