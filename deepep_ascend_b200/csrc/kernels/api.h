@@ -250,7 +250,18 @@ struct GemmArgs {
     const uint64_t* a_ready_flags;    // all-gather fused into the loads: rows of M tile t may be read once
     uint64_t a_ready_value;           //   a_ready_flags[a_flag_of_tile[t]] >= a_ready_value
     const int32_t* a_flag_of_tile;
+    // one-kernel fusion with a collective over peer memory (EP_GEMM_FUSE_*); needs a cooperative launch
+    int fuse;
+    RankCtx ctx;
+    int num_copy_ctas;                // AG: CTAs (at the end of the grid) that pull the remote shards over NVLink
+    uint64_t off_full;                // AG: gathered A [M, K] inside every rank's symmetric buffer; rank r owns rows
+                                      //     [r * M / R, (r + 1) * M / R) and writes its shard there before the call
+    uint64_t off_slots;               // RS: two sets of [R][M / R][N] bf16 partial results inside every rank's buffer
+    uint64_t slot_set_bytes;
+    void* rs_out;                     // RS: [M / R, N] bf16
+    int m_tile_offset;                // M tiles are visited starting from this one (local shard first)
 };
+enum { EP_GEMM_FUSE_NONE = 0, EP_GEMM_FUSE_ALL_GATHER = 1, EP_GEMM_FUSE_REDUCE_SCATTER = 2 };
 
 namespace ep {
 cudaError_t launch_gemm(const GemmArgs& args, int num_sms, cudaStream_t stream);

@@ -17,7 +17,7 @@
 
 #include <mutex>
 
-#include "api.h"
+#include "common.cuh"
 #include "gemm_sm100.cuh"
 
 namespace ep {
@@ -25,17 +25,21 @@ namespace ep {
 namespace {
 
 constexpr int kBlockM = 128, kBlockN = 128, kTileBytes = 128 * 128;   // one operand tile: 128 rows x 128 bytes
-constexpr int kStages = 6;
+constexpr int kStages = 5;
+constexpr int kEpiRowBytes = kBlockN * 2 + 16;          // one staged bf16 output row, padded against bank conflicts
+constexpr int kEpiStageBytes = 4 * 32 * kEpiRowBytes;   // four epilogue warps x 32 rows
+constexpr int kCopyWarps = 5;
 constexpr int kGemmThreads = 192;
 constexpr int kTmemColumns = 256;   // two accumulator buffers of kBlockN fp32 columns
 constexpr uint64_t kWaitLimitNs = 4ull * 1000 * 1000 * 1000;
 
 struct GemmSmem {
     uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
+    uint64_t copy_bar[kCopyWarps][2];
     uint32_t tmem_base;
     int failed;
 };
-constexpr int kGemmSmemBytes = 2 * kStages * kTileBytes + 1024;
+constexpr int kGemmSmemBytes = 2 * kStages * kTileBytes + 1024 + kEpiStageBytes;
 
 __device__ __forceinline__ uint64_t gemm_timer() {
     uint64_t t;
@@ -86,6 +90,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int num_m = (g.M + kBlockM - 1) / kBlockM, num_n = (g.N + kBlockN - 1) / kBlockN;
     const int num_k = (g.K + kBlockK - 1) / kBlockK;
     const int num_tiles = num_m * num_n;
+    const int gemm_ctas = static_cast<int>(gridDim.x) - g.num_copy_ctas;
+    const bool is_copier = static_cast<int>(blockIdx.x) >= gemm_ctas;
+    uint8_t* s_epi = smem + 2 * kStages * kTileBytes + 1024;
+    Workspace* ws = g.fuse != EP_GEMM_FUSE_NONE ? local_ws(g.ctx) : nullptr;
+    const uint64_t epoch = ws != nullptr ? ws->epoch[EP_CH_GEMM] + 1 : 0;
+    const int tiles_per_shard = g.fuse != EP_GEMM_FUSE_NONE ? num_m / g.ctx.num_ranks : num_m;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) {
@@ -115,10 +125,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (lane == 0) {
             PipeState p;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m_blk = tile / num_n, n_blk = tile % num_n;
+            for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
+                const int m_blk = (tile / num_n + g.m_tile_offset) % num_m, n_blk = tile % num_n;
                 const int grp = g.tile_group != nullptr ? g.tile_group[m_blk] : 0;
                 if (grp < 0) continue;
+                if (g.fuse == EP_GEMM_FUSE_ALL_GATHER && m_blk / tiles_per_shard != g.ctx.rank) {
+                    // rows of a remote shard: wait until a copier CTA of this kernel has landed the tile locally
+                    const uint64_t* flag = &ws->tile_flags[m_blk];
+                    const uint64_t t0 = gemm_timer();
+                    while (ptx::ld_acquire_sys(flag) < epoch) {
+                        if (gemm_timer() - t0 > kWaitLimitNs || *reinterpret_cast<volatile int*>(&sm->failed)) {
+                            sm->failed = 3;
+                            if (g.error != nullptr) atomicCAS(g.error, 0, 3);
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok) break;
+                    ptx::fence_proxy_async_all();   // the tile was written through the async proxy of another SM
+                }
                 if (g.a_ready_flags != nullptr) {
                     // rows of this M tile arrive from another rank: wait (bounded) for their flag
                     const uint64_t* flag = g.a_ready_flags + (g.a_flag_of_tile != nullptr ? g.a_flag_of_tile[m_blk] : m_blk);
@@ -150,8 +175,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m_blk = tile / num_n;
+            for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
+                const int m_blk = (tile / num_n + g.m_tile_offset) % num_m;
                 const int grp = g.tile_group != nullptr ? g.tile_group[m_blk] : 0;
                 if (grp < 0) continue;
                 if (!kFp8) {
@@ -195,8 +220,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         uint32_t acc_phase = 0;
         bool ok = true;
         uint8_t* cb = reinterpret_cast<uint8_t*>(g.c);
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            const int m_blk = tile / num_n, n_blk = tile % num_n;
+        for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
+            const int m_blk = (tile / num_n + g.m_tile_offset) % num_m, n_blk = tile % num_n;
             const int grp = g.tile_group != nullptr ? g.tile_group[m_blk] : 0;
             if (grp < 0) continue;
             const int row = m_blk * kBlockM + quad * 32 + lane;
@@ -207,6 +232,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 umma::fence_after_thread_sync();
+                const bool to_peer = g.fuse == EP_GEMM_FUSE_REDUCE_SCATTER;
+                uint8_t* my_stage = s_epi + (quad * 32 + lane) * kEpiRowBytes;
+                if (to_peer) {
+                    ptx::bulk_wait_read<0>();     // the staging rows were the source of the previous tile's stores
+                    __syncwarp();
+                }
 #pragma unroll
                 for (int c = 0; c < kBlockN / 32; ++c) {
                     uint32_t r[32];
@@ -222,10 +253,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
                                 for (int j = 0; j < 4; ++j)
                                     h[j] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
-                                *reinterpret_cast<int4*>(cb + (static_cast<int64_t>(row) * g.ldc + col) * 2) = out;
+                                if (to_peer) *reinterpret_cast<int4*>(my_stage + (c * 32 + v * 8) * 2) = out;
+                                else *reinterpret_cast<int4*>(cb + (static_cast<int64_t>(row) * g.ldc + col) * 2) = out;
                             }
                         }
                     }
+                }
+                if (to_peer) {
+                    // GEMM -> reduce-scatter: this row of the partial result goes to the rank that owns it, into the
+                    // slot reserved for this source rank (one 256-byte bulk store per row over NVLink)
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    const int rows_per_rank = g.M / g.ctx.num_ranks;
+                    const int owner = row / rows_per_rank, local_row = row - owner * rows_per_rank;
+                    uint8_t* dst = g.ctx.peer_base[owner] + g.off_slots + (epoch & 1) * g.slot_set_bytes +
+                                   ((static_cast<int64_t>(g.ctx.rank) * rows_per_rank + local_row) * g.N + n0) * 2;
+                    ptx::bulk_store(dst, my_stage, kBlockN * 2);
+                    ptx::bulk_commit();
                 }
                 umma::fence_before_thread_sync();
                 __syncwarp();
@@ -272,9 +316,133 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
         }
     }
+    if (g.fuse == EP_GEMM_FUSE_ALL_GATHER && is_copier && warp < kCopyWarps) {
+        // ------------------------------------------------------------------ all-gather fused into this kernel
+        // Copier CTAs pull the remote shards of A, one 128-row tile at a time, from the owners' symmetric buffers
+        // (TMA bulk loads over NVLink, no multicast) into the local copy and publish one flag per tile.
+        const RankCtx& ctx = g.ctx;
+        const int copier = static_cast<int>(blockIdx.x) - gemm_ctas;
+        const int row_bytes = g.K * (kFp8 ? 1 : 2);
+        uint8_t* stage = smem + static_cast<size_t>(warp) * 2 * 16384;
+        uint64_t* bars = sm->copy_bar[warp];
+        if (lane == 0) {
+            ptx::mbar_init(&bars[0], 1);
+            ptx::mbar_init(&bars[1], 1);
+            ptx::mbar_fence_init();
+        }
+        __syncwarp();
+        bool alive = !is_aborted(ws);
+        // every rank's shard must be in place: the first copier runs the cross-GPU barrier, the others wait for it
+        uint64_t* entry_word = &ws->tile_flags[EP_MAX_TILE_FLAGS - 1];
+        if (copier == 0 && warp == 0) {
+            if (lane < ctx.num_ranks) {
+                Workspace* pws = reinterpret_cast<Workspace*>(ctx.peer_base[lane]);
+                ptx::red_add_release_sys(&pws->xbar[EP_CH_GEMM][ctx.rank], 1ull);
+                const uint64_t* mine = &ws->xbar[EP_CH_GEMM][lane];
+                alive = bounded_wait(
+                    ctx, ws, EP_PH_XGPU_BARRIER, lane, 2 * epoch - 1, [&] { return ptx::ld_acquire_sys(mine) >= 2 * epoch - 1; },
+                    [&] { return ptx::ld_relaxed_sys(mine); });
+            }
+            alive = __all_sync(0xffffffffu, alive);
+            if (lane == 0 && alive) ptx::st_release_sys(entry_word, epoch);
+        }
+        if (alive)
+            alive = bounded_wait(
+                ctx, ws, EP_PH_TILE_FLAG, -1, epoch, [&] { return ptx::ld_acquire_sys(entry_word) >= epoch; },
+                [&] { return ptx::ld_relaxed_sys(entry_word); });
+        alive = __all_sync(0xffffffffu, alive);
+        if (!alive) sm->failed = 7;
+        asm volatile("bar.sync 1, %0;" ::"r"(kCopyWarps * 32) : "memory");
+        if (*reinterpret_cast<volatile int*>(&sm->failed)) alive = false;
+        uint32_t n_loaded = 0;
+        for (int s = 1; s < ctx.num_ranks && alive; ++s) {
+            const int src = (ctx.rank + s) % ctx.num_ranks;
+            for (int j = copier; j < tiles_per_shard && alive; j += g.num_copy_ctas) {
+                const int m_blk = src * tiles_per_shard + j;
+                for (int r = warp; r < kBlockM && alive; r += kCopyWarps) {
+                    const int64_t off = g.off_full + (static_cast<int64_t>(m_blk) * kBlockM + r) * row_bytes;
+                    const int st = n_loaded & 1;
+                    ptx::bulk_wait_read<1>();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::mbar_arrive_expect_tx(&bars[st], row_bytes);
+                        ptx::bulk_load(stage + st * 16384, ctx.peer_base[src] + off, row_bytes, &bars[st]);
+                    }
+                    alive = mbar_wait_bounded(ctx, ws, &bars[st], (n_loaded >> 1) & 1, EP_PH_COMBINE_LOAD);
+                    ++n_loaded;
+                    if (!alive) {
+                        sm->failed = 7;
+                        break;
+                    }
+                    if (lane == 0) ptx::bulk_store(ctx.peer_base[ctx.rank] + off, stage + st * 16384, row_bytes);
+                    ptx::bulk_commit();
+                }
+                ptx::bulk_wait<0>();
+                __threadfence();
+                // all copy warps of this CTA have finished their rows of the tile -> publish it
+                asm volatile("bar.sync 1, %0;" ::"r"(kCopyWarps * 32) : "memory");
+                if (*reinterpret_cast<volatile int*>(&sm->failed)) alive = false;   // same decision in every copy warp
+                if (warp == 0 && lane == 0 && alive) ptx::st_release_sys(&ws->tile_flags[m_blk], epoch);
+            }
+        }
+    }
+    if (g.fuse == EP_GEMM_FUSE_REDUCE_SCATTER) {
+        ptx::bulk_commit();
+        ptx::bulk_wait<0>();
+        __threadfence_system();
+    }
     umma::fence_before_thread_sync();
     __syncthreads();
     if (warp == 1) umma::tmem_dealloc(tmem_base, kTmemColumns);
+
+    if (g.fuse != EP_GEMM_FUSE_NONE) {
+        // All partial rows have left this rank (RS) / all pulls from the peers are done (AG): cross-GPU barrier.
+        const RankCtx& ctx = g.ctx;
+        bool alive = grid_sync(ctx, ws, EP_CH_GEMM, EP_PH_GRID_SYNC);
+        if (blockIdx.x == 0) {
+            // arrival number 2 * epoch of this channel (the AG entry barrier used 2 * epoch - 1)
+            int ok = alive ? 1 : 0;
+            if (alive && threadIdx.x < ctx.num_ranks) {
+                Workspace* pws = reinterpret_cast<Workspace*>(ctx.peer_base[threadIdx.x]);
+                if (g.fuse == EP_GEMM_FUSE_REDUCE_SCATTER) ptx::red_add_release_sys(&pws->xbar[EP_CH_GEMM][ctx.rank], 1ull);   // stands in for the entry arrival
+                ptx::red_add_release_sys(&pws->xbar[EP_CH_GEMM][ctx.rank], 1ull);
+                const uint64_t* mine = &ws->xbar[EP_CH_GEMM][threadIdx.x];
+                ok = bounded_wait(
+                    ctx, ws, EP_PH_XGPU_BARRIER, threadIdx.x, 2 * epoch, [&] { return ptx::ld_acquire_sys(mine) >= 2 * epoch; },
+                    [&] { return ptx::ld_relaxed_sys(mine); });
+            }
+            alive = __syncthreads_and(ok) != 0;
+        }
+        alive = grid_sync(ctx, ws, EP_CH_GEMM, EP_PH_GRID_SYNC) && alive;
+        if (g.fuse == EP_GEMM_FUSE_REDUCE_SCATTER && alive) {
+            // every rank's partial rows for this rank have arrived: sum the R slots in rank order in fp32
+            const int rows_per_rank = g.M / ctx.num_ranks;
+            const int64_t vecs = static_cast<int64_t>(rows_per_rank) * g.N / 8;
+            const uint8_t* slots = ctx.peer_base[ctx.rank] + g.off_slots + (epoch & 1) * g.slot_set_bytes;
+            const int64_t slot_bytes = static_cast<int64_t>(rows_per_rank) * g.N * 2;
+            for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < vecs; v += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                for (int r = 0; r < ctx.num_ranks; ++r) {
+                    const int4 raw = __ldcg(reinterpret_cast<const int4*>(slots + r * slot_bytes + v * 16));
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __bfloat1622float2(h[j]);
+                        acc[2 * j] += f.x;
+                        acc[2 * j + 1] += f.y;
+                    }
+                }
+                int4 out;
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                *reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(g.rs_out) + v * 16) = out;
+            }
+        }
+        if (blockIdx.x == 0 && threadIdx.x == 0) ws->epoch[EP_CH_GEMM] = epoch;
+    }
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -323,8 +491,17 @@ cudaError_t launch_gemm(const GemmArgs& g, int num_sms, cudaStream_t stream) {
     if (err != cudaSuccess) return err;
     const int num_tiles = ((g.M + kBlockM - 1) / kBlockM) * ((g.N + kBlockN - 1) / kBlockN);
     int ctas = num_sms < 1 ? 1 : num_sms;
-    if (ctas > num_tiles) ctas = num_tiles;
     void* params[] = {&map_a, &map_b, const_cast<GemmArgs*>(&g)};
+    if (g.fuse != EP_GEMM_FUSE_NONE) {
+        // the CTAs of a fused launch wait on one another (grid barrier, copier -> producer flags): cooperative launch
+        const int R = g.ctx.num_ranks;
+        if (g.is_fp8 || g.M % (kBlockM * R) != 0 || g.N % kBlockN != 0 || g.K * 2 > 16384 || g.tile_group != nullptr) return cudaErrorInvalidValue;
+        if (g.fuse == EP_GEMM_FUSE_ALL_GATHER && (g.num_copy_ctas < 1 || g.num_copy_ctas >= ctas)) return cudaErrorInvalidValue;
+        if (g.fuse == EP_GEMM_FUSE_REDUCE_SCATTER && g.num_copy_ctas != 0) return cudaErrorInvalidValue;
+        if (g.M / kBlockM >= EP_MAX_TILE_FLAGS - 1) return cudaErrorInvalidValue;
+        return cudaLaunchCooperativeKernel(fn, dim3(ctas, 1, 1), dim3(kGemmThreads, 1, 1), params, kGemmSmemBytes, stream);
+    }
+    if (ctas > num_tiles) ctas = num_tiles;
     return cudaLaunchKernel(fn, dim3(ctas, 1, 1), dim3(kGemmThreads, 1, 1), params, kGemmSmemBytes, stream);
 }
 

@@ -123,6 +123,69 @@ at::Tensor gemm_nt(const at::Tensor& a, const at::Tensor& b, const std::optional
     return c;
 }
 
+// One-kernel all-gather + GEMM: `a_full` is the gathered [M, K] bf16 matrix inside the symmetric buffer (this rank
+// has already written its own rows); copier CTAs of the GEMM kernel pull the other ranks' rows over NVLink while
+// the tensor-core CTAs start on the local rows.  -> bf16 [M, N]
+at::Tensor ag_gemm(ElasticBufferCore& core, int64_t off_full, int64_t M, int64_t K, const at::Tensor& b, int64_t num_sms, int64_t num_copy_ctas) {
+    TORCH_CHECK(b.is_cuda() && b.dim() == 2 && b.is_contiguous() && b.scalar_type() == at::kBFloat16 && b.size(1) == K, "B must be contiguous bf16 [N, K]");
+    const int64_t N = b.size(0);
+    at::Tensor a_full = core.view(off_full, {M, K}, {K, 1}, at::kBFloat16);
+    at::Tensor c = at::empty({M, N}, b.options());
+    GemmArgs g{};
+    g.a = a_full.data_ptr();
+    g.b = b.data_ptr();
+    g.c = c.data_ptr();
+    g.M = static_cast<int>(M);
+    g.N = static_cast<int>(N);
+    g.K = static_cast<int>(K);
+    g.num_groups = 1;
+    g.lda = K;
+    g.ldb = K;
+    g.ldc = N;
+    g.error = gemm_error_flag(b.get_device()).data_ptr<int>();
+    g.fuse = EP_GEMM_FUSE_ALL_GATHER;
+    g.ctx = core.ctx();
+    g.num_copy_ctas = static_cast<int>(num_copy_ctas);
+    g.off_full = off_full;
+    g.m_tile_offset = static_cast<int>(core.rank() * (M / 128 / core.num_ranks()));
+    core.check_status();
+    cuda_check(ep::launch_gemm(g, static_cast<int>(num_sms), at::cuda::getCurrentCUDAStream()), "all-gather GEMM launch");
+    return c;
+}
+
+// One-kernel GEMM + reduce-scatter: partial = a [M, K_local] @ b [N, K_local]^T; the epilogue bulk-stores every row
+// of the partial result into the slot of the rank that owns it; after a cross-GPU barrier the same kernel sums the
+// R slots.  -> bf16 [M / R, N]
+at::Tensor gemm_rs(ElasticBufferCore& core, const at::Tensor& a, const at::Tensor& b, int64_t off_slots, int64_t slot_set_bytes, int64_t num_sms) {
+    TORCH_CHECK(a.is_cuda() && a.dim() == 2 && a.is_contiguous() && a.scalar_type() == at::kBFloat16, "A must be contiguous bf16 [M, K]");
+    TORCH_CHECK(b.is_cuda() && b.dim() == 2 && b.is_contiguous() && b.scalar_type() == at::kBFloat16 && b.size(1) == a.size(1), "B must be contiguous bf16 [N, K]");
+    const int64_t M = a.size(0), K = a.size(1), N = b.size(0), R = core.num_ranks();
+    TORCH_CHECK(off_slots % 16 == 0 && slot_set_bytes >= M * N * 2 && off_slots + 2 * slot_set_bytes <= core.num_bytes(), "slot region too small");
+    at::Tensor out = at::empty({M / R, N}, a.options());
+    GemmArgs g{};
+    g.a = a.data_ptr();
+    g.b = b.data_ptr();
+    g.c = out.data_ptr();
+    g.M = static_cast<int>(M);
+    g.N = static_cast<int>(N);
+    g.K = static_cast<int>(K);
+    g.num_groups = 1;
+    g.lda = K;
+    g.ldb = K;
+    g.ldc = N;
+    g.error = gemm_error_flag(a.get_device()).data_ptr<int>();
+    g.fuse = EP_GEMM_FUSE_REDUCE_SCATTER;
+    g.ctx = core.ctx();
+    g.off_slots = off_slots;
+    g.slot_set_bytes = slot_set_bytes;
+    g.rs_out = out.data_ptr();
+    // start with the tiles that belong to the next rank so that the ranks do not all write to the same owner at once
+    g.m_tile_offset = static_cast<int>(((core.rank() + 1) % R) * (M / 128 / R));
+    core.check_status();
+    cuda_check(ep::launch_gemm(g, static_cast<int>(num_sms), at::cuda::getCurrentCUDAStream()), "GEMM reduce-scatter launch");
+    return out;
+}
+
 // h [rows, 2I] bf16 (gate | up) -> (e4m3 [rows, I], fp32 scales [rows, I/128], optional bf16 activation)
 std::vector<at::Tensor> swiglu_quant(const at::Tensor& h, bool keep_bf16) {
     TORCH_CHECK(h.is_cuda() && h.dim() == 2 && h.stride(1) == 1 && h.scalar_type() == at::kBFloat16 && h.size(1) % 32 == 0,
@@ -339,6 +402,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_nt", &gemm_nt, py::arg("a"), py::arg("b"), py::arg("sfa") = py::none(), py::arg("sfb") = py::none(),
           py::arg("tile_group") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0, py::arg("a_ready_flags") = py::none(),
           py::arg("a_ready_value") = 0, py::arg("a_flag_of_tile") = py::none());
+    m.def("ag_gemm", &ag_gemm);
+    m.def("gemm_rs", &gemm_rs);
     m.def("swiglu_quant", &swiglu_quant, py::arg("h"), py::arg("keep_bf16") = false);
     m.def("gemm_error", [](int device) { return gemm_error_flag(device).item<int>(); });
     m.def("install_segv_backtrace", [] { signal(SIGSEGV, segv_backtrace_handler); });

@@ -162,3 +162,50 @@ def test_multi_process_collectives_ll_legacy(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f'needs {world} GPUs')
     mp.spawn(_worker_misc, args=(world, _free_port()), nprocs=world, join=True)
+
+
+def _worker_tp(rank: int, world: int, port: int):
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    try:
+        import deepep_ascend_b200 as ep
+        from deepep_ascend_b200.parallel.tp import TensorParallelGemm
+        group = dist.new_group(list(range(world)))
+        M, K, N = 128 * world * 3, 1024, 512
+        buf = ep.ElasticBuffer(group, num_max_tokens_per_rank=16, hidden=256, num_topk=2, extra_bytes=TensorParallelGemm.size_hint(M, K, N),
+                               num_gpu_timeout_secs=10)
+        tp = TensorParallelGemm(buf, M, K, N, num_sms=32, num_copy_ctas=4)
+        for it in range(3):
+            g = torch.Generator('cuda').manual_seed(100 * it + rank)
+            x_shard = torch.randn(M // world, K, device='cuda', generator=g).bfloat16()
+            w = torch.randn(N, K, device='cuda', generator=g).bfloat16() * 0.1
+            c = tp.ag_gemm(x_shard, w)
+            gathered = [torch.empty_like(x_shard) for _ in range(world)]
+            dist.all_gather(gathered, x_shard, group=group)
+            ref = torch.cat(gathered).float() @ w.float().t()
+            assert float((c.float() - ref).abs().max()) <= 2e-2 * float(ref.abs().max()) + 1e-2
+            # reduce-scatter of the partial products
+            x = torch.randn(M, K, device='cuda', generator=g).bfloat16()
+            out = tp.gemm_rs(x, w)
+            partial = (x.float() @ w.float().t()).bfloat16()
+            parts = [torch.empty_like(partial) for _ in range(world)]
+            dist.all_gather(parts, partial, group=group)
+            rows = slice(rank * (M // world), (rank + 1) * (M // world))
+            acc = torch.zeros(M // world, N, device='cuda')
+            for p in parts:
+                acc += p[rows].float()
+            assert float((out.float() - acc).abs().max()) <= 2e-2 * float(acc.abs().max()) + 1e-2
+        torch.cuda.synchronize()
+        buf.check_status()
+        assert buf._C.gemm_error(rank) == 0
+        buf.destroy()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('world', [2, 8])
+def test_multi_process_fused_tp_gemm(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f'needs {world} GPUs')
+    mp.spawn(_worker_tp, args=(world, _free_port()), nprocs=world, join=True)
