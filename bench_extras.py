@@ -1,0 +1,287 @@
+"""Secondary benchmarks (one JSON line per measurement, rank 0): low-latency decode in a CUDA graph, fused MoE layer
+forward+backward, skewed (Zipf) routing, fused tensor-parallel GEMMs, the NCCL all-to-all baseline, the plain
+tcgen05 GEMM, and a per-phase breakdown of dispatch / combine.
+
+    python bench_extras.py --gpus 1 --what gemm,ll
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench_extras.py --gpus 8 --what all
+
+All multi-GPU numbers are device times (CUDA events behind a GPU spin that hides launch latency), max over ranks.
+"""
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from deepep_ascend_b200 import ElasticBuffer
+from deepep_ascend_b200.utils import gate
+from deepep_ascend_b200.utils.testing import flush_l2_cache
+
+SLEEP = 6_000_000
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument('--gpus', type=int, default=1)
+    p.add_argument('--what', default='all')
+    p.add_argument('--iters', type=int, default=20)
+    args = p.parse_args()
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    lr = int(os.environ.get('LOCAL_RANK', '0'))
+    assert world == args.gpus
+    torch.cuda.set_device(lr)
+    group = None
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', lr))
+        group = dist.new_group(list(range(world)))
+    what = set(args.what.split(','))
+    want = lambda k: 'all' in what or k in what
+
+    def emit(**kw):
+        if rank == 0:
+            print(json.dumps(kw), flush=True)
+
+    def reduce_max(ts):
+        t = torch.tensor(ts, dtype=torch.float64, device='cuda')
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return t.cpu().numpy()
+
+    def timeit(fn, buf=None, iters=args.iters, warm=3, flush=True):
+        evs = []
+        for i in range(warm + iters):
+            if flush:
+                flush_l2_cache()
+            if buf is not None and world > 1:
+                buf.barrier(use_comm_stream=False)
+            torch.cuda._sleep(SLEEP)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            if i >= warm:
+                evs.append((a, b))
+        torch.cuda.synchronize()
+        return reduce_max([a.elapsed_time(b) for a, b in evs])
+
+    # ------------------------------------------------------------------ plain tcgen05 GEMM (single GPU view)
+    if want('gemm'):
+        from deepep_ascend_b200.ops import gemm as G
+        for (M, N, K) in [(8192, 7168, 7168), (8192, 4096, 7168)]:
+            a = torch.randn(M, K, device='cuda').bfloat16()
+            b = torch.randn(N, K, device='cuda').bfloat16()
+            t = timeit(lambda: G.gemm_nt(a, b), flush=False)
+            t_ref = timeit(lambda: torch.matmul(a, b.t()), flush=False)
+            emit(bench='gemm_bf16_tcgen05', M=M, N=N, K=K, ms=float(np.median(t)), tflops=2 * M * N * K / np.median(t) / 1e9,
+                 cublas_ms=float(np.median(t_ref)), cublas_tflops=2 * M * N * K / np.median(t_ref) / 1e9)
+
+    T, H, E, K = 8192, 7168, 256, 8
+    # ------------------------------------------------------------------ dispatch / combine phase breakdown + variants
+    if want('phases'):
+        buf = ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=True, num_gpu_timeout_secs=20)
+        gen = torch.Generator().manual_seed(1234 + rank)
+        x = torch.randn(T, H, generator=gen).bfloat16().cuda()
+        w, idx = torch.softmax(torch.randn(T, E, generator=gen), -1).topk(K, -1)
+        w, idx = w.cuda(), idx.cuda()
+        st = {}
+
+        def disp(sms, **kw):
+            def f():
+                st['h'] = buf.dispatch(x, idx, w, num_experts=E, num_sms=sms, do_cpu_sync=False, **kw)[3]
+            return f
+        disp(64)()
+        torch.cuda.synchronize()
+        rows = float(st['h'].psum_num_recv_tokens_per_scaleup_rank[-1])
+        for sms in (24, 64):
+            t = np.median(timeit(disp(sms), buf))
+            emit(bench='dispatch', num_sms=sms, ms=float(t), gbs=rows * 7488 / t / 1e6)
+            buf.enable_profiling(True)
+            disp(sms)()
+            buf.combine(buf.get_combine_buffer(st['h']), st['h'], num_sms=sms)
+            emit(bench='phase_times_us', num_sms=sms, **buf.phase_times())
+            os.environ['EP_PROFILE_SKIP_SIDE_STORES'] = '1'
+            t2 = np.median(timeit(disp(sms), buf))
+            os.environ['EP_PROFILE_SKIP_SIDE_STORES'] = '0'
+            buf.enable_profiling(False)
+            emit(bench='dispatch_without_side_stores', num_sms=sms, ms=float(t2), gbs=rows * 7488 / t2 / 1e6)
+            h0 = st['h']
+            t3 = np.median(timeit(lambda: buf.dispatch(x, handle=h0, topk_weights=w, num_sms=sms), buf))
+            emit(bench='dispatch_cached_layout', num_sms=sms, ms=float(t3), gbs=rows * 7488 / t3 / 1e6)
+            q = buf._C.per_token_cast_to_fp8(x, False, False)
+            t4 = np.median(timeit(lambda: buf.dispatch((q[0], q[1]), idx, w, num_experts=E, num_sms=sms, do_cpu_sync=False), buf))
+            emit(bench='dispatch_prequantized_fp8', num_sms=sms, ms=float(t4), gbs=rows * 7488 / t4 / 1e6)
+            t5 = np.median(timeit(lambda: buf.combine(buf.get_combine_buffer(st['h']), st['h'], num_sms=sms), buf))
+            emit(bench='combine', num_sms=sms, ms=float(t5), gbs=rows * 14368 / t5 / 1e6)
+        buf.destroy()
+
+    # ------------------------------------------------------------------ NCCL all_to_all_single baseline (same bytes)
+    if want('nccl') and world > 1:
+        from deepep_ascend_b200.utils import refs
+        gen = torch.Generator().manual_seed(1234 + rank)
+        x = torch.randn(T, H, generator=gen).bfloat16().cuda()
+        w, idx = torch.softmax(torch.randn(T, E, generator=gen), -1).topk(K, -1)
+        w, idx = w.cuda(), idx.cuda()
+        q = torch.empty(T, H, device='cuda', dtype=torch.float8_e4m3fn)
+        sf = torch.rand(T, H // 128, device='cuda')
+        out = refs.dispatch_nccl((q, sf), idx, w, T, E, group)
+        rows = float(out[0][0].shape[0])
+        t = np.median(timeit(lambda: refs.dispatch_nccl((q, sf), idx, w, T, E, group)))
+        emit(bench='nccl_all_to_all_dispatch_baseline', ms=float(t), gbs=rows * 7488 / t / 1e6, note='torch gather + 6 all_to_all_single calls')
+        send = torch.empty(int(rows), H, device='cuda', dtype=torch.bfloat16)
+        recv = torch.empty_like(send)
+        splits = [int(rows) // world] * world
+        splits[-1] += int(rows) - sum(splits)
+        t = np.median(timeit(lambda: dist.all_to_all_single(recv, send, splits, splits, group=group)))
+        emit(bench='nccl_all_to_all_single_bf16_rows', ms=float(t), gbs=rows * H * 2 / t / 1e6)
+
+    # ------------------------------------------------------------------ low-latency decode in a CUDA graph
+    if want('ll'):
+        M, Tll = 128, 128
+        extra = ElasticBuffer.get_low_latency_size_hint(M, H, world, E, K)
+        buf = ElasticBuffer(group, num_max_tokens_per_rank=M, hidden=H, num_topk=K, extra_bytes=extra, num_gpu_timeout_secs=20)
+        gen = torch.Generator().manual_seed(77 + rank)
+        x = torch.randn(Tll, H, generator=gen).bfloat16().cuda()
+        idx = torch.rand(Tll, E, generator=gen).topk(K, -1).indices.cuda()     # uniform random logits
+        w = torch.rand(Tll, K, generator=gen).cuda()
+        El = E // world
+        y = torch.randn(El, world * M, H, device='cuda').bfloat16()
+        cur = torch.cuda.current_stream()
+        for sms in (32, 64, 132):
+            def d():
+                return buf.low_latency_dispatch(x, idx, M, E, use_fp8=True, return_recv_hook=True, num_sms=sms)
+            def run_pair():
+                recv, cnt, handle, _, hook = d()
+                hook()
+                out, _, hook2 = buf.low_latency_combine(y, idx, w, handle, return_recv_hook=True, num_sms=sms)
+                hook2()
+                return handle
+            handle = run_pair()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier(group=group)
+            # one graph holds a dispatch, another a combine, so that each can be timed by itself
+            gd, gc = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(gd, stream=side):
+                    recv, cnt, handle, _, hook = d()
+                    hook()
+                with torch.cuda.graph(gc, stream=side):
+                    out, _, hook2 = buf.low_latency_combine(y, idx, w, handle, return_recv_hook=True, num_sms=sms)
+                    hook2()
+            torch.cuda.synchronize()
+            td, tc = [], []
+            for i in range(5 + 100):
+                if world > 1:
+                    buf.barrier(use_comm_stream=False)
+                torch.cuda._sleep(1_000_000)
+                e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+                e[0].record()
+                gd.replay()
+                e[1].record()
+                gc.replay()
+                e[2].record()
+                if i >= 5:
+                    td.append((e[0], e[1]))
+                    tc.append((e[1], e[2]))
+            torch.cuda.synchronize()
+            td = reduce_max([a.elapsed_time(b) * 1e3 for a, b in td])
+            tc = reduce_max([a.elapsed_time(b) * 1e3 for a, b in tc])
+            emit(bench='low_latency_cuda_graph', num_sms=sms, tokens=Tll, dispatch_p50_us=float(np.percentile(td, 50)),
+                 dispatch_p99_us=float(np.percentile(td, 99)), combine_p50_us=float(np.percentile(tc, 50)),
+                 combine_p99_us=float(np.percentile(tc, 99)), reference='77 / 114 us (H800 + CX7 RDMA, published)')
+            buf.check_status()
+        buf.destroy()
+
+    # ------------------------------------------------------------------ fused MoE layer forward + backward
+    if want('moe'):
+        from deepep_ascend_b200.models.moe import FusedMoE
+        Tm, I = 4096, 2048
+        buf = ElasticBuffer(group, num_max_tokens_per_rank=Tm, hidden=H, num_topk=K, enable_expand=True, num_experts=E,
+                            expert_alignment=128, num_gpu_timeout_secs=30)
+        layer = FusedMoE(buf, E, H, I, init_std=0.02, num_sms=64)
+        gen = torch.Generator().manual_seed(5 + rank)
+        x = torch.randn(Tm, H, generator=gen).bfloat16().cuda().requires_grad_(True)
+        w, idx = torch.softmax(torch.randn(Tm, E, generator=gen), -1).topk(K, -1)
+        w, idx = w.cuda().requires_grad_(True), idx.cuda()
+        g = torch.randn(Tm, H, device='cuda').bfloat16()
+
+        def fwd():
+            return layer(x, idx, w)
+
+        def fwd_bwd():
+            layer(x, idx, w).backward(g)
+        tf = np.median(timeit(fwd, buf, iters=5, warm=2))
+        tfb = np.median(timeit(fwd_bwd, buf, iters=5, warm=2))
+        rows = float(idx.numel())
+        flops_fwd = rows * (2 * H * 2 * I + 2 * I * H)
+        emit(bench='fused_moe_layer', tokens_per_rank=Tm, hidden=H, intermediate=I, fwd_ms=float(tf), fwd_bwd_ms=float(tfb),
+             fwd_expert_tflops_per_gpu=flops_fwd / tf / 1e9, note='includes the host sync of dispatch (exact sizes)')
+        buf.destroy()
+
+    # ------------------------------------------------------------------ Zipf-skewed routing
+    if want('zipf'):
+        Tz, Hz, Ez, Kz = 4096, 4096, 64, 6
+        buf = ElasticBuffer(group, num_max_tokens_per_rank=Tz, hidden=Hz, num_topk=Kz, num_gpu_timeout_secs=20)
+        x = torch.randn(Tz, Hz, device='cuda').bfloat16()
+        scores = gate.get_zipf_scores(Tz, Ez, 1.2, device='cuda')
+        w, idx = torch.softmax(scores, -1).topk(Kz, -1)
+        st = {}
+
+        def dz():
+            st['h'] = buf.dispatch(x, idx, w.contiguous(), num_experts=Ez, num_sms=64, do_cpu_sync=False)[3]
+        dz()
+        torch.cuda.synchronize()
+        rows = torch.tensor([float(st['h'].psum_num_recv_tokens_per_scaleup_rank[-1])], device='cuda')
+        rows_max = rows.clone()
+        if world > 1:
+            dist.all_reduce(rows_max, op=dist.ReduceOp.MAX, group=group)
+        td = np.median(timeit(dz, buf))
+        tc = np.median(timeit(lambda: buf.combine(buf.get_combine_buffer(st['h']), st['h'], num_sms=64), buf))
+        row_d, row_c = Hz * 2 + Kz * 12, Hz * 2 + Kz * 4
+        emit(bench='zipf_routing_bf16', s=1.2, experts=Ez, topk=Kz, hidden=Hz, hottest_rank_rows=float(rows_max), dispatch_ms=float(td),
+             combine_ms=float(tc), dispatch_gbs_hottest=float(rows_max) * row_d / td / 1e6, combine_gbs_hottest=float(rows_max) * row_c / tc / 1e6)
+        buf.destroy()
+
+    # ------------------------------------------------------------------ fused tensor-parallel GEMMs
+    if want('tp') and world > 1:
+        from deepep_ascend_b200.parallel.tp import TensorParallelGemm
+        M, Kt, N = 8192, 7168, 7168
+        buf = ElasticBuffer(group, num_max_tokens_per_rank=16, hidden=256, num_topk=2, extra_bytes=TensorParallelGemm.size_hint(M, Kt, N),
+                            num_gpu_timeout_secs=20)
+        tp = TensorParallelGemm(buf, M, Kt, N, num_copy_ctas=16)
+        xs = torch.randn(M // world, Kt, device='cuda').bfloat16()
+        w_col = torch.randn(N // world, Kt, device='cuda').bfloat16()          # column-parallel weight
+        t = np.median(timeit(lambda: tp.ag_gemm(xs, w_col), buf, iters=10))
+        emit(bench='ag_gemm_fused', M=M, K=Kt, N_local=N // world, ms=float(t), tflops_per_gpu=2 * M * Kt * (N // world) / t / 1e9,
+             nvlink_gbs_in=(world - 1) / world * M * Kt * 2 / t / 1e6)
+        xk = torch.randn(M, Kt // world, device='cuda').bfloat16()             # row-parallel: K is sharded
+        w_row = torch.randn(N, Kt // world, device='cuda').bfloat16()
+        t = np.median(timeit(lambda: tp.gemm_rs(xk, w_row), buf, iters=10))
+        emit(bench='gemm_rs_fused', M=M, K_local=Kt // world, N=N, ms=float(t), tflops_per_gpu=2 * M * (Kt // world) * N / t / 1e9,
+             nvlink_gbs_out=(world - 1) / world * M * N * 2 / t / 1e6)
+        # unfused baseline: NCCL all-gather then cuBLAS, cuBLAS then NCCL reduce-scatter
+        full = torch.empty(M, Kt, device='cuda', dtype=torch.bfloat16)
+        t = np.median(timeit(lambda: (dist.all_gather_into_tensor(full, xs, group=group), torch.matmul(full, w_col.t())), buf, iters=10))
+        emit(bench='ag_gemm_nccl_cublas_baseline', ms=float(t))
+        outrs = torch.empty(M // world, N, device='cuda', dtype=torch.bfloat16)
+        t = np.median(timeit(lambda: dist.reduce_scatter_tensor(outrs, torch.matmul(xk, w_row.t()), group=group), buf, iters=10))
+        emit(bench='gemm_rs_nccl_cublas_baseline', ms=float(t))
+        buf.check_status()
+        emit(bench='gemm_error_flag', value=buf._C.gemm_error(lr))
+        buf.destroy()
+
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

@@ -31,6 +31,7 @@ struct DispatchSmemPlan {
     int off_tot;        // uint32 [E]   expert totals over sources
     int off_before;     // uint32 [E]   selections from lower source ranks
     int off_start;      // uint32 [E]   first row of each expert at its rank
+    int off_prefix;     // uint32 [R]   rows of lower ranks / CTAs per destination
     int off_wc_rank;    // uint32 [W][R]
     int off_wc_expert;  // uint32 [W][E]
     int off_bar;        // uint64 [W][3]
@@ -51,6 +52,7 @@ __host__ __device__ inline DispatchSmemPlan make_smem_plan(const DispatchArgs& a
     p.off_tot = off;        off += align_int(E * 4, 16);
     p.off_before = off;     off += align_int(E * 4, 16);
     p.off_start = off;      off += align_int(E * 4, 16);
+    p.off_prefix = off;     off += EP_MAX_RANKS * 4;
     p.off_wc_rank = off;    off += align_int(num_warps * R * 4, 16);
     p.off_wc_expert = off;  off += align_int(num_warps * E * 4, 16);
     p.off_bar = off;        off += num_warps * 3 * 8;
@@ -235,6 +237,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
     uint32_t* s_tot = reinterpret_cast<uint32_t*>(smem + sp.off_tot);
     uint32_t* s_before = reinterpret_cast<uint32_t*>(smem + sp.off_before);
     uint32_t* s_start = reinterpret_cast<uint32_t*>(smem + sp.off_start);
+    uint32_t* s_prefix = reinterpret_cast<uint32_t*>(smem + sp.off_prefix);
     uint32_t* s_wc_rank = reinterpret_cast<uint32_t*>(smem + sp.off_wc_rank);
     uint32_t* s_wc_expert = reinterpret_cast<uint32_t*>(smem + sp.off_wc_expert);
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + sp.off_bar) + warp * 3;
@@ -317,15 +320,24 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
 
         // ---------------------------------------------------------------- 3. assign: counts -> first rows
         if (alive) {
-            if (!a.do_expand && tid < R) {
-                const int d = tid;
-                uint32_t running = 0;
-                for (int s = 0; s < me; ++s) running += count_of(ptx::ld_relaxed_sys(&ws->disp_rank_count[s][d]));
-                for (int c = 0; c < cta; ++c) running += __ldcg(&ws->cta_rank_count[c][d]);
-                for (int w = 0; w < num_warps; ++w) {
-                    const uint32_t n = s_wc_rank[w * R + d];
-                    s_wc_rank[w * R + d] = running;
-                    running += n;
+            const uint32_t A = max(1, a.expert_alignment);
+            if (tid < R) s_prefix[tid] = 0;
+            __syncthreads();
+            if (!a.do_expand) {
+                // rows of lower source ranks and of lower CTAs of this rank, summed by all threads in parallel
+                for (int p = tid; p < (me + cta) * R; p += nthreads) {
+                    const int d = p % R, i = p / R;
+                    const uint32_t n = i < me ? count_of(ptx::ld_relaxed_sys(&ws->disp_rank_count[i][d])) : __ldcg(&ws->cta_rank_count[i - me][d]);
+                    if (n) atomicAdd(&s_prefix[d], n);
+                }
+                __syncthreads();
+                if (tid < R) {
+                    uint32_t running = s_prefix[tid];
+                    for (int w = 0; w < num_warps; ++w) {
+                        const uint32_t n = s_wc_rank[w * R + tid];
+                        s_wc_rank[w * R + tid] = running;
+                        running += n;
+                    }
                 }
             }
             if (need_experts) {
@@ -340,20 +352,34 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                     s_before[e] = before;
                 }
                 __syncthreads();
-                if (tid < R) {
-                    const uint32_t A = max(1, a.expert_alignment);
-                    uint32_t end = 0;
-                    for (int j = 0; j < El; ++j) {
-                        const uint32_t start = (end + A - 1) / A * A;
-                        s_start[tid * El + j] = start;
-                        end = start + s_tot[tid * El + j];
+                // first row of every expert at its rank = exclusive prefix sum of the aligned totals of that rank
+                // (every segment start is a multiple of the alignment); one warp scans one rank
+                for (int d = warp; d < R; d += num_warps) {
+                    uint32_t carry = 0;
+                    for (int base = 0; base < El; base += 32) {
+                        const int j = base + lane;
+                        const uint32_t al = j < El ? (s_tot[d * El + j] + A - 1) / A * A : 0;
+                        uint32_t incl = al;
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+                            if (lane >= o) incl += up;
+                        }
+                        if (j < El) s_start[d * El + j] = carry + incl - al;
+                        carry += __shfl_sync(0xffffffffu, incl, 31);
+                    }
+                }
+                if (a.do_expand) {
+                    // selections of lower CTAs of this rank
+                    for (int p = tid; p < cta * E; p += nthreads) {
+                        const uint32_t n = __ldcg(&ws->cta_expert_count[p / E][p % E]);
+                        if (n) atomicAdd(&s_before[p % E], n);
                     }
                 }
                 __syncthreads();
                 if (a.do_expand) {
                     for (int e = tid; e < E; e += nthreads) {
                         uint32_t running = s_start[e] + s_before[e];
-                        for (int c = 0; c < cta; ++c) running += __ldcg(&ws->cta_expert_count[c][e]);
                         for (int w = 0; w < num_warps; ++w) {
                             const uint32_t n = s_wc_expert[w * E + e];
                             s_wc_expert[w * E + e] = running;
@@ -362,12 +388,13 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                     }
                 }
                 if (cta == 0) {
-                    // what this rank receives: handle tensors + host-visible counters
+                    // what this rank receives: handle tensors + host-visible counters (each word carries its own
+                    // epoch tag, so the host needs no ordering between them)
                     volatile uint64_t* st = ctx.status;
-                    const uint32_t A = max(1, a.expert_alignment);
                     for (int j = tid; j < El; j += nthreads) {
-                        const uint32_t n = s_tot[me * El + j];
+                        const uint32_t n = s_tot[me * El + j], start = s_start[me * El + j];
                         a.recv_per_expert[j] = n;
+                        a.psum_expert[j] = a.do_expand ? start + n : start + (n + A - 1) / A * A;
                         if (a.stats != nullptr) a.stats[j] += n;
                         st[EP_STATUS_EXPERT_BASE + j] = tag_value(epoch, n);
                     }
@@ -377,20 +404,10 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                             psum += count_of(ptx::ld_relaxed_sys(&ws->disp_rank_count[s][me]));
                             a.psum_rank[s] = psum;
                         }
-                        uint32_t acc = 0, end = 0;
-                        for (int j = 0; j < El; ++j) {
-                            const uint32_t n = s_tot[me * El + j];
-                            if (a.do_expand) {
-                                end = s_start[me * El + j] + n;
-                                a.psum_expert[j] = end;
-                            } else {
-                                acc += (n + A - 1) / A * A;
-                                a.psum_expert[j] = acc;
-                            }
-                        }
-                        st[EP_STATUS_NUM_EXPANDED] = tag_value(epoch, a.do_expand ? (end + A - 1) / A * A : 0);
+                        const uint32_t last = me * El + El - 1;
+                        const uint32_t expanded = s_start[last] + (s_tot[last] + A - 1) / A * A;
+                        st[EP_STATUS_NUM_EXPANDED] = tag_value(epoch, a.do_expand ? expanded : 0);
                         st[EP_STATUS_NUM_RECV] = tag_value(epoch, psum);
-                        __threadfence_system();
                     }
                 }
             }
