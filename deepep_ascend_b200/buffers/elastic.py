@@ -102,7 +102,7 @@ class _DispatchState:
     """Book-keeping between the three steps of a dispatch (prepare -> launch -> finish)."""
     __slots__ = ('call', 'T', 'H', 'K', 'E', 'fp8_out', 'do_expand', 'alignment', 'slot_idx', 'slot', 'handle_tensors',
                  'topk_idx', 'topk_weights', 'do_cpu_sync', 'num_sms', 'col_major_sf', 'cached_handle', 'x_dtype',
-                 'keep_alive', 'do_handle_copy')
+                 'keep_alive', 'do_handle_copy', 'side')
 
 
 class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
@@ -428,6 +428,19 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         G = (H + 127) // 128
         call.sf_stride_row, call.sf_stride_col = (1, cap) if col_major_sf else (G, 1)
         call.recv_capacity_rows = cap
+        side = None
+        if not do_expand and not col_major_sf and os.environ.get('EP_DISABLE_PACKED_SIDE', '0') != '1':
+            # scales, expert ids, weights and source ids of a row travel as one packed record
+            sf_bytes = G * 4 if fp8_out else 0
+            off_idx = align(sf_bytes, 8)
+            off_w = off_idx + K * idx.element_size()
+            off_meta = align(off_w + K * 4, 8)
+            side_bytes = align(off_meta + 8, 16)
+            assert side_bytes <= self.regions.side_bytes, 'side record larger than the buffer was sized for'
+            call.side_packed = True
+            call.side_bytes, call.side_off_idx, call.side_off_w, call.side_off_meta = side_bytes, off_idx, off_w, off_meta
+            call.off_recv_side = slot.side
+            side = (side_bytes, off_idx, off_w, off_meta)
         if self.profile is not None:
             call.prof = self.profile['dispatch']
             call.skip_side_stores = bool(int(os.environ.get('EP_PROFILE_SKIP_SIDE_STORES', '0')))
@@ -441,6 +454,7 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         st.cached_handle = handle
         st.x_dtype = x_in.dtype
         st.do_handle_copy = do_handle_copy
+        st.side = side
         return st
 
     def _finish_dispatch(self, st: _DispatchState, do_zero_padding: bool = False):
@@ -462,16 +476,26 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         G = (H + 127) // 128
         x_dtype = torch.float8_e4m3fn if st.fp8_out else torch.bfloat16
         recv_x = core.view(st.slot.x, [rows, H], [H, 1], x_dtype)
-        recv_sf = None
-        if st.fp8_out:
-            strides = [1, cap] if st.col_major_sf else [G, 1]
-            recv_sf = core.view(st.slot.sf, [rows, G], strides, torch.float32)
-        recv_idx = None if st.do_expand else core.view(st.slot.idx, [rows, K], [K, 1], st.topk_idx.dtype)
-        recv_w = None
-        if st.topk_weights is not None:
-            recv_w = core.view(st.slot.w, [rows], [1], torch.float32) if st.do_expand else \
-                core.view(st.slot.w, [rows, K], [K, 1], torch.float32)
-        meta = core.view(st.slot.meta, [rows, 2], [2, 1], torch.int32)
+        recv_sf = recv_w = None
+        if st.side is not None:
+            # strided views over the packed side records
+            side_bytes, off_idx, off_w, off_meta = st.side
+            if st.fp8_out:
+                recv_sf = core.view(st.slot.side, [rows, G], [side_bytes // 4, 1], torch.float32)
+            isz = st.topk_idx.element_size()
+            recv_idx = core.view(st.slot.side + off_idx, [rows, K], [side_bytes // isz, 1], st.topk_idx.dtype)
+            if st.topk_weights is not None:
+                recv_w = core.view(st.slot.side + off_w, [rows, K], [side_bytes // 4, 1], torch.float32)
+            meta = core.view(st.slot.side + off_meta, [rows, 2], [side_bytes // 4, 1], torch.int32)
+        else:
+            if st.fp8_out:
+                strides = [1, cap] if st.col_major_sf else [G, 1]
+                recv_sf = core.view(st.slot.sf, [rows, G], strides, torch.float32)
+            recv_idx = None if st.do_expand else core.view(st.slot.idx, [rows, K], [K, 1], st.topk_idx.dtype)
+            if st.topk_weights is not None:
+                recv_w = core.view(st.slot.w, [rows], [1], torch.float32) if st.do_expand else \
+                    core.view(st.slot.w, [rows, K], [K, 1], torch.float32)
+            meta = core.view(st.slot.meta, [rows, 2], [2, 1], torch.int32)
         if do_zero_padding and st.do_expand and st.cached_handle is None:
             self._zero_padding(recv_x, st.call.psum_expert, st.alignment, rows)
         if not self.zero_copy:

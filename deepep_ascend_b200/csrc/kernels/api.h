@@ -98,6 +98,11 @@ struct DispatchArgs {
     int64_t sf_stride_row, sf_stride_col;   // element strides of the receiver's scale tensor
     int recv_capacity_rows;
     uint64_t* prof;                // optional [8] phase timestamps (ns) written by CTA 0, or null
+    // packed side records (non-expand layout, row-major scales): {scales | global expert ids | weights | source id}
+    // travel as ONE extra bulk store per destination row; the receiver localises the ids after the final barrier
+    int side_packed;
+    int side_bytes, side_off_idx, side_off_w, side_off_meta;
+    uint64_t off_recv_side;
     int skip_side_stores;          // profiling only: leave out the per-row scale / index / weight / metadata stores
 };
 

@@ -22,6 +22,7 @@ namespace {
 constexpr int kCombineMaxWarps = 16;
 constexpr int kCombineMaxRing = 32;              // chunk buffers (and mbarriers) per warp
 constexpr int kCombineSmemBudget = 208 * 1024;
+constexpr int kCombineQueue = 64;                // claimed-token queue per warp (producer -> consumer)
 
 template <int kUnroll>
 struct CombineCfg {
@@ -30,13 +31,14 @@ struct CombineCfg {
 
 // Shared-memory plan: [peer table | mbarriers W x ring | chunk buffers W x ring]
 struct CombineSmemPlan {
-    int num_warps, ring, off_bar, off_data, total;
+    int num_warps, ring, off_bar, off_queue, off_data, total;
 };
 __host__ __device__ inline CombineSmemPlan combine_smem_plan(int chunk_bytes, int num_warps) {
     CombineSmemPlan p;
     p.num_warps = num_warps;
     p.off_bar = 128;
-    p.off_data = 128 + num_warps * kCombineMaxRing * 8;
+    p.off_queue = 128 + num_warps * kCombineMaxRing * 8;
+    p.off_data = p.off_queue + num_warps * kCombineQueue * 4;
     p.off_data = (p.off_data + 1023) / 1024 * 1024;
     int ring = (kCombineSmemBudget - p.off_data) / (num_warps * chunk_bytes);
     p.ring = ring > kCombineMaxRing ? kCombineMaxRing : ring;
@@ -71,6 +73,8 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
     uint8_t** s_peer = reinterpret_cast<uint8_t**>(smem);
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + sp.off_bar) + warp * kCombineMaxRing;
     uint8_t* s_data = smem + sp.off_data + static_cast<size_t>(warp) * ring * kChunk;
+    int* s_queue = reinterpret_cast<int*>(smem + sp.off_queue) + warp * kCombineQueue;
+    if (blockIdx.x == 0 && tid == 0) atomicExch(&ws->dyn_counter[EP_CH_COMBINE], 0u);   // ordered before its first use by the grid barrier
 
     if (tid < EP_MAX_RANKS) s_peer[tid] = tid < ctx.num_ranks ? ctx.peer_base[tid] : nullptr;
     if (lane == 0)
@@ -89,11 +93,20 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
     alive = grid_sync(ctx, ws, EP_CH_COMBINE, EP_PH_GRID_SYNC) && alive;
     stamp(1);
 
-    // a warp owns tokens first, first + stride, ... and walks the column chunks of each token in order, so the
-    // plan row of a token is read once
-    const int stride = static_cast<int>(gridDim.x) * num_warps;
-    const int first = static_cast<int>(blockIdx.x) * num_warps + warp;
-
+    // Tokens are claimed dynamically from a counter shared by all CTAs of this rank (SMs that get a smaller share of
+    // the NVLink bandwidth claim fewer tokens, so no CTA is left with a tail).  The producer cursor claims; the
+    // claimed ids travel through a small per-warp queue to the consumer cursor, which follows in the same order.
+    uint32_t claimed = 0, started = 0;     // tokens claimed by the producer / started by the consumer
+    auto claim_token = [&]() -> int {
+        int tkn = 0;
+        if (lane == 0) {
+            tkn = static_cast<int>(atomicAdd(&ws->dyn_counter[EP_CH_COMBINE], 1u));
+            s_queue[claimed % kCombineQueue] = tkn;
+        }
+        __syncwarp();
+        ++claimed;
+        return __shfl_sync(0xffffffffu, tkn, 0);
+    };
     auto load_token = [&](PullCursor& c) {
         c.chunk = 0;
         c.plan_k = -1;
@@ -104,26 +117,32 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
         }
         c.pending = c.sources;
     };
-    auto next_chunk = [&](PullCursor& c) {
-        if (++c.chunk == num_chunks) {
-            c.token += stride;
-            load_token(c);
-        } else {
-            c.pending = c.sources;
-        }
+    // producer: move to its next token (claims one); returns false when the queue is too full to claim right now
+    auto producer_next_token = [&](PullCursor& c) -> bool {
+        if (claimed - started >= static_cast<uint32_t>(kCombineQueue - 8)) return false;
+        c.token = c.token < T ? claim_token() : T;
+        load_token(c);
+        return true;
     };
 
     if (alive) {
-        PullCursor prod{first, 0, -1, 0, 0}, cons{first, 0, -1, 0, 0};
+        PullCursor prod{0, 0, -1, 0, 0}, cons{0, 0, -1, 0, 0};
+        prod.token = claim_token();
         load_token(prod);
-        load_token(cons);
         uint32_t issued = 0, consumed = 0;   // loads issued / consumed by this warp; buffer = counter % ring
 
         // issue loads in sequence order until the ring is full or the warp's work is exhausted
         auto issue_ahead = [&]() {
             while (issued - consumed < static_cast<uint32_t>(ring) && prod.token < T) {
                 if (prod.pending == 0) {
-                    next_chunk(prod);
+                    if (++prod.chunk == num_chunks) {
+                        if (!producer_next_token(prod)) {
+                            prod.chunk = num_chunks - 1;   // retry the claim on the next call
+                            break;
+                        }
+                    } else {
+                        prod.pending = prod.sources;
+                    }
                     continue;
                 }
                 const int k = __ffs(prod.pending) - 1;
@@ -142,7 +161,19 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
             }
         };
 
-        for (; cons.token < T && alive; next_chunk(cons)) {
+        // consumer: pop the next claimed token (making the producer claim one if it has not run ahead)
+        auto consumer_next_token = [&](PullCursor& c) {
+            if (started == claimed) {
+                // the producer has consumed all its claims too: it sits at the end of its current token
+                prod.token = prod.token < T ? claim_token() : T;
+                load_token(prod);
+            }
+            c.token = s_queue[started % kCombineQueue];
+            ++started;
+            load_token(c);
+        };
+        consumer_next_token(cons);
+        for (; cons.token < T && alive;) {
             const int t = cons.token, c = cons.chunk;
             const int bytes = min(kChunk, row_bytes - c * kChunk);
             const int col0 = c * kChunk;   // byte offset inside the row
@@ -228,6 +259,8 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
                     ptx::st_na_v4(out + off, raw);
                 }
             }
+            if (++cons.chunk == num_chunks) consumer_next_token(cons);
+            else cons.pending = cons.sources;
         }
         // loads still in flight belong to nobody once the loop was left early: wait for them (bounded) so that
         // no copy lands in shared memory after the CTA has exited

@@ -27,7 +27,8 @@ struct Workspace {
     uint64_t epoch[EP_NUM_CHANNELS];      // completed calls per channel
     uint64_t bar_seq[EP_NUM_CHANNELS];    // cross-GPU barriers executed per channel
     uint32_t abort_flag;
-    uint32_t pad0[31];
+    uint32_t dyn_counter[EP_NUM_CHANNELS];   // next unclaimed work item of the running kernel (dynamic scheduling)
+    uint32_t pad0[31 - EP_NUM_CHANNELS];
     // ---- written by peers over NVLink
     alignas(128) uint64_t xbar[EP_NUM_CHANNELS][EP_MAX_RANKS];           // [channel][source]: arrivals
     alignas(128) uint64_t disp_rank_count[EP_MAX_RANKS][EP_MAX_RANKS];   // [source][dest], epoch-tagged

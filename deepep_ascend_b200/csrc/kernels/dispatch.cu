@@ -36,6 +36,7 @@ struct DispatchSmemPlan {
     int off_wc_expert;  // uint32 [W][E]
     int off_bar;        // uint64 [W][3]
     int off_sf;         // float  [W][2][G]
+    int off_side;       // bytes  [W][2][side_bytes] packed side records being sent
     int off_stage;      // per warp: stage buffers
     int in_bytes, out_bytes, n_in, n_out, warp_stage_bytes;
     int total;
@@ -55,8 +56,9 @@ __host__ __device__ inline DispatchSmemPlan make_smem_plan(const DispatchArgs& a
     p.off_prefix = off;     off += EP_MAX_RANKS * 4;
     p.off_wc_rank = off;    off += align_int(num_warps * R * 4, 16);
     p.off_wc_expert = off;  off += align_int(num_warps * E * 4, 16);
-    p.off_bar = off;        off += num_warps * 3 * 8;
+    p.off_bar = off;        off += align_int(num_warps * 3 * 8, 16);   // keeps everything behind it 16-byte aligned (bulk copy sources)
     p.off_sf = off;         off += align_int(num_warps * 2 * G * 4, 16);
+    p.off_side = off;       off += a.side_packed ? num_warps * 2 * align_int(a.side_bytes, 16) : 0;
     off = align_int(off, 128);
     p.off_stage = off;
     const int in_row = a.hidden * (a.x_is_fp8 ? 1 : 2);
@@ -242,9 +244,11 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
     uint32_t* s_wc_expert = reinterpret_cast<uint32_t*>(smem + sp.off_wc_expert);
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + sp.off_bar) + warp * 3;
     float* s_sf = reinterpret_cast<float*>(smem + sp.off_sf) + warp * 2 * G;
+    uint8_t* s_side = smem + sp.off_side + warp * 2 * align_int(a.side_bytes, 16);
     uint8_t* s_stage = smem + sp.off_stage + warp * sp.warp_stage_bytes;
 
     const uint64_t epoch = ws->epoch[EP_CH_DISPATCH] + 1;
+    if (cta == 0 && tid == 0) atomicExch(&ws->dyn_counter[EP_CH_DISPATCH], 0u);   // ordered before its first use by a grid barrier
     if (tid < EP_MAX_RANKS) s_peer[tid] = tid < R ? ctx.peer_base[tid] : nullptr;
     if (lane == 0) {
         ptx::mbar_init(&s_bar[0], 1);
@@ -414,6 +418,8 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
             __syncthreads();
             layout_pass<true>(a, sl, s_wc_rank + warp * R, s_wc_expert + warp * E);
         }
+        // every row number is now in global memory: from here on any warp may send any token
+        alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && alive;
     } else {
         // cached layout: only the entry barrier (receivers must be done with the previous contents)
         if (cta == 0) alive = xgpu_barrier(ctx, ws, EP_CH_DISPATCH, EP_PH_XGPU_BARRIER) && alive;
@@ -430,28 +436,45 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
         uint8_t* in_stage = s_stage;
         uint8_t* out_stage = s_stage + sp.n_in * sp.in_bytes;
         const uint8_t* xb = reinterpret_cast<const uint8_t*>(a.x);
-        const int count = sl.end - sl.begin;
         const int S_in = kQuant ? 1 : sp.n_in;
         const int num_batches = ((a.hidden + 255) / 256 + kCastSteps - 1) / kCastSteps;
+        // Tokens are claimed dynamically, two at a time, from a counter shared by all CTAs of this rank: SMs that get
+        // a smaller share of the NVLink bandwidth simply claim fewer tokens, so no CTA is left with a long tail.
+        constexpr int kClaim = 2;
+        auto claim = [&]() -> int {
+            int b = 0;
+            if (lane == 0) b = static_cast<int>(atomicAdd(&ws->dyn_counter[EP_CH_DISPATCH], static_cast<uint32_t>(kClaim)));
+            return __shfl_sync(0xffffffffu, b, 0);
+        };
+        int chunk_base = claim(), next_base = claim(), in_chunk = 0;
+        auto next_token = [&]() -> int {
+            if (in_chunk == kClaim) {
+                chunk_base = next_base;
+                next_base = chunk_base < T ? claim() : T;
+                in_chunk = 0;
+            }
+            const int t = chunk_base + in_chunk++;
+            return t < T ? t : -1;
+        };
+        int t = next_token(), t_next = next_token();
         RowBatch cur;
         if (kQuant) {
-            if (count > 0) load_batch(cur, xb + static_cast<int64_t>(sl.begin) * in_row, a.hidden, 0);
-        } else if (count > 0 && lane == 0) {
+            if (t >= 0) load_batch(cur, xb + static_cast<int64_t>(t) * in_row, a.hidden, 0);
+        } else if (t >= 0 && lane == 0) {
             ptx::mbar_arrive_expect_tx(&s_bar[0], in_row);
-            ptx::bulk_load(in_stage, xb + static_cast<int64_t>(sl.begin) * in_row, in_row, &s_bar[0]);
+            ptx::bulk_load(in_stage, xb + static_cast<int64_t>(t) * in_row, in_row, &s_bar[0]);
         }
-        for (int n = 0; n < count && alive; ++n) {
-            const int t = sl.begin + n;
+        for (int n = 0; t >= 0 && alive; ++n, t = t_next, t_next = next_token()) {
             const int st = n % S_in;
             const uint32_t parity = (n / S_in) & 1;
             if (!kQuant) {
-                // prefetch token n+1; its stage was the source of the bulk stores of token n-2
+                // prefetch the next token; its stage was the source of the bulk stores of token n-2
                 ptx::bulk_wait_read<1>();
                 __syncwarp();
-                if (n + 1 < count && lane == 0) {
+                if (t_next >= 0 && lane == 0) {
                     const int ns = (n + 1) % S_in;
                     ptx::mbar_arrive_expect_tx(&s_bar[ns], in_row);
-                    ptx::bulk_load(in_stage + ns * sp.in_bytes, xb + static_cast<int64_t>(t + 1) * in_row, in_row, &s_bar[ns]);
+                    ptx::bulk_load(in_stage + ns * sp.in_bytes, xb + static_cast<int64_t>(t_next) * in_row, in_row, &s_bar[ns]);
                 }
             }
             int e_k = -1, plan_k = -1;
@@ -461,7 +484,8 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                 plan_k = a.plan[static_cast<int64_t>(t) * K + lane];
                 if (a.topk_weights != nullptr) w_k = __ldg(a.topk_weights + static_cast<int64_t>(t) * K + lane);
             }
-            float* sf_cur = s_sf + (n & 1) * G;
+            uint8_t* side_cur = s_side + (n & 1) * align_int(a.side_bytes, 16);
+            float* sf_cur = a.side_packed ? reinterpret_cast<float*>(side_cur) : s_sf + (n & 1) * G;
             if (!kQuant && has_sf)
                 for (int j = lane; j < G; j += 32) sf_cur[j] = __ldg(a.sf + static_cast<int64_t>(t) * G + j);
             const uint8_t* src_smem;
@@ -474,7 +498,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                 for (int b = 0; b < num_batches; ++b) {
                     RowBatch nxt;
                     if (b + 1 < num_batches) load_batch(nxt, row, a.hidden, b + 1);
-                    else if (n + 1 < count) load_batch(nxt, row + in_row, a.hidden, 0);   // first batch of the next token
+                    else if (t_next >= 0) load_batch(nxt, xb + static_cast<int64_t>(t_next) * in_row, a.hidden, 0);   // first batch of the next token
                     cast_batch(cur, o, sf_cur, a.hidden, b);
                     cur = nxt;
                 }
@@ -487,11 +511,25 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                 src_smem = in_stage + st * sp.in_bytes;
                 __syncwarp();
             }
-            // one bulk store per destination row, issued by the lane that owns the plan entry
+            if (a.side_packed) {
+                // the side record is the same for every destination: scales (already in place), GLOBAL expert ids,
+                // weights and the source token id; the receiver localises the ids after the final barrier
+                if (lane < K) {
+                    if (a.idx_is_64) reinterpret_cast<long long*>(side_cur + a.side_off_idx)[lane] = e_k;
+                    else reinterpret_cast<int*>(side_cur + a.side_off_idx)[lane] = e_k;
+                    reinterpret_cast<float*>(side_cur + a.side_off_w)[lane] = w_k;
+                }
+                if (lane == 0) *reinterpret_cast<int2*>(side_cur + a.side_off_meta) = make_int2(me * a.num_max_tokens + t, 0);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+            }
+            // one bulk store per destination row (two with a side record), issued by the lane that owns the plan entry
             if (plan_k >= 0) {
                 const int d = plan_k >> 24, row = plan_k & 0xffffff;
                 if (row < a.recv_capacity_rows) {
                     ptx::bulk_store(s_peer[d] + a.off_recv_x + static_cast<int64_t>(row) * out_row, src_smem, out_row);
+                    if (a.side_packed)
+                        ptx::bulk_store(s_peer[d] + a.off_recv_side + static_cast<int64_t>(row) * a.side_bytes, side_cur, a.side_bytes);
                 } else {
                     report_failure(ctx, ws, EP_ERR_BOUNDS, EP_PH_DISPATCH_LOAD, d, a.recv_capacity_rows, row);
                     plan_k = -1;
@@ -500,7 +538,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
             ptx::bulk_commit();
             // small per-row pieces go out as plain peer stores
             uint32_t sends = __ballot_sync(0xffffffffu, plan_k >= 0);
-            if (a.skip_side_stores) sends = 0;
+            if (a.skip_side_stores || a.side_packed) sends = 0;
             while (sends) {
                 const int k = __ffs(sends) - 1;
                 sends &= sends - 1;
@@ -546,6 +584,38 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
         if (alive) alive = xgpu_barrier(ctx, ws, EP_CH_DISPATCH, EP_PH_DISPATCH_DONE);
         stamp(6);
         if (tid == 0) ws->epoch[EP_CH_DISPATCH] = epoch;
+    }
+    if (a.side_packed) {
+        // every row has arrived: turn the global expert ids of the received side records into ids relative to this
+        // rank's first expert (-1 for experts of other ranks) and fill in source rank * K + the lane that sent the row
+        alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && alive;
+        if (alive) {
+            const int num_recv = __ldcg(a.psum_rank + (R - 1));
+            const int lo = me * El;
+            for (int row = cta * nthreads + tid; row < num_recv; row += num_ctas * nthreads) {
+                uint8_t* rec = s_peer[me] + a.off_recv_side + static_cast<int64_t>(row) * a.side_bytes;
+                int master = 0;
+                for (int k = 0; k < K; ++k) {
+                    if (a.idx_is_64) {
+                        long long* p = reinterpret_cast<long long*>(rec + a.side_off_idx) + k;
+                        const long long gidx = __ldcg(p);
+                        const bool mine = gidx >= lo && gidx < lo + El;
+                        if (mine) master = k;
+                        *p = mine ? gidx - lo : -1;
+                    } else {
+                        int* p = reinterpret_cast<int*>(rec + a.side_off_idx) + k;
+                        const int gidx = __ldcg(p);
+                        const bool mine = gidx >= lo && gidx < lo + El;
+                        if (mine) master = k;
+                        *p = mine ? gidx - lo : -1;
+                    }
+                }
+                int2* mp = reinterpret_cast<int2*>(rec + a.side_off_meta);
+                int2 m = __ldcg(mp);
+                m.y = (m.x / a.num_max_tokens) * K + master;
+                *mp = m;
+            }
+        }
     }
 }
 

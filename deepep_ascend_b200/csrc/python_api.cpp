@@ -247,11 +247,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readonly("sf", &RecvSlot::sf)
         .def_readonly("idx", &RecvSlot::idx)
         .def_readonly("w", &RecvSlot::w)
-        .def_readonly("meta", &RecvSlot::meta);
+        .def_readonly("meta", &RecvSlot::meta)
+        .def_readonly("side", &RecvSlot::side);
     py::class_<RegionLayout>(m, "RegionLayout")
         .def_readonly("capacity_rows", &RegionLayout::capacity_rows)
         .def_readonly("x_row_bytes", &RegionLayout::x_row_bytes)
         .def_readonly("sf_cols", &RegionLayout::sf_cols)
+        .def_readonly("side_bytes", &RegionLayout::side_bytes)
         .def_readonly("num_recv_slots", &RegionLayout::num_recv_slots)
         .def("slot", [](const RegionLayout& r, int i) {
             TORCH_CHECK(i >= 0 && i < r.num_recv_slots, "slot index out of range");
@@ -291,7 +293,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("sf_stride_col", &DispatchCall::sf_stride_col)
         .def_readwrite("recv_capacity_rows", &DispatchCall::recv_capacity_rows)
         .def_readwrite("prof", &DispatchCall::prof)
-        .def_readwrite("skip_side_stores", &DispatchCall::skip_side_stores);
+        .def_readwrite("skip_side_stores", &DispatchCall::skip_side_stores)
+        .def_readwrite("side_packed", &DispatchCall::side_packed)
+        .def_readwrite("side_bytes", &DispatchCall::side_bytes)
+        .def_readwrite("side_off_idx", &DispatchCall::side_off_idx)
+        .def_readwrite("side_off_w", &DispatchCall::side_off_w)
+        .def_readwrite("side_off_meta", &DispatchCall::side_off_meta)
+        .def_readwrite("off_recv_side", &DispatchCall::off_recv_side);
     py::class_<CombineCall>(m, "CombineCall")
         .def(py::init<>())
         .def_readwrite("off_x", &CombineCall::off_x)

@@ -45,6 +45,8 @@ struct DispatchCall {
     int64_t recv_capacity_rows = 0;
     OptTensor prof;               // int64 [8]: phase timestamps of CTA 0 (profiling)
     bool skip_side_stores = false;
+    bool side_packed = false;
+    int64_t side_bytes = 0, side_off_idx = 0, side_off_w = 0, side_off_meta = 0, off_recv_side = 0;
 };
 
 struct CombineCall {
@@ -362,6 +364,20 @@ private:
             a.prof = reinterpret_cast<uint64_t*>(c.prof->data_ptr<int64_t>());
         }
         a.skip_side_stores = c.skip_side_stores;
+        if (c.side_packed) {
+            TORCH_CHECK(!c.do_expand && c.sf_stride_col == 1, "packed side records need the non-expand layout and row-major scales");
+            TORCH_CHECK(c.side_bytes % 16 == 0 && c.side_off_idx % 8 == 0 && c.side_off_w % 4 == 0 && c.side_off_meta % 8 == 0 &&
+                            c.side_off_idx >= ((c.quantize || fp8) ? G * 4 : 0) && c.side_off_w >= c.side_off_idx + K * (a.idx_is_64 ? 8 : 4) &&
+                            c.side_off_meta >= c.side_off_w + K * 4 && c.side_bytes >= c.side_off_meta + 8,
+                        "inconsistent side record layout");
+            check_region(c.off_recv_side, cap * c.side_bytes, "recv side records");
+            a.side_packed = 1;
+            a.side_bytes = static_cast<int>(c.side_bytes);
+            a.side_off_idx = static_cast<int>(c.side_off_idx);
+            a.side_off_w = static_cast<int>(c.side_off_w);
+            a.side_off_meta = static_cast<int>(c.side_off_meta);
+            a.off_recv_side = c.off_recv_side;
+        }
         return a;
     }
 

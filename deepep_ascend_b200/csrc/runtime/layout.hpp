@@ -41,12 +41,14 @@ struct MoeShape {
 
 struct RecvSlot {
     int64_t x = 0, sf = 0, idx = 0, w = 0, meta = 0;
+    int64_t side = 0;   // packed per-row side records {scales | expert ids | weights | source metadata}
 };
 
 struct RegionLayout {
     int64_t capacity_rows = 0;     // rows a rank can receive in one dispatch
     int64_t x_row_bytes = 0;       // widest row dispatch may write (bf16 unless fp8-only)
     int64_t sf_cols = 0;
+    int64_t side_bytes = 0;        // bytes of one packed side record (multiple of 16)
     int num_recv_slots = 0;
     RecvSlot slots[4];
     int64_t combine_x = 0, combine_w = 0;
@@ -74,6 +76,7 @@ inline RegionLayout plan_regions(const MoeShape& s) {
     r.capacity_rows = recv_capacity_rows(s);
     r.x_row_bytes = s.use_fp8_dispatch ? s.hidden : checked_mul(s.hidden, 2);
     r.sf_cols = (s.hidden + 127) / 128;
+    r.side_bytes = align_up(r.sf_cols * 4 + static_cast<int64_t>(s.num_topk) * 12 + 8, 16);
     r.num_recv_slots = s.num_recv_slots;
     const int64_t A = 1024;
     int64_t off = EP_WORKSPACE_BYTES;
@@ -83,6 +86,7 @@ inline RegionLayout plan_regions(const MoeShape& s) {
         r.slots[i].idx = off;  off = align_up(checked_add(off, checked_mul(r.capacity_rows, s.num_topk * 8)), A);
         r.slots[i].w = off;    off = align_up(checked_add(off, checked_mul(r.capacity_rows, s.num_topk * 4)), A);
         r.slots[i].meta = off; off = align_up(checked_add(off, checked_mul(r.capacity_rows, 8)), A);
+        r.slots[i].side = off; off = align_up(checked_add(off, checked_mul(r.capacity_rows, r.side_bytes)), A);
     }
     r.combine_x = off; off = align_up(checked_add(off, checked_mul(r.capacity_rows, checked_mul(s.hidden, 2))), A);
     r.combine_w = off; off = align_up(checked_add(off, checked_mul(r.capacity_rows, s.num_topk * 4)), A);
