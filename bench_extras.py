@@ -219,6 +219,33 @@ def main():
 
         def fwd_bwd():
             layer(x, idx, w).backward(g)
+        # breakdown of the forward pass
+        from deepep_ascend_b200.ops import gemm as G
+        st = {}
+
+        def d_only():
+            st['o'] = buf.dispatch(x.detach(), idx, w.detach(), num_experts=E, do_expand=True, expert_alignment=G.BLOCK_M,
+                                   fused_fp8_cast=True, num_sms=64)
+        d_only()
+        (rx, rsf), _, rw, hd, _ = st['o']
+        tile_group, valid_row = G.expert_tile_groups(hd.psum_num_recv_tokens_per_expert, hd.num_rows)
+        q13, s13, q2, s2 = layer.fp8_weights()
+        t_disp = np.median(timeit(d_only, buf, iters=5, warm=2))
+        hbuf = {}
+
+        def g1():
+            hbuf['h'] = G.grouped_gemm_nt(rx, q13, tile_group, sfa=rsf, sfb=s13)
+        t_g1 = np.median(timeit(g1, None, iters=5, warm=2))
+
+        def sw():
+            hbuf['a'] = G.swiglu_quant(hbuf['h'], keep_bf16=True)
+        t_sw = np.median(timeit(sw, None, iters=5, warm=2))
+        ybuf = buf.get_combine_buffer(hd)
+        t_g2 = np.median(timeit(lambda: G.grouped_gemm_nt(hbuf['a'][0], q2, tile_group, out=ybuf, sfa=hbuf['a'][1], sfb=s2), None, iters=5, warm=2))
+        t_comb = np.median(timeit(lambda: buf.combine(ybuf, hd, weighted=True, num_sms=64), buf, iters=5, warm=2))
+        emit(bench='fused_moe_forward_breakdown_ms', rows=hd.num_rows, dispatch_expand_fp8=float(t_disp), gemm1_fp8=float(t_g1),
+             swiglu_cast=float(t_sw), gemm2_fp8=float(t_g2), combine_weighted=float(t_comb),
+             gemm1_tflops=2 * hd.num_rows * H * 2 * I / t_g1 / 1e9, gemm2_tflops=2 * hd.num_rows * H * I / t_g2 / 1e9)
         tf = np.median(timeit(fwd, buf, iters=5, warm=2))
         tfb = np.median(timeit(fwd_bwd, buf, iters=5, warm=2))
         rows = float(idx.numel())

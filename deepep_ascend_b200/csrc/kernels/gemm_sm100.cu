@@ -354,36 +354,47 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (!alive) sm->failed = 7;
         asm volatile("bar.sync 1, %0;" ::"r"(kCopyWarps * 32) : "memory");
         if (*reinterpret_cast<volatile int*>(&sm->failed)) alive = false;
+        // work item = one 128-row tile of a remote shard, visited in the order in which the tensor-core CTAs need
+        // them (nearest rank first); each copy warp keeps two row loads in flight
         uint32_t n_loaded = 0;
-        for (int s = 1; s < ctx.num_ranks && alive; ++s) {
-            const int src = (ctx.rank + s) % ctx.num_ranks;
-            for (int j = copier; j < tiles_per_shard && alive; j += g.num_copy_ctas) {
-                const int m_blk = src * tiles_per_shard + j;
-                for (int r = warp; r < kBlockM && alive; r += kCopyWarps) {
-                    const int64_t off = g.off_full + (static_cast<int64_t>(m_blk) * kBlockM + r) * row_bytes;
-                    const int st = n_loaded & 1;
-                    ptx::bulk_wait_read<1>();
-                    __syncwarp();
-                    if (lane == 0) {
-                        ptx::mbar_arrive_expect_tx(&bars[st], row_bytes);
-                        ptx::bulk_load(stage + st * 16384, ctx.peer_base[src] + off, row_bytes, &bars[st]);
-                    }
-                    alive = mbar_wait_bounded(ctx, ws, &bars[st], (n_loaded >> 1) & 1, EP_PH_COMBINE_LOAD);
-                    ++n_loaded;
-                    if (!alive) {
-                        sm->failed = 7;
-                        break;
-                    }
-                    if (lane == 0) ptx::bulk_store(ctx.peer_base[ctx.rank] + off, stage + st * 16384, row_bytes);
-                    ptx::bulk_commit();
+        const int num_items = (ctx.num_ranks - 1) * tiles_per_shard;
+        for (int item = copier; item < num_items && alive; item += g.num_copy_ctas) {
+            const int src = (ctx.rank + 1 + item / tiles_per_shard) % ctx.num_ranks;
+            const int m_blk = src * tiles_per_shard + item % tiles_per_shard;
+            const int my_rows = (kBlockM - warp + kCopyWarps - 1) / kCopyWarps;
+            auto row_offset = [&](int i) { return g.off_full + (static_cast<int64_t>(m_blk) * kBlockM + warp + i * kCopyWarps) * row_bytes; };
+            auto issue_load = [&](int i) {
+                const uint32_t l = n_loaded + i;
+                if (lane == 0) {
+                    ptx::mbar_arrive_expect_tx(&bars[l & 1], row_bytes);
+                    ptx::bulk_load(stage + (l & 1) * 16384, ctx.peer_base[src] + row_offset(i), row_bytes, &bars[l & 1]);
                 }
-                ptx::bulk_wait<0>();
-                __threadfence();
-                // all copy warps of this CTA have finished their rows of the tile -> publish it
-                asm volatile("bar.sync 1, %0;" ::"r"(kCopyWarps * 32) : "memory");
-                if (*reinterpret_cast<volatile int*>(&sm->failed)) alive = false;   // same decision in every copy warp
-                if (warp == 0 && lane == 0 && alive) ptx::st_release_sys(&ws->tile_flags[m_blk], epoch);
+            };
+            ptx::bulk_wait_read<0>();
+            __syncwarp();
+            issue_load(0);
+            for (int i = 0; i < my_rows && alive; ++i) {
+                if (i + 1 < my_rows) {
+                    ptx::bulk_wait_read<0>();   // the other stage was the source of the previous row's store
+                    __syncwarp();
+                    issue_load(i + 1);
+                }
+                const uint32_t l = n_loaded + i;
+                alive = mbar_wait_bounded(ctx, ws, &bars[l & 1], (l >> 1) & 1, EP_PH_COMBINE_LOAD);
+                if (!alive) {
+                    sm->failed = 7;
+                    break;
+                }
+                if (lane == 0) ptx::bulk_store(ctx.peer_base[ctx.rank] + row_offset(i), stage + (l & 1) * 16384, row_bytes);
+                ptx::bulk_commit();
             }
+            n_loaded += my_rows;
+            ptx::bulk_wait<0>();
+            __threadfence();
+            // all copy warps of this CTA have finished their rows of the tile -> publish it
+            asm volatile("bar.sync 1, %0;" ::"r"(kCopyWarps * 32) : "memory");
+            if (*reinterpret_cast<volatile int*>(&sm->failed)) alive = false;   // same decision in every copy warp
+            if (warp == 0 && lane == 0 && alive) ptx::st_release_sys(&ws->tile_flags[m_blk], epoch);
         }
     }
     if (g.fuse == EP_GEMM_FUSE_REDUCE_SCATTER) {

@@ -159,7 +159,10 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
     if (a.phases & EP_LL_RECV) {
         const uint8_t* slab = s_peer[me] + a.off_slab[set];
         const int64_t rows_per_expert = static_cast<int64_t>(R) * M;
-        for (int j = blockIdx.x; j < El && alive; j += gridDim.x) {
+        // work unit = (local expert, source rank): every CTA that works on expert j waits for all its sources' counts
+        // (the packed position of a source's messages is the sum of the counts of the lower sources)
+        for (int p = blockIdx.x; p < El * R && alive; p += gridDim.x) {
+            const int j = p / R, s = p % R;
             __syncthreads();
             int ok = 1;
             if (tid < R) {
@@ -181,7 +184,7 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
                             [&] { return ptx::ld_relaxed_sys(sig); });
                         if (ok) n_recv = count_low32(ptx::ld_relaxed_sys(sig));
                     }
-                    if (a.wait_stats != nullptr && j == static_cast<int>(blockIdx.x))
+                    if (a.wait_stats != nullptr && s == 0)
                         atomicAdd(reinterpret_cast<unsigned long long*>(a.wait_stats + src), globaltimer_ns() - t0);
                 }
                 s_count[src] = n_recv;
@@ -190,40 +193,47 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
             if (!alive) break;
             if (tid == 0) {
                 uint32_t begin = 0;
-                for (int s = 0; s < R; ++s) {
-                    s_begin[s] = begin;
-                    a.layout_range[j * R + s] = (static_cast<int64_t>(begin) << 32) | s_count[s];
-                    begin += s_count[s];
+                for (int q = 0; q < R; ++q) {
+                    s_begin[q] = begin;
+                    begin += s_count[q];
                 }
-                a.packed_count[j] = begin;
-                if (a.stats != nullptr) a.stats[j] += begin;
+                a.layout_range[j * R + s] = (static_cast<int64_t>(s_begin[s]) << 32) | s_count[s];
+                if (s == 0) {
+                    a.packed_count[j] = begin;
+                    if (a.stats != nullptr) a.stats[j] += begin;
+                }
             }
             __syncthreads();
-            // one warp per message
-            for (int s = 0; s < R; ++s) {
-                const uint32_t cnt = s_count[s], begin = s_begin[s];
-                for (uint32_t i = warp; i < cnt; i += kLLWarps) {
-                    const uint8_t* m = slab + ((static_cast<int64_t>(j) * R + s) * M + i) * a.msg_bytes;
-                    const int64_t pos = static_cast<int64_t>(j) * rows_per_expert + begin + i;
-                    const int4 hdr = __ldcg(reinterpret_cast<const int4*>(m));
-                    if (lane == 0) a.packed_src_info[pos] = (hdr.y << 20) | hdr.x;
-                    uint8_t* out = reinterpret_cast<uint8_t*>(a.packed_x) + pos * payload;
-                    for (int off = lane * 16; off < payload; off += 32 * 16)
-                        *reinterpret_cast<int4*>(out + off) = __ldcg(reinterpret_cast<const int4*>(m + 16 + off));
-                    if (a.use_fp8) {
-                        const float* sf = reinterpret_cast<const float*>(m + 16 + H);
-                        if (a.use_ue8m0) {
-                            // four exponents per int32, groups along the slow axis: [E_local, ceil(G/4), R*M]
-                            uint8_t* dst = reinterpret_cast<uint8_t*>(a.packed_sf);
-                            const int64_t G4 = (G + 3) / 4;
-                            for (int g = lane; g < G; g += 32)
-                                dst[((static_cast<int64_t>(j) * G4 + g / 4) * rows_per_expert + begin + i) * 4 + (g & 3)] =
-                                    static_cast<uint8_t>(__float_as_uint(sf[g]) >> 23);
-                        } else {
-                            float* dst = reinterpret_cast<float*>(a.packed_sf);
-                            for (int g = lane; g < G; g += 32)
-                                dst[(static_cast<int64_t>(j) * G + g) * rows_per_expert + begin + i] = sf[g];
-                        }
+            // one warp per message, loads issued four at a time
+            const uint32_t cnt = s_count[s], begin = s_begin[s];
+            for (uint32_t i = warp; i < cnt; i += kLLWarps) {
+                const uint8_t* m = slab + ((static_cast<int64_t>(j) * R + s) * M + i) * a.msg_bytes;
+                const int64_t pos = static_cast<int64_t>(j) * rows_per_expert + begin + i;
+                const int4 hdr = __ldcg(reinterpret_cast<const int4*>(m));
+                if (lane == 0) a.packed_src_info[pos] = (hdr.y << 20) | hdr.x;
+                uint8_t* out = reinterpret_cast<uint8_t*>(a.packed_x) + pos * payload;
+                for (int off = lane * 16; off < payload; off += 4 * 32 * 16) {
+                    int4 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (off + u * 512 < payload) v[u] = __ldcg(reinterpret_cast<const int4*>(m + 16 + off + u * 512));
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (off + u * 512 < payload) *reinterpret_cast<int4*>(out + off + u * 512) = v[u];
+                }
+                if (a.use_fp8) {
+                    const float* sf = reinterpret_cast<const float*>(m + 16 + H);
+                    if (a.use_ue8m0) {
+                        // four exponents per int32, groups along the slow axis: [E_local, ceil(G/4), R*M]
+                        uint8_t* dst = reinterpret_cast<uint8_t*>(a.packed_sf);
+                        const int64_t G4 = (G + 3) / 4;
+                        for (int g = lane; g < G; g += 32)
+                            dst[((static_cast<int64_t>(j) * G4 + g / 4) * rows_per_expert + begin + i) * 4 + (g & 3)] =
+                                static_cast<uint8_t>(__float_as_uint(__ldcg(sf + g)) >> 23);
+                    } else {
+                        float* dst = reinterpret_cast<float*>(a.packed_sf);
+                        for (int g = lane; g < G; g += 32)
+                            dst[(static_cast<int64_t>(j) * G + g) * rows_per_expert + begin + i] = __ldcg(sf + g);
                     }
                 }
             }
@@ -246,7 +256,6 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
     const uint64_t epoch = ws->epoch[EP_CH_LL_COMBINE] + 1;
     const int set = static_cast<int>(epoch & 1);
     __shared__ uint8_t* s_peer[EP_MAX_RANKS];
-    __shared__ uint32_t s_count[EP_MAX_RANKS], s_begin[EP_MAX_RANKS + 1];
     if (tid < EP_MAX_RANKS) s_peer[tid] = tid < R ? ctx.peer_base[tid] : nullptr;
     // per warp: two staging rows and two mbarriers
     const int send_warps = ll_combine_send_warps(H);
@@ -265,38 +274,31 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
         const uint8_t* xb = reinterpret_cast<const uint8_t*>(a.x);
         const int64_t rows_per_expert = static_cast<int64_t>(R) * M;
         uint32_t n_loaded = 0;   // loads issued by this warp so far (selects stage and mbarrier parity)
-        for (int j = blockIdx.x; j < El && alive; j += gridDim.x) {
-            __syncthreads();
-            if (tid < R) {
-                const int64_t lr = a.layout_range[j * R + tid];
-                s_count[tid] = static_cast<uint32_t>(lr & 0xffffffffll);
-                s_begin[tid] = static_cast<uint32_t>(lr >> 32);
-            }
-            __syncthreads();
-            for (int s = 0; s < R && alive; ++s) {
-                if (rank_masked(a.mask, s)) continue;
-                const uint32_t cnt = s_count[s], begin = s_begin[s];
-                for (uint32_t i = warp; warp < send_warps && i < cnt && alive; i += send_warps) {
-                    const int64_t pos = static_cast<int64_t>(j) * rows_per_expert + begin + i;
-                    const int info = a.src_info[pos];
-                    const int t = info & 0xfffff, k = info >> 20;
-                    const int st = n_loaded & 1;
-                    // the stage was the source of the store issued two rows ago
-                    ptx::bulk_wait_read<1>();
-                    __syncwarp();
-                    if (lane == 0) {
-                        ptx::mbar_arrive_expect_tx(&bars[st], row_bytes);
-                        ptx::bulk_load(stage + st * row_bytes, xb + pos * row_bytes, row_bytes, &bars[st]);
-                    }
-                    alive = mbar_wait_bounded(ctx, ws, &bars[st], (n_loaded >> 1) & 1, EP_PH_COMBINE_LOAD);
-                    ++n_loaded;
-                    if (!alive) break;
-                    if (lane == 0) {
-                        uint8_t* dst = s_peer[s] + a.off_slab[set] + (static_cast<int64_t>(t) * K + k) * row_bytes;
-                        ptx::bulk_store(dst, stage + st * row_bytes, row_bytes);
-                    }
-                    ptx::bulk_commit();
+        for (int p = blockIdx.x; p < El * R && alive; p += gridDim.x) {
+            const int j = p / R, s = p % R;
+            if (rank_masked(a.mask, s)) continue;
+            const int64_t lr = a.layout_range[j * R + s];
+            const uint32_t cnt = static_cast<uint32_t>(lr & 0xffffffffll), begin = static_cast<uint32_t>(lr >> 32);
+            for (uint32_t i = warp; warp < send_warps && i < cnt && alive; i += send_warps) {
+                const int64_t pos = static_cast<int64_t>(j) * rows_per_expert + begin + i;
+                const int info = a.src_info[pos];
+                const int t = info & 0xfffff, k = info >> 20;
+                const int st = n_loaded & 1;
+                // the stage was the source of the store issued two rows ago
+                ptx::bulk_wait_read<1>();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive_expect_tx(&bars[st], row_bytes);
+                    ptx::bulk_load(stage + st * row_bytes, xb + pos * row_bytes, row_bytes, &bars[st]);
                 }
+                alive = mbar_wait_bounded(ctx, ws, &bars[st], (n_loaded >> 1) & 1, EP_PH_COMBINE_LOAD);
+                ++n_loaded;
+                if (!alive) break;
+                if (lane == 0) {
+                    uint8_t* dst = s_peer[s] + a.off_slab[set] + (static_cast<int64_t>(t) * K + k) * row_bytes;
+                    ptx::bulk_store(dst, stage + st * row_bytes, row_bytes);
+                }
+                ptx::bulk_commit();
             }
         }
         ptx::bulk_commit();
