@@ -65,6 +65,22 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, GemmSme
     return true;
 }
 
+// Tile order: M tiles are walked in groups of `group_m`; inside a group consecutive tiles step through M first, so
+// the tiles that run at the same time share few distinct A and B tiles and stay in L2.
+struct TileCoord {
+    int m, n;
+};
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int group_m, int m_offset) {
+    const int per_group = group_m * num_n;
+    const int grp = tile / per_group, in_grp = tile - grp * per_group;
+    const int first_m = grp * group_m;
+    const int gm = min(group_m, num_m - first_m);
+    TileCoord c;
+    c.m = (first_m + in_grp % gm + m_offset) % num_m;
+    c.n = in_grp / gm;
+    return c;
+}
+
 struct PipeState {
     int stage = 0;
     uint32_t phase = 0;
@@ -96,6 +112,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     Workspace* ws = g.fuse != EP_GEMM_FUSE_NONE ? local_ws(g.ctx) : nullptr;
     const uint64_t epoch = ws != nullptr ? ws->epoch[EP_CH_GEMM] + 1 : 0;
     const int tiles_per_shard = g.fuse != EP_GEMM_FUSE_NONE ? num_m / g.ctx.num_ranks : num_m;
+    // all-gather fusion wants the M tiles in arrival order, so its groups never span two shards
+    const int group_m = g.fuse == EP_GEMM_FUSE_ALL_GATHER ? min(8, tiles_per_shard) : 16;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) {
@@ -126,7 +144,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             PipeState p;
             bool ok = true;
             for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
-                const int m_blk = (tile / num_n + g.m_tile_offset) % num_m, n_blk = tile % num_n;
+                const TileCoord tc = tile_coord(tile, num_m, num_n, group_m, g.m_tile_offset);
+                const int m_blk = tc.m, n_blk = tc.n;
                 const int grp = g.tile_group != nullptr ? g.tile_group[m_blk] : 0;
                 if (grp < 0) continue;
                 if (g.fuse == EP_GEMM_FUSE_ALL_GATHER && m_blk / tiles_per_shard != g.ctx.rank) {
@@ -176,7 +195,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             uint32_t acc_phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
-                const int m_blk = (tile / num_n + g.m_tile_offset) % num_m;
+                const int m_blk = tile_coord(tile, num_m, num_n, group_m, g.m_tile_offset).m;
                 const int grp = g.tile_group != nullptr ? g.tile_group[m_blk] : 0;
                 if (grp < 0) continue;
                 if (!kFp8) {
@@ -221,7 +240,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         bool ok = true;
         uint8_t* cb = reinterpret_cast<uint8_t*>(g.c);
         for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
-            const int m_blk = (tile / num_n + g.m_tile_offset) % num_m, n_blk = tile % num_n;
+            const TileCoord tc = tile_coord(tile, num_m, num_n, group_m, g.m_tile_offset);
+            const int m_blk = tc.m, n_blk = tc.n;
             const int grp = g.tile_group != nullptr ? g.tile_group[m_blk] : 0;
             if (grp < 0) continue;
             const int row = m_blk * kBlockM + quad * 32 + lane;
