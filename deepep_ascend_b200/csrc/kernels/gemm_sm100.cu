@@ -24,22 +24,26 @@ namespace ep {
 
 namespace {
 
-constexpr int kBlockM = 128, kBlockN = 128, kTileBytes = 128 * 128;   // one operand tile: 128 rows x 128 bytes
-constexpr int kStages = 5;
-constexpr int kEpiRowBytes = kBlockN * 2 + 16;          // one staged bf16 output row, padded against bank conflicts
+constexpr int kBlockM = 128, kTileBytes = 128 * 128;   // A tile: 128 rows x 128 bytes; B tile: kBlockN rows x 128 bytes
+constexpr int kMaxStages = 5;
+constexpr int kEpiRowBytes = 128 * 2 + 16;              // one staged bf16 output row (128 columns), padded against bank conflicts
 constexpr int kEpiStageBytes = 4 * 32 * kEpiRowBytes;   // four epilogue warps x 32 rows
+// shared memory: [A stages | B stages | barriers (1 KB) | epilogue staging]
+__host__ __device__ constexpr int stage_bytes(int block_n) { return kTileBytes + block_n * 128; }
+__host__ __device__ constexpr int num_stages(int block_n) { return block_n == 256 ? 4 : 5; }
+__host__ __device__ constexpr int gemm_smem_bytes(int block_n) {
+    return num_stages(block_n) * stage_bytes(block_n) + 1024 + (block_n == 128 ? kEpiStageBytes : 0);
+}
 constexpr int kCopyWarps = 5;
 constexpr int kGemmThreads = 192;
-constexpr int kTmemColumns = 256;   // two accumulator buffers of kBlockN fp32 columns
 constexpr uint64_t kWaitLimitNs = 4ull * 1000 * 1000 * 1000;
 
 struct GemmSmem {
-    uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
+    uint64_t full[kMaxStages], empty[kMaxStages], tmem_full[2], tmem_empty[2];
     uint64_t copy_bar[kCopyWarps][2];
     uint32_t tmem_base;
     int failed;
 };
-constexpr int kGemmSmemBytes = 2 * kStages * kTileBytes + 1024 + kEpiStageBytes;
 
 __device__ __forceinline__ uint64_t gemm_timer() {
     uint64_t t;
@@ -81,6 +85,7 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
     return c;
 }
 
+template <int kStages>
 struct PipeState {
     int stage = 0;
     uint32_t phase = 0;
@@ -92,13 +97,16 @@ struct PipeState {
     }
 };
 
-template <bool kFp8>
+template <bool kFp8, int kBlockN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
     extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr int kStages = num_stages(kBlockN);
+    constexpr int kTileBytesB = kBlockN * 128;
+    constexpr int kTmemColumns = 2 * kBlockN;       // two accumulator buffers of kBlockN fp32 columns
     uint8_t* s_a = smem;
     uint8_t* s_b = smem + kStages * kTileBytes;
-    GemmSmem* sm = reinterpret_cast<GemmSmem*>(smem + 2 * kStages * kTileBytes);
+    GemmSmem* sm = reinterpret_cast<GemmSmem*>(smem + kStages * (kTileBytes + kTileBytesB));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int kBlockK = kFp8 ? 128 : 64;          // elements per 128-byte row
     constexpr int kUmmaK = kFp8 ? 32 : 16;            // elements per tcgen05.mma (32 bytes of K)
@@ -108,7 +116,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int num_tiles = num_m * num_n;
     const int gemm_ctas = static_cast<int>(gridDim.x) - g.num_copy_ctas;
     const bool is_copier = static_cast<int>(blockIdx.x) >= gemm_ctas;
-    uint8_t* s_epi = smem + 2 * kStages * kTileBytes + 1024;
+    uint8_t* s_epi = smem + kStages * (kTileBytes + kTileBytesB) + 1024;   // present only in the 128-column variant
     Workspace* ws = g.fuse != EP_GEMM_FUSE_NONE ? local_ws(g.ctx) : nullptr;
     const uint64_t epoch = ws != nullptr ? ws->epoch[EP_CH_GEMM] + 1 : 0;
     const int tiles_per_shard = g.fuse != EP_GEMM_FUSE_NONE ? num_m / g.ctx.num_ranks : num_m;
@@ -141,7 +149,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            PipeState p;
+            PipeState<kStages> p;
             bool ok = true;
             for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
                 const TileCoord tc = tile_coord(tile, num_m, num_n, group_m, g.m_tile_offset);
@@ -180,9 +188,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 for (int kb = 0; kb < num_k && ok; ++kb) {
                     ok = wait_bar(&sm->empty[p.stage], p.phase ^ 1, sm, g.error, 1);
                     if (!ok) break;
-                    ptx::mbar_arrive_expect_tx(&sm->full[p.stage], 2 * kTileBytes);
+                    ptx::mbar_arrive_expect_tx(&sm->full[p.stage], kTileBytes + kTileBytesB);
                     umma::tma_load_2d(s_a + p.stage * kTileBytes, &map_a, kb * kBlockK, m_blk * kBlockM, &sm->full[p.stage]);
-                    umma::tma_load_2d(s_b + p.stage * kTileBytes, &map_b, kb * kBlockK, grp * g.N + n_blk * kBlockN, &sm->full[p.stage]);
+                    umma::tma_load_2d(s_b + p.stage * kTileBytesB, &map_b, kb * kBlockK, grp * g.N + n_blk * kBlockN, &sm->full[p.stage]);
                     p.advance();
                 }
             }
@@ -190,7 +198,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            PipeState p;
+            PipeState<kStages> p;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
@@ -212,7 +220,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     if (!ok) break;
                     umma::fence_after_thread_sync();
                     const uint64_t desc_a = umma::make_smem_desc_sw128(s_a + p.stage * kTileBytes);
-                    const uint64_t desc_b = umma::make_smem_desc_sw128(s_b + p.stage * kTileBytes);
+                    const uint64_t desc_b = umma::make_smem_desc_sw128(s_b + p.stage * kTileBytesB);
 #pragma unroll
                     for (int k = 0; k < kBlockK / kUmmaK; ++k) {
                         const uint32_t accumulate = kFp8 ? (k != 0) : ((kb | k) != 0);
@@ -252,7 +260,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 umma::fence_after_thread_sync();
-                const bool to_peer = g.fuse == EP_GEMM_FUSE_REDUCE_SCATTER;
+                const bool to_peer = kBlockN == 128 && g.fuse == EP_GEMM_FUSE_REDUCE_SCATTER;
                 uint8_t* my_stage = s_epi + (quad * 32 + lane) * kEpiRowBytes;
                 if (to_peer) {
                     ptx::bulk_wait_read<0>();     // the staging rows were the source of the previous tile's stores
@@ -492,13 +500,13 @@ EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-// K-major [rows, K] operand, box = 128 rows x 128 bytes, 128B swizzle, out-of-range elements read as zero
-bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld_elems, bool fp8) {
+// K-major [rows, K] operand, box = box_rows (128 or 256) rows x 128 bytes, 128B swizzle, out-of-range elements read as zero
+bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld_elems, bool fp8, int box_rows) {
     EncodeTiledFn encode = get_encode_fn();
     if (encode == nullptr) return false;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems * (fp8 ? 1 : 2))};
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(fp8 ? 128 : 64), 128};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(fp8 ? 128 : 64), static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t elem_strides[2] = {1, 1};
     return encode(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                   elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -513,20 +521,25 @@ cudaError_t launch_gemm(const GemmArgs& g, int num_sms, cudaStream_t stream) {
     if ((g.lda * elem) % 16 != 0 || (g.ldb * elem) % 16 != 0 || g.ldc % 8 != 0 || g.N % 8 != 0) return cudaErrorInvalidValue;
     if (reinterpret_cast<uintptr_t>(g.a) % 16 != 0 || reinterpret_cast<uintptr_t>(g.b) % 16 != 0 || reinterpret_cast<uintptr_t>(g.c) % 16 != 0)
         return cudaErrorInvalidValue;
+    // bf16: 128 x 256 output tiles (fewer A re-reads, longer MMAs); the block-scaled FP8 path and the reduce-scatter
+    // epilogue (which stages 128-column rows) use 128 x 128 tiles
+    const int block_n = (!g.is_fp8 && g.fuse != EP_GEMM_FUSE_REDUCE_SCATTER && g.N >= 256) ? 256 : 128;
     CUtensorMap map_a, map_b;
-    if (!make_operand_map(&map_a, g.a, g.M, g.K, g.lda, g.is_fp8) ||
-        !make_operand_map(&map_b, g.b, static_cast<int64_t>(g.num_groups) * g.N, g.K, g.ldb, g.is_fp8))
+    if (!make_operand_map(&map_a, g.a, g.M, g.K, g.lda, g.is_fp8, 128) ||
+        !make_operand_map(&map_b, g.b, static_cast<int64_t>(g.num_groups) * g.N, g.K, g.ldb, g.is_fp8, block_n))
         return cudaErrorInvalidValue;
-    const void* fn = g.is_fp8 ? (const void*)gemm_kernel<true> : (const void*)gemm_kernel<false>;
+    const void* fn = g.is_fp8 ? (const void*)gemm_kernel<true, 128>
+                              : (block_n == 256 ? (const void*)gemm_kernel<false, 256> : (const void*)gemm_kernel<false, 128>);
+    const int kGemmSmemBytes = gemm_smem_bytes(block_n);
     cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
     if (err != cudaSuccess) return err;
-    const int num_tiles = ((g.M + kBlockM - 1) / kBlockM) * ((g.N + kBlockN - 1) / kBlockN);
+    const int num_tiles = ((g.M + kBlockM - 1) / kBlockM) * ((g.N + block_n - 1) / block_n);
     int ctas = num_sms < 1 ? 1 : num_sms;
     void* params[] = {&map_a, &map_b, const_cast<GemmArgs*>(&g)};
     if (g.fuse != EP_GEMM_FUSE_NONE) {
         // the CTAs of a fused launch wait on one another (grid barrier, copier -> producer flags): cooperative launch
         const int R = g.ctx.num_ranks;
-        if (g.is_fp8 || g.M % (kBlockM * R) != 0 || g.N % kBlockN != 0 || g.K * 2 > 16384 || g.tile_group != nullptr) return cudaErrorInvalidValue;
+        if (g.is_fp8 || g.M % (kBlockM * R) != 0 || g.N % 128 != 0 || g.K * 2 > 16384 || g.tile_group != nullptr) return cudaErrorInvalidValue;
         if (g.fuse == EP_GEMM_FUSE_ALL_GATHER && (g.num_copy_ctas < 1 || g.num_copy_ctas >= ctas)) return cudaErrorInvalidValue;
         if (g.fuse == EP_GEMM_FUSE_REDUCE_SCATTER && g.num_copy_ctas != 0) return cudaErrorInvalidValue;
         if (g.M / kBlockM >= EP_MAX_TILE_FLAGS - 1) return cudaErrorInvalidValue;
