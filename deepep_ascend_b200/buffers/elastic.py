@@ -642,7 +642,7 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         """Microseconds spent in each phase of the last dispatch and combine."""
         torch.cuda.synchronize()
         d, c = self.profile['dispatch'].tolist(), self.profile['combine'].tolist()
-        names_d = ['layout_count', 'count_exchange', 'assign_rows', 'scatter', 'grid_drain', 'peer_done']
+        names_d = ['layout_count', 'count_exchange', 'assign_rows', 'scatter', 'grid_drain', 'peer_done', 'localise_ids']
         names_c = ['entry_barrier', 'pull_reduce', 'grid_drain', 'exit_barrier']
         return {'dispatch': {n: (d[i + 1] - d[i]) / 1e3 for i, n in enumerate(names_d) if d[i + 1] and d[i]},
                 'combine': {n: (c[i + 1] - c[i]) / 1e3 for i, n in enumerate(names_c) if c[i + 1] and c[i]}}

@@ -33,6 +33,7 @@ struct Workspace {
     alignas(128) uint64_t xbar[EP_NUM_CHANNELS][EP_MAX_RANKS];           // [channel][source]: arrivals
     alignas(128) uint64_t disp_rank_count[EP_MAX_RANKS][EP_MAX_RANKS];   // [source][dest], epoch-tagged
     alignas(128) uint64_t disp_expert_count[EP_MAX_RANKS][EP_MAX_EXPERTS];  // [source][expert], epoch-tagged
+    alignas(128) uint64_t disp_done[EP_MAX_RANKS];                         // [source]: dispatch epoch whose rows have all arrived
     alignas(128) uint64_t ll_signal[2][EP_MAX_EXPERTS * EP_MAX_RANKS];    // low-latency count / flag words
     alignas(128) uint64_t pp_signal[4][64];                                // pipeline FIFO credits
     alignas(128) uint64_t tile_flags[EP_MAX_TILE_FLAGS];                   // fused GEMM+collective tile flags

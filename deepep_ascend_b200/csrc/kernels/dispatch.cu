@@ -580,43 +580,68 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
     const bool cta_ok = __syncthreads_and(alive ? 1 : 0) != 0;
     alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && cta_ok;
     stamp(5);
-    if (cta == 0) {
-        if (alive) alive = xgpu_barrier(ctx, ws, EP_CH_DISPATCH, EP_PH_DISPATCH_DONE);
-        stamp(6);
-        if (tid == 0) ws->epoch[EP_CH_DISPATCH] = epoch;
+    // Completion: after the grid barrier every store of this rank has been drained, so CTA 0 tells every peer
+    // "all rows of my dispatch number `epoch` have arrived"; then EVERY CTA waits for all peers' words itself (no
+    // second grid barrier) before it touches received data.
+    if (cta == 0 && alive && tid < R) {
+        Workspace* pws = reinterpret_cast<Workspace*>(s_peer[tid]);
+        ptx::st_release_sys(&pws->disp_done[me], epoch);
     }
-    if (a.side_packed) {
+    {
+        int ok = alive ? 1 : 0;
+        if (alive && tid < R) {
+            const uint64_t* word = &ws->disp_done[tid];
+            ok = bounded_wait(
+                ctx, ws, EP_PH_DISPATCH_DONE, tid, epoch, [&] { return ptx::ld_acquire_sys(word) >= epoch; },
+                [&] { return ptx::ld_relaxed_sys(word); });
+        }
+        alive = __syncthreads_and(ok) != 0;
+    }
+    stamp(6);
+    if (a.side_packed && alive) {
         // every row has arrived: turn the global expert ids of the received side records into ids relative to this
-        // rank's first expert (-1 for experts of other ranks) and fill in source rank * K + the lane that sent the row
-        alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && alive;
-        if (alive) {
-            const int num_recv = __ldcg(a.psum_rank + (R - 1));
-            const int lo = me * El;
-            for (int row = cta * nthreads + tid; row < num_recv; row += num_ctas * nthreads) {
-                uint8_t* rec = s_peer[me] + a.off_recv_side + static_cast<int64_t>(row) * a.side_bytes;
-                int master = 0;
-                for (int k = 0; k < K; ++k) {
-                    if (a.idx_is_64) {
-                        long long* p = reinterpret_cast<long long*>(rec + a.side_off_idx) + k;
-                        const long long gidx = __ldcg(p);
-                        const bool mine = gidx >= lo && gidx < lo + El;
+        // rank's first expert (-1 for experts of other ranks) and fill in source rank * K + the lane that sent the row.
+        // One thread per row; all ids of a row are loaded before any is written back.
+        const int num_recv = __ldcg(a.psum_rank + (R - 1));
+        const int lo = me * El;
+        for (int row = cta * nthreads + tid; row < num_recv; row += num_ctas * nthreads) {
+            uint8_t* rec = s_peer[me] + a.off_recv_side + static_cast<int64_t>(row) * a.side_bytes;
+            int2* mp = reinterpret_cast<int2*>(rec + a.side_off_meta);
+            int2 m = __ldcg(mp);
+            int master = 0;
+            if (a.idx_is_64) {
+                long long* p = reinterpret_cast<long long*>(rec + a.side_off_idx);
+                long long gidx[EP_MAX_TOPK];
+#pragma unroll
+                for (int k = 0; k < EP_MAX_TOPK; ++k)
+                    if (k < K) gidx[k] = __ldcg(p + k);
+#pragma unroll
+                for (int k = 0; k < EP_MAX_TOPK; ++k)
+                    if (k < K) {
+                        const bool mine = gidx[k] >= lo && gidx[k] < lo + El;
                         if (mine) master = k;
-                        *p = mine ? gidx - lo : -1;
-                    } else {
-                        int* p = reinterpret_cast<int*>(rec + a.side_off_idx) + k;
-                        const int gidx = __ldcg(p);
-                        const bool mine = gidx >= lo && gidx < lo + El;
-                        if (mine) master = k;
-                        *p = mine ? gidx - lo : -1;
+                        p[k] = mine ? gidx[k] - lo : -1;
                     }
-                }
-                int2* mp = reinterpret_cast<int2*>(rec + a.side_off_meta);
-                int2 m = __ldcg(mp);
-                m.y = (m.x / a.num_max_tokens) * K + master;
-                *mp = m;
+            } else {
+                int* p = reinterpret_cast<int*>(rec + a.side_off_idx);
+                int gidx[EP_MAX_TOPK];
+#pragma unroll
+                for (int k = 0; k < EP_MAX_TOPK; ++k)
+                    if (k < K) gidx[k] = __ldcg(p + k);
+#pragma unroll
+                for (int k = 0; k < EP_MAX_TOPK; ++k)
+                    if (k < K) {
+                        const bool mine = gidx[k] >= lo && gidx[k] < lo + El;
+                        if (mine) master = k;
+                        p[k] = mine ? gidx[k] - lo : -1;
+                    }
             }
+            m.y = (m.x / a.num_max_tokens) * K + master;
+            *mp = m;
         }
     }
+    stamp(7);
+    if (cta == 0 && tid == 0) ws->epoch[EP_CH_DISPATCH] = epoch;
 }
 
 template <bool kQuant>
