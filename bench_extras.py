@@ -205,12 +205,14 @@ def main():
     if want('moe'):
         from deepep_ascend_b200.models.moe import FusedMoE
         Tm, I = 4096, 2048
-        buf = ElasticBuffer(group, num_max_tokens_per_rank=Tm, hidden=H, num_topk=K, enable_expand=True, num_experts=E,
+        # 32 experts per rank, as at EP8 with 256 experts (a single GPU would otherwise hold all 256 and stream 22 GB of weights)
+        Em = E if world > 1 else 32
+        buf = ElasticBuffer(group, num_max_tokens_per_rank=Tm, hidden=H, num_topk=K, enable_expand=True, num_experts=Em,
                             expert_alignment=128, num_gpu_timeout_secs=30)
-        layer = FusedMoE(buf, E, H, I, init_std=0.02, num_sms=64)
+        layer = FusedMoE(buf, Em, H, I, init_std=0.02, num_sms=64)
         gen = torch.Generator().manual_seed(5 + rank)
         x = torch.randn(Tm, H, generator=gen).bfloat16().cuda().requires_grad_(True)
-        w, idx = torch.softmax(torch.randn(Tm, E, generator=gen), -1).topk(K, -1)
+        w, idx = torch.softmax(torch.randn(Tm, Em, generator=gen), -1).topk(K, -1)
         w, idx = w.cuda().requires_grad_(True), idx.cuda()
         g = torch.randn(Tm, H, device='cuda').bfloat16()
 
@@ -218,13 +220,15 @@ def main():
             return layer(x, idx, w)
 
         def fwd_bwd():
+            layer.zero_grad(set_to_none=True)      # as a training loop does: gradients are assigned, not accumulated
+            x.grad = w.grad = None
             layer(x, idx, w).backward(g)
         # breakdown of the forward pass
         from deepep_ascend_b200.ops import gemm as G
         st = {}
 
         def d_only():
-            st['o'] = buf.dispatch(x.detach(), idx, w.detach(), num_experts=E, do_expand=True, expert_alignment=G.BLOCK_M,
+            st['o'] = buf.dispatch(x.detach(), idx, w.detach(), num_experts=Em, do_expand=True, expert_alignment=G.BLOCK_M,
                                    fused_fp8_cast=True, num_sms=64)
         d_only()
         (rx, rsf), _, rw, hd, _ = st['o']
@@ -238,7 +242,7 @@ def main():
         t_g1 = np.median(timeit(g1, None, iters=5, warm=2))
 
         def sw():
-            hbuf['a'] = G.swiglu_quant(hbuf['h'], keep_bf16=True)
+            hbuf['a'] = G.swiglu_quant(hbuf['h'])
         t_sw = np.median(timeit(sw, None, iters=5, warm=2))
         ybuf = buf.get_combine_buffer(hd)
         t_g2 = np.median(timeit(lambda: G.grouped_gemm_nt(hbuf['a'][0], q2, tile_group, out=ybuf, sfa=hbuf['a'][1], sfb=s2), None, iters=5, warm=2))
@@ -246,11 +250,42 @@ def main():
         emit(bench='fused_moe_forward_breakdown_ms', rows=hd.num_rows, dispatch_expand_fp8=float(t_disp), gemm1_fp8=float(t_g1),
              swiglu_cast=float(t_sw), gemm2_fp8=float(t_g2), combine_weighted=float(t_comb),
              gemm1_tflops=2 * hd.num_rows * H * 2 * I / t_g1 / 1e9, gemm2_tflops=2 * hd.num_rows * H * I / t_g2 / 1e9)
+        # backward pieces, timed one by one on this rank's rows
+        g_rows = torch.randn(hd.num_rows, H, device='cuda').bfloat16()
+        rwc = rw.contiguous()
+        seg_off = G.segment_offsets(hd.psum_num_recv_tokens_per_expert)
+        w2_t, w13_t = layer.transposed_weights()
+        bb = {}
+
+        def prep():
+            bb['dy'], bb['dy_t'], bb['dot'] = G.moe_bwd_prep(g_rows, ybuf, rwc, valid_row)
+        t_prep = np.median(timeit(prep, None, iters=5, warm=2))
+
+        def dgrad2():
+            bb['d_act'] = G.grouped_gemm_nt(bb['dy'], w2_t, tile_group)
+        t_dg2 = np.median(timeit(dgrad2, None, iters=5, warm=2))
+
+        def swb():
+            bb['dh'], bb['dh_t'], bb['act_t'] = G.swiglu_bwd(bb['d_act'], hbuf['h'], valid_row)
+        t_swb = np.median(timeit(swb, None, iters=5, warm=2))
+        t_dg1 = np.median(timeit(lambda: G.grouped_gemm_nt(bb['dh'], w13_t, tile_group, out=ybuf), None, iters=5, warm=2))
+
+        def xt():
+            bb['x_t'] = G.dequant_transpose(rx, rsf, valid_row)
+        t_xt = np.median(timeit(xt, None, iters=5, warm=2))
+        t_wg2 = np.median(timeit(lambda: G.gemm_kgrouped(bb['dy_t'], bb['act_t'], seg_off), None, iters=5, warm=2))
+        t_wg1 = np.median(timeit(lambda: G.gemm_kgrouped(bb['dh_t'], bb['x_t'], seg_off), None, iters=5, warm=2))
+        emit(bench='fused_moe_backward_breakdown_ms', rows=hd.num_rows, combine_bwd_prep=float(t_prep), dgrad_down_bf16=float(t_dg2),
+             swiglu_bwd=float(t_swb), dgrad_up_bf16=float(t_dg1), dequant_transpose=float(t_xt), wgrad_down=float(t_wg2),
+             wgrad_up=float(t_wg1), dgrad_down_tflops=2 * hd.num_rows * H * I / t_dg2 / 1e9,
+             dgrad_up_tflops=2 * hd.num_rows * H * 2 * I / t_dg1 / 1e9, wgrad_down_tflops=2 * hd.num_rows * H * I / t_wg2 / 1e9,
+             wgrad_up_tflops=2 * hd.num_rows * H * 2 * I / t_wg1 / 1e9)
+        del bb, g_rows
         tf = np.median(timeit(fwd, buf, iters=5, warm=2))
         tfb = np.median(timeit(fwd_bwd, buf, iters=5, warm=2))
         rows = float(idx.numel())
         flops_fwd = rows * (2 * H * 2 * I + 2 * I * H)
-        emit(bench='fused_moe_layer', tokens_per_rank=Tm, hidden=H, intermediate=I, fwd_ms=float(tf), fwd_bwd_ms=float(tfb),
+        emit(bench='fused_moe_layer', tokens_per_rank=Tm, hidden=H, intermediate=I, experts_per_rank=Em // world, fwd_ms=float(tf), fwd_bwd_ms=float(tfb),
              fwd_expert_tflops_per_gpu=flops_fwd / tf / 1e9, note='includes the host sync of dispatch (exact sizes)')
         buf.destroy()
 

@@ -265,6 +265,10 @@ struct GemmArgs {
     uint64_t slot_set_bytes;
     void* rs_out;                     // RS: [M / R, N] bf16
     int m_tile_offset;                // M tiles are visited starting from this one (local shard first)
+    // K-grouped product (weight gradients of a grouped layer): C[e][M, N] = A[:, k0:k1] * B[:, k0:k1]^T with
+    // k0 = k_group_off[e], k1 = k_group_off[e + 1] (device array of num_groups + 1 multiples of 64); C is
+    // [num_groups * M, N]; an empty range gives zeros.  bf16 only; null when unused.
+    const int32_t* k_group_off;
 };
 enum { EP_GEMM_FUSE_NONE = 0, EP_GEMM_FUSE_ALL_GATHER = 1, EP_GEMM_FUSE_REDUCE_SCATTER = 2 };
 
@@ -284,6 +288,31 @@ struct SwigluQuantArgs {
     int rows, inter;
 };
 
+// Element-wise kernels of the MoE backward pass.  Each also writes the TRANSPOSE of its result ([channels, rows]),
+// which is the K-major operand layout the weight-gradient GEMM needs (K = rows), so no separate transpose pass runs.
+// `valid` (one byte per row, 0 = alignment padding row) zeroes the results of padding rows.  rows % 64 == 0.
+enum { EP_MOE_BWD_PREP = 0, EP_MOE_BWD_SWIGLU = 1, EP_MOE_BWD_DEQUANT_T = 2 };
+struct MoeBwdArgs {
+    int op;
+    int rows, cols;               // PREP / DEQUANT_T: cols = hidden; SWIGLU: cols = intermediate size I
+    const uint8_t* valid;         // [rows]
+    // PREP: g [rows, H] bf16 (gradient of the combined output at every expert row), y [rows, H] bf16 (the expert
+    //       outputs), w [rows] fp32 -> out = g * w [rows, H], out_t = out^T [H, rows], row_dot[row] = sum(g * y)
+    // SWIGLU: g = d_act [rows, I], y = h [rows, 2I] (gate | up) -> out = d_h [rows, 2I], out_t = d_h^T [2I, rows],
+    //       out2_t = (silu(gate) * up)^T [I, rows]
+    // DEQUANT_T: y = q [rows, H] e4m3, w = scales (row, 128-block) at w[row * sf_stride_row + blk * sf_stride_col]
+    //       -> out_t = (q * scale)^T [H, rows] bf16
+    const void* g;
+    const void* y;
+    const float* w;
+    int64_t sf_stride_row, sf_stride_col;
+    void* out;
+    void* out_t;
+    void* out2_t;
+    float* row_dot;
+};
+
 namespace ep {
 cudaError_t launch_swiglu_quant(const SwigluQuantArgs& args, cudaStream_t stream);
+cudaError_t launch_moe_bwd(const MoeBwdArgs& args, cudaStream_t stream);
 }  // namespace ep

@@ -85,6 +85,35 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
     return c;
 }
 
+// What one tile index means: output tile (m, n), weights group of B, K blocks [kb0, kb1), first output row of its group.
+struct TileWork {
+    int m, n, grp, kb0, kb1;
+    int64_t c_row0;
+};
+__device__ __forceinline__ TileWork tile_work(const GemmArgs& g, int tile, int num_m, int num_n, int num_k, int group_m, int block_k) {
+    TileWork w;
+    int e = 0;
+    if (g.k_group_off != nullptr) {
+        e = tile / (num_m * num_n);
+        tile -= e * num_m * num_n;
+    }
+    const TileCoord tc = tile_coord(tile, num_m, num_n, group_m, g.m_tile_offset);
+    w.m = tc.m;
+    w.n = tc.n;
+    if (g.k_group_off != nullptr) {
+        w.grp = 0;
+        w.kb0 = __ldg(g.k_group_off + e) / block_k;
+        w.kb1 = __ldg(g.k_group_off + e + 1) / block_k;
+        w.c_row0 = static_cast<int64_t>(e) * g.M;
+    } else {
+        w.grp = g.tile_group != nullptr ? __ldg(g.tile_group + tc.m) : 0;
+        w.kb0 = 0;
+        w.kb1 = num_k;
+        w.c_row0 = 0;
+    }
+    return w;
+}
+
 template <int kStages>
 struct PipeState {
     int stage = 0;
@@ -113,7 +142,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     constexpr uint32_t kIdesc = umma::make_instr_desc(kBlockM, kBlockN, kFp8 ? umma::kFormatE4M3 : umma::kFormatBF16);
     const int num_m = (g.M + kBlockM - 1) / kBlockM, num_n = (g.N + kBlockN - 1) / kBlockN;
     const int num_k = (g.K + kBlockK - 1) / kBlockK;
-    const int num_tiles = num_m * num_n;
+    const int num_tiles = num_m * num_n * (g.k_group_off != nullptr ? g.num_groups : 1);
     const int gemm_ctas = static_cast<int>(gridDim.x) - g.num_copy_ctas;
     const bool is_copier = static_cast<int>(blockIdx.x) >= gemm_ctas;
     uint8_t* s_epi = smem + kStages * (kTileBytes + kTileBytesB) + 1024;   // present only in the 128-column variant
@@ -152,10 +181,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             PipeState<kStages> p;
             bool ok = true;
             for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
-                const TileCoord tc = tile_coord(tile, num_m, num_n, group_m, g.m_tile_offset);
-                const int m_blk = tc.m, n_blk = tc.n;
-                const int grp = g.tile_group != nullptr ? g.tile_group[m_blk] : 0;
-                if (grp < 0) continue;
+                const TileWork tw = tile_work(g, tile, num_m, num_n, num_k, group_m, kBlockK);
+                const int m_blk = tw.m, n_blk = tw.n, grp = tw.grp;
+                if (grp < 0 || tw.kb1 <= tw.kb0) continue;
                 if (g.fuse == EP_GEMM_FUSE_ALL_GATHER && m_blk / tiles_per_shard != g.ctx.rank) {
                     // rows of a remote shard: wait until a copier CTA of this kernel has landed the tile locally
                     const uint64_t* flag = &ws->tile_flags[m_blk];
@@ -185,7 +213,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     }
                     if (!ok) break;
                 }
-                for (int kb = 0; kb < num_k && ok; ++kb) {
+                for (int kb = tw.kb0; kb < tw.kb1 && ok; ++kb) {
                     ok = wait_bar(&sm->empty[p.stage], p.phase ^ 1, sm, g.error, 1);
                     if (!ok) break;
                     ptx::mbar_arrive_expect_tx(&sm->full[p.stage], kTileBytes + kTileBytesB);
@@ -203,15 +231,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             uint32_t acc_phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
-                const int m_blk = tile_coord(tile, num_m, num_n, group_m, g.m_tile_offset).m;
-                const int grp = g.tile_group != nullptr ? g.tile_group[m_blk] : 0;
-                if (grp < 0) continue;
+                const TileWork tw = tile_work(g, tile, num_m, num_n, num_k, group_m, kBlockK);
+                if (tw.grp < 0 || tw.kb1 <= tw.kb0) continue;
                 if (!kFp8) {
                     ok = wait_bar(&sm->tmem_empty[acc], acc_phase ^ 1, sm, g.error, 2);
                     if (!ok) break;
                     umma::fence_after_thread_sync();
                 }
-                for (int kb = 0; kb < num_k && ok; ++kb) {
+                for (int kb = tw.kb0; kb < tw.kb1 && ok; ++kb) {
                     if (kFp8) {
                         ok = wait_bar(&sm->tmem_empty[acc], acc_phase ^ 1, sm, g.error, 2);
                         if (!ok) break;
@@ -223,7 +250,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const uint64_t desc_b = umma::make_smem_desc_sw128(s_b + p.stage * kTileBytesB);
 #pragma unroll
                     for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                        const uint32_t accumulate = kFp8 ? (k != 0) : ((kb | k) != 0);
+                        const uint32_t accumulate = kFp8 ? (k != 0) : (kb != tw.kb0 || k != 0);
                         umma::mma_ss<kFp8>(tmem_base + acc * kBlockN, umma::advance_desc_k(desc_a, k * 32), umma::advance_desc_k(desc_b, k * 32),
                                            kIdesc, accumulate);
                     }
@@ -248,12 +275,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         bool ok = true;
         uint8_t* cb = reinterpret_cast<uint8_t*>(g.c);
         for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
-            const TileCoord tc = tile_coord(tile, num_m, num_n, group_m, g.m_tile_offset);
-            const int m_blk = tc.m, n_blk = tc.n;
-            const int grp = g.tile_group != nullptr ? g.tile_group[m_blk] : 0;
+            const TileWork tw = tile_work(g, tile, num_m, num_n, num_k, group_m, kBlockK);
+            const int m_blk = tw.m, n_blk = tw.n, grp = tw.grp;
             if (grp < 0) continue;
             const int row = m_blk * kBlockM + quad * 32 + lane;
             const int n0 = n_blk * kBlockN;
+            if (tw.kb1 <= tw.kb0) {
+                // empty K range (an expert without tokens): the product is zero
+                if (row < g.M)
+                    for (int col = n0; col < min(n0 + kBlockN, g.N); col += 8)
+                        *reinterpret_cast<int4*>(cb + ((tw.c_row0 + row) * g.ldc + col) * 2) = make_int4(0, 0, 0, 0);
+                continue;
+            }
             const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
             if (!kFp8) {
                 ok = wait_bar(&sm->tmem_full[acc], acc_phase, sm, g.error, 5);
@@ -282,7 +315,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                                 for (int j = 0; j < 4; ++j)
                                     h[j] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
                                 if (to_peer) *reinterpret_cast<int4*>(my_stage + (c * 32 + v * 8) * 2) = out;
-                                else *reinterpret_cast<int4*>(cb + (static_cast<int64_t>(row) * g.ldc + col) * 2) = out;
+                                else *reinterpret_cast<int4*>(cb + ((tw.c_row0 + row) * g.ldc + col) * 2) = out;
                             }
                         }
                     }
@@ -526,14 +559,15 @@ cudaError_t launch_gemm(const GemmArgs& g, int num_sms, cudaStream_t stream) {
     const int block_n = (!g.is_fp8 && g.fuse != EP_GEMM_FUSE_REDUCE_SCATTER && g.N >= 256) ? 256 : 128;
     CUtensorMap map_a, map_b;
     if (!make_operand_map(&map_a, g.a, g.M, g.K, g.lda, g.is_fp8, 128) ||
-        !make_operand_map(&map_b, g.b, static_cast<int64_t>(g.num_groups) * g.N, g.K, g.ldb, g.is_fp8, block_n))
+        !make_operand_map(&map_b, g.b, static_cast<int64_t>(g.k_group_off != nullptr ? 1 : g.num_groups) * g.N, g.K, g.ldb, g.is_fp8, block_n))
         return cudaErrorInvalidValue;
     const void* fn = g.is_fp8 ? (const void*)gemm_kernel<true, 128>
                               : (block_n == 256 ? (const void*)gemm_kernel<false, 256> : (const void*)gemm_kernel<false, 128>);
     const int kGemmSmemBytes = gemm_smem_bytes(block_n);
     cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
     if (err != cudaSuccess) return err;
-    const int num_tiles = ((g.M + kBlockM - 1) / kBlockM) * ((g.N + block_n - 1) / block_n);
+    if (g.k_group_off != nullptr && (g.is_fp8 || g.fuse != EP_GEMM_FUSE_NONE || g.tile_group != nullptr || g.num_groups < 1)) return cudaErrorInvalidValue;
+    const int num_tiles = ((g.M + kBlockM - 1) / kBlockM) * ((g.N + block_n - 1) / block_n) * (g.k_group_off != nullptr ? g.num_groups : 1);
     int ctas = num_sms < 1 ? 1 : num_sms;
     void* params[] = {&map_a, &map_b, const_cast<GemmArgs*>(&g)};
     if (g.fuse != EP_GEMM_FUSE_NONE) {

@@ -1,6 +1,9 @@
 // Element-wise pieces of the MoE expert FFN that sit between the two grouped GEMMs: SwiGLU fused with the
 // e4m3 (1x128 scales) cast of the second GEMM's input, so the activation is written once in FP8 instead of being
-// written in bf16 and re-read by a separate quantisation kernel.
+// written in bf16 and re-read by a separate quantisation kernel; and the element-wise kernels of the backward pass,
+// which also emit the transposed operands of the weight-gradient GEMMs.
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace ep {
@@ -61,7 +64,192 @@ __global__ void swiglu_quant_kernel(const SwigluQuantArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------- backward pass
+// 64 x 64 tiles, 256 threads: thread (pair = tid / 8, c8 = tid % 8) owns rows 2 * pair, 2 * pair + 1 and the eight
+// columns c8 * 8 ...  Results are written row-major straight from registers and, through a transposed
+// shared-memory tile, column-major in 128-byte runs.
+constexpr int kTile = 64, kTileThreads = 256;
+constexpr int kTStride = 66;   // bf16 elements per transposed tile row (132 bytes: 4-byte aligned, 2-way bank conflicts at most)
+
+struct TileT {
+    __nv_bfloat16 v[kTile][kTStride];
+};
+
+// stash the two rows' values of column `col` (rows 2 * pair and 2 * pair + 1 of the tile) as one 4-byte word
+__device__ __forceinline__ void stash_pair(TileT& t, int col, int pair, float lo, float hi) {
+    *reinterpret_cast<__nv_bfloat162*>(&t.v[col][2 * pair]) = __floats2bfloat162_rn(lo, hi);
+}
+// write the tile transposed: out_t[(col0 + c) * ld + row0 + 0..63], one 128-byte run per warp instruction
+__device__ __forceinline__ void flush_transposed(const TileT& t, void* out_t, int64_t ld, int col0, int row0) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < kTile / (kTileThreads / 32); ++i) {
+        const int c = warp * (kTile / (kTileThreads / 32)) + i;
+        const uint32_t word = *reinterpret_cast<const uint32_t*>(&t.v[c][2 * lane]);
+        *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(out_t) + ((col0 + c) * ld + row0 + 2 * lane) * 2) = word;
+    }
+}
+__device__ __forceinline__ void unpack8(const int4& raw, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 v = __bfloat1622float2(h[j]);
+        f[2 * j] = v.x;
+        f[2 * j + 1] = v.y;
+    }
+}
+__device__ __forceinline__ int4 pack8(const float (&f)[8]) {
+    int4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+    return raw;
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// one CTA = one strip of 64 rows, all columns (the per-row dot product needs the whole row)
+__global__ void __launch_bounds__(kTileThreads) moe_bwd_prep_kernel(const MoeBwdArgs a) {
+    __shared__ TileT tile;
+    const int pair = threadIdx.x >> 3, c8 = threadIdx.x & 7;
+    const int row0 = blockIdx.x * kTile;
+    const int H = a.cols;
+    const uint8_t* gb = reinterpret_cast<const uint8_t*>(a.g);
+    const uint8_t* yb = reinterpret_cast<const uint8_t*>(a.y);
+    uint8_t* ob = reinterpret_cast<uint8_t*>(a.out);
+    float dot[2] = {0.f, 0.f}, w[2];
+    bool ok[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = row0 + 2 * pair + r;
+        ok[r] = a.valid[row] != 0;
+        w[r] = ok[r] ? a.w[row] : 0.f;
+    }
+    for (int col0 = 0; col0 < H; col0 += kTile) {
+        float res[2][8];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int64_t off = (static_cast<int64_t>(row0 + 2 * pair + r) * H + col0 + c8 * 8) * 2;
+            float g[8], y[8];
+            if (ok[r]) {
+                unpack8(ptx::ld_nc_v4(gb + off), g);
+                unpack8(ptx::ld_nc_v4(yb + off), y);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) g[j] = y[j] = 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                dot[r] = fmaf(g[j], y[j], dot[r]);
+                res[r][j] = round_bf16(g[j] * w[r]);
+            }
+            *reinterpret_cast<int4*>(ob + off) = pack8(res[r]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) stash_pair(tile, c8 * 8 + j, pair, res[0][j], res[1][j]);
+        __syncthreads();
+        flush_transposed(tile, a.out_t, a.rows, col0, row0);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float d = dot[r];
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        d += __shfl_xor_sync(0xffffffffu, d, 4);
+        if (c8 == 0) a.row_dot[row0 + 2 * pair + r] = d;
+    }
+}
+
+// grid (rows / 64, I / 64)
+__global__ void __launch_bounds__(kTileThreads) moe_bwd_swiglu_kernel(const MoeBwdArgs a) {
+    __shared__ TileT t_gate, t_up, t_act;
+    const int pair = threadIdx.x >> 3, c8 = threadIdx.x & 7;
+    const int row0 = blockIdx.x * kTile, col0 = blockIdx.y * kTile;
+    const int I = a.cols;
+    const uint8_t* db = reinterpret_cast<const uint8_t*>(a.g);
+    const uint8_t* hb = reinterpret_cast<const uint8_t*>(a.y);
+    uint8_t* ob = reinterpret_cast<uint8_t*>(a.out);
+    float dg[2][8], du[2][8], act[2][8];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = row0 + 2 * pair + r;
+        const int col = col0 + c8 * 8;
+        if (a.valid[row] != 0) {
+            float d[8], gate[8], up[8];
+            unpack8(ptx::ld_nc_v4(db + (static_cast<int64_t>(row) * I + col) * 2), d);
+            unpack8(ptx::ld_nc_v4(hb + (static_cast<int64_t>(row) * 2 * I + col) * 2), gate);
+            unpack8(ptx::ld_nc_v4(hb + (static_cast<int64_t>(row) * 2 * I + I + col) * 2), up);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float sig = 1.f / (1.f + __expf(-gate[j]));
+                act[r][j] = round_bf16(gate[j] * sig * up[j]);
+                du[r][j] = round_bf16(d[j] * gate[j] * sig);
+                dg[r][j] = round_bf16(d[j] * up[j] * sig * (1.f + gate[j] * (1.f - sig)));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) act[r][j] = du[r][j] = dg[r][j] = 0.f;
+        }
+        *reinterpret_cast<int4*>(ob + (static_cast<int64_t>(row) * 2 * I + col) * 2) = pack8(dg[r]);
+        *reinterpret_cast<int4*>(ob + (static_cast<int64_t>(row) * 2 * I + I + col) * 2) = pack8(du[r]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        stash_pair(t_gate, c8 * 8 + j, pair, dg[0][j], dg[1][j]);
+        stash_pair(t_up, c8 * 8 + j, pair, du[0][j], du[1][j]);
+        stash_pair(t_act, c8 * 8 + j, pair, act[0][j], act[1][j]);
+    }
+    __syncthreads();
+    flush_transposed(t_gate, a.out_t, a.rows, col0, row0);
+    flush_transposed(t_up, a.out_t, a.rows, I + col0, row0);
+    flush_transposed(t_act, a.out2_t, a.rows, col0, row0);
+}
+
+// grid (rows / 64, H / 64)
+__global__ void __launch_bounds__(kTileThreads) moe_bwd_dequant_t_kernel(const MoeBwdArgs a) {
+    __shared__ TileT tile;
+    const int pair = threadIdx.x >> 3, c8 = threadIdx.x & 7;
+    const int row0 = blockIdx.x * kTile, col0 = blockIdx.y * kTile;
+    const int H = a.cols;
+    const uint8_t* qb = reinterpret_cast<const uint8_t*>(a.y);
+    float x[2][8];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = row0 + 2 * pair + r;
+        const int col = col0 + c8 * 8;
+        if (a.valid[row] != 0) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(qb + static_cast<int64_t>(row) * H + col);
+            const float sf = __ldg(a.w + row * a.sf_stride_row + (col / 128) * a.sf_stride_col);
+            const __nv_fp8x2_storage_t* p = reinterpret_cast<const __nv_fp8x2_storage_t*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(p[j], __NV_E4M3);
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+                x[r][2 * j] = f.x * sf;
+                x[r][2 * j + 1] = f.y * sf;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[r][j] = 0.f;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) stash_pair(tile, c8 * 8 + j, pair, x[0][j], x[1][j]);
+    __syncthreads();
+    flush_transposed(tile, a.out_t, a.rows, col0, row0);
+}
+
 }  // namespace
+
+cudaError_t launch_moe_bwd(const MoeBwdArgs& a, cudaStream_t stream) {
+    if (a.rows == 0) return cudaSuccess;
+    if (a.rows % kTile != 0 || a.cols % kTile != 0) return cudaErrorInvalidValue;
+    if (a.op == EP_MOE_BWD_PREP) moe_bwd_prep_kernel<<<a.rows / kTile, kTileThreads, 0, stream>>>(a);
+    else if (a.op == EP_MOE_BWD_SWIGLU) moe_bwd_swiglu_kernel<<<dim3(a.rows / kTile, a.cols / kTile), kTileThreads, 0, stream>>>(a);
+    else if (a.op == EP_MOE_BWD_DEQUANT_T) moe_bwd_dequant_t_kernel<<<dim3(a.rows / kTile, a.cols / kTile), kTileThreads, 0, stream>>>(a);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
 
 cudaError_t launch_swiglu_quant(const SwigluQuantArgs& a, cudaStream_t stream) {
     if (a.rows == 0) return cudaSuccess;

@@ -209,6 +209,102 @@ std::vector<at::Tensor> swiglu_quant(const at::Tensor& h, bool keep_bf16) {
     return {q, sf};
 }
 
+// Weight gradients of a grouped layer: out[e] = a_t[:, k0:k1] @ b_t[:, k0:k1]^T with (k0, k1) = k_off[e], k_off[e + 1]
+// (a_t [M, K_total], b_t [N, K_total] bf16, K = rows of the expert segment; k_off int32 [G + 1], multiples of 64).
+at::Tensor gemm_kgrouped(const at::Tensor& a_t, const at::Tensor& b_t, const at::Tensor& k_off, int64_t num_sms) {
+    TORCH_CHECK(a_t.is_cuda() && a_t.dim() == 2 && a_t.is_contiguous() && a_t.scalar_type() == at::kBFloat16, "a_t must be contiguous bf16 [M, K]");
+    TORCH_CHECK(b_t.is_cuda() && b_t.dim() == 2 && b_t.is_contiguous() && b_t.scalar_type() == at::kBFloat16 && b_t.size(1) == a_t.size(1),
+                "b_t must be contiguous bf16 [N, K]");
+    TORCH_CHECK(k_off.is_cuda() && k_off.scalar_type() == at::kInt && k_off.is_contiguous() && k_off.numel() >= 2, "k_off must be int32 [G + 1]");
+    const int64_t M = a_t.size(0), N = b_t.size(0), K = a_t.size(1), G = k_off.numel() - 1;
+    at::Tensor c = at::empty({G, M, N}, a_t.options());
+    GemmArgs g{};
+    g.a = a_t.data_ptr();
+    g.b = b_t.data_ptr();
+    g.c = c.data_ptr();
+    g.M = static_cast<int>(M);
+    g.N = static_cast<int>(N);
+    g.K = static_cast<int>(K);
+    g.num_groups = static_cast<int>(G);
+    g.lda = K;
+    g.ldb = K;
+    g.ldc = N;
+    g.k_group_off = k_off.data_ptr<int32_t>();
+    g.error = gemm_error_flag(a_t.get_device()).data_ptr<int>();
+    const int sms = num_sms > 0 ? static_cast<int>(num_sms) : at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    cuda_check(ep::launch_gemm(g, sms, at::cuda::getCurrentCUDAStream()), "K-grouped tcgen05 GEMM launch");
+    return c;
+}
+
+const uint8_t* valid_ptr(const at::Tensor& valid, int64_t rows) {
+    TORCH_CHECK(valid.is_cuda() && valid.is_contiguous() && valid.numel() == rows && (valid.scalar_type() == at::kBool || valid.scalar_type() == at::kByte),
+                "valid must be a bool / uint8 tensor with one entry per row");
+    return reinterpret_cast<const uint8_t*>(valid.data_ptr());
+}
+
+// Backward of the weighted combine at the expert rows: (g * w [rows, H], its transpose [H, rows], sum(g * y) per row)
+std::vector<at::Tensor> moe_bwd_prep(const at::Tensor& g_rows, const at::Tensor& y, const at::Tensor& w, const at::Tensor& valid) {
+    TORCH_CHECK(g_rows.is_cuda() && g_rows.dim() == 2 && g_rows.is_contiguous() && g_rows.scalar_type() == at::kBFloat16, "g must be contiguous bf16 [rows, H]");
+    TORCH_CHECK(y.is_contiguous() && y.scalar_type() == at::kBFloat16 && y.sizes() == g_rows.sizes(), "y must match g");
+    const int64_t rows = g_rows.size(0), H = g_rows.size(1);
+    TORCH_CHECK(w.is_contiguous() && w.scalar_type() == at::kFloat && w.numel() == rows, "w must be fp32 [rows]");
+    at::Tensor out = at::empty({rows, H}, g_rows.options()), out_t = at::empty({H, rows}, g_rows.options());
+    at::Tensor dot = at::empty({rows}, g_rows.options().dtype(at::kFloat));
+    MoeBwdArgs a{};
+    a.op = EP_MOE_BWD_PREP;
+    a.rows = static_cast<int>(rows);
+    a.cols = static_cast<int>(H);
+    a.valid = valid_ptr(valid, rows);
+    a.g = g_rows.data_ptr();
+    a.y = y.data_ptr();
+    a.w = w.data_ptr<float>();
+    a.out = out.data_ptr();
+    a.out_t = out_t.data_ptr();
+    a.row_dot = dot.data_ptr<float>();
+    cuda_check(ep::launch_moe_bwd(a, at::cuda::getCurrentCUDAStream()), "MoE backward prep launch");
+    return {out, out_t, dot};
+}
+
+// Backward of SwiGLU: (d_h [rows, 2I], d_h^T [2I, rows], activation^T [I, rows])
+std::vector<at::Tensor> swiglu_bwd(const at::Tensor& d_act, const at::Tensor& h, const at::Tensor& valid) {
+    TORCH_CHECK(d_act.is_cuda() && d_act.dim() == 2 && d_act.is_contiguous() && d_act.scalar_type() == at::kBFloat16, "d_act must be contiguous bf16 [rows, I]");
+    const int64_t rows = d_act.size(0), I = d_act.size(1);
+    TORCH_CHECK(h.is_contiguous() && h.scalar_type() == at::kBFloat16 && h.dim() == 2 && h.size(0) == rows && h.size(1) == 2 * I, "h must be bf16 [rows, 2I]");
+    at::Tensor out = at::empty({rows, 2 * I}, h.options()), out_t = at::empty({2 * I, rows}, h.options()), act_t = at::empty({I, rows}, h.options());
+    MoeBwdArgs a{};
+    a.op = EP_MOE_BWD_SWIGLU;
+    a.rows = static_cast<int>(rows);
+    a.cols = static_cast<int>(I);
+    a.valid = valid_ptr(valid, rows);
+    a.g = d_act.data_ptr();
+    a.y = h.data_ptr();
+    a.out = out.data_ptr();
+    a.out_t = out_t.data_ptr();
+    a.out2_t = act_t.data_ptr();
+    cuda_check(ep::launch_moe_bwd(a, at::cuda::getCurrentCUDAStream()), "SwiGLU backward launch");
+    return {out, out_t, act_t};
+}
+
+// (q e4m3 [rows, H], scales per (row, 128 channels), any strides) -> bf16 (q * scale)^T [H, rows]
+at::Tensor dequant_transpose(const at::Tensor& q, const at::Tensor& sf, const at::Tensor& valid) {
+    TORCH_CHECK(q.is_cuda() && q.dim() == 2 && q.is_contiguous() && q.scalar_type() == at::kFloat8_e4m3fn, "q must be contiguous e4m3 [rows, H]");
+    const int64_t rows = q.size(0), H = q.size(1);
+    TORCH_CHECK(sf.scalar_type() == at::kFloat && sf.dim() == 2 && sf.size(0) >= rows && sf.size(1) == (H + 127) / 128, "bad scales");
+    at::Tensor out_t = at::empty({H, rows}, q.options().dtype(at::kBFloat16));
+    MoeBwdArgs a{};
+    a.op = EP_MOE_BWD_DEQUANT_T;
+    a.rows = static_cast<int>(rows);
+    a.cols = static_cast<int>(H);
+    a.valid = valid_ptr(valid, rows);
+    a.y = q.data_ptr();
+    a.w = sf.data_ptr<float>();
+    a.sf_stride_row = sf.stride(0);
+    a.sf_stride_col = sf.stride(1);
+    a.out_t = out_t.data_ptr();
+    cuda_check(ep::launch_moe_bwd(a, at::cuda::getCurrentCUDAStream()), "dequant-transpose launch");
+    return out_t;
+}
+
 // Debug aid: print the native call stack when the process receives SIGSEGV, then re-raise.
 void segv_backtrace_handler(int sig) {
     void* frames[64];
@@ -413,6 +509,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("ag_gemm", &ag_gemm);
     m.def("gemm_rs", &gemm_rs);
     m.def("swiglu_quant", &swiglu_quant, py::arg("h"), py::arg("keep_bf16") = false);
+    m.def("gemm_kgrouped", &gemm_kgrouped, py::arg("a_t"), py::arg("b_t"), py::arg("k_off"), py::arg("num_sms") = 0);
+    m.def("moe_bwd_prep", &moe_bwd_prep);
+    m.def("swiglu_bwd", &swiglu_bwd);
+    m.def("dequant_transpose", &dequant_transpose);
     m.def("gemm_error", [](int device) { return gemm_error_flag(device).item<int>(); });
     m.def("install_segv_backtrace", [] { signal(SIGSEGV, segv_backtrace_handler); });
     m.def("get_dispatch_layout", &get_dispatch_layout);

@@ -17,7 +17,6 @@ import torch.nn as nn
 
 from ..buffers.elastic import ElasticBuffer
 from ..ops import gemm as G
-from ..utils.math import per_token_cast_back
 
 
 class _MoEFunction(torch.autograd.Function):
@@ -31,54 +30,37 @@ class _MoEFunction(torch.autograd.Function):
         tile_group, valid_row = G.expert_tile_groups(handle.psum_num_recv_tokens_per_expert, rows)
         q13, s13, q2, s2 = layer.fp8_weights()
         h = G.grouped_gemm_nt(rx, q13, tile_group, sfa=rsf, sfb=s13)                       # [rows, 2I]
-        a2, sf2, act = G.swiglu_quant(h, keep_bf16=True)
+        a2, sf2 = G.swiglu_quant(h)
         y = buf.get_combine_buffer(handle)
         G.grouped_gemm_nt(a2, q2, tile_group, out=y, sfa=sf2, sfb=s2)                      # [rows, H] in the combine region
         out, _, _ = buf.combine(y, handle, weighted=True, num_sms=layer.num_sms)
         ctx.layer, ctx.handle = layer, handle
-        ctx.save_for_backward(rx, rsf, recv_w, h, act, y.clone(), tile_group, valid_row, w13, w2)
+        # the combine region is reused by the next call, so the expert outputs (needed for d loss / d weight) are copied
+        ctx.save_for_backward(rx, rsf, recv_w, h, y.clone(), tile_group, valid_row)
         return out
 
     @staticmethod
     def backward(ctx, d_out):
         layer, handle = ctx.layer, ctx.handle
         buf: ElasticBuffer = layer.buffer
-        rx, rsf, recv_w, h, act, y, tile_group, valid_row, w13, w2 = ctx.saved_tensors
-        I = act.shape[1]
-        El = w13.shape[0]
-        # backward of the weighted combine: every expert row receives its token's gradient
+        rx, rsf, recv_w, h, y, tile_group, valid_row = ctx.saved_tensors
+        seg_off = G.segment_offsets(handle.psum_num_recv_tokens_per_expert)
+        # backward of the weighted combine: every expert row receives its token's gradient (cached dispatch), then one
+        # kernel forms d y = g * w (row-major for the data gradient, transposed for the weight gradient) and d w = <g, y>
         g_rows, _, _, _, _ = buf.dispatch(d_out.contiguous(), handle=handle, fused_fp8_cast=False, num_sms=layer.num_sms)
-        g_rows = torch.where(valid_row.unsqueeze(1), g_rows, torch.zeros_like(g_rows))
-        d_w_rows = (g_rows.float() * y.float()).sum(dim=1)                                  # d loss / d weight of each row
-        dy = (g_rows.float() * recv_w.unsqueeze(1)).to(torch.bfloat16)
-        # down projection
+        dy, dy_t, d_w_rows = G.moe_bwd_prep(g_rows, y, recv_w.contiguous(), valid_row)
         w2_t, w13_t = layer.transposed_weights()
+        # down projection
         d_act = G.grouped_gemm_nt(dy, w2_t, tile_group)                                     # [rows, I]
-        d_act = torch.where(valid_row.unsqueeze(1), d_act, torch.zeros_like(d_act))
-        gate, up = h[:, :I].float(), h[:, I:].float()
-        sig = torch.sigmoid(gate)
-        d_up = d_act.float() * gate * sig
-        d_gate = d_act.float() * up * sig * (1 + gate * (1 - sig))
-        dh = torch.cat([d_gate, d_up], dim=1).to(torch.bfloat16)
-        dh = torch.where(valid_row.unsqueeze(1), dh, torch.zeros_like(dh))
+        dh, dh_t, act_t = G.swiglu_bwd(d_act, h, valid_row)
         # up projection: the gradient rows go into the combine region and travel home (backward of dispatch)
         d_recv = buf.get_combine_buffer(handle)
         G.grouped_gemm_nt(dh, w13_t, tile_group, out=d_recv)
         dx, d_topk_w, _ = buf.combine(d_recv, handle, topk_weights=d_w_rows, num_sms=layer.num_sms)
-        # weight gradients, one expert segment at a time (K = rows of the segment)
-        x_rows = per_token_cast_back(rx, rsf.contiguous() if rsf.stride(1) != 1 else rsf)
-        x_rows = torch.where(valid_row.unsqueeze(1), x_rows, torch.zeros_like(x_rows))
-        act_m = torch.where(valid_row.unsqueeze(1), act, torch.zeros_like(act))
-        d_w13, d_w2 = torch.zeros_like(w13), torch.zeros_like(w2)
-        ends = handle.psum_num_recv_tokens_per_expert.tolist()
-        start = 0
-        for e in range(El):
-            stop = (ends[e] + G.BLOCK_M - 1) // G.BLOCK_M * G.BLOCK_M
-            if ends[e] > start:
-                seg = slice(start, stop)
-                d_w2[e] = G.gemm_nt(dy[seg].t().contiguous(), act_m[seg].t().contiguous())
-                d_w13[e] = G.gemm_nt(dh[seg].t().contiguous(), x_rows[seg].t().contiguous())
-            start = stop
+        # weight gradients: one K-grouped GEMM per weight tensor, reduction over the rows of every expert segment
+        x_t = G.dequant_transpose(rx, rsf, valid_row)
+        d_w2 = G.gemm_kgrouped(dy_t, act_t, seg_off)                                        # [El, H, I]
+        d_w13 = G.gemm_kgrouped(dh_t, x_t, seg_off)                                         # [El, 2I, H]
         return dx, d_topk_w, d_w13, d_w2, None, None
 
 

@@ -60,3 +60,35 @@ def expert_tile_groups(psum_expert_ends: torch.Tensor, num_rows: int, alignment:
 def swiglu_quant(h: torch.Tensor, keep_bf16: bool = False):
     """``h [rows, 2I]`` bf16 (gate | up) -> ``(e4m3 [rows, I], scales [rows, I/128][, bf16 activation])``."""
     return _native.load().swiglu_quant(h, keep_bf16)
+
+
+def gemm_kgrouped(a_t: torch.Tensor, b_t: torch.Tensor, k_off: torch.Tensor, num_sms: int = 0) -> torch.Tensor:
+    """Weight gradients of a grouped layer in one launch: ``out[e] = a_t[:, k0:k1] @ b_t[:, k0:k1]^T`` with
+    ``(k0, k1) = (k_off[e], k_off[e + 1])``; ``a_t [M, rows]``, ``b_t [N, rows]`` bf16 (the transposed activations and
+    gradients, so that the reduction dimension = rows of the expert segment is contiguous), ``k_off`` int32
+    ``[G + 1]`` multiples of 64 on the device.  -> bf16 ``[G, M, N]``; an expert without rows gets zeros."""
+    return _native.load().gemm_kgrouped(a_t, b_t, k_off, num_sms)
+
+
+def segment_offsets(psum_expert_ends: torch.Tensor, alignment: int = BLOCK_M) -> torch.Tensor:
+    """Expand-layout segment boundaries as ``int32 [G + 1]``: segment ``e`` covers rows ``[off[e], off[e + 1])``
+    including its alignment padding.  Stays on the device."""
+    ends = psum_expert_ends.to(torch.int64)
+    aligned = (ends + alignment - 1) // alignment * alignment
+    return torch.cat([torch.zeros(1, dtype=torch.int64, device=ends.device), aligned]).to(torch.int32).contiguous()
+
+
+def moe_bwd_prep(g_rows: torch.Tensor, y: torch.Tensor, w: torch.Tensor, valid_row: torch.Tensor):
+    """Backward of the weighted combine at the expert rows -> ``(g * w [rows, H], (g * w)^T [H, rows], sum(g * y) [rows])``;
+    padding rows give zeros."""
+    return _native.load().moe_bwd_prep(g_rows, y, w, valid_row)
+
+
+def swiglu_bwd(d_act: torch.Tensor, h: torch.Tensor, valid_row: torch.Tensor):
+    """Backward of ``silu(gate) * up`` -> ``(d_h [rows, 2I], d_h^T [2I, rows], activation^T [I, rows])``."""
+    return _native.load().swiglu_bwd(d_act, h, valid_row)
+
+
+def dequant_transpose(q: torch.Tensor, sf: torch.Tensor, valid_row: torch.Tensor) -> torch.Tensor:
+    """e4m3 rows with 1 x 128 scales -> bf16 ``(q * scale)^T [H, rows]``; padding rows give zeros."""
+    return _native.load().dequant_transpose(q, sf, valid_row)

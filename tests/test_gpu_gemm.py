@@ -65,3 +65,27 @@ def test_fp8_blockscaled_grouped_gemm(M, N, K, G):
         ref = a_deq[rows] @ b_deq.t()
         err = (c[rows].float() - ref).abs().max().item()
         assert err <= 2e-2 * ref.abs().max().item() + 1e-2, (t, err)
+
+
+@pytest.mark.parametrize('M,N,segs', [(128, 128, [64, 0, 192]), (384, 520, [128, 256, 0, 0, 640]), (2048, 7168, [1152, 1024, 0, 1280])])
+def test_k_grouped_gemm(M, N, segs):
+    """out[e] = a_t[:, seg_e] @ b_t[:, seg_e]^T (weight gradients of a grouped layer); empty segments give zeros."""
+    from deepep_ascend_b200.ops import gemm as G
+    C = _C()
+    g = torch.Generator(device='cuda').manual_seed(M + N)
+    K = sum(segs)
+    a_t = torch.randn(M, K, device='cuda', generator=g).bfloat16()
+    b_t = torch.randn(N, K, device='cuda', generator=g).bfloat16()
+    off = torch.tensor([0] + list(torch.tensor(segs).cumsum(0)), dtype=torch.int32, device='cuda')
+    out = G.gemm_kgrouped(a_t, b_t, off)
+    torch.cuda.synchronize()
+    assert C.gemm_error(0) == 0
+    assert out.shape == (len(segs), M, N)
+    k0 = 0
+    for e, n in enumerate(segs):
+        ref = a_t[:, k0:k0 + n].float() @ b_t[:, k0:k0 + n].float().t()
+        err = (out[e].float() - ref).abs().max().item()
+        assert err <= 2e-2 * max(ref.abs().max().item(), 1.0) + 1e-2, (e, err)
+        if n == 0:
+            assert out[e].abs().max().item() == 0
+        k0 += n

@@ -40,3 +40,40 @@ def test_fused_moe_forward_backward(T, H, I, E, K):
         assert calc_diff(layer.w13.grad.float(), w13.grad) < 3e-3, calc_diff(layer.w13.grad.float(), w13.grad)
     finally:
         buf.destroy()
+
+
+@pytest.mark.parametrize('rows,H,I', [(128, 256, 128), (640, 1024, 512)])
+def test_backward_elementwise_kernels(rows, H, I):
+    """The three element-wise kernels of the backward pass (row-major and transposed outputs) vs PyTorch."""
+    from deepep_ascend_b200.ops import gemm as G
+    from deepep_ascend_b200.utils.math import per_token_cast_to_fp8, per_token_cast_back
+    torch.manual_seed(rows)
+    valid = torch.rand(rows, device='cuda') > 0.2
+    g = torch.randn(rows, H, device='cuda').bfloat16()
+    y = torch.randn(rows, H, device='cuda').bfloat16()
+    w = torch.rand(rows, device='cuda')
+    dy, dy_t, dot = G.moe_bwd_prep(g, y, w, valid)
+    vm = valid.unsqueeze(1)
+    ref_dy = torch.where(vm, (g.float() * w.unsqueeze(1)).bfloat16(), torch.zeros_like(g))
+    assert torch.equal(dy, ref_dy)
+    assert torch.equal(dy_t, ref_dy.t().contiguous())
+    ref_dot = torch.where(valid, (g.float() * y.float()).sum(1), torch.zeros_like(w))
+    torch.testing.assert_close(dot, ref_dot, rtol=1e-4, atol=1e-3)
+
+    d_act = torch.randn(rows, I, device='cuda').bfloat16()
+    h = torch.randn(rows, 2 * I, device='cuda').bfloat16()
+    dh, dh_t, act_t = G.swiglu_bwd(d_act, h, valid)
+    gate, up, d = h[:, :I].float(), h[:, I:].float(), d_act.float()
+    sig = torch.sigmoid(gate)
+    ref_dh = torch.cat([d * up * sig * (1 + gate * (1 - sig)), d * gate * sig], dim=1)
+    ref_dh = torch.where(vm, ref_dh, torch.zeros_like(ref_dh))
+    ref_act = torch.where(vm, gate * sig * up, torch.zeros_like(gate))
+    torch.testing.assert_close(dh.float(), ref_dh, rtol=2e-2, atol=2e-2)
+    assert torch.equal(dh_t, dh.t().contiguous())
+    torch.testing.assert_close(act_t.float(), ref_act.t(), rtol=2e-2, atol=2e-2)
+
+    x = torch.randn(rows, H, device='cuda').bfloat16()
+    q, sf = per_token_cast_to_fp8(x)
+    x_t = G.dequant_transpose(q, sf, valid)
+    ref_x = torch.where(vm, per_token_cast_back(q, sf).bfloat16(), torch.zeros_like(x))
+    assert torch.equal(x_t, ref_x.t().contiguous())
