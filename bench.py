@@ -236,18 +236,36 @@ def main():
     e2e = None
     if not args.no_e2e:
         # end to end through the public API: every step copies its inputs from pinned host memory, runs
-        # dispatch + combine, and reads one fp32 checksum of the combined tokens back to the host
+        # dispatch + combine, and reads one fp32 checksum of the combined tokens back to the host; all `steps`
+        # copies happen inside the timed region
         steps = max(3, min(args.steps, 10))
-        x_d, idx_d, w_d = torch.empty_like(x), torch.empty_like(idx), torch.empty_like(w)
+        # two sets of device input buffers: the copy of step i+1 (on its own stream) overlaps the kernels of step i
+        x_d = [torch.empty_like(x) for _ in range(2)]
+        idx_d = [torch.empty_like(idx) for _ in range(2)]
+        w_d = [torch.empty_like(w) for _ in range(2)]
+        copy_stream = torch.cuda.Stream()
+        ready = [torch.cuda.Event(), torch.cuda.Event()]
+
+        def prefetch(i):
+            b = i & 1
+            with torch.cuda.stream(copy_stream):
+                x_d[b].copy_(x_host, non_blocking=True)
+                idx_d[b].copy_(idx_host, non_blocking=True)
+                w_d[b].copy_(w_host, non_blocking=True)
+                ready[b].record(copy_stream)
         checksum = 0.0
-        for i in range(3 + steps):
+        total = 3 + steps
+        for i in range(total):
             if i == 3:
                 sync_all()
                 t0 = time.perf_counter()
-            x_d.copy_(x_host, non_blocking=True)
-            idx_d.copy_(idx_host, non_blocking=True)
-            w_d.copy_(w_host, non_blocking=True)
-            _, _, _, hd, _ = buf.dispatch(x_d, idx_d, w_d, num_experts=E, num_sms=args.num_sms)
+            if i == 0 or i == 3:
+                prefetch(i)            # nothing is in flight at the start of the warm-up and of the timed region
+            b = i & 1
+            torch.cuda.current_stream().wait_event(ready[b])
+            if i + 1 < total and i + 1 != 3:
+                prefetch(i + 1)        # its buffers were last read by step i-1, which has completed (host read of its result)
+            _, _, _, hd, _ = buf.dispatch(x_d[b], idx_d[b], w_d[b], num_experts=E, num_sms=args.num_sms)
             out, _, _ = buf.combine(buf.get_combine_buffer(hd), hd, num_sms=args.combine_sms or args.num_sms)
             checksum = float(out.sum(dtype=torch.float32).item())
         torch.cuda.synchronize()

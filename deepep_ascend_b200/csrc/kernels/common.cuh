@@ -41,6 +41,7 @@ struct Workspace {
     alignas(128) uint32_t cta_rank_count[EP_MAX_CTAS][EP_MAX_RANKS];
     alignas(128) uint32_t cta_expert_count[EP_MAX_CTAS][EP_MAX_EXPERTS];
     alignas(128) uint32_t ll_counters[4][EP_MAX_EXPERTS];                  // low-latency slot / finish counters
+    alignas(128) uint32_t arrive[EP_NUM_CHANNELS][2];                      // CTAs that finished a phase (arrive_is_last)
 };
 static_assert(sizeof(Workspace) <= EP_WORKSPACE_BYTES, "workspace region too small");
 
@@ -118,6 +119,23 @@ __device__ __forceinline__ bool grid_sync(const RankCtx& ctx, Workspace* ws, int
         __threadfence();
     }
     return __syncthreads_and(ok) != 0;
+}
+
+// Arrival without waiting: returns true in exactly one CTA of the rank's grid row, the last one to get here; the
+// global writes every other CTA made before its own arrival are visible to that CTA.  The counter resets itself, so
+// it can be used again by the next phase that is ordered behind this one.  Needs no co-residency.
+__device__ __forceinline__ bool arrive_is_last(uint32_t* counter) {
+    __shared__ int s_last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const bool last = atomicAdd(counter, 1u) == gridDim.x - 1;
+        if (last) atomicExch(counter, 0u);
+        __threadfence();
+        s_last = last ? 1 : 0;
+    }
+    __syncthreads();
+    return s_last != 0;
 }
 
 // Barrier over all ranks, executed by one whole CTA per rank: every rank adds one arrival to each peer's

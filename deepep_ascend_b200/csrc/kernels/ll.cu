@@ -142,10 +142,10 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
         ptx::bulk_commit();
         ptx::bulk_wait<0>();
         __threadfence_system();
-        alive = grid_sync(ctx, ws, EP_CH_LL_DISPATCH, EP_PH_GRID_SYNC) && alive;
-        // publish how many messages every expert got from this rank (a tagged zero means "none")
-        if (alive) {
-            for (int e = blockIdx.x * blockDim.x + tid; e < E; e += gridDim.x * blockDim.x) {
+        // No grid barrier: the last CTA of this rank to finish its sends publishes how many messages every expert got
+        // from this rank (a tagged zero means "none"); the others go straight on to the receive phase.
+        if (arrive_is_last(&ws->arrive[EP_CH_LL_DISPATCH][0]) && !is_aborted(ws)) {
+            for (int e = tid; e < E; e += blockDim.x) {
                 const uint32_t n_sent = min(__ldcg(&slot_counter[e]), static_cast<uint32_t>(M));
                 __stcg(&slot_counter[e], 0u);
                 if (!rank_masked(a.mask, e / El)) {
@@ -204,24 +204,30 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
                 }
             }
             __syncthreads();
-            // one warp per message, loads issued four at a time
+            // work item = (message, 2 KB piece): the pieces of one message are copied by different warps at the same
+            // time, four 16-byte loads in flight per lane
             const uint32_t cnt = s_count[s], begin = s_begin[s];
-            for (uint32_t i = warp; i < cnt; i += kLLWarps) {
+            const uint32_t pieces = (payload + 2047) / 2048;
+            for (uint32_t u = warp; u < cnt * pieces; u += kLLWarps) {
+                const uint32_t i = u / pieces, c = u - i * pieces;
                 const uint8_t* m = slab + ((static_cast<int64_t>(j) * R + s) * M + i) * a.msg_bytes;
                 const int64_t pos = static_cast<int64_t>(j) * rows_per_expert + begin + i;
-                const int4 hdr = __ldcg(reinterpret_cast<const int4*>(m));
-                if (lane == 0) a.packed_src_info[pos] = (hdr.y << 20) | hdr.x;
                 uint8_t* out = reinterpret_cast<uint8_t*>(a.packed_x) + pos * payload;
-                for (int off = lane * 16; off < payload; off += 4 * 32 * 16) {
+                {
+                    const int off = c * 2048 + lane * 16;
                     int4 v[4];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u)
-                        if (off + u * 512 < payload) v[u] = __ldcg(reinterpret_cast<const int4*>(m + 16 + off + u * 512));
+                    for (int q = 0; q < 4; ++q)
+                        if (off + q * 512 < payload) v[q] = __ldcg(reinterpret_cast<const int4*>(m + 16 + off + q * 512));
 #pragma unroll
-                    for (int u = 0; u < 4; ++u)
-                        if (off + u * 512 < payload) *reinterpret_cast<int4*>(out + off + u * 512) = v[u];
+                    for (int q = 0; q < 4; ++q)
+                        if (off + q * 512 < payload) *reinterpret_cast<int4*>(out + off + q * 512) = v[q];
                 }
-                if (a.use_fp8) {
+                if (c == 0 && lane == 0) {
+                    const int4 hdr = __ldcg(reinterpret_cast<const int4*>(m));
+                    a.packed_src_info[pos] = (hdr.y << 20) | hdr.x;
+                }
+                if (a.use_fp8 && c == pieces - 1) {
                     const float* sf = reinterpret_cast<const float*>(m + 16 + H);
                     if (a.use_ue8m0) {
                         // four exponents per int32, groups along the slow axis: [E_local, ceil(G/4), R*M]
@@ -238,9 +244,8 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
                 }
             }
         }
-        const bool cta_ok = __syncthreads_and(alive ? 1 : 0) != 0;
-        alive = grid_sync(ctx, ws, EP_CH_LL_DISPATCH, EP_PH_GRID_SYNC) && cta_ok;
-        if (blockIdx.x == 0 && tid == 0) ws->epoch[EP_CH_LL_DISPATCH] = epoch;
+        // the call is complete when the last CTA gets here (every CTA read the epoch before it arrived)
+        if (arrive_is_last(&ws->arrive[EP_CH_LL_DISPATCH][1]) && tid == 0) ws->epoch[EP_CH_LL_DISPATCH] = epoch;
     }
 }
 
@@ -304,9 +309,8 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
         ptx::bulk_commit();
         ptx::bulk_wait<0>();
         __threadfence_system();
-        const bool cta_ok = __syncthreads_and(alive ? 1 : 0) != 0;
-        alive = grid_sync(ctx, ws, EP_CH_LL_COMBINE, EP_PH_GRID_SYNC) && cta_ok;
-        if (alive && blockIdx.x == 0 && tid < R && !rank_masked(a.mask, tid)) {
+        // the last CTA of this rank to finish its stores raises this rank's flag at every peer (no grid barrier)
+        if (arrive_is_last(&ws->arrive[EP_CH_LL_COMBINE][0]) && !is_aborted(ws) && tid < R && !rank_masked(a.mask, tid)) {
             Workspace* pws = reinterpret_cast<Workspace*>(s_peer[tid]);
             ptx::st_release_sys(&pws->ll_signal[1][me], tag_value(epoch, 1));
         }
@@ -384,10 +388,7 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
                 }
             }
         }
-        const bool cta_ok = __syncthreads_and(alive ? 1 : 0) != 0;
-        grid_sync(ctx, ws, EP_CH_LL_COMBINE, EP_PH_GRID_SYNC);
-        (void)cta_ok;
-        if (blockIdx.x == 0 && tid == 0) ws->epoch[EP_CH_LL_COMBINE] = epoch;
+        if (arrive_is_last(&ws->arrive[EP_CH_LL_COMBINE][1]) && tid == 0) ws->epoch[EP_CH_LL_COMBINE] = epoch;
     }
 }
 
