@@ -601,43 +601,48 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
     if (a.side_packed && alive) {
         // every row has arrived: turn the global expert ids of the received side records into ids relative to this
         // rank's first expert (-1 for experts of other ranks) and fill in source rank * K + the lane that sent the row.
-        // One thread per row; all ids of a row are loaded before any is written back.
+        // One lane per (row, top-k lane), so the ids of a row are read and written as one contiguous run; four rows'
+        // worth of loads are in flight per lane before the first store.
         const int num_recv = __ldcg(a.psum_rank + (R - 1));
         const int lo = me * El;
-        for (int row = cta * nthreads + tid; row < num_recv; row += num_ctas * nthreads) {
-            uint8_t* rec = s_peer[me] + a.off_recv_side + static_cast<int64_t>(row) * a.side_bytes;
-            int2* mp = reinterpret_cast<int2*>(rec + a.side_off_meta);
-            int2 m = __ldcg(mp);
-            int master = 0;
-            if (a.idx_is_64) {
-                long long* p = reinterpret_cast<long long*>(rec + a.side_off_idx);
-                long long gidx[EP_MAX_TOPK];
+        const int grp = K <= 8 ? 8 : 16, rows_per_step = 32 / grp;
+        const int sub = lane / grp, k = lane - sub * grp;
+        const uint32_t grp_mask = (grp == 8 ? 0xffu : 0xffffu) << (sub * grp);
+        constexpr int kBatch = 4;
+        const int stride = num_ctas * num_warps * rows_per_step;
+        for (int row0 = (cta * num_warps + warp) * rows_per_step; row0 < num_recv; row0 += kBatch * stride) {
+            long long gidx[kBatch];
+            int2 meta[kBatch];
 #pragma unroll
-                for (int k = 0; k < EP_MAX_TOPK; ++k)
-                    if (k < K) gidx[k] = __ldcg(p + k);
-#pragma unroll
-                for (int k = 0; k < EP_MAX_TOPK; ++k)
-                    if (k < K) {
-                        const bool mine = gidx[k] >= lo && gidx[k] < lo + El;
-                        if (mine) master = k;
-                        p[k] = mine ? gidx[k] - lo : -1;
-                    }
-            } else {
-                int* p = reinterpret_cast<int*>(rec + a.side_off_idx);
-                int gidx[EP_MAX_TOPK];
-#pragma unroll
-                for (int k = 0; k < EP_MAX_TOPK; ++k)
-                    if (k < K) gidx[k] = __ldcg(p + k);
-#pragma unroll
-                for (int k = 0; k < EP_MAX_TOPK; ++k)
-                    if (k < K) {
-                        const bool mine = gidx[k] >= lo && gidx[k] < lo + El;
-                        if (mine) master = k;
-                        p[k] = mine ? gidx[k] - lo : -1;
-                    }
+            for (int b = 0; b < kBatch; ++b) {
+                const int row = row0 + b * stride + sub;
+                gidx[b] = -1;
+                if (row < num_recv) {
+                    const uint8_t* rec = s_peer[me] + a.off_recv_side + static_cast<int64_t>(row) * a.side_bytes;
+                    if (k < K)
+                        gidx[b] = a.idx_is_64 ? __ldcg(reinterpret_cast<const long long*>(rec + a.side_off_idx) + k)
+                                              : static_cast<long long>(__ldcg(reinterpret_cast<const int*>(rec + a.side_off_idx) + k));
+                    if (k == 0) meta[b] = __ldcg(reinterpret_cast<const int2*>(rec + a.side_off_meta));
+                }
             }
-            m.y = (m.x / a.num_max_tokens) * K + master;
-            *mp = m;
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+                const int row = row0 + b * stride + sub;
+                const bool mine = gidx[b] >= lo && gidx[b] < lo + El;
+                const uint32_t hits = __ballot_sync(0xffffffffu, mine) & grp_mask;
+                if (row < num_recv) {
+                    uint8_t* rec = s_peer[me] + a.off_recv_side + static_cast<int64_t>(row) * a.side_bytes;
+                    if (k < K) {
+                        const long long local = mine ? gidx[b] - lo : -1;
+                        if (a.idx_is_64) reinterpret_cast<long long*>(rec + a.side_off_idx)[k] = local;
+                        else reinterpret_cast<int*>(rec + a.side_off_idx)[k] = static_cast<int>(local);
+                    }
+                    if (k == 0) {
+                        const int master = hits ? (31 - __clz(hits)) - sub * grp : 0;
+                        *reinterpret_cast<int2*>(rec + a.side_off_meta) = make_int2(meta[b].x, (meta[b].x / a.num_max_tokens) * K + master);
+                    }
+                }
+            }
         }
     }
     stamp(7);
