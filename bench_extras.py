@@ -154,14 +154,17 @@ def main():
         El = E // world
         y = torch.randn(El, world * M, H, device='cuda').bfloat16()
         cur = torch.cuda.current_stream()
-        for sms in (32, 64, 132):
+        for sms, hooked in ((32, False), (64, False), (132, False), (132, True)):
+            # hooked = the send and the receive phase are separate launches (no SM is held while data is in flight)
             def d():
-                return buf.low_latency_dispatch(x, idx, M, E, use_fp8=True, return_recv_hook=True, num_sms=sms)
+                return buf.low_latency_dispatch(x, idx, M, E, use_fp8=True, return_recv_hook=hooked, num_sms=sms)
             def run_pair():
                 recv, cnt, handle, _, hook = d()
-                hook()
-                out, _, hook2 = buf.low_latency_combine(y, idx, w, handle, return_recv_hook=True, num_sms=sms)
-                hook2()
+                if hooked:
+                    hook()
+                out, _, hook2 = buf.low_latency_combine(y, idx, w, handle, return_recv_hook=hooked, num_sms=sms)
+                if hooked:
+                    hook2()
                 return handle
             handle = run_pair()
             torch.cuda.synchronize()
@@ -173,10 +176,12 @@ def main():
             with torch.cuda.stream(side):
                 with torch.cuda.graph(gd, stream=side):
                     recv, cnt, handle, _, hook = d()
-                    hook()
+                    if hooked:
+                        hook()
                 with torch.cuda.graph(gc, stream=side):
-                    out, _, hook2 = buf.low_latency_combine(y, idx, w, handle, return_recv_hook=True, num_sms=sms)
-                    hook2()
+                    out, _, hook2 = buf.low_latency_combine(y, idx, w, handle, return_recv_hook=hooked, num_sms=sms)
+                    if hooked:
+                        hook2()
             torch.cuda.synchronize()
             td, tc = [], []
             for i in range(5 + 100):
@@ -195,10 +200,20 @@ def main():
             torch.cuda.synchronize()
             td = reduce_max([a.elapsed_time(b) * 1e3 for a, b in td])
             tc = reduce_max([a.elapsed_time(b) * 1e3 for a, b in tc])
-            emit(bench='low_latency_cuda_graph', num_sms=sms, tokens=Tll, dispatch_p50_us=float(np.percentile(td, 50)),
+            emit(bench='low_latency_cuda_graph', num_sms=sms, send_recv_split=hooked, tokens=Tll, dispatch_p50_us=float(np.percentile(td, 50)),
                  dispatch_p99_us=float(np.percentile(td, 99)), combine_p50_us=float(np.percentile(tc, 50)),
                  combine_p99_us=float(np.percentile(tc, 99)), reference='77 / 114 us (H800 + CX7 RDMA, published)')
             buf.check_status()
+            if not hooked and sms == 132:
+                # where the time goes: device timestamps of one eager call per kernel (us since kernel start, this rank)
+                buf.enable_profiling(True)
+                for _ in range(3):
+                    if world > 1:
+                        buf.barrier(use_comm_stream=False)
+                    run_pair()
+                pt = buf.phase_times()
+                buf.enable_profiling(False)
+                emit(bench='low_latency_phase_us', num_sms=sms, dispatch=pt['ll_dispatch'], combine=pt['ll_combine'])
         buf.destroy()
 
     # ------------------------------------------------------------------ fused MoE layer forward + backward

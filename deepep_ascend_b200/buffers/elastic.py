@@ -636,7 +636,8 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         """Make dispatch / combine record device-side phase timestamps (ns, CTA 0 of this rank); read them with
         :meth:`phase_times`.  Dispatch: start, counted, exchanged, assigned, scattered, grid drained, peers done.
         Combine: start, entry barrier, pulled, grid drained, exit barrier."""
-        self.profile = {k: torch.zeros(8, dtype=torch.int64, device='cuda') for k in ('dispatch', 'combine')} if enabled else None
+        keys = ('dispatch', 'combine', 'll_dispatch', 'll_combine')
+        self.profile = {k: torch.zeros(8, dtype=torch.int64, device='cuda') for k in keys} if enabled else None
 
     def phase_times(self) -> dict:
         """Microseconds spent in each phase of the last dispatch and combine."""
@@ -644,8 +645,16 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         d, c = self.profile['dispatch'].tolist(), self.profile['combine'].tolist()
         names_d = ['layout_count', 'count_exchange', 'assign_rows', 'scatter', 'grid_drain', 'peer_done', 'localise_ids']
         names_c = ['entry_barrier', 'pull_reduce', 'grid_drain', 'exit_barrier']
-        return {'dispatch': {n: (d[i + 1] - d[i]) / 1e3 for i, n in enumerate(names_d) if d[i + 1] and d[i]},
-                'combine': {n: (c[i + 1] - c[i]) / 1e3 for i, n in enumerate(names_c) if c[i + 1] and c[i]}}
+        out = {'dispatch': {n: (d[i + 1] - d[i]) / 1e3 for i, n in enumerate(names_d) if d[i + 1] and d[i]},
+               'combine': {n: (c[i + 1] - c[i]) / 1e3 for i, n in enumerate(names_c) if c[i + 1] and c[i]}}
+        # low-latency kernels: microseconds since the start of the kernel at which each point was reached (CTA 0, except
+        # "published", which the last CTA to finish its sends records)
+        names = {'ll_dispatch': ['sends_issued', 'sends_complete', 'counts_published', 'counts_received', 'packed', 'end'],
+                 'll_combine': ['stores_issued', 'stores_complete', 'flags_published', 'flags_received', 'reduced', 'end']}
+        for key, ns in names.items():
+            v = self.profile[key].tolist()
+            out[key] = {n: (v[i + 1] - v[0]) / 1e3 for i, n in enumerate(ns) if v[i + 1] and v[0]}
+        return out
 
     # ------------------------------------------------------------------------------------------ failures
     def check_status(self) -> None:

@@ -85,6 +85,8 @@ class LowLatencyMixin:
             call.stats = cumulative_stats
         if wait_stats is not None:
             call.wait_stats = wait_stats
+        if self.profile is not None:
+            call.prof = self.profile['ll_dispatch']
         call.mask = ll['mask']
         call.shrink = self.low_latency_shrink
         return call, sf_view
@@ -141,6 +143,8 @@ class LowLatencyMixin:
         call.off_slab0, call.off_slab1 = ll['combine'][0], ll['combine'][1]
         if wait_stats is not None:
             call.wait_stats = wait_stats
+        if self.profile is not None:
+            call.prof = self.profile['ll_combine']
         call.mask = ll['mask']
         call.shrink = self.low_latency_shrink
         return call

@@ -185,6 +185,8 @@ struct LLDispatchArgs {
     int64_t* wait_stats;         // [R] accumulated wait ns per source rank, or null
     int32_t* mask;               // [R] ranks to ignore (shrink mode) or null
     int shrink;                  // a source that never arrives is masked instead of poisoning the buffer
+    uint64_t* prof;              // [8] phase timestamps (ns) or null: start, sends issued, sends complete, counts published
+                                 //     (by the last CTA), first counts received, packed, end
 };
 
 struct LLCombineArgs {
@@ -202,6 +204,8 @@ struct LLCombineArgs {
     int64_t* wait_stats;
     int32_t* mask;
     int shrink;
+    uint64_t* prof;              // [8] phase timestamps (ns) or null: start, stores issued, stores complete, flags published
+                                 //     (by the last CTA), flags received, reduced
 };
 
 namespace ep {

@@ -80,6 +80,10 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
     __syncthreads();
     bool alive = !is_aborted(ws);
     uint32_t* slot_counter = ws->ll_counters[0];
+    auto stamp = [&](int i) {
+        if (a.prof != nullptr && blockIdx.x == 0 && tid == 0) a.prof[i] = globaltimer_ns();
+    };
+    stamp(0);
 
     if (a.phases & EP_LL_SEND) {
         if (blockIdx.x == 0)
@@ -140,8 +144,10 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
             }
         }
         ptx::bulk_commit();
+        stamp(1);
         ptx::bulk_wait<0>();
         __threadfence_system();
+        stamp(2);
         // No grid barrier: the last CTA of this rank to finish its sends publishes how many messages every expert got
         // from this rank (a tagged zero means "none"); the others go straight on to the receive phase.
         if (arrive_is_last(&ws->arrive[EP_CH_LL_DISPATCH][0]) && !is_aborted(ws)) {
@@ -153,6 +159,7 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
                     ptx::st_release_sys(&pws->ll_signal[0][(e % El) * R + me], tag_value(epoch, n_sent));
                 }
             }
+            if (a.prof != nullptr && tid == 0) a.prof[3] = globaltimer_ns();
         }
     }
 
@@ -191,6 +198,7 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
             }
             alive = __syncthreads_and(ok) != 0;
             if (!alive) break;
+            if (p == 0) stamp(4);
             if (tid == 0) {
                 uint32_t begin = 0;
                 for (int q = 0; q < R; ++q) {
@@ -244,8 +252,12 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
                 }
             }
         }
+        stamp(5);
         // the call is complete when the last CTA gets here (every CTA read the epoch before it arrived)
-        if (arrive_is_last(&ws->arrive[EP_CH_LL_DISPATCH][1]) && tid == 0) ws->epoch[EP_CH_LL_DISPATCH] = epoch;
+        if (arrive_is_last(&ws->arrive[EP_CH_LL_DISPATCH][1]) && tid == 0) {
+            ws->epoch[EP_CH_LL_DISPATCH] = epoch;
+            if (a.prof != nullptr) a.prof[6] = globaltimer_ns();
+        }
     }
 }
 
@@ -274,6 +286,10 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
     __syncthreads();
     ptx::fence_proxy_async_smem();
     bool alive = !is_aborted(ws);
+    auto stamp = [&](int i) {
+        if (a.prof != nullptr && blockIdx.x == 0 && tid == 0) a.prof[i] = globaltimer_ns();
+    };
+    stamp(0);
 
     if (a.phases & EP_LL_SEND) {
         const uint8_t* xb = reinterpret_cast<const uint8_t*>(a.x);
@@ -307,12 +323,17 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
             }
         }
         ptx::bulk_commit();
+        stamp(1);
         ptx::bulk_wait<0>();
         __threadfence_system();
+        stamp(2);
         // the last CTA of this rank to finish its stores raises this rank's flag at every peer (no grid barrier)
-        if (arrive_is_last(&ws->arrive[EP_CH_LL_COMBINE][0]) && !is_aborted(ws) && tid < R && !rank_masked(a.mask, tid)) {
-            Workspace* pws = reinterpret_cast<Workspace*>(s_peer[tid]);
-            ptx::st_release_sys(&pws->ll_signal[1][me], tag_value(epoch, 1));
+        if (arrive_is_last(&ws->arrive[EP_CH_LL_COMBINE][0]) && !is_aborted(ws)) {
+            if (tid < R && !rank_masked(a.mask, tid)) {
+                Workspace* pws = reinterpret_cast<Workspace*>(s_peer[tid]);
+                ptx::st_release_sys(&pws->ll_signal[1][me], tag_value(epoch, 1));
+            }
+            if (a.prof != nullptr && tid == 0) a.prof[3] = globaltimer_ns();
         }
     }
 
@@ -335,15 +356,18 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
                 atomicAdd(reinterpret_cast<unsigned long long*>(a.wait_stats + tid), globaltimer_ns() - t0);
         }
         alive = __syncthreads_and(ok) != 0;
+        stamp(4);
         if (alive) {
-            // out[t] = sum_k w[t, k] * slot[t, k]; work item = (token, 4 KB column chunk), one warp each
+            // out[t] = sum_k w[t, k] * slot[t, k]; work item = (token, 512-byte column chunk), one warp each: every lane
+            // has the 16-byte loads of all top-k rows in flight at once, so an item costs one memory round trip
             const uint8_t* slab = s_peer[me] + a.off_slab[set];
-            constexpr int kChunk = 32 * 16 * 8;
+            constexpr int kChunk = 32 * 16;
             const int num_chunks = (row_bytes + kChunk - 1) / kChunk;
             const int64_t items = static_cast<int64_t>(a.num_tokens) * num_chunks;
             for (int64_t it = static_cast<int64_t>(blockIdx.x) * kLLWarps + warp; it < items; it += static_cast<int64_t>(gridDim.x) * kLLWarps) {
                 const int t = static_cast<int>(it / num_chunks), c = static_cast<int>(it % num_chunks);
-                const int bytes = min(kChunk, row_bytes - c * kChunk);
+                const int off = c * kChunk + lane * 16;
+                const bool in_row = off < row_bytes;
                 int e_k = -1;
                 float w_k = 0.f;
                 if (lane < K) {
@@ -351,44 +375,44 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
                     w_k = __ldg(a.topk_weights + static_cast<int64_t>(t) * K + lane);
                     if (e_k >= 0 && rank_masked(a.mask, e_k / El)) e_k = -1;
                 }
-                float acc[64];
-#pragma unroll
-                for (int i = 0; i < 64; ++i) acc[i] = 0.f;
                 const uint32_t srcs = __ballot_sync(0xffffffffu, e_k >= 0 && e_k < E);
-                for (int k = 0; k < K; ++k) {
-                    if (!((srcs >> k) & 1u)) continue;
-                    const float w = __shfl_sync(0xffffffffu, w_k, k);
-                    const uint8_t* row = slab + (static_cast<int64_t>(t) * K + k) * row_bytes + static_cast<int64_t>(c) * kChunk;
+                const uint8_t* rows = slab + static_cast<int64_t>(t) * K * row_bytes + off;
+                int4 raw[EP_MAX_TOPK];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const int off = (u * 32 + lane) * 16;
-                        if (off < bytes) {
-                            const int4 raw = __ldcg(reinterpret_cast<const int4*>(row + off));
-                            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                for (int k = 0; k < EP_MAX_TOPK; ++k)
+                    if (k < K && ((srcs >> k) & 1u) && in_row) raw[k] = __ldcg(reinterpret_cast<const int4*>(rows + static_cast<int64_t>(k) * row_bytes));
+                float acc[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+                for (int k = 0; k < EP_MAX_TOPK; ++k) {
+                    if (k < K && ((srcs >> k) & 1u)) {
+                        const float w = __shfl_sync(0xffffffffu, w_k, k);
+                        if (in_row) {
+                            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[k]);
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
                                 const float2 f = __bfloat1622float2(h[q]);
-                                acc[u * 8 + 2 * q] = fmaf(w, f.x, acc[u * 8 + 2 * q]);
-                                acc[u * 8 + 2 * q + 1] = fmaf(w, f.y, acc[u * 8 + 2 * q + 1]);
+                                acc[2 * q] = fmaf(w, f.x, acc[2 * q]);
+                                acc[2 * q + 1] = fmaf(w, f.y, acc[2 * q + 1]);
                             }
                         }
                     }
                 }
-                uint8_t* out = reinterpret_cast<uint8_t*>(a.out) + static_cast<int64_t>(t) * row_bytes + static_cast<int64_t>(c) * kChunk;
+                if (in_row) {
+                    int4 outv;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&outv);
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int off = (u * 32 + lane) * 16;
-                    if (off < bytes) {
-                        int4 raw;
-                        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(acc[u * 8 + 2 * q], acc[u * 8 + 2 * q + 1]);
-                        *reinterpret_cast<int4*>(out + off) = raw;
-                    }
+                    for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+                    *reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(a.out) + static_cast<int64_t>(t) * row_bytes + off) = outv;
                 }
             }
         }
-        if (arrive_is_last(&ws->arrive[EP_CH_LL_COMBINE][1]) && tid == 0) ws->epoch[EP_CH_LL_COMBINE] = epoch;
+        stamp(5);
+        if (arrive_is_last(&ws->arrive[EP_CH_LL_COMBINE][1]) && tid == 0) {
+            ws->epoch[EP_CH_LL_COMBINE] = epoch;
+            if (a.prof != nullptr) a.prof[6] = globaltimer_ns();
+        }
     }
 }
 

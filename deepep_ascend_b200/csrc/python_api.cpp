@@ -463,6 +463,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("packed_count", &LLDispatchCall::packed_count)
         .def_readwrite("stats", &LLDispatchCall::stats)
         .def_readwrite("wait_stats", &LLDispatchCall::wait_stats)
+        .def_readwrite("prof", &LLDispatchCall::prof)
         .def_readwrite("mask", &LLDispatchCall::mask)
         .def_readwrite("shrink", &LLDispatchCall::shrink);
     py::class_<LLCombineCall>(m, "LLCombineCall")
@@ -479,6 +480,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("off_slab0", &LLCombineCall::off_slab0)
         .def_readwrite("off_slab1", &LLCombineCall::off_slab1)
         .def_readwrite("wait_stats", &LLCombineCall::wait_stats)
+        .def_readwrite("prof", &LLCombineCall::prof)
         .def_readwrite("mask", &LLCombineCall::mask)
         .def_readwrite("shrink", &LLCombineCall::shrink);
     m.def("ll_dispatch_group", &ll_dispatch_group);

@@ -14,7 +14,7 @@ struct LLDispatchCall {
     int64_t phases = EP_LL_SEND | EP_LL_RECV;
     int64_t off_slab0 = 0, off_slab1 = 0, msg_bytes = 0;
     at::Tensor packed_x, packed_src_info, layout_range, packed_count;
-    OptTensor packed_sf, stats, wait_stats, mask;
+    OptTensor packed_sf, stats, wait_stats, mask, prof;
     bool shrink = false;
 };
 
@@ -24,7 +24,7 @@ struct LLCombineCall {
     int64_t num_experts = 0, num_max_tokens = 0;
     int64_t phases = EP_LL_SEND | EP_LL_RECV;
     int64_t off_slab0 = 0, off_slab1 = 0;
-    OptTensor wait_stats, mask;
+    OptTensor wait_stats, mask, prof;
     bool shrink = false;
 };
 
@@ -94,6 +94,10 @@ inline LLDispatchArgs make_ll_dispatch_args(ElasticBufferCore& core, const LLDis
     a.wait_stats = c.wait_stats.has_value() ? c.wait_stats->data_ptr<int64_t>() : nullptr;
     a.mask = c.mask.has_value() ? c.mask->data_ptr<int32_t>() : nullptr;
     a.shrink = c.shrink;
+    if (c.prof.has_value()) {
+        TORCH_CHECK(c.prof->scalar_type() == at::kLong && c.prof->numel() >= 8 && c.prof->is_cuda(), "prof must be int64 [8] on the GPU");
+        a.prof = reinterpret_cast<uint64_t*>(c.prof->data_ptr<int64_t>());
+    }
     return a;
 }
 
@@ -135,6 +139,10 @@ inline LLCombineArgs make_ll_combine_args(ElasticBufferCore& core, const LLCombi
     a.wait_stats = c.wait_stats.has_value() ? c.wait_stats->data_ptr<int64_t>() : nullptr;
     a.mask = c.mask.has_value() ? c.mask->data_ptr<int32_t>() : nullptr;
     a.shrink = c.shrink;
+    if (c.prof.has_value()) {
+        TORCH_CHECK(c.prof->scalar_type() == at::kLong && c.prof->numel() >= 8 && c.prof->is_cuda(), "prof must be int64 [8] on the GPU");
+        a.prof = reinterpret_cast<uint64_t*>(c.prof->data_ptr<int64_t>());
+    }
     return a;
 }
 
