@@ -64,6 +64,40 @@ __device__ __forceinline__ uint2 cast_8(const float (&v)[8], int round_scale, fl
     return make_uint2(packed[0], packed[1]);
 }
 
+// In-place exclusive prefix sum of data[0, n) in shared memory (n <= 2 * blockDim.x); data[n] receives the total.
+// Called by all threads of the CTA.
+__device__ __forceinline__ void block_exclusive_scan(uint32_t* data, int n) {
+    __shared__ uint32_t s_warp_total[kLLWarps];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t v0 = 2 * tid < n ? data[2 * tid] : 0u, v1 = 2 * tid + 1 < n ? data[2 * tid + 1] : 0u;
+    uint32_t incl = v0 + v1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    if (lane == 31) s_warp_total[warp] = incl;
+    __syncthreads();
+    uint32_t base = 0;
+    for (int w = 0; w < warp; ++w) base += s_warp_total[w];
+    const uint32_t excl = base + incl - (v0 + v1);
+    if (2 * tid < n) data[2 * tid] = excl;
+    if (2 * tid + 1 < n) data[2 * tid + 1] = excl + v0;
+    if (tid == blockDim.x - 1) data[n] = base + incl;
+    __syncthreads();
+}
+
+// index of the segment that holds item g: largest p with pref[p] <= g (pref is an exclusive prefix sum of n counts)
+__device__ __forceinline__ int find_segment(const uint32_t* pref, int n, uint32_t g) {
+    int lo = 0, hi = n;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (pref[mid] <= g) lo = mid;
+        else hi = mid;
+    }
+    return lo;
+}
+
 __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const RankCtx& ctx = a.ctx;
@@ -75,7 +109,7 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
     const int set = static_cast<int>(epoch & 1);
     const int payload = a.use_fp8 ? H : 2 * H;
     __shared__ uint8_t* s_peer[EP_MAX_RANKS];
-    __shared__ uint32_t s_count[EP_MAX_RANKS], s_begin[EP_MAX_RANKS];
+    __shared__ uint32_t s_pref[EP_MAX_EXPERTS + 1];   // counts, then exclusive prefix, of the (local expert, source) pairs
     if (tid < EP_MAX_RANKS) s_peer[tid] = tid < R ? ctx.peer_base[tid] : nullptr;
     __syncthreads();
     bool alive = !is_aborted(ws);
@@ -166,59 +200,60 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
     if (a.phases & EP_LL_RECV) {
         const uint8_t* slab = s_peer[me] + a.off_slab[set];
         const int64_t rows_per_expert = static_cast<int64_t>(R) * M;
-        // work unit = (local expert, source rank): every CTA that works on expert j waits for all its sources' counts
-        // (the packed position of a source's messages is the sum of the counts of the lower sources)
-        for (int p = blockIdx.x; p < El * R && alive; p += gridDim.x) {
-            const int j = p / R, s = p % R;
-            __syncthreads();
-            int ok = 1;
-            if (tid < R) {
-                const int src = tid;
-                uint32_t n_recv = 0;
-                if (!rank_masked(a.mask, src)) {
-                    const uint64_t* sig = &ws->ll_signal[0][j * R + src];
-                    const uint64_t t0 = globaltimer_ns();
-                    if (a.shrink) {
-                        // shrink mode: a source that stays silent is masked out instead of failing the call
-                        bool got = false;
-                        while (!(got = tag_matches(ptx::ld_acquire_sys(sig), epoch)))
-                            if (globaltimer_ns() - t0 > ctx.timeout_ns) break;
-                        if (!got) atomicExch(a.mask + src, 1);
-                        else n_recv = count_low32(ptx::ld_relaxed_sys(sig));
-                    } else {
-                        ok = bounded_wait(
-                            ctx, ws, EP_PH_LL_RECV_COUNT, src, epoch, [&] { return tag_matches(ptx::ld_acquire_sys(sig), epoch); },
-                            [&] { return ptx::ld_relaxed_sys(sig); });
-                        if (ok) n_recv = count_low32(ptx::ld_relaxed_sys(sig));
+        // Every CTA waits for the counts of all (local expert, source rank) pairs, turns them into one prefix sum over
+        // all received messages and then takes an equal share of the (message, 2 KB piece) copy items, so no CTA is left
+        // with a long pair.  The packed position of a source's messages inside its expert is the sum of the counts of
+        // the lower sources.
+        const int P = El * R;
+        int ok = alive ? 1 : 0;
+        for (int p = tid; p < P && alive; p += blockDim.x) {
+            const int src = p % R;
+            uint32_t n_recv = 0;
+            if (!rank_masked(a.mask, src)) {
+                const uint64_t* sig = &ws->ll_signal[0][p];
+                const uint64_t t0 = globaltimer_ns();
+                if (a.shrink) {
+                    // shrink mode: a source that stays silent is masked out instead of failing the call
+                    bool got = false;
+                    while (!(got = tag_matches(ptx::ld_acquire_sys(sig), epoch)))
+                        if (globaltimer_ns() - t0 > ctx.timeout_ns) break;
+                    if (!got) atomicExch(a.mask + src, 1);
+                    else n_recv = count_low32(ptx::ld_relaxed_sys(sig));
+                } else {
+                    const int got = bounded_wait(
+                        ctx, ws, EP_PH_LL_RECV_COUNT, src, epoch, [&] { return tag_matches(ptx::ld_acquire_sys(sig), epoch); },
+                        [&] { return ptx::ld_relaxed_sys(sig); });
+                    if (got) n_recv = count_low32(ptx::ld_relaxed_sys(sig));
+                    else ok = 0;
+                }
+                if (a.wait_stats != nullptr && blockIdx.x == 0)
+                    atomicAdd(reinterpret_cast<unsigned long long*>(a.wait_stats + src), globaltimer_ns() - t0);
+            }
+            s_pref[p] = n_recv;
+        }
+        alive = __syncthreads_and(ok) != 0;
+        stamp(4);
+        if (alive) {
+            block_exclusive_scan(s_pref, P);
+            if (blockIdx.x == 0) {
+                for (int p = tid; p < P; p += blockDim.x) {
+                    const int j = p / R;
+                    a.layout_range[p] = (static_cast<int64_t>(s_pref[p] - s_pref[j * R]) << 32) | (s_pref[p + 1] - s_pref[p]);
+                    if (p % R == 0) {
+                        const uint32_t total = s_pref[(j + 1) * R] - s_pref[j * R];
+                        a.packed_count[j] = total;
+                        if (a.stats != nullptr) a.stats[j] += total;
                     }
-                    if (a.wait_stats != nullptr && s == 0)
-                        atomicAdd(reinterpret_cast<unsigned long long*>(a.wait_stats + src), globaltimer_ns() - t0);
-                }
-                s_count[src] = n_recv;
-            }
-            alive = __syncthreads_and(ok) != 0;
-            if (!alive) break;
-            if (p == 0) stamp(4);
-            if (tid == 0) {
-                uint32_t begin = 0;
-                for (int q = 0; q < R; ++q) {
-                    s_begin[q] = begin;
-                    begin += s_count[q];
-                }
-                a.layout_range[j * R + s] = (static_cast<int64_t>(s_begin[s]) << 32) | s_count[s];
-                if (s == 0) {
-                    a.packed_count[j] = begin;
-                    if (a.stats != nullptr) a.stats[j] += begin;
                 }
             }
-            __syncthreads();
-            // work item = (message, 2 KB piece): the pieces of one message are copied by different warps at the same
-            // time, four 16-byte loads in flight per lane
-            const uint32_t cnt = s_count[s], begin = s_begin[s];
             const uint32_t pieces = (payload + 2047) / 2048;
-            for (uint32_t u = warp; u < cnt * pieces; u += kLLWarps) {
-                const uint32_t i = u / pieces, c = u - i * pieces;
-                const uint8_t* m = slab + ((static_cast<int64_t>(j) * R + s) * M + i) * a.msg_bytes;
+            const uint32_t items = s_pref[P] * pieces;
+            for (uint32_t u = blockIdx.x * kLLWarps + warp; u < items; u += gridDim.x * kLLWarps) {
+                const uint32_t g = u / pieces, c = u - g * pieces;
+                const int p = find_segment(s_pref, P, g);
+                const int j = p / R;
+                const uint32_t i = g - s_pref[p], begin = s_pref[p] - s_pref[j * R];
+                const uint8_t* m = slab + (static_cast<int64_t>(p) * M + i) * a.msg_bytes;
                 const int64_t pos = static_cast<int64_t>(j) * rows_per_expert + begin + i;
                 uint8_t* out = reinterpret_cast<uint8_t*>(a.packed_x) + pos * payload;
                 {
@@ -241,13 +276,13 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
                         // four exponents per int32, groups along the slow axis: [E_local, ceil(G/4), R*M]
                         uint8_t* dst = reinterpret_cast<uint8_t*>(a.packed_sf);
                         const int64_t G4 = (G + 3) / 4;
-                        for (int g = lane; g < G; g += 32)
-                            dst[((static_cast<int64_t>(j) * G4 + g / 4) * rows_per_expert + begin + i) * 4 + (g & 3)] =
-                                static_cast<uint8_t>(__float_as_uint(__ldcg(sf + g)) >> 23);
+                        for (int gi = lane; gi < G; gi += 32)
+                            dst[((static_cast<int64_t>(j) * G4 + gi / 4) * rows_per_expert + begin + i) * 4 + (gi & 3)] =
+                                static_cast<uint8_t>(__float_as_uint(__ldcg(sf + gi)) >> 23);
                     } else {
                         float* dst = reinterpret_cast<float*>(a.packed_sf);
-                        for (int g = lane; g < G; g += 32)
-                            dst[(static_cast<int64_t>(j) * G + g) * rows_per_expert + begin + i] = __ldcg(sf + g);
+                        for (int gi = lane; gi < G; gi += 32)
+                            dst[(static_cast<int64_t>(j) * G + gi) * rows_per_expert + begin + i] = __ldcg(sf + gi);
                     }
                 }
             }
@@ -273,6 +308,7 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
     const uint64_t epoch = ws->epoch[EP_CH_LL_COMBINE] + 1;
     const int set = static_cast<int>(epoch & 1);
     __shared__ uint8_t* s_peer[EP_MAX_RANKS];
+    __shared__ uint32_t s_pref[EP_MAX_EXPERTS + 1], s_begin[EP_MAX_EXPERTS];
     if (tid < EP_MAX_RANKS) s_peer[tid] = tid < R ? ctx.peer_base[tid] : nullptr;
     // per warp: two staging rows and two mbarriers
     const int send_warps = ll_combine_send_warps(H);
@@ -295,32 +331,54 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
         const uint8_t* xb = reinterpret_cast<const uint8_t*>(a.x);
         const int64_t rows_per_expert = static_cast<int64_t>(R) * M;
         uint32_t n_loaded = 0;   // loads issued by this warp so far (selects stage and mbarrier parity)
-        for (int p = blockIdx.x; p < El * R && alive; p += gridDim.x) {
-            const int j = p / R, s = p % R;
-            if (rank_masked(a.mask, s)) continue;
-            const int64_t lr = a.layout_range[j * R + s];
-            const uint32_t cnt = static_cast<uint32_t>(lr & 0xffffffffll), begin = static_cast<uint32_t>(lr >> 32);
-            for (uint32_t i = warp; warp < send_warps && i < cnt && alive; i += send_warps) {
-                const int64_t pos = static_cast<int64_t>(j) * rows_per_expert + begin + i;
-                const int info = a.src_info[pos];
-                const int t = info & 0xfffff, k = info >> 20;
-                const int st = n_loaded & 1;
-                // the stage was the source of the store issued two rows ago
-                ptx::bulk_wait_read<1>();
-                __syncwarp();
-                if (lane == 0) {
-                    ptx::mbar_arrive_expect_tx(&bars[st], row_bytes);
-                    ptx::bulk_load(stage + st * row_bytes, xb + pos * row_bytes, row_bytes, &bars[st]);
-                }
-                alive = mbar_wait_bounded(ctx, ws, &bars[st], (n_loaded >> 1) & 1, EP_PH_COMBINE_LOAD);
-                ++n_loaded;
-                if (!alive) break;
-                if (lane == 0) {
-                    uint8_t* dst = s_peer[s] + a.off_slab[set] + (static_cast<int64_t>(t) * K + k) * row_bytes;
-                    ptx::bulk_store(dst, stage + st * row_bytes, row_bytes);
-                }
-                ptx::bulk_commit();
+        // all packed rows of this rank form one list (prefix sum over the (local expert, source rank) pairs) that the
+        // staging warps of all CTAs share evenly
+        const int P = El * R;
+        for (int p = tid; p < P; p += blockDim.x) {
+            const int64_t lr = a.layout_range[p];
+            s_pref[p] = rank_masked(a.mask, p % R) ? 0u : static_cast<uint32_t>(lr & 0xffffffffll);
+            s_begin[p] = static_cast<uint32_t>(lr >> 32);
+        }
+        __syncthreads();
+        block_exclusive_scan(s_pref, P);
+        const uint32_t total = s_pref[P];
+        // one row load is always in flight ahead of the row being stored
+        const uint32_t g_stride = gridDim.x * send_warps;
+        int next_src = 0;   // source rank of the row whose load was issued last
+        auto issue_load = [&](uint32_t g, uint32_t n) {
+            const int p = find_segment(s_pref, P, g);
+            next_src = p % R;
+            const int64_t pos = static_cast<int64_t>(p / R) * rows_per_expert + s_begin[p] + (g - s_pref[p]);
+            if (lane == 0) {
+                ptx::mbar_arrive_expect_tx(&bars[n & 1], row_bytes);
+                ptx::bulk_load(stage + (n & 1) * row_bytes, xb + pos * row_bytes, row_bytes, &bars[n & 1]);
             }
+            return pos;
+        };
+        uint32_t g = blockIdx.x * send_warps + warp;
+        int64_t pos = 0;
+        if (warp < send_warps && g < total && alive) pos = issue_load(g, 0);
+        for (; warp < send_warps && g < total && alive; g += g_stride) {
+            const int s = next_src;
+            const int info = a.src_info[pos];
+            const int t = info & 0xfffff, k = info >> 20;
+            const int st = n_loaded & 1;
+            int64_t next_pos = 0;
+            if (g + g_stride < total) {
+                // the other stage was the source of the previous row's store
+                ptx::bulk_wait_read<0>();
+                __syncwarp();
+                next_pos = issue_load(g + g_stride, n_loaded + 1);
+            }
+            alive = mbar_wait_bounded(ctx, ws, &bars[st], (n_loaded >> 1) & 1, EP_PH_COMBINE_LOAD);
+            ++n_loaded;
+            if (!alive) break;
+            if (lane == 0) {
+                uint8_t* dst = s_peer[s] + a.off_slab[set] + (static_cast<int64_t>(t) * K + k) * row_bytes;
+                ptx::bulk_store(dst, stage + st * row_bytes, row_bytes);
+            }
+            ptx::bulk_commit();
+            pos = next_pos;
         }
         ptx::bulk_commit();
         stamp(1);
