@@ -31,6 +31,8 @@ def main():
     p.add_argument('--gpus', type=int, default=1)
     p.add_argument('--what', default='all')
     p.add_argument('--iters', type=int, default=20)
+    p.add_argument('--moe-tokens', type=int, default=4096, help='tokens per rank of the fused MoE benchmark')
+    p.add_argument('--moe-experts', type=int, default=0, help='experts of the fused MoE benchmark (default 256, or 32 on one GPU)')
     args = p.parse_args()
     world = int(os.environ.get('WORLD_SIZE', '1'))
     rank = int(os.environ.get('RANK', '0'))
@@ -219,9 +221,10 @@ def main():
     # ------------------------------------------------------------------ fused MoE layer forward + backward
     if want('moe'):
         from deepep_ascend_b200.models.moe import FusedMoE
-        Tm, I = 4096, 2048
+        Tm, I = args.moe_tokens, 2048
+        bi, bw = min(5, args.iters), (2 if args.iters > 1 else 0)     # iterations / warm-up of every piece of the breakdown
         # 32 experts per rank, as at EP8 with 256 experts (a single GPU would otherwise hold all 256 and stream 22 GB of weights)
-        Em = E if world > 1 else 32
+        Em = args.moe_experts or (E if world > 1 else 32)
         buf = ElasticBuffer(group, num_max_tokens_per_rank=Tm, hidden=H, num_topk=K, enable_expand=True, num_experts=Em,
                             expert_alignment=128, num_gpu_timeout_secs=30)
         layer = FusedMoE(buf, Em, H, I, init_std=0.02, num_sms=64)
@@ -249,19 +252,19 @@ def main():
         (rx, rsf), _, rw, hd, _ = st['o']
         tile_group, valid_row = G.expert_tile_groups(hd.psum_num_recv_tokens_per_expert, hd.num_rows)
         q13, s13, q2, s2 = layer.fp8_weights()
-        t_disp = np.median(timeit(d_only, buf, iters=5, warm=2))
+        t_disp = np.median(timeit(d_only, buf, iters=bi, warm=bw))
         hbuf = {}
 
         def g1():
             hbuf['h'] = G.grouped_gemm_nt(rx, q13, tile_group, sfa=rsf, sfb=s13)
-        t_g1 = np.median(timeit(g1, None, iters=5, warm=2))
+        t_g1 = np.median(timeit(g1, None, iters=bi, warm=bw))
 
         def sw():
             hbuf['a'] = G.swiglu_quant(hbuf['h'])
-        t_sw = np.median(timeit(sw, None, iters=5, warm=2))
+        t_sw = np.median(timeit(sw, None, iters=bi, warm=bw))
         ybuf = buf.get_combine_buffer(hd)
-        t_g2 = np.median(timeit(lambda: G.grouped_gemm_nt(hbuf['a'][0], q2, tile_group, out=ybuf, sfa=hbuf['a'][1], sfb=s2), None, iters=5, warm=2))
-        t_comb = np.median(timeit(lambda: buf.combine(ybuf, hd, weighted=True, num_sms=64), buf, iters=5, warm=2))
+        t_g2 = np.median(timeit(lambda: G.grouped_gemm_nt(hbuf['a'][0], q2, tile_group, out=ybuf, sfa=hbuf['a'][1], sfb=s2), None, iters=bi, warm=bw))
+        t_comb = np.median(timeit(lambda: buf.combine(ybuf, hd, weighted=True, num_sms=64), buf, iters=bi, warm=bw))
         emit(bench='fused_moe_forward_breakdown_ms', rows=hd.num_rows, dispatch_expand_fp8=float(t_disp), gemm1_fp8=float(t_g1),
              swiglu_cast=float(t_sw), gemm2_fp8=float(t_g2), combine_weighted=float(t_comb),
              gemm1_tflops=2 * hd.num_rows * H * 2 * I / t_g1 / 1e9, gemm2_tflops=2 * hd.num_rows * H * I / t_g2 / 1e9)
@@ -274,30 +277,30 @@ def main():
 
         def prep():
             bb['dy'], bb['dy_t'], bb['dot'] = G.moe_bwd_prep(g_rows, ybuf, rwc, valid_row)
-        t_prep = np.median(timeit(prep, None, iters=5, warm=2))
+        t_prep = np.median(timeit(prep, None, iters=bi, warm=bw))
 
         def dgrad2():
             bb['d_act'] = G.grouped_gemm_nt(bb['dy'], w2_t, tile_group)
-        t_dg2 = np.median(timeit(dgrad2, None, iters=5, warm=2))
+        t_dg2 = np.median(timeit(dgrad2, None, iters=bi, warm=bw))
 
         def swb():
             bb['dh'], bb['dh_t'], bb['act_t'] = G.swiglu_bwd(bb['d_act'], hbuf['h'], valid_row)
-        t_swb = np.median(timeit(swb, None, iters=5, warm=2))
-        t_dg1 = np.median(timeit(lambda: G.grouped_gemm_nt(bb['dh'], w13_t, tile_group, out=ybuf), None, iters=5, warm=2))
+        t_swb = np.median(timeit(swb, None, iters=bi, warm=bw))
+        t_dg1 = np.median(timeit(lambda: G.grouped_gemm_nt(bb['dh'], w13_t, tile_group, out=ybuf), None, iters=bi, warm=bw))
 
         def xt():
             bb['x_t'] = G.dequant_transpose(rx, rsf, valid_row)
-        t_xt = np.median(timeit(xt, None, iters=5, warm=2))
-        t_wg2 = np.median(timeit(lambda: G.gemm_kgrouped(bb['dy_t'], bb['act_t'], seg_off), None, iters=5, warm=2))
-        t_wg1 = np.median(timeit(lambda: G.gemm_kgrouped(bb['dh_t'], bb['x_t'], seg_off), None, iters=5, warm=2))
+        t_xt = np.median(timeit(xt, None, iters=bi, warm=bw))
+        t_wg2 = np.median(timeit(lambda: G.gemm_kgrouped(bb['dy_t'], bb['act_t'], seg_off), None, iters=bi, warm=bw))
+        t_wg1 = np.median(timeit(lambda: G.gemm_kgrouped(bb['dh_t'], bb['x_t'], seg_off), None, iters=bi, warm=bw))
         emit(bench='fused_moe_backward_breakdown_ms', rows=hd.num_rows, combine_bwd_prep=float(t_prep), dgrad_down_bf16=float(t_dg2),
              swiglu_bwd=float(t_swb), dgrad_up_bf16=float(t_dg1), dequant_transpose=float(t_xt), wgrad_down=float(t_wg2),
              wgrad_up=float(t_wg1), dgrad_down_tflops=2 * hd.num_rows * H * I / t_dg2 / 1e9,
              dgrad_up_tflops=2 * hd.num_rows * H * 2 * I / t_dg1 / 1e9, wgrad_down_tflops=2 * hd.num_rows * H * I / t_wg2 / 1e9,
              wgrad_up_tflops=2 * hd.num_rows * H * 2 * I / t_wg1 / 1e9)
         del bb, g_rows
-        tf = np.median(timeit(fwd, buf, iters=5, warm=2))
-        tfb = np.median(timeit(fwd_bwd, buf, iters=5, warm=2))
+        tf = np.median(timeit(fwd, buf, iters=bi, warm=bw))
+        tfb = np.median(timeit(fwd_bwd, buf, iters=bi, warm=bw))
         rows = float(idx.numel())
         flops_fwd = rows * (2 * H * 2 * I + 2 * I * H)
         emit(bench='fused_moe_layer', tokens_per_rank=Tm, hidden=H, intermediate=I, experts_per_rank=Em // world, fwd_ms=float(tf), fwd_bwd_ms=float(tfb),
