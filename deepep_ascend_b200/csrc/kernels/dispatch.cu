@@ -7,10 +7,13 @@
 //                 arrive only once the peer has entered the same call);
 //   3. assign   - prefix sums turn the counts into FINAL row numbers in the receivers' output tensors, in
 //                 (source rank, token) order, so the result is deterministic and needs no second pass;
-//   4. scatter  - per token: TMA bulk load into shared memory, optional fused bf16 -> e4m3 cast with 1x128
-//                 scales, then one bulk store per destination rank straight into that rank's recv_x through
-//                 its peer mapping, plus small direct stores for scales / expert ids / weights / metadata;
-//   5. finish   - drain the bulk stores, grid barrier, cross-GPU arrival signal, wait for all peers' signals.
+//   4. scatter  - tokens are claimed dynamically by the warps of all CTAs; per token: optional fused bf16 -> e4m3
+//                 cast with 1x128 scales (register batches straight from global memory) or a TMA bulk load,
+//                 then one bulk store per destination rank straight into that rank's recv_x through its peer
+//                 mapping, plus ONE more bulk store of a packed side record (scales, global expert ids, weights,
+//                 source token);
+//   5. finish   - drain the bulk stores, grid barrier, CTA 0 tells every peer "my rows have arrived"; every CTA waits
+//                 for all peers' words itself and then rewrites its share of the received expert ids as local ids.
 //
 // Parity: does the work of dispatch_impl + dispatch_copy_epilogue_impl
 // (deep_ep/include/deep_ep/impls/dispatch.cuh:17-409, dispatch_copy_epilogue.cuh:11-323) and of the fused

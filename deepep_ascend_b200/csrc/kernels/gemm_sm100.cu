@@ -5,16 +5,18 @@
 //              flag per M tile (all-gather fused into the loads)
 //   warp 1   : MMA issuer   - one elected thread issues tcgen05.mma (kind::f16 for bf16, kind::f8f6f4 for e4m3)
 //              with fp32 accumulators in tensor memory; tcgen05.commit releases stages and publishes accumulators
-//   warps 2-5: epilogue     - tcgen05.ld the accumulator (each warp its 32 TMEM lanes), scale / convert, store bf16
+//   warps 2-5 (2-9 for e4m3): epilogue - tcgen05.ld the accumulator (each warp its 32 TMEM lanes), scale / convert, store bf16
 //
 // bf16 operands: one accumulator per output tile, two TMEM buffers so the epilogue of tile i overlaps the MMAs of
 // tile i+1.  e4m3 operands with fp32 block scales (A: per row x 128 channels, B: per 128 x 128 block): every
 // 128-channel block is accumulated into its own TMEM buffer and promoted into fp32 registers with its scale by
-// the epilogue warps (two buffers, so promotion of block j overlaps the MMAs of block j+1).
+// EIGHT epilogue warps (two per TMEM lane quadrant, 64 columns each, both tcgen05.ld of a block in flight before one
+// wait); four TMEM buffers let the MMAs run up to three blocks ahead of the promotion.
 // Grouped (MoE) use: `tile_group[m_tile]` selects the expert whose weights multiply that 128-row tile.
 // Every pipeline wait is bounded; on expiry the kernel raises `*error`, leaves its loops and frees its TMEM.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -25,21 +27,24 @@ namespace ep {
 namespace {
 
 constexpr int kBlockM = 128, kTileBytes = 128 * 128;   // A tile: 128 rows x 128 bytes; B tile: kBlockN rows x 128 bytes
-constexpr int kMaxStages = 5;
+constexpr int kMaxStages = 7;
 constexpr int kEpiRowBytes = 128 * 2 + 16;              // one staged bf16 output row (128 columns), padded against bank conflicts
 constexpr int kEpiStageBytes = 4 * 32 * kEpiRowBytes;   // four epilogue warps x 32 rows
 // shared memory: [A stages | B stages | barriers (1 KB) | epilogue staging]
 __host__ __device__ constexpr int stage_bytes(int block_n) { return kTileBytes + block_n * 128; }
-__host__ __device__ constexpr int num_stages(int block_n) { return block_n == 256 ? 4 : 5; }
-__host__ __device__ constexpr int gemm_smem_bytes(int block_n) {
-    return num_stages(block_n) * stage_bytes(block_n) + 1024 + (block_n == 128 ? kEpiStageBytes : 0);
+// e4m3 tiles carry half the math per byte of bf16 tiles, so that kernel keeps as many bytes in flight as fit (7 stages)
+__host__ __device__ constexpr int num_stages(int block_n, bool fp8) { return block_n == 256 ? 4 : (fp8 ? 7 : 5); }
+__host__ __device__ constexpr int gemm_smem_bytes(int block_n, bool fp8) {
+    return num_stages(block_n, fp8) * stage_bytes(block_n) + 1024 + (block_n == 128 && !fp8 ? kEpiStageBytes : 0);
 }
 constexpr int kCopyWarps = 5;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 192;        // bf16: TMA warp, MMA warp, 4 epilogue warps
+constexpr int kGemmThreadsFp8 = 320;     // e4m3: TMA warp, MMA warp, 8 epilogue warps
+constexpr int kMaxAccBufs = 4;
 constexpr uint64_t kWaitLimitNs = 4ull * 1000 * 1000 * 1000;
 
 struct GemmSmem {
-    uint64_t full[kMaxStages], empty[kMaxStages], tmem_full[2], tmem_empty[2];
+    uint64_t full[kMaxStages], empty[kMaxStages], tmem_full[kMaxAccBufs], tmem_empty[kMaxAccBufs];
     uint64_t copy_bar[kCopyWarps][2];
     uint32_t tmem_base;
     int failed;
@@ -127,12 +132,14 @@ struct PipeState {
 };
 
 template <bool kFp8, int kBlockN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kFp8 ? kGemmThreadsFp8 : kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    constexpr int kStages = num_stages(kBlockN);
+    constexpr int kStages = num_stages(kBlockN, kFp8);
     constexpr int kTileBytesB = kBlockN * 128;
-    constexpr int kTmemColumns = 2 * kBlockN;       // two accumulator buffers of kBlockN fp32 columns
+    constexpr int kAccBufs = (kFp8 && kBlockN == 128) ? 4 : 2;   // accumulator buffers of kBlockN fp32 columns in tensor memory
+    constexpr int kEpiWarps = kFp8 ? 8 : 4;
+    constexpr int kTmemColumns = kAccBufs * kBlockN;
     uint8_t* s_a = smem;
     uint8_t* s_b = smem + kStages * kTileBytes;
     GemmSmem* sm = reinterpret_cast<GemmSmem*>(smem + kStages * (kTileBytes + kTileBytesB));
@@ -157,9 +164,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             ptx::mbar_init(&sm->full[i], 1);
             ptx::mbar_init(&sm->empty[i], 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kAccBufs; ++i) {
             ptx::mbar_init(&sm->tmem_full[i], 1);
-            ptx::mbar_init(&sm->tmem_empty[i], 4);
+            ptx::mbar_init(&sm->tmem_empty[i], kEpiWarps);
         }
         sm->failed = 0;
         ptx::mbar_fence_init();
@@ -258,12 +265,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     p.advance();
                     if (kFp8) {
                         umma::mma_commit(&sm->tmem_full[acc]);   // one 128-channel block is ready for promotion
-                        if ((acc ^= 1) == 0) acc_phase ^= 1;
+                        if (++acc == kAccBufs) {
+                            acc = 0;
+                            acc_phase ^= 1;
+                        }
                     }
                 }
                 if (!kFp8 && ok) {
                     umma::mma_commit(&sm->tmem_full[acc]);
-                    if ((acc ^= 1) == 0) acc_phase ^= 1;
+                    if (++acc == kAccBufs) {
+                        acc = 0;
+                        acc_phase ^= 1;
+                    }
                 }
             }
         }
@@ -335,36 +348,67 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 umma::fence_before_thread_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
-                if ((acc ^= 1) == 0) acc_phase ^= 1;
+                if (++acc == kAccBufs) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
             } else {
-                float sum[kBlockN];
+                // this warp promotes one half of the tile's columns for its 32 rows
+                constexpr int kCols = kBlockN / 2;
+                const int col_half = (warp - 2) >> 2;
+                float sum[kCols];
 #pragma unroll
-                for (int i = 0; i < kBlockN; ++i) sum[i] = 0.f;
+                for (int i = 0; i < kCols; ++i) sum[i] = 0.f;
                 const int num_kb_sf = (g.K + 127) / 128, num_nb_sf = (g.N + 127) / 128;
-                const float* sfb = g.sfb + (static_cast<int64_t>(grp) * num_nb_sf + n_blk) * num_kb_sf;
+                // the B scale block of this warp's columns (a half tile never straddles two 128-column blocks)
+                const int nb_sf = min((n0 + col_half * kCols) / 128, num_nb_sf - 1);
+                const float* sfb = g.sfb + (static_cast<int64_t>(grp) * num_nb_sf + nb_sf) * num_kb_sf;
+                float scale_next = (row < g.M ? __ldg(g.sfa + row * g.sfa_stride_row) : 0.f) * __ldg(sfb);
                 for (int kb = 0; kb < num_k && ok; ++kb) {
-                    const float scale = (row < g.M ? __ldg(g.sfa + row * g.sfa_stride_row + kb * g.sfa_stride_kb) : 0.f) * __ldg(sfb + kb);
+                    const float scale = scale_next;
+                    if (kb + 1 < num_k)
+                        scale_next = (row < g.M ? __ldg(g.sfa + row * g.sfa_stride_row + (kb + 1) * g.sfa_stride_kb) : 0.f) * __ldg(sfb + kb + 1);
                     ok = wait_bar(&sm->tmem_full[acc], acc_phase, sm, g.error, 5);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     umma::fence_after_thread_sync();
-#pragma unroll
-                    for (int c = 0; c < kBlockN / 32; ++c) {
-                        uint32_t r[32];
-                        umma::tmem_ld_32x32(tmem_base + lane_addr + acc * kBlockN + c * 32, r);
+                    const uint32_t taddr = tmem_base + lane_addr + acc * kBlockN + col_half * kCols;
+                    if (kCols == 64) {
+                        uint32_t r0[32], r1[32];
+                        umma::tmem_ld_32x32(taddr, r0);
+                        umma::tmem_ld_32x32(taddr + 32, r1);
                         umma::tmem_ld_wait();
+                        // the values are in registers: hand the buffer back before the arithmetic
+                        umma::fence_before_thread_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) sum[c * 32 + i] = fmaf(scale, __uint_as_float(r[i]), sum[c * 32 + i]);
+                        for (int i = 0; i < 32; ++i) {
+                            sum[i] = fmaf(scale, __uint_as_float(r0[i]), sum[i]);
+                            sum[32 + i] = fmaf(scale, __uint_as_float(r1[i]), sum[32 + i]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < kCols / 32; ++c) {
+                            uint32_t r[32];
+                            umma::tmem_ld_32x32(taddr + c * 32, r);
+                            umma::tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) sum[c * 32 + i] = fmaf(scale, __uint_as_float(r[i]), sum[c * 32 + i]);
+                        }
+                        umma::fence_before_thread_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
                     }
-                    umma::fence_before_thread_sync();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
-                    if ((acc ^= 1) == 0) acc_phase ^= 1;
+                    if (++acc == kAccBufs) {
+                        acc = 0;
+                        acc_phase ^= 1;
+                    }
                 }
                 if (ok && row < g.M) {
 #pragma unroll
-                    for (int v = 0; v < kBlockN / 8; ++v) {
-                        const int col = n0 + v * 8;
+                    for (int v = 0; v < kCols / 8; ++v) {
+                        const int col = n0 + col_half * kCols + v * 8;
                         if (col + 8 <= g.N) {
                             int4 out;
                             __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
@@ -556,14 +600,14 @@ cudaError_t launch_gemm(const GemmArgs& g, int num_sms, cudaStream_t stream) {
         return cudaErrorInvalidValue;
     // bf16: 128 x 256 output tiles (fewer A re-reads, longer MMAs); the block-scaled FP8 path and the reduce-scatter
     // epilogue (which stages 128-column rows) use 128 x 128 tiles
-    const int block_n = (!g.is_fp8 && g.fuse != EP_GEMM_FUSE_REDUCE_SCATTER && g.N >= 256) ? 256 : 128;
+    const int block_n = (g.fuse != EP_GEMM_FUSE_REDUCE_SCATTER && g.N >= 256 && !(g.is_fp8 && getenv("EP_GEMM_FP8_N128") != nullptr)) ? 256 : 128;
     CUtensorMap map_a, map_b;
     if (!make_operand_map(&map_a, g.a, g.M, g.K, g.lda, g.is_fp8, 128) ||
         !make_operand_map(&map_b, g.b, static_cast<int64_t>(g.k_group_off != nullptr ? 1 : g.num_groups) * g.N, g.K, g.ldb, g.is_fp8, block_n))
         return cudaErrorInvalidValue;
-    const void* fn = g.is_fp8 ? (const void*)gemm_kernel<true, 128>
+    const void* fn = g.is_fp8 ? (block_n == 256 ? (const void*)gemm_kernel<true, 256> : (const void*)gemm_kernel<true, 128>)
                               : (block_n == 256 ? (const void*)gemm_kernel<false, 256> : (const void*)gemm_kernel<false, 128>);
-    const int kGemmSmemBytes = gemm_smem_bytes(block_n);
+    const int kGemmSmemBytes = gemm_smem_bytes(block_n, g.is_fp8 != 0);
     cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
     if (err != cudaSuccess) return err;
     if (g.k_group_off != nullptr && (g.is_fp8 || g.fuse != EP_GEMM_FUSE_NONE || g.tile_group != nullptr || g.num_groups < 1)) return cudaErrorInvalidValue;
@@ -580,7 +624,7 @@ cudaError_t launch_gemm(const GemmArgs& g, int num_sms, cudaStream_t stream) {
         return cudaLaunchCooperativeKernel(fn, dim3(ctas, 1, 1), dim3(kGemmThreads, 1, 1), params, kGemmSmemBytes, stream);
     }
     if (ctas > num_tiles) ctas = num_tiles;
-    return cudaLaunchKernel(fn, dim3(ctas, 1, 1), dim3(kGemmThreads, 1, 1), params, kGemmSmemBytes, stream);
+    return cudaLaunchKernel(fn, dim3(ctas, 1, 1), dim3(g.is_fp8 ? kGemmThreadsFp8 : kGemmThreads, 1, 1), params, kGemmSmemBytes, stream);
 }
 
 }  // namespace ep

@@ -5,12 +5,16 @@
 //                    power-of-two or UE8M0) into a message {16 B header, payload, scales} in shared memory, then
 //                    warp k claims a slot for expert topk[k] and bulk-stores the message into the slab
 //                    [local expert][source rank][slot] of the expert's rank through its peer mapping;
-//                    after a grid barrier the per-expert counts go out as epoch-tagged words.
-//            RECV  - one CTA per local expert: wait for every source's count, then pack the messages into
-//                    [local expert, ranks * max_tokens, hidden] (+ column-major scales, source info, ranges).
-// Combine:   SEND  - one CTA per local expert: every packed row is bulk-copied into the slot
-//                    [source token][top-k lane] of the token's home rank; then one epoch-tagged flag per rank pair.
+//                    the last CTA to have its stores acknowledged sends the per-expert counts as epoch-tagged words.
+//            RECV  - every CTA waits for all counts, forms one prefix sum over the received messages and copies an
+//                    equal share of them into [local expert, ranks * max_tokens, hidden] (+ column-major scales,
+//                    source info, ranges).
+// Combine:   SEND  - the packed rows of all local experts form one list shared evenly by the staging warps of all
+//                    CTAs: every row is bulk-copied into the slot [source token][top-k lane] of the token's home
+//                    rank; the last CTA to finish raises one epoch-tagged flag per rank pair.
 //            RECV  - wait for all ranks' flags, then out[t] = sum_k w[t,k] * slot[t,k] in fp32 -> bf16.
+// No CTA waits for another CTA of its own rank (no grid barrier): phases end with an arrival counter whose last
+// arriver does the publishing.
 // SEND and RECV can be launched separately (phases argument) so that no SM is held while data is in flight.
 //
 // Parity: csrc/kernels/legacy/internode_ll.cu:128-554 (dispatch) and 714-1238 (combine) of the reference.
