@@ -300,10 +300,11 @@ def main():
              wgrad_up_tflops=2 * hd.num_rows * H * 2 * I / t_wg1 / 1e9)
         del bb, g_rows
         tf = np.median(timeit(fwd, buf, iters=bi, warm=bw))
-        tfb = np.median(timeit(fwd_bwd, buf, iters=bi, warm=bw))
+        tfb_all = timeit(fwd_bwd, buf, iters=bi, warm=bw)
+        tfb = np.median(tfb_all)
         rows = float(idx.numel())
         flops_fwd = rows * (2 * H * 2 * I + 2 * I * H)
-        emit(bench='fused_moe_layer', tokens_per_rank=Tm, hidden=H, intermediate=I, experts_per_rank=Em // world, fwd_ms=float(tf), fwd_bwd_ms=float(tfb),
+        emit(bench='fused_moe_layer', tokens_per_rank=Tm, hidden=H, intermediate=I, experts_per_rank=Em // world, fwd_ms=float(tf), fwd_bwd_ms=float(tfb), fwd_bwd_ms_all=[round(float(v), 3) for v in tfb_all],
              fwd_expert_tflops_per_gpu=flops_fwd / tf / 1e9, note='includes the host sync of dispatch (exact sizes)')
         buf.destroy()
 

@@ -39,7 +39,20 @@ __host__ __device__ constexpr int gemm_smem_bytes(int block_n, bool fp8) {
 }
 constexpr int kCopyWarps = 5;
 constexpr int kGemmThreads = 192;        // bf16: TMA warp, MMA warp, 4 epilogue warps
-constexpr int kGemmThreadsFp8 = 320;     // e4m3: TMA warp, MMA warp, 8 epilogue warps
+constexpr int kGemmThreadsFp8 = 320;     // e4m3, 128-column tiles: TMA warp, MMA warp, 8 epilogue warps
+constexpr int kGemmThreadsFp8Wide = 384; // e4m3, 256-column tiles: one producer warpgroup (TMA, MMA, two idle warps) that gives its
+                                         // registers to the two epilogue warpgroups (128 fp32 sums + 64 loaded values per thread)
+__host__ __device__ constexpr int gemm_threads(bool fp8, int block_n) {
+    return fp8 ? (block_n == 256 ? kGemmThreadsFp8Wide : kGemmThreadsFp8) : kGemmThreads;
+}
+template <int kRegs>
+__device__ __forceinline__ void reg_alloc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void reg_dealloc() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
 constexpr int kMaxAccBufs = 4;
 constexpr uint64_t kWaitLimitNs = 4ull * 1000 * 1000 * 1000;
 
@@ -132,13 +145,15 @@ struct PipeState {
 };
 
 template <bool kFp8, int kBlockN>
-__global__ void __launch_bounds__(kFp8 ? kGemmThreadsFp8 : kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads(kFp8, kBlockN), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr int kStages = num_stages(kBlockN, kFp8);
     constexpr int kTileBytesB = kBlockN * 128;
     constexpr int kAccBufs = (kFp8 && kBlockN == 128) ? 4 : 2;   // accumulator buffers of kBlockN fp32 columns in tensor memory
     constexpr int kEpiWarps = kFp8 ? 8 : 4;
+    constexpr bool kWide = kFp8 && kBlockN == 256;   // register re-allocation between warpgroups
+    constexpr int kEpiWarp0 = kWide ? 4 : 2;         // first epilogue warp
     constexpr int kTmemColumns = kAccBufs * kBlockN;
     uint8_t* s_a = smem;
     uint8_t* s_b = smem + kStages * kTileBytes;
@@ -182,6 +197,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     umma::fence_after_thread_sync();
     const uint32_t tmem_base = sm->tmem_base;
 
+    if (warp < kEpiWarp0) {
+    // ---------------------------------------------------------------------- producer warps (not re-indented)
+    // wide e4m3 kernel: warps 0-3 (TMA, MMA, two idle) keep 40 registers each so that the epilogue warps can take 232
+    if (kWide) reg_dealloc<40>();
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -280,8 +299,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
             }
         }
+    }
     } else {
-        // ------------------------------------------------------------------ epilogue (4 warps, 32 TMEM lanes each)
+        // ------------------------------------------------------------------ epilogue (32 TMEM lanes per warp)
+        if (kWide) reg_alloc<232>();
         const int quad = warp & 3;
         int acc = 0;
         uint32_t acc_phase = 0;
@@ -355,7 +376,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             } else {
                 // this warp promotes one half of the tile's columns for its 32 rows
                 constexpr int kCols = kBlockN / 2;
-                const int col_half = (warp - 2) >> 2;
+                const int col_half = (warp - kEpiWarp0) >> 2;
                 float sum[kCols];
 #pragma unroll
                 for (int i = 0; i < kCols; ++i) sum[i] = 0.f;
@@ -388,17 +409,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             sum[32 + i] = fmaf(scale, __uint_as_float(r1[i]), sum[32 + i]);
                         }
                     } else {
+                        // 128 columns in two steps of two loads each (64 loaded values live at a time)
 #pragma unroll
-                        for (int c = 0; c < kCols / 32; ++c) {
-                            uint32_t r[32];
-                            umma::tmem_ld_32x32(taddr + c * 32, r);
+                        for (int c = 0; c < kCols / 64; ++c) {
+                            uint32_t r0[32], r1[32];
+                            umma::tmem_ld_32x32(taddr + c * 64, r0);
+                            umma::tmem_ld_32x32(taddr + c * 64 + 32, r1);
                             umma::tmem_ld_wait();
+                            if (c == kCols / 64 - 1) {
+                                umma::fence_before_thread_sync();
+                                __syncwarp();
+                                if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
+                            }
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) sum[c * 32 + i] = fmaf(scale, __uint_as_float(r[i]), sum[c * 32 + i]);
+                            for (int i = 0; i < 32; ++i) {
+                                sum[c * 64 + i] = fmaf(scale, __uint_as_float(r0[i]), sum[c * 64 + i]);
+                                sum[c * 64 + 32 + i] = fmaf(scale, __uint_as_float(r1[i]), sum[c * 64 + 32 + i]);
+                            }
                         }
-                        umma::fence_before_thread_sync();
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
                     }
                     if (++acc == kAccBufs) {
                         acc = 0;
@@ -421,7 +449,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
         }
     }
-    if (g.fuse == EP_GEMM_FUSE_ALL_GATHER && is_copier && warp < kCopyWarps) {
+    if (!kFp8 && g.fuse == EP_GEMM_FUSE_ALL_GATHER && is_copier && warp < kCopyWarps) {
         // ------------------------------------------------------------------ all-gather fused into this kernel
         // Copier CTAs pull the remote shards of A, one 128-row tile at a time, from the owners' symmetric buffers
         // (TMA bulk loads over NVLink, no multicast) into the local copy and publish one flag per tile.
@@ -502,7 +530,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             if (warp == 0 && lane == 0 && alive) ptx::st_release_sys(&ws->tile_flags[m_blk], epoch);
         }
     }
-    if (g.fuse == EP_GEMM_FUSE_REDUCE_SCATTER) {
+    if (!kFp8 && g.fuse == EP_GEMM_FUSE_REDUCE_SCATTER) {
         ptx::bulk_commit();
         ptx::bulk_wait<0>();
         __threadfence_system();
@@ -511,7 +539,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     __syncthreads();
     if (warp == 1) umma::tmem_dealloc(tmem_base, kTmemColumns);
 
-    if (g.fuse != EP_GEMM_FUSE_NONE) {
+    if (!kFp8 && g.fuse != EP_GEMM_FUSE_NONE) {
         // All partial rows have left this rank (RS) / all pulls from the peers are done (AG): cross-GPU barrier.
         const RankCtx& ctx = g.ctx;
         bool alive = grid_sync(ctx, ws, EP_CH_GEMM, EP_PH_GRID_SYNC);
@@ -624,7 +652,7 @@ cudaError_t launch_gemm(const GemmArgs& g, int num_sms, cudaStream_t stream) {
         return cudaLaunchCooperativeKernel(fn, dim3(ctas, 1, 1), dim3(kGemmThreads, 1, 1), params, kGemmSmemBytes, stream);
     }
     if (ctas > num_tiles) ctas = num_tiles;
-    return cudaLaunchKernel(fn, dim3(ctas, 1, 1), dim3(g.is_fp8 ? kGemmThreadsFp8 : kGemmThreads, 1, 1), params, kGemmSmemBytes, stream);
+    return cudaLaunchKernel(fn, dim3(ctas, 1, 1), dim3(gemm_threads(g.is_fp8 != 0, block_n), 1, 1), params, kGemmSmemBytes, stream);
 }
 
 }  // namespace ep
