@@ -301,7 +301,8 @@ struct MoeBwdArgs {
     int rows, cols;               // PREP / DEQUANT_T: cols = hidden; SWIGLU: cols = intermediate size I
     const uint8_t* valid;         // [rows]
     // PREP: g [rows, H] bf16 (gradient of the combined output at every expert row), y [rows, H] bf16 (the expert
-    //       outputs), w [rows] fp32 -> out = g * w [rows, H], out_t = out^T [H, rows], row_dot[row] = sum(g * y)
+    //       outputs), w [rows] fp32 -> out = g * w [rows, H], out_t = out^T [H, rows], row_dot[b * rows + row] = sum(g * y) over
+//       the columns of column block b (moe_bwd_prep_col_blocks of them; the caller adds them up)
     // SWIGLU: g = d_act [rows, I], y = h [rows, 2I] (gate | up) -> out = d_h [rows, 2I], out_t = d_h^T [2I, rows],
     //       out2_t = (silu(gate) * up)^T [I, rows]
     // DEQUANT_T: y = q [rows, H] e4m3, w = scales (row, 128-block) at w[row * sf_stride_row + blk * sf_stride_col]
@@ -319,4 +320,5 @@ struct MoeBwdArgs {
 namespace ep {
 cudaError_t launch_swiglu_quant(const SwigluQuantArgs& args, cudaStream_t stream);
 cudaError_t launch_moe_bwd(const MoeBwdArgs& args, cudaStream_t stream);
+int moe_bwd_prep_col_blocks(int cols);   // PREP writes row_dot as [col_blocks, rows] partial sums
 }  // namespace ep

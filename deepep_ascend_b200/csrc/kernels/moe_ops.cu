@@ -107,12 +107,16 @@ __device__ __forceinline__ int4 pack8(const float (&f)[8]) {
 }
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
-// one CTA = one strip of 64 rows, all columns (the per-row dot product needs the whole row)
+// grid (rows / 64, ceil(H / kPrepCols)): one CTA = 64 rows x kPrepCols columns; the per-row dot product of its columns goes
+// to row_dot[blockIdx.y * rows + row] and the caller adds the column blocks up (fixed order, so the result is deterministic)
+constexpr int kPrepCols = 512;
+
 __global__ void __launch_bounds__(kTileThreads) moe_bwd_prep_kernel(const MoeBwdArgs a) {
     __shared__ TileT tile;
     const int pair = threadIdx.x >> 3, c8 = threadIdx.x & 7;
     const int row0 = blockIdx.x * kTile;
     const int H = a.cols;
+    const int col_begin = blockIdx.y * kPrepCols, col_end = min(H, col_begin + kPrepCols);
     const uint8_t* gb = reinterpret_cast<const uint8_t*>(a.g);
     const uint8_t* yb = reinterpret_cast<const uint8_t*>(a.y);
     uint8_t* ob = reinterpret_cast<uint8_t*>(a.out);
@@ -124,7 +128,7 @@ __global__ void __launch_bounds__(kTileThreads) moe_bwd_prep_kernel(const MoeBwd
         ok[r] = a.valid[row] != 0;
         w[r] = ok[r] ? a.w[row] : 0.f;
     }
-    for (int col0 = 0; col0 < H; col0 += kTile) {
+    for (int col0 = col_begin; col0 < col_end; col0 += kTile) {
         float res[2][8];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -156,7 +160,7 @@ __global__ void __launch_bounds__(kTileThreads) moe_bwd_prep_kernel(const MoeBwd
         d += __shfl_xor_sync(0xffffffffu, d, 1);
         d += __shfl_xor_sync(0xffffffffu, d, 2);
         d += __shfl_xor_sync(0xffffffffu, d, 4);
-        if (c8 == 0) a.row_dot[row0 + 2 * pair + r] = d;
+        if (c8 == 0) a.row_dot[static_cast<int64_t>(blockIdx.y) * a.rows + row0 + 2 * pair + r] = d;
     }
 }
 
@@ -241,10 +245,12 @@ __global__ void __launch_bounds__(kTileThreads) moe_bwd_dequant_t_kernel(const M
 
 }  // namespace
 
+int moe_bwd_prep_col_blocks(int cols) { return (cols + kPrepCols - 1) / kPrepCols; }
+
 cudaError_t launch_moe_bwd(const MoeBwdArgs& a, cudaStream_t stream) {
     if (a.rows == 0) return cudaSuccess;
     if (a.rows % kTile != 0 || a.cols % kTile != 0) return cudaErrorInvalidValue;
-    if (a.op == EP_MOE_BWD_PREP) moe_bwd_prep_kernel<<<a.rows / kTile, kTileThreads, 0, stream>>>(a);
+    if (a.op == EP_MOE_BWD_PREP) moe_bwd_prep_kernel<<<dim3(a.rows / kTile, (a.cols + kPrepCols - 1) / kPrepCols), kTileThreads, 0, stream>>>(a);
     else if (a.op == EP_MOE_BWD_SWIGLU) moe_bwd_swiglu_kernel<<<dim3(a.rows / kTile, a.cols / kTile), kTileThreads, 0, stream>>>(a);
     else if (a.op == EP_MOE_BWD_DEQUANT_T) moe_bwd_dequant_t_kernel<<<dim3(a.rows / kTile, a.cols / kTile), kTileThreads, 0, stream>>>(a);
     else return cudaErrorInvalidValue;

@@ -249,7 +249,7 @@ std::vector<at::Tensor> moe_bwd_prep(const at::Tensor& g_rows, const at::Tensor&
     const int64_t rows = g_rows.size(0), H = g_rows.size(1);
     TORCH_CHECK(w.is_contiguous() && w.scalar_type() == at::kFloat && w.numel() == rows, "w must be fp32 [rows]");
     at::Tensor out = at::empty({rows, H}, g_rows.options()), out_t = at::empty({H, rows}, g_rows.options());
-    at::Tensor dot = at::empty({rows}, g_rows.options().dtype(at::kFloat));
+    at::Tensor dot = at::empty({static_cast<int64_t>(ep::moe_bwd_prep_col_blocks(static_cast<int>(H))), rows}, g_rows.options().dtype(at::kFloat));
     MoeBwdArgs a{};
     a.op = EP_MOE_BWD_PREP;
     a.rows = static_cast<int>(rows);
@@ -262,7 +262,7 @@ std::vector<at::Tensor> moe_bwd_prep(const at::Tensor& g_rows, const at::Tensor&
     a.out_t = out_t.data_ptr();
     a.row_dot = dot.data_ptr<float>();
     cuda_check(ep::launch_moe_bwd(a, at::cuda::getCurrentCUDAStream()), "MoE backward prep launch");
-    return {out, out_t, dot};
+    return {out, out_t, dot.sum(0)};
 }
 
 // Backward of SwiGLU: (d_h [rows, 2I], d_h^T [2I, rows], activation^T [I, rows])

@@ -88,3 +88,34 @@ def test_get_dispatch_layout_ref():
     assert per_rank.tolist() == [2, 0, 1, 1]
     assert per_expert.tolist() == [1, 1, 0, 0, 0, 1, 1, 1]
     assert in_rank.tolist() == [[True, False, True, False], [True, False, False, True]]
+
+
+def test_expert_tile_groups_and_segment_offsets():
+    """Host-free helpers that map the expand layout's expert segments onto GEMM tiles (CPU tensors work as well)."""
+    import torch
+    from deepep_ascend_b200.ops import gemm as G
+    torch.manual_seed(3)
+    for _ in range(20):
+        num_experts = int(torch.randint(1, 9, (1,)))
+        counts = torch.randint(0, 400, (num_experts,))
+        counts[torch.rand(num_experts) < 0.3] = 0
+        ends, start = [], 0
+        for c in counts.tolist():
+            ends.append(start + c)
+            start = (start + c + 127) // 128 * 128
+        rows = max(start, 128)
+        ends_t = torch.tensor(ends, dtype=torch.int32)
+        tile_group, valid = G.expert_tile_groups(ends_t, rows)
+        off = G.segment_offsets(ends_t)
+        exp_group = torch.full((rows // 128,), -1, dtype=torch.int32)
+        exp_valid = torch.zeros(rows, dtype=torch.bool)
+        s = 0
+        for e, c in enumerate(counts.tolist()):
+            exp_valid[s:s + c] = True
+            for t in range(s // 128, (s + c + 127) // 128):
+                exp_group[t] = e
+            assert off[e].item() == s
+            s = (s + c + 127) // 128 * 128
+        assert off[-1].item() == s
+        assert torch.equal(tile_group[:rows // 128], exp_group), (counts, tile_group, exp_group)
+        assert torch.equal(valid, exp_valid)
