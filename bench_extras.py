@@ -276,15 +276,15 @@ def main():
         bb = {}
 
         def prep():
-            bb['dy'], bb['dy_t'], bb['dot'] = G.moe_bwd_prep(g_rows, ybuf, rwc, valid_row)
+            bb['dy_t'] = G.weighted_transpose(g_rows, rwc, valid_row)
         t_prep = np.median(timeit(prep, None, iters=bi, warm=bw))
 
         def dgrad2():
-            bb['d_act'] = G.grouped_gemm_nt(bb['dy'], w2_t, tile_group)
+            bb['d_act'] = G.grouped_gemm_nt(g_rows, w2_t, tile_group)
         t_dg2 = np.median(timeit(dgrad2, None, iters=bi, warm=bw))
 
         def swb():
-            bb['dh'], bb['dh_t'], bb['act_t'] = G.swiglu_bwd(bb['d_act'], hbuf['h'], valid_row)
+            bb['dh'], bb['dh_t'], bb['act_t'], bb['dot'] = G.swiglu_bwd(bb['d_act'], hbuf['h'], valid_row, row_weight=rwc)
         t_swb = np.median(timeit(swb, None, iters=bi, warm=bw))
         t_dg1 = np.median(timeit(lambda: G.grouped_gemm_nt(bb['dh'], w13_t, tile_group, out=ybuf), None, iters=bi, warm=bw))
 
@@ -293,7 +293,7 @@ def main():
         t_xt = np.median(timeit(xt, None, iters=bi, warm=bw))
         t_wg2 = np.median(timeit(lambda: G.gemm_kgrouped(bb['dy_t'], bb['act_t'], seg_off), None, iters=bi, warm=bw))
         t_wg1 = np.median(timeit(lambda: G.gemm_kgrouped(bb['dh_t'], bb['x_t'], seg_off), None, iters=bi, warm=bw))
-        emit(bench='fused_moe_backward_breakdown_ms', rows=hd.num_rows, combine_bwd_prep=float(t_prep), dgrad_down_bf16=float(t_dg2),
+        emit(bench='fused_moe_backward_breakdown_ms', rows=hd.num_rows, weighted_transpose=float(t_prep), dgrad_down_bf16=float(t_dg2),
              swiglu_bwd=float(t_swb), dgrad_up_bf16=float(t_dg1), dequant_transpose=float(t_xt), wgrad_down=float(t_wg2),
              wgrad_up=float(t_wg1), dgrad_down_tflops=2 * hd.num_rows * H * I / t_dg2 / 1e9,
              dgrad_up_tflops=2 * hd.num_rows * H * 2 * I / t_dg1 / 1e9, wgrad_down_tflops=2 * hd.num_rows * H * I / t_wg2 / 1e9,

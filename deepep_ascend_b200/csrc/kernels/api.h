@@ -303,8 +303,10 @@ struct MoeBwdArgs {
     // PREP: g [rows, H] bf16 (gradient of the combined output at every expert row), y [rows, H] bf16 (the expert
     //       outputs), w [rows] fp32 -> out = g * w [rows, H], out_t = out^T [H, rows], row_dot[b * rows + row] = sum(g * y) over
 //       the columns of column block b (moe_bwd_prep_col_blocks of them; the caller adds them up)
+    //       (y, out and row_dot may each be null: that piece is then skipped)
     // SWIGLU: g = d_act [rows, I], y = h [rows, 2I] (gate | up) -> out = d_h [rows, 2I], out_t = d_h^T [2I, rows],
-    //       out2_t = (silu(gate) * up)^T [I, rows]
+    //       out2_t = (silu(gate) * up)^T [I, rows]; optional w [rows]: d_act is multiplied by w[row] first, and
+    //       optional row_dot[b * rows + row] = sum over the 64 columns of block b of d_act * activation (before w)
     // DEQUANT_T: y = q [rows, H] e4m3, w = scales (row, 128-block) at w[row * sf_stride_row + blk * sf_stride_col]
     //       -> out_t = (q * scale)^T [H, rows] bf16
     const void* g;

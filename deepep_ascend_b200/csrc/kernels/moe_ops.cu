@@ -136,7 +136,11 @@ __global__ void __launch_bounds__(kTileThreads) moe_bwd_prep_kernel(const MoeBwd
             float g[8], y[8];
             if (ok[r]) {
                 unpack8(ptx::ld_nc_v4(gb + off), g);
-                unpack8(ptx::ld_nc_v4(yb + off), y);
+                if (yb != nullptr) unpack8(ptx::ld_nc_v4(yb + off), y);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) y[j] = 0.f;
+                }
             } else {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) g[j] = y[j] = 0.f;
@@ -146,7 +150,7 @@ __global__ void __launch_bounds__(kTileThreads) moe_bwd_prep_kernel(const MoeBwd
                 dot[r] = fmaf(g[j], y[j], dot[r]);
                 res[r][j] = round_bf16(g[j] * w[r]);
             }
-            *reinterpret_cast<int4*>(ob + off) = pack8(res[r]);
+            if (ob != nullptr) *reinterpret_cast<int4*>(ob + off) = pack8(res[r]);
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) stash_pair(tile, c8 * 8 + j, pair, res[0][j], res[1][j]);
@@ -160,7 +164,7 @@ __global__ void __launch_bounds__(kTileThreads) moe_bwd_prep_kernel(const MoeBwd
         d += __shfl_xor_sync(0xffffffffu, d, 1);
         d += __shfl_xor_sync(0xffffffffu, d, 2);
         d += __shfl_xor_sync(0xffffffffu, d, 4);
-        if (c8 == 0) a.row_dot[static_cast<int64_t>(blockIdx.y) * a.rows + row0 + 2 * pair + r] = d;
+        if (c8 == 0 && a.row_dot != nullptr) a.row_dot[static_cast<int64_t>(blockIdx.y) * a.rows + row0 + 2 * pair + r] = d;
     }
 }
 
@@ -173,7 +177,7 @@ __global__ void __launch_bounds__(kTileThreads) moe_bwd_swiglu_kernel(const MoeB
     const uint8_t* db = reinterpret_cast<const uint8_t*>(a.g);
     const uint8_t* hb = reinterpret_cast<const uint8_t*>(a.y);
     uint8_t* ob = reinterpret_cast<uint8_t*>(a.out);
-    float dg[2][8], du[2][8], act[2][8];
+    float dg[2][8], du[2][8], act[2][8], dot[2] = {0.f, 0.f};
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = row0 + 2 * pair + r;
@@ -181,14 +185,19 @@ __global__ void __launch_bounds__(kTileThreads) moe_bwd_swiglu_kernel(const MoeB
         if (a.valid[row] != 0) {
             float d[8], gate[8], up[8];
             unpack8(ptx::ld_nc_v4(db + (static_cast<int64_t>(row) * I + col) * 2), d);
+            const float wr = a.w != nullptr ? a.w[row] : 1.f;
             unpack8(ptx::ld_nc_v4(hb + (static_cast<int64_t>(row) * 2 * I + col) * 2), gate);
             unpack8(ptx::ld_nc_v4(hb + (static_cast<int64_t>(row) * 2 * I + I + col) * 2), up);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const float sig = 1.f / (1.f + __expf(-gate[j]));
                 act[r][j] = round_bf16(gate[j] * sig * up[j]);
-                du[r][j] = round_bf16(d[j] * gate[j] * sig);
-                dg[r][j] = round_bf16(d[j] * up[j] * sig * (1.f + gate[j] * (1.f - sig)));
+                // d[j] is the gradient w.r.t. the UNWEIGHTED activation when a row weight is given: its product with the
+                // activation is d loss / d weight, and the weight enters the gradients that flow on
+                dot[r] = fmaf(d[j], act[r][j], dot[r]);
+                const float dj = d[j] * wr;
+                du[r][j] = round_bf16(dj * gate[j] * sig);
+                dg[r][j] = round_bf16(dj * up[j] * sig * (1.f + gate[j] * (1.f - sig)));
             }
         } else {
 #pragma unroll
@@ -207,6 +216,16 @@ __global__ void __launch_bounds__(kTileThreads) moe_bwd_swiglu_kernel(const MoeB
     flush_transposed(t_gate, a.out_t, a.rows, col0, row0);
     flush_transposed(t_up, a.out_t, a.rows, I + col0, row0);
     flush_transposed(t_act, a.out2_t, a.rows, col0, row0);
+    if (a.row_dot != nullptr) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float d = dot[r];
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            d += __shfl_xor_sync(0xffffffffu, d, 4);
+            if (c8 == 0) a.row_dot[static_cast<int64_t>(blockIdx.y) * a.rows + row0 + 2 * pair + r] = d;
+        }
+    }
 }
 
 // grid (rows / 64, H / 64)

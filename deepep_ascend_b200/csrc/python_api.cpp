@@ -265,12 +265,15 @@ std::vector<at::Tensor> moe_bwd_prep(const at::Tensor& g_rows, const at::Tensor&
     return {out, out_t, dot.sum(0)};
 }
 
-// Backward of SwiGLU: (d_h [rows, 2I], d_h^T [2I, rows], activation^T [I, rows])
-std::vector<at::Tensor> swiglu_bwd(const at::Tensor& d_act, const at::Tensor& h, const at::Tensor& valid) {
+// Backward of SwiGLU: (d_h [rows, 2I], d_h^T [2I, rows], activation^T [I, rows]).  With `row_weight` [rows] the incoming
+// gradient is multiplied by it first and a fourth result, sum_i d_act[row, i] * activation[row, i] (the gradient of the
+// row weight), is returned.
+std::vector<at::Tensor> swiglu_bwd(const at::Tensor& d_act, const at::Tensor& h, const at::Tensor& valid, const std::optional<at::Tensor>& row_weight) {
     TORCH_CHECK(d_act.is_cuda() && d_act.dim() == 2 && d_act.is_contiguous() && d_act.scalar_type() == at::kBFloat16, "d_act must be contiguous bf16 [rows, I]");
     const int64_t rows = d_act.size(0), I = d_act.size(1);
     TORCH_CHECK(h.is_contiguous() && h.scalar_type() == at::kBFloat16 && h.dim() == 2 && h.size(0) == rows && h.size(1) == 2 * I, "h must be bf16 [rows, 2I]");
     at::Tensor out = at::empty({rows, 2 * I}, h.options()), out_t = at::empty({2 * I, rows}, h.options()), act_t = at::empty({I, rows}, h.options());
+    at::Tensor dot;
     MoeBwdArgs a{};
     a.op = EP_MOE_BWD_SWIGLU;
     a.rows = static_cast<int>(rows);
@@ -281,8 +284,34 @@ std::vector<at::Tensor> swiglu_bwd(const at::Tensor& d_act, const at::Tensor& h,
     a.out = out.data_ptr();
     a.out_t = out_t.data_ptr();
     a.out2_t = act_t.data_ptr();
+    if (row_weight.has_value()) {
+        TORCH_CHECK(row_weight->is_cuda() && row_weight->is_contiguous() && row_weight->scalar_type() == at::kFloat && row_weight->numel() == rows,
+                    "row_weight must be fp32 [rows]");
+        dot = at::empty({I / 64, rows}, h.options().dtype(at::kFloat));
+        a.w = row_weight->data_ptr<float>();
+        a.row_dot = dot.data_ptr<float>();
+    }
     cuda_check(ep::launch_moe_bwd(a, at::cuda::getCurrentCUDAStream()), "SwiGLU backward launch");
+    if (row_weight.has_value()) return {out, out_t, act_t, dot.sum(0)};
     return {out, out_t, act_t};
+}
+
+// (g * w)^T [H, rows] in bf16 (padding rows zero): the transposed operand of the down-projection weight gradient
+at::Tensor weighted_transpose(const at::Tensor& g_rows, const at::Tensor& w, const at::Tensor& valid) {
+    TORCH_CHECK(g_rows.is_cuda() && g_rows.dim() == 2 && g_rows.is_contiguous() && g_rows.scalar_type() == at::kBFloat16, "g must be contiguous bf16 [rows, H]");
+    const int64_t rows = g_rows.size(0), H = g_rows.size(1);
+    TORCH_CHECK(w.is_contiguous() && w.scalar_type() == at::kFloat && w.numel() == rows, "w must be fp32 [rows]");
+    at::Tensor out_t = at::empty({H, rows}, g_rows.options());
+    MoeBwdArgs a{};
+    a.op = EP_MOE_BWD_PREP;
+    a.rows = static_cast<int>(rows);
+    a.cols = static_cast<int>(H);
+    a.valid = valid_ptr(valid, rows);
+    a.g = g_rows.data_ptr();
+    a.w = w.data_ptr<float>();
+    a.out_t = out_t.data_ptr();
+    cuda_check(ep::launch_moe_bwd(a, at::cuda::getCurrentCUDAStream()), "weighted transpose launch");
+    return out_t;
 }
 
 // (q e4m3 [rows, H], scales per (row, 128 channels), any strides) -> bf16 (q * scale)^T [H, rows]
@@ -513,7 +542,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("swiglu_quant", &swiglu_quant, py::arg("h"), py::arg("keep_bf16") = false);
     m.def("gemm_kgrouped", &gemm_kgrouped, py::arg("a_t"), py::arg("b_t"), py::arg("k_off"), py::arg("num_sms") = 0);
     m.def("moe_bwd_prep", &moe_bwd_prep);
-    m.def("swiglu_bwd", &swiglu_bwd);
+    m.def("swiglu_bwd", &swiglu_bwd, py::arg("d_act"), py::arg("h"), py::arg("valid"), py::arg("row_weight") = py::none());
+    m.def("weighted_transpose", &weighted_transpose);
     m.def("dequant_transpose", &dequant_transpose);
     m.def("gemm_error", [](int device) { return gemm_error_flag(device).item<int>(); });
     m.def("install_segv_backtrace", [] { signal(SIGSEGV, segv_backtrace_handler); });

@@ -35,29 +35,33 @@ class _MoEFunction(torch.autograd.Function):
         G.grouped_gemm_nt(a2, q2, tile_group, out=y, sfa=sf2, sfb=s2)                      # [rows, H] in the combine region
         out, _, _ = buf.combine(y, handle, weighted=True, num_sms=layer.num_sms)
         ctx.layer, ctx.handle = layer, handle
-        # the combine region is reused by the next call, so the expert outputs (needed for d loss / d weight) are copied
-        ctx.save_for_backward(rx, rsf, recv_w, h, y.clone(), tile_group, valid_row)
+        if layer.copy_saved_rows:
+            # the received rows live in a receive slot of the buffer that later dispatches (other layers) will reuse
+            rx, rsf, recv_w = rx.clone(), rsf.clone(), recv_w.clone()
+        ctx.save_for_backward(rx, rsf, recv_w, h, tile_group, valid_row)
         return out
 
     @staticmethod
     def backward(ctx, d_out):
         layer, handle = ctx.layer, ctx.handle
         buf: ElasticBuffer = layer.buffer
-        rx, rsf, recv_w, h, y, tile_group, valid_row = ctx.saved_tensors
+        rx, rsf, recv_w, h, tile_group, valid_row = ctx.saved_tensors
         seg_off = G.segment_offsets(handle.psum_num_recv_tokens_per_expert)
-        # backward of the weighted combine: every expert row receives its token's gradient (cached dispatch), then one
-        # kernel forms d y = g * w (row-major for the data gradient, transposed for the weight gradient) and d w = <g, y>
+        rw = recv_w.contiguous()
+        # backward of the weighted combine: every expert row receives its token's gradient g (cached dispatch)
         g_rows, _, _, _, _ = buf.dispatch(d_out.contiguous(), handle=handle, fused_fp8_cast=False, num_sms=layer.num_sms)
-        dy, dy_t, d_w_rows = G.moe_bwd_prep(g_rows, y, recv_w.contiguous(), valid_row)
         w2_t, w13_t = layer.transposed_weights()
-        # down projection
-        d_act = G.grouped_gemm_nt(dy, w2_t, tile_group)                                     # [rows, I]
-        dh, dh_t, act_t = G.swiglu_bwd(d_act, h, valid_row)
+        # down projection on the UNWEIGHTED gradient: d loss / d weight of a row is <g W2, activation> (= <g, y>, so the
+        # expert outputs need not be kept), and the weight is applied inside the SwiGLU backward kernel.  Padding rows of
+        # g_rows hold stale data; every consumer masks them.
+        d_act_u = G.grouped_gemm_nt(g_rows, w2_t, tile_group)                               # [rows, I]
+        dh, dh_t, act_t, d_w_rows = G.swiglu_bwd(d_act_u, h, valid_row, row_weight=rw)
         # up projection: the gradient rows go into the combine region and travel home (backward of dispatch)
         d_recv = buf.get_combine_buffer(handle)
         G.grouped_gemm_nt(dh, w13_t, tile_group, out=d_recv)
         dx, d_topk_w, _ = buf.combine(d_recv, handle, topk_weights=d_w_rows, num_sms=layer.num_sms)
         # weight gradients: one K-grouped GEMM per weight tensor, reduction over the rows of every expert segment
+        dy_t = G.weighted_transpose(g_rows, rw, valid_row)                                  # (g * w)^T [H, rows]
         x_t = G.dequant_transpose(rx, rsf, valid_row)
         d_w2 = G.gemm_kgrouped(dy_t, act_t, seg_off)                                        # [El, H, I]
         d_w13 = G.gemm_kgrouped(dh_t, x_t, seg_off)                                         # [El, 2I, H]
@@ -74,12 +78,15 @@ class FusedMoE(nn.Module):
     """
 
     def __init__(self, buffer: ElasticBuffer, num_experts: int, hidden: int, intermediate: int, init_std: float = 0.02,
-                 num_sms: int = 0, device='cuda'):
+                 num_sms: int = 0, device='cuda', copy_saved_rows: bool = False):
         super().__init__()
         assert num_experts % buffer.num_ranks == 0 and hidden % 128 == 0 and intermediate % 128 == 0
         assert buffer.enable_expand, 'construct the buffer with enable_expand=True, expert_alignment=128'
         self.buffer, self.num_experts, self.hidden, self.intermediate = buffer, num_experts, hidden, intermediate
         self.num_sms = num_sms
+        # False: the backward pass reads the dispatched rows in place (valid while no other dispatch but this layer's own
+        # backward one runs on the buffer in between); True: they are copied, as needed when several layers share the buffer
+        self.copy_saved_rows = copy_saved_rows
         el = num_experts // buffer.num_ranks
         self.w13 = nn.Parameter((torch.randn(el, 2 * intermediate, hidden, device=device) * init_std).bfloat16())
         self.w2 = nn.Parameter((torch.randn(el, hidden, intermediate, device=device) * init_std).bfloat16())

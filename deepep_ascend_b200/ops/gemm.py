@@ -84,9 +84,17 @@ def moe_bwd_prep(g_rows: torch.Tensor, y: torch.Tensor, w: torch.Tensor, valid_r
     return _native.load().moe_bwd_prep(g_rows, y, w, valid_row)
 
 
-def swiglu_bwd(d_act: torch.Tensor, h: torch.Tensor, valid_row: torch.Tensor):
-    """Backward of ``silu(gate) * up`` -> ``(d_h [rows, 2I], d_h^T [2I, rows], activation^T [I, rows])``."""
-    return _native.load().swiglu_bwd(d_act, h, valid_row)
+def swiglu_bwd(d_act: torch.Tensor, h: torch.Tensor, valid_row: torch.Tensor, row_weight: Optional[torch.Tensor] = None):
+    """Backward of ``silu(gate) * up`` -> ``(d_h [rows, 2I], d_h^T [2I, rows], activation^T [I, rows])``.  With
+    ``row_weight [rows]`` the incoming gradient is taken as the gradient of the UNWEIGHTED activation: it is multiplied by
+    the weight before it flows on, and ``sum_i d_act[r, i] * activation[r, i]`` (= d loss / d weight) is returned as a
+    fourth tensor."""
+    return _native.load().swiglu_bwd(d_act, h, valid_row, row_weight)
+
+
+def weighted_transpose(g_rows: torch.Tensor, w: torch.Tensor, valid_row: torch.Tensor) -> torch.Tensor:
+    """``(g * w[:, None])^T`` as bf16 ``[H, rows]`` with zero columns for padding rows."""
+    return _native.load().weighted_transpose(g_rows, w, valid_row)
 
 
 def dequant_transpose(q: torch.Tensor, sf: torch.Tensor, valid_row: torch.Tensor) -> torch.Tensor:

@@ -6,8 +6,9 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize('copy_rows', [False, True])
 @pytest.mark.parametrize('T,H,I,E,K', [(200, 256, 128, 4, 2), (512, 1024, 512, 8, 4)])
-def test_fused_moe_forward_backward(T, H, I, E, K):
+def test_fused_moe_forward_backward(T, H, I, E, K, copy_rows):
     from deepep_ascend_b200 import ElasticBuffer
     from deepep_ascend_b200.models.moe import FusedMoE, moe_reference
     from deepep_ascend_b200.utils.math import calc_diff
@@ -15,7 +16,7 @@ def test_fused_moe_forward_backward(T, H, I, E, K):
     buf = ElasticBuffer(None, num_max_tokens_per_rank=T, hidden=H, num_topk=K, enable_expand=True, num_experts=E,
                         expert_alignment=128)
     try:
-        layer = FusedMoE(buf, E, H, I, init_std=0.05, num_sms=16)
+        layer = FusedMoE(buf, E, H, I, init_std=0.05, num_sms=16, copy_saved_rows=copy_rows)
         x = torch.randn(T, H, device='cuda').bfloat16().requires_grad_(True)
         scores = torch.softmax(torch.randn(T, E, device='cuda'), dim=-1)
         w, idx = scores.topk(K, dim=-1)
@@ -71,6 +72,15 @@ def test_backward_elementwise_kernels(rows, H, I):
     torch.testing.assert_close(dh.float(), ref_dh, rtol=2e-2, atol=2e-2)
     assert torch.equal(dh_t, dh.t().contiguous())
     torch.testing.assert_close(act_t.float(), ref_act.t(), rtol=2e-2, atol=2e-2)
+
+    dh2, dh2_t, act2_t, dot2 = G.swiglu_bwd(d_act, h, valid, row_weight=w)
+    ref_dh2 = torch.where(vm, ref_dh * w.unsqueeze(1), torch.zeros_like(ref_dh))
+    torch.testing.assert_close(dh2.float(), ref_dh2, rtol=2e-2, atol=2e-2)
+    assert torch.equal(dh2_t, dh2.t().contiguous()) and torch.equal(act2_t, act_t)
+    ref_dot2 = torch.where(valid, (d * act_t.t().float()).sum(1), torch.zeros_like(w))
+    torch.testing.assert_close(dot2, ref_dot2, rtol=1e-3, atol=1e-2)
+    gw_t = G.weighted_transpose(g, w, valid)
+    assert torch.equal(gw_t, ref_dy.t().contiguous())
 
     x = torch.randn(rows, H, device='cuda').bfloat16()
     q, sf = per_token_cast_to_fp8(x)
