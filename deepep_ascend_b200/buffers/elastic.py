@@ -340,7 +340,6 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         the kernel; ``fused_fp8_cast=False`` sends bf16 rows even on an FP8 buffer (backward passes).
         """
         assert not self._destroyed
-        assert not do_zero_padding or do_expand, '`do_zero_padding` requires `do_expand`'
         if handle is not None:
             assert topk_idx is None, '`topk_idx` comes from the cached handle'
             num_experts = handle.num_experts
@@ -350,6 +349,7 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
             do_cpu_sync = False if do_cpu_sync is None else do_cpu_sync
             assert not do_cpu_sync, 'a cached dispatch already knows its sizes'
         do_cpu_sync = value_or(do_cpu_sync, True)
+        assert not do_zero_padding or do_expand, '`do_zero_padding` requires `do_expand` (or a cached expand handle)'
         assert num_experts is not None and num_experts % self.num_ranks == 0
         num_max_tokens_per_rank = value_or(num_max_tokens_per_rank, self.num_max_tokens_per_rank)
         expert_alignment = value_or(expert_alignment, 1)
