@@ -1,0 +1,86 @@
+"""Routing-score generators (precise hot-rank ratio, Zipf skew) and the exact public surface of the package and of the
+native module (a rename or a dropped binding fails here, on the CPU tier)."""
+import torch
+
+
+def test_precise_unbalanced_scores_hit_the_requested_ratio():
+    from deepep_ascend_b200.utils import gate
+    torch.manual_seed(0)
+    checked = 0
+    for per_rank in (1, 4, 8):
+        for num_ranks in (2, 4, 8, 16):
+            E = per_rank * num_ranks
+            for K in (1, 2, 4, 6, 8):
+                if K > E:
+                    continue
+                for ratio in (1.0, 2.0, 4.0):
+                    lo = max(1, -(-K // per_rank))
+                    hi = min(K, num_ranks, int((num_ranks - 1) / ratio) + 1)
+                    if lo > hi:
+                        continue
+                    total = torch.zeros(num_ranks)
+                    for _ in range(num_ranks):
+                        s = gate.get_unbalanced_scores(4096, E, num_ranks, K, ratio, True, device='cpu')
+                        idx = s.topk(K, dim=-1).indices
+                        total += gate.rank_hit_counts(idx, E, num_ranks).float()
+                    got = total[0].item() / max(total[1:].min().item(), 1)
+                    spread = total[1:].max().item() / max(total[1:].min().item(), 1)
+                    assert abs(got - ratio) / ratio < 0.1 and spread < 1.02, (per_rank, num_ranks, K, ratio, got, spread)
+                    checked += 1
+    assert checked > 50
+
+
+def test_random_unbalanced_and_zipf_scores_are_skewed():
+    from deepep_ascend_b200.utils import gate
+    torch.manual_seed(1)
+    s = gate.get_unbalanced_scores(4096, 64, 8, 4, 3.0, False, device='cpu')
+    c = gate.rank_hit_counts(s.topk(4, dim=-1).indices, 64, 8).float()
+    assert 2.0 < c[0] / c[1:].mean() < 4.5
+    z = gate.get_zipf_scores(8192, 64, 1.2, device='cpu')
+    first = (z.topk(6, dim=-1).indices == 0).any(dim=1).float().mean()
+    last = (z.topk(6, dim=-1).indices == 63).any(dim=1).float().mean()
+    assert first > 0.6 and last < 0.1
+    b = gate.get_balanced_scores(4096, 64, device='cpu')
+    cb = gate.rank_hit_counts(b.topk(4, dim=-1).indices, 64, 8).float()
+    assert cb.max() / cb.min() < 1.15
+
+
+PACKAGE_EXPORTS = ['Buffer', 'Config', 'EPHandle', 'ElasticBuffer', 'EventHandle', 'EventOverlap', 'get_logical_domain_size',
+                   'get_physical_domain_size', 'topk_idx_t']
+BUFFER_METHODS = ['all_gather', 'barrier', 'capture', 'combine', 'destroy', 'dispatch', 'engram_fetch', 'engram_write',
+                  'get_buffer_size_hint', 'get_comm_stream', 'get_theoretical_num_sms', 'low_latency_combine', 'low_latency_dispatch',
+                  'pp_recv', 'pp_send', 'pp_set_config']
+NATIVE_FUNCTIONS = ['ag_gemm', 'dequant_transpose', 'gemm_error', 'gemm_kgrouped', 'gemm_nt', 'gemm_rs', 'get_dispatch_layout',
+                    'get_elastic_buffer_alignment', 'get_platform', 'get_workspace_bytes', 'moe_bwd_prep', 'per_token_cast_to_fp8',
+                    'swiglu_bwd', 'swiglu_quant', 'weighted_transpose']
+NATIVE_CLASSES = ['CombineCall', 'DispatchCall', 'ElasticBuffer', 'RecvSlot', 'LLCombineCall', 'LLDispatchCall', 'MoeShape', 'RegionLayout']
+
+
+def test_public_surface():
+    import deepep_ascend_b200 as ep
+    for name in PACKAGE_EXPORTS:
+        assert hasattr(ep, name), name
+    for name in BUFFER_METHODS:
+        assert callable(getattr(ep.ElasticBuffer, name, None)), name
+    for name in ('dispatch', 'combine', 'get_dispatch_layout', 'low_latency_dispatch', 'low_latency_combine',
+                 'clean_low_latency_buffer', 'get_next_low_latency_combine_buffer'):
+        assert callable(getattr(ep.Buffer, name, None)), name
+    handle_fields = ['do_expand', 'num_experts', 'expert_alignment', 'num_max_tokens_per_rank', 'num_sms', 'topk_idx', 'num_recv_tokens',
+                     'num_expanded_tokens', 'psum_num_recv_tokens_per_scaleup_rank', 'psum_num_recv_tokens_per_expert',
+                     'num_unaligned_recv_tokens_per_expert', 'recv_src_metadata', 'dst_buffer_slot_idx']
+    import inspect
+    params = inspect.signature(ep.EPHandle.__init__).parameters
+    for f in handle_fields:
+        assert f in params, f
+
+
+def test_native_module_surface():
+    from deepep_ascend_b200 import _native
+    C = _native.load()
+    assert C.get_platform() == 'cuda-sm100a'
+    for name in NATIVE_FUNCTIONS:
+        assert callable(getattr(C, name, None)), name
+    for name in NATIVE_CLASSES:
+        assert isinstance(getattr(C, name, None), type), name
+    assert C.MAX_RANKS == 8 and C.MAX_TOPK == 16 and C.MAX_EXPERTS == 1024
+    assert C.get_workspace_bytes() == 4 << 20
