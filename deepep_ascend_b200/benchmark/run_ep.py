@@ -326,8 +326,10 @@ def _worker(rank: int, world: int, port: int, backend: str, profile_name: str, m
                     say('case %s raised on rank %d:\n%s' % (case.case_id, rank, traceback.format_exc()))
                     raise
                 results.append(res)
-                say('%s %s dispatch %.1f us combine %.1f us' % (res['case_id'], res['status'], res['performance']['dispatch']['avg_us'],
-                                                               res['performance']['combine']['avg_us']))
+                bad = [op for op in CORRECTNESS_OPERATIONS if not res['correctness'][op]]
+                say('%s %s dispatch %.1f us combine %.1f us%s' % (res['case_id'], res['status'], res['performance']['dispatch']['avg_us'],
+                                                                 res['performance']['combine']['avg_us'],
+                                                                 (' wrong: ' + ', '.join(bad)) if bad else ''))
             buf.destroy()
         if rank == 0:
             order = {c.case_id: i for i, c in enumerate(cases)}

@@ -496,8 +496,9 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
                 recv_w = core.view(st.slot.w, [rows], [1], torch.float32) if st.do_expand else \
                     core.view(st.slot.w, [rows, K], [K, 1], torch.float32)
             meta = core.view(st.slot.meta, [rows, 2], [2, 1], torch.int32)
-        if do_zero_padding and st.do_expand and st.cached_handle is None:
-            self._zero_padding(recv_x, st.call.psum_expert, st.alignment, rows)
+        if do_zero_padding and st.do_expand:
+            psum = st.call.psum_expert if st.cached_handle is None else st.cached_handle.psum_num_recv_tokens_per_expert
+            self._zero_padding(recv_x, psum, st.alignment, rows)
         if not self.zero_copy:
             recv_x = recv_x.clone()
             recv_sf = None if recv_sf is None else recv_sf.clone()
