@@ -198,108 +198,108 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const uint32_t tmem_base = sm->tmem_base;
 
     if (warp < kEpiWarp0) {
-    // ---------------------------------------------------------------------- producer warps (not re-indented)
-    // wide e4m3 kernel: warps 0-3 (TMA, MMA, two idle) keep 40 registers each so that the epilogue warps can take 232
-    if (kWide) reg_dealloc<40>();
-    if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            PipeState<kStages> p;
-            bool ok = true;
-            for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
-                const TileWork tw = tile_work(g, tile, num_m, num_n, num_k, group_m, kBlockK);
-                const int m_blk = tw.m, n_blk = tw.n, grp = tw.grp;
-                if (grp < 0 || tw.kb1 <= tw.kb0) continue;
-                if (g.fuse == EP_GEMM_FUSE_ALL_GATHER && m_blk / tiles_per_shard != g.ctx.rank) {
-                    // rows of a remote shard: wait until a copier CTA of this kernel has landed the tile locally
-                    const uint64_t* flag = &ws->tile_flags[m_blk];
-                    const uint64_t t0 = gemm_timer();
-                    while (ptx::ld_acquire_sys(flag) < epoch) {
-                        if (gemm_timer() - t0 > kWaitLimitNs || *reinterpret_cast<volatile int*>(&sm->failed)) {
-                            sm->failed = 3;
-                            if (g.error != nullptr) atomicCAS(g.error, 0, 3);
-                            ok = false;
-                            break;
+        // ---------------------------------------------------------------------- producer warps
+        // wide e4m3 kernel: warps 0-3 (TMA, MMA, two idle) keep 40 registers each so that the epilogue warps can take 232
+        if (kWide) reg_dealloc<40>();
+        if (warp == 0) {
+            // ------------------------------------------------------------------ TMA producer
+            if (lane == 0) {
+                PipeState<kStages> p;
+                bool ok = true;
+                for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
+                    const TileWork tw = tile_work(g, tile, num_m, num_n, num_k, group_m, kBlockK);
+                    const int m_blk = tw.m, n_blk = tw.n, grp = tw.grp;
+                    if (grp < 0 || tw.kb1 <= tw.kb0) continue;
+                    if (g.fuse == EP_GEMM_FUSE_ALL_GATHER && m_blk / tiles_per_shard != g.ctx.rank) {
+                        // rows of a remote shard: wait until a copier CTA of this kernel has landed the tile locally
+                        const uint64_t* flag = &ws->tile_flags[m_blk];
+                        const uint64_t t0 = gemm_timer();
+                        while (ptx::ld_acquire_sys(flag) < epoch) {
+                            if (gemm_timer() - t0 > kWaitLimitNs || *reinterpret_cast<volatile int*>(&sm->failed)) {
+                                sm->failed = 3;
+                                if (g.error != nullptr) atomicCAS(g.error, 0, 3);
+                                ok = false;
+                                break;
+                            }
                         }
+                        if (!ok) break;
+                        ptx::fence_proxy_async_all();   // the tile was written through the async proxy of another SM
                     }
-                    if (!ok) break;
-                    ptx::fence_proxy_async_all();   // the tile was written through the async proxy of another SM
-                }
-                if (g.a_ready_flags != nullptr) {
-                    // rows of this M tile arrive from another rank: wait (bounded) for their flag
-                    const uint64_t* flag = g.a_ready_flags + (g.a_flag_of_tile != nullptr ? g.a_flag_of_tile[m_blk] : m_blk);
-                    const uint64_t t0 = gemm_timer();
-                    while (ptx::ld_acquire_sys(flag) < g.a_ready_value) {
-                        if (gemm_timer() - t0 > kWaitLimitNs || *reinterpret_cast<volatile int*>(&sm->failed)) {
-                            sm->failed = 3;
-                            if (g.error != nullptr) atomicCAS(g.error, 0, 3);
-                            ok = false;
-                            break;
+                    if (g.a_ready_flags != nullptr) {
+                        // rows of this M tile arrive from another rank: wait (bounded) for their flag
+                        const uint64_t* flag = g.a_ready_flags + (g.a_flag_of_tile != nullptr ? g.a_flag_of_tile[m_blk] : m_blk);
+                        const uint64_t t0 = gemm_timer();
+                        while (ptx::ld_acquire_sys(flag) < g.a_ready_value) {
+                            if (gemm_timer() - t0 > kWaitLimitNs || *reinterpret_cast<volatile int*>(&sm->failed)) {
+                                sm->failed = 3;
+                                if (g.error != nullptr) atomicCAS(g.error, 0, 3);
+                                ok = false;
+                                break;
+                            }
                         }
-                    }
-                    if (!ok) break;
-                }
-                for (int kb = tw.kb0; kb < tw.kb1 && ok; ++kb) {
-                    ok = wait_bar(&sm->empty[p.stage], p.phase ^ 1, sm, g.error, 1);
-                    if (!ok) break;
-                    ptx::mbar_arrive_expect_tx(&sm->full[p.stage], kTileBytes + kTileBytesB);
-                    umma::tma_load_2d(s_a + p.stage * kTileBytes, &map_a, kb * kBlockK, m_blk * kBlockM, &sm->full[p.stage]);
-                    umma::tma_load_2d(s_b + p.stage * kTileBytesB, &map_b, kb * kBlockK, grp * g.N + n_blk * kBlockN, &sm->full[p.stage]);
-                    p.advance();
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            PipeState<kStages> p;
-            int acc = 0;
-            uint32_t acc_phase = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
-                const TileWork tw = tile_work(g, tile, num_m, num_n, num_k, group_m, kBlockK);
-                if (tw.grp < 0 || tw.kb1 <= tw.kb0) continue;
-                if (!kFp8) {
-                    ok = wait_bar(&sm->tmem_empty[acc], acc_phase ^ 1, sm, g.error, 2);
-                    if (!ok) break;
-                    umma::fence_after_thread_sync();
-                }
-                for (int kb = tw.kb0; kb < tw.kb1 && ok; ++kb) {
-                    if (kFp8) {
-                        ok = wait_bar(&sm->tmem_empty[acc], acc_phase ^ 1, sm, g.error, 2);
                         if (!ok) break;
                     }
-                    ok = wait_bar(&sm->full[p.stage], p.phase, sm, g.error, 4);
-                    if (!ok) break;
-                    umma::fence_after_thread_sync();
-                    const uint64_t desc_a = umma::make_smem_desc_sw128(s_a + p.stage * kTileBytes);
-                    const uint64_t desc_b = umma::make_smem_desc_sw128(s_b + p.stage * kTileBytesB);
-#pragma unroll
-                    for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                        const uint32_t accumulate = kFp8 ? (k != 0) : (kb != tw.kb0 || k != 0);
-                        umma::mma_ss<kFp8>(tmem_base + acc * kBlockN, umma::advance_desc_k(desc_a, k * 32), umma::advance_desc_k(desc_b, k * 32),
-                                           kIdesc, accumulate);
+                    for (int kb = tw.kb0; kb < tw.kb1 && ok; ++kb) {
+                        ok = wait_bar(&sm->empty[p.stage], p.phase ^ 1, sm, g.error, 1);
+                        if (!ok) break;
+                        ptx::mbar_arrive_expect_tx(&sm->full[p.stage], kTileBytes + kTileBytesB);
+                        umma::tma_load_2d(s_a + p.stage * kTileBytes, &map_a, kb * kBlockK, m_blk * kBlockM, &sm->full[p.stage]);
+                        umma::tma_load_2d(s_b + p.stage * kTileBytesB, &map_b, kb * kBlockK, grp * g.N + n_blk * kBlockN, &sm->full[p.stage]);
+                        p.advance();
                     }
-                    umma::mma_commit(&sm->empty[p.stage]);       // the stage may be refilled once these MMAs are done
-                    p.advance();
-                    if (kFp8) {
-                        umma::mma_commit(&sm->tmem_full[acc]);   // one 128-channel block is ready for promotion
+                }
+            }
+        } else if (warp == 1) {
+            // ------------------------------------------------------------------ MMA issuer
+            if (lane == 0) {
+                PipeState<kStages> p;
+                int acc = 0;
+                uint32_t acc_phase = 0;
+                bool ok = true;
+                for (int tile = blockIdx.x; !is_copier && tile < num_tiles && ok; tile += gemm_ctas) {
+                    const TileWork tw = tile_work(g, tile, num_m, num_n, num_k, group_m, kBlockK);
+                    if (tw.grp < 0 || tw.kb1 <= tw.kb0) continue;
+                    if (!kFp8) {
+                        ok = wait_bar(&sm->tmem_empty[acc], acc_phase ^ 1, sm, g.error, 2);
+                        if (!ok) break;
+                        umma::fence_after_thread_sync();
+                    }
+                    for (int kb = tw.kb0; kb < tw.kb1 && ok; ++kb) {
+                        if (kFp8) {
+                            ok = wait_bar(&sm->tmem_empty[acc], acc_phase ^ 1, sm, g.error, 2);
+                            if (!ok) break;
+                        }
+                        ok = wait_bar(&sm->full[p.stage], p.phase, sm, g.error, 4);
+                        if (!ok) break;
+                        umma::fence_after_thread_sync();
+                        const uint64_t desc_a = umma::make_smem_desc_sw128(s_a + p.stage * kTileBytes);
+                        const uint64_t desc_b = umma::make_smem_desc_sw128(s_b + p.stage * kTileBytesB);
+#pragma unroll
+                        for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                            const uint32_t accumulate = kFp8 ? (k != 0) : (kb != tw.kb0 || k != 0);
+                            umma::mma_ss<kFp8>(tmem_base + acc * kBlockN, umma::advance_desc_k(desc_a, k * 32), umma::advance_desc_k(desc_b, k * 32),
+                                               kIdesc, accumulate);
+                        }
+                        umma::mma_commit(&sm->empty[p.stage]);       // the stage may be refilled once these MMAs are done
+                        p.advance();
+                        if (kFp8) {
+                            umma::mma_commit(&sm->tmem_full[acc]);   // one 128-channel block is ready for promotion
+                            if (++acc == kAccBufs) {
+                                acc = 0;
+                                acc_phase ^= 1;
+                            }
+                        }
+                    }
+                    if (!kFp8 && ok) {
+                        umma::mma_commit(&sm->tmem_full[acc]);
                         if (++acc == kAccBufs) {
                             acc = 0;
                             acc_phase ^= 1;
                         }
                     }
                 }
-                if (!kFp8 && ok) {
-                    umma::mma_commit(&sm->tmem_full[acc]);
-                    if (++acc == kAccBufs) {
-                        acc = 0;
-                        acc_phase ^= 1;
-                    }
-                }
             }
         }
-    }
     } else {
         // ------------------------------------------------------------------ epilogue (32 TMEM lanes per warp)
         if (kWide) reg_alloc<232>();
