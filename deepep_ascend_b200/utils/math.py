@@ -41,7 +41,7 @@ def per_token_cast_to_fp8(x: torch.Tensor, round_scale: bool = False,
     assert x.dim() == 2
     m, n = x.shape
     aligned_n = align(n, FP8_BLOCK)
-    xp = torch.nn.functional.pad(x.float(), (0, aligned_n - n)).view(m, -1, FP8_BLOCK)
+    xp = torch.nn.functional.pad(x.float(), (0, aligned_n - n)).view(m, aligned_n // FP8_BLOCK, FP8_BLOCK)
     amax = xp.abs().amax(dim=2).clamp(1e-4)
     if round_scale or use_ue8m0:
         sf = torch.exp2(torch.ceil(torch.log2(amax / FP8_E4M3_MAX)))

@@ -44,7 +44,7 @@ def _check_dispatch(outs, expect, fp8, do_expand):
 
 
 @pytest.mark.parametrize('R,T,H,E,K', [(2, 128, 256, 8, 2), (4, 200, 1024, 32, 4), (8, 96, 7168, 256, 8), (1, 64, 512, 4, 2),
-                                       (8, 77, 2048, 64, 6)])
+                                       (8, 77, 2048, 64, 6), (8, 16, 128, 8, 2)])
 @pytest.mark.parametrize('mode', ['bf16', 'fp8_in', 'quant'])
 @pytest.mark.parametrize('do_expand', [False, True])
 def test_dispatch_combine(R, T, H, E, K, mode, do_expand):
