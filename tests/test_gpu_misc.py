@@ -63,3 +63,38 @@ def test_barrier_and_bounded_wait_reports_status():
         assert float(torch.ones(4, device='cuda').sum()) == 4.0
     finally:
         world.destroy()
+
+
+def test_poison_fill_no_stray_writes():
+    """All MoE regions of every rank are filled with 0xFF before a dispatch; afterwards only the rows the layout assigns have
+    changed: the tail of the used receive slot and the whole unused slot still hold the poison."""
+    from deepep_ascend_b200.backends.emulated import EmulatedWorld
+    R, T, H, E, K = 4, 64, 512, 16, 4
+    world = EmulatedWorld(R, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=True, num_experts=E)
+    try:
+        ws_bytes = world.buffers[0]._C.get_workspace_bytes()
+        for b in world.buffers:
+            b.core.view(ws_bytes, [b.regions.moe_bytes - ws_bytes], [1], torch.uint8).fill_(0xFF)
+        g = torch.Generator().manual_seed(3)
+        xs = [torch.randn(T, H, generator=g).bfloat16().cuda() for _ in range(R)]
+        idxs = [torch.rand(T, E, generator=g).topk(K, -1).indices.cuda() for _ in range(R)]
+        ws = [torch.rand(T, K, generator=g).cuda() for _ in range(R)]
+        outs = world.dispatch(xs, idxs, ws, E, num_sms=6)
+        torch.cuda.synchronize()
+        for b, (x, idx, w, handle) in zip(world.buffers, outs):
+            b.check_status()
+            q, sf = x
+            rows, cap, reg = handle.num_rows, b.regions.capacity_rows, b.regions
+            assert 0 < rows < cap
+            used, other = reg.slot(handle.recv_slot), reg.slot((handle.recv_slot + 1) % reg.num_recv_slots)
+            x_tail = b.core.view(used.x + rows * H, [cap * reg.x_row_bytes - rows * H], [1], torch.uint8)
+            assert bool((x_tail == 0xFF).all()), 'payload written behind the last received row'
+            side_stride = sf.stride(0) * 4
+            side_tail = b.core.view(used.side + rows * side_stride, [cap * reg.side_bytes - rows * side_stride], [1], torch.uint8)
+            assert bool((side_tail == 0xFF).all()), 'side record written behind the last received row'
+            assert bool((b.core.view(other.x, [cap * reg.x_row_bytes], [1], torch.uint8) == 0xFF).all()), 'the unused slot was touched'
+            # every received row was written: e4m3 never produces the byte pattern 0xFF for finite inputs in all 512 channels
+            assert not bool((q.view(torch.uint8) == 0xFF).all(dim=1).any())
+            assert bool(torch.isfinite(sf).all()) and bool((idx >= -1).all())
+    finally:
+        world.destroy()
