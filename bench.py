@@ -3,7 +3,9 @@
 One step = one ``ElasticBuffer.dispatch`` (bf16 tokens in, FP8 e4m3 + 1x128 scales out, cast fused into the NVLink
 scatter) followed by one ``ElasticBuffer.combine`` (bf16 pull + fp32 reduce) of 8192 tokens per rank, hidden 7168,
 top-8 of 256 experts.  Bandwidth is the reference's "logical bandwidth": received rows x bytes per row, local-rank
-rows included (reference: tests/elastic/test_ep.py:444-451, 523-550, README.md:53).
+rows included (reference: tests/elastic/test_ep.py:444-451, 523-550, README.md:53).  The same JSON line also carries
+the 24-SM numbers, the combine of a plain tensor (staging copy inside the interval), the dispatch with a cached layout,
+and the low-latency decode pair replayed from CUDA graphs (p50 / p99).
 
     python bench.py --gpus 1 --steps 20 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
@@ -40,6 +42,10 @@ def parse_args():
     p.add_argument('--num-sms', type=int, default=int(os.environ.get('EP_BENCH_NUM_SMS', '64')))
     p.add_argument('--combine-sms', type=int, default=0)
     p.add_argument('--no-e2e', action='store_true')
+    p.add_argument('--min-sms', type=int, default=24, help='also measure with this many SMs (0 = skip)')
+    p.add_argument('--no-variants', action='store_true', help='skip the plain-tensor combine and the cached-layout dispatch')
+    p.add_argument('--ll-replays', type=int, default=200, help='CUDA-graph replays of the low-latency pair (0 = skip)')
+    p.add_argument('--ll-tokens', type=int, default=128)
     p.add_argument('--sweep-sms', default='', help='comma separated SM counts: print one extra JSON line per count')
     return p.parse_args()
 
@@ -146,8 +152,12 @@ def main():
 
     T, H, E, K = args.tokens, args.hidden, args.experts, args.topk
     G = (H + 127) // 128
+    M_LL = args.ll_tokens
+    ll_extra = ElasticBuffer.get_low_latency_size_hint(M_LL, H, world, E, K) if args.ll_replays > 0 else 0
     buf = ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=True,
-                        prefer_overlap_with_compute=False, num_gpu_timeout_secs=20, num_cpu_timeout_secs=60)
+                        prefer_overlap_with_compute=False, num_gpu_timeout_secs=20, num_cpu_timeout_secs=60,
+                        extra_bytes=ll_extra + (1 << 20))
+    buf.enable_kernel_timing(True)
 
     # synthetic routed tokens: x ~ N(0,1) bf16, top-8 of N(0,1) logits with softmax weights; pinned host copies
     gen = torch.Generator().manual_seed(1234 + rank)
@@ -157,10 +167,12 @@ def main():
     w_host, idx_host = w_host.contiguous().pin_memory(), idx_host.contiguous().pin_memory()
     x, idx, w = x_host.cuda(), idx_host.cuda(), w_host.cuda()
     h2d_bytes = x_host.numel() * 2 + idx_host.numel() * 8 + w_host.numel() * 4
+    launches = {'n': 0}
 
     def gpu_barrier():
         if world > 1:
             buf.barrier(use_comm_stream=False)
+            launches['n'] += 1
 
     def sync_all():
         torch.cuda.synchronize()
@@ -168,47 +180,70 @@ def main():
             dist.barrier(group=group)
         torch.cuda.synchronize()
 
-    def run(num_sms, combine_sms, steps, warmup):
+    def reduce_max(vals):
+        t = torch.tensor(vals, dtype=torch.float64, device='cuda')
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return t
+
+    def run(num_sms, combine_sms, steps, warmup, plain_combine=False, cached=False):
+        """-> (mean, median) ms of the dispatch kernel and of the combine step, max over ranks per step.
+        Kernel times are CUDA events recorded on the communication stream right around each kernel (the library's
+        kernel timing).  With `plain_combine` the combine input is an ordinary tensor, and the interval (events on the
+        caller's stream) also holds the copy of the rows into the symmetric buffer."""
         handle = None
-        times = []
+        outer = []
+        y_plain = None
+        buf.kernel_times_ms('dispatch'), buf.kernel_times_ms('combine')
         for i in range(warmup + steps):
-            timed = i >= warmup
             if i == warmup:
                 sync_all()
                 sampler.mark()
+                launches['n'] = 0
+                buf.kernel_times_ms('dispatch'), buf.kernel_times_ms('combine')
             flush_l2_cache()
             gpu_barrier()
-            # keep the GPU busy for ~1 ms so that the host has enqueued the timed kernel before the start event
-            # fires: the interval then holds device time only, not launch latency
+            # keep the GPU busy for ~1 ms so that the host has enqueued the timed kernel before it can start: the
+            # interval then holds device time only, not launch latency
             torch.cuda._sleep(SLEEP_CYCLES)
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-            ev[0].record()
             # no host sync inside the timed kernels: outputs get their worst-case size and the host runs ahead
-            recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x, idx, w, num_experts=E, num_sms=num_sms, do_cpu_sync=False)
-            ev[1].record()
-            y = buf.get_combine_buffer(handle)
-            if i == 0:
-                y.normal_()
+            if cached and handle is not None:
+                recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x, handle=handle, topk_weights=w, num_sms=num_sms)
+            else:
+                recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x, idx, w, num_experts=E, num_sms=num_sms, do_cpu_sync=False,
+                                                                   do_handle_copy=False)
+            launches['n'] += 1
+            if plain_combine:
+                if y_plain is None:
+                    y_plain = torch.randn(handle.num_rows, H, device='cuda', dtype=torch.bfloat16)
+                y = y_plain
+            else:
+                y = buf.get_combine_buffer(handle)
+                if i < 2:
+                    y.normal_()              # both input regions get defined contents
             flush_l2_cache()
             gpu_barrier()
             torch.cuda._sleep(SLEEP_CYCLES)
-            ev[2].record()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
             out, _, _ = buf.combine(y, handle, num_sms=combine_sms or num_sms)
-            ev[3].record()
-            if timed:
-                times.append(ev)
+            e1.record()
+            launches['n'] += 2 if plain_combine else 1
+            if i >= warmup:
+                outer.append((e0, e1))
         sync_all()
         buf.check_status()
-        t = torch.tensor([[e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3])] for e in times], dtype=torch.float64, device='cuda')
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
-        return t.mean(dim=0).tolist(), t.median(dim=0).values.tolist(), handle
+        td = buf.kernel_times_ms('dispatch')
+        tc = [a.elapsed_time(b) for a, b in outer] if plain_combine else buf.kernel_times_ms('combine')
+        t = reduce_max([td[-steps:], tc[-steps:]])
+        return t.mean(dim=1).tolist(), t.median(dim=1).values.tolist(), handle
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     wall0 = time.perf_counter()
     (t_disp, t_comb), (t_disp_med, t_comb_med), handle = run(args.num_sms, args.combine_sms, args.steps, args.warmup)
+    timed_launches = launches['n']
     wall = time.perf_counter() - wall0
     clocks = sampler.stop() if rank == 0 else None
 
@@ -218,20 +253,41 @@ def main():
         dist.all_reduce(rows, op=dist.ReduceOp.SUM, group=group)
         dist.all_reduce(rows_min, op=dist.ReduceOp.MIN, group=group)
     rows_total, rows_min = float(rows.item()), float(rows_min.item())
+    # bytes that move per received row (the reference's "logical bandwidth" formulas, tests/elastic/test_ep.py:444-451,
+    # 523-550): dispatch = e4m3 row + 1x128 scales + expert ids + weights; combine = bf16 row (no weights are carried
+    # back in the timed call, so none are counted)
     disp_row_bytes = H + G * 4 + K * 8 + K * 4
-    comb_row_bytes = H * 2 + K * 4
-    disp_gbs = rows_total / world * disp_row_bytes / (t_disp * 1e-3) / 1e9
-    comb_gbs = rows_total / world * comb_row_bytes / (t_comb * 1e-3) / 1e9
+    comb_row_bytes = H * 2
+
+    def gbs(ms, row_bytes):
+        return rows_total / world * row_bytes / (ms * 1e-3) / 1e9
+    disp_gbs, comb_gbs = gbs(t_disp, disp_row_bytes), gbs(t_comb, comb_row_bytes)
     ms_per_step = t_disp + t_comb
     value = rows_total * (disp_row_bytes + comb_row_bytes) / (ms_per_step * 1e-3) / 1e9
     ref_per_gpu = (disp_row_bytes + comb_row_bytes) / (disp_row_bytes / REF_DISPATCH_GBS + comb_row_bytes / REF_COMBINE_GBS)
 
+    extra = {}
+    short = max(5, args.steps // 2)
+    if args.min_sms > 0:
+        # the same kernels with the reference's "min #SM" setting (24 SMs; published 643 / 675 GB/s at EP8)
+        (td, tc), _, _ = run(args.min_sms, args.min_sms, short, 3)
+        extra.update({f'dispatch_gbs_{args.min_sms}sms': gbs(td, disp_row_bytes), f'combine_gbs_{args.min_sms}sms': gbs(tc, comb_row_bytes),
+                      f'dispatch_ms_{args.min_sms}sms': td, f'combine_ms_{args.min_sms}sms': tc})
+    if not args.no_variants:
+        (_, tc), _, _ = run(args.num_sms, args.combine_sms, short, 3, plain_combine=True)
+        extra.update({'combine_gbs_plain_tensor': gbs(tc, comb_row_bytes), 'combine_ms_plain_tensor': tc})
+        (td, _), _, _ = run(args.num_sms, args.combine_sms, short, 3, cached=True)
+        extra.update({'dispatch_gbs_cached_layout': gbs(td, disp_row_bytes), 'dispatch_ms_cached_layout': td})
+
     sweep = {}
-    for s in [int(v) for v in args.sweep_sms.split(',') if v]:
-        (td, tc), _, _ = run(s, s, max(3, args.steps // 2), 3)
-        sweep[str(s)] = {'dispatch_ms': td, 'combine_ms': tc,
-                         'dispatch_gbs_per_gpu': rows_total / world * disp_row_bytes / (td * 1e-3) / 1e9,
-                         'combine_gbs_per_gpu': rows_total / world * comb_row_bytes / (tc * 1e-3) / 1e9}
+    for sms in [int(v) for v in args.sweep_sms.split(',') if v]:
+        (td, tc), _, _ = run(sms, sms, short, 3)
+        sweep[str(sms)] = {'dispatch_ms': td, 'combine_ms': tc, 'dispatch_gbs_per_gpu': gbs(td, disp_row_bytes),
+                           'combine_gbs_per_gpu': gbs(tc, comb_row_bytes)}
+
+    ll = None
+    if args.ll_replays > 0:
+        ll = low_latency_in_a_graph(buf, group, world, rank, M_LL, H, E, K, args.ll_replays, reduce_max)
 
     e2e = None
     if not args.no_e2e:
@@ -269,29 +325,35 @@ def main():
             out, _, _ = buf.combine(buf.get_combine_buffer(hd), hd, num_sms=args.combine_sms or args.num_sms)
             checksum = float(out.sum(dtype=torch.float32).item())
         torch.cuda.synchronize()
-        dt = torch.tensor([(time.perf_counter() - t0) / steps], dtype=torch.float64, device='cuda')
-        if world > 1:
-            dist.all_reduce(dt, op=dist.ReduceOp.MAX, group=group)
+        dt = reduce_max([(time.perf_counter() - t0) / steps])
         e2e = {'value': rows_total * (disp_row_bytes + comb_row_bytes) / float(dt.item()) / 1e9, 'unit': 'GB/s',
                'ms_per_step': float(dt.item()) * 1e3, 'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': 4,
                'checksum_finite': checksum == checksum}
 
     if rank == 0:
+        at_ref_size = world == 8
         line = {
             'metric': 'ep_dispatch_combine_logical_bandwidth', 'value': value, 'unit': 'GB/s', 'n_gpus': world,
             'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True,
-            'scaling': 'weak', 'vs_baseline': value / world / ref_per_gpu, 'dtype': 'fp8_e4m3 dispatch (fused cast from bf16) + bf16 combine',
+            'scaling': 'weak', 'vs_baseline': value / world / ref_per_gpu if at_ref_size else None,
+            'vs_baseline_note': 'the published numbers are for EP8 over NVLink; with fewer ranks most rows stay local, so no ratio is given',
+            'dtype': 'fp8_e4m3 dispatch (fused cast from bf16) + bf16 combine',
             'data': 'synthetic', 'impl': 'ours',
             'config': {'model': 'DeepSeek-V3 MoE routing shape', 'global_batch': T * world, 'seq_len': 1,
                        'tokens_per_rank': T, 'hidden': H, 'num_experts': E, 'num_topk': K, 'parallelism': f'ep{world}',
                        'num_sms_dispatch': args.num_sms, 'num_sms_combine': args.combine_sms or args.num_sms,
-                       'l2': 'flushed (256 MB write) before every timed kernel', 'timing': 'CUDA events per kernel behind a ~1 ms GPU spin (hides launch latency), max over ranks, mean over steps',
+                       'l2': 'flushed (256 MB write) before every timed kernel',
+                       'timing': 'CUDA events on the launching (communication) stream right around each kernel, behind a cross-GPU barrier and a ~1 ms GPU spin (hides launch latency and rank skew), max over ranks per step, mean over steps',
+                       'bytes': f'dispatch {disp_row_bytes} B per received row (e4m3 row + scales + ids + weights), combine {comb_row_bytes} B (bf16 row)',
                        'baseline': f'{ref_per_gpu:.1f} GB/s per GPU = published 726 (dispatch) / 740 (combine) GB/s at EP8, 64 SMs'},
             'dispatch_ms': t_disp, 'combine_ms': t_comb, 'dispatch_ms_median': t_disp_med, 'combine_ms_median': t_comb_med, 'dispatch_gbs_per_gpu': disp_gbs, 'combine_gbs_per_gpu': comb_gbs,
-            'dispatch_vs_ref': disp_gbs / REF_DISPATCH_GBS, 'combine_vs_ref': comb_gbs / REF_COMBINE_GBS,
+            'dispatch_vs_ref': disp_gbs / REF_DISPATCH_GBS if at_ref_size else None, 'combine_vs_ref': comb_gbs / REF_COMBINE_GBS if at_ref_size else None,
             'recv_rows_total': rows_total, 'recv_rows_min_rank': rows_min, 'wall_s_timed_run': wall,
-            'clocks': clocks, 'e2e': e2e, 'gpu_launches': args.steps * (2 + (2 if world > 1 else 0)),
+            'clocks': clocks, 'e2e': e2e, 'gpu_launches': timed_launches,
         }
+        line.update(extra)
+        if ll is not None:
+            line.update(ll)
         if sweep:
             line['sm_sweep'] = sweep
         print(json.dumps(line), flush=True)
@@ -299,6 +361,64 @@ def main():
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def low_latency_in_a_graph(buf, group, world, rank, M, H, E, K, replays, reduce_max):
+    """Low-latency decode (128 tokens per rank, FP8 dispatch, BF16 combine): one CUDA graph holds a dispatch, another a
+    combine; each replay is timed by events behind a cross-GPU barrier and a short GPU spin; p50 / p99 over the replays
+    of the per-replay maximum over ranks."""
+    import numpy as np
+    import torch
+    gen = torch.Generator().manual_seed(99 + rank)
+    x = torch.randn(M, H, generator=gen).bfloat16().cuda()
+    idx = torch.rand(M, E, generator=gen).topk(K, dim=-1).indices.cuda()     # uniform random logits
+    w = torch.softmax(torch.randn(M, K, generator=gen), dim=-1).cuda()
+    El = E // world
+    y = torch.randn(El, world * M, H, device='cuda', dtype=torch.bfloat16)
+    sms = torch.cuda.get_device_properties('cuda').multi_processor_count
+
+    def d():
+        return buf.low_latency_dispatch(x, idx, M, E, use_fp8=True, num_sms=sms)
+    for _ in range(3):
+        recv, cnt, handle, _, _ = d()
+        buf.low_latency_combine(y, idx, w, handle, num_sms=sms)
+    torch.cuda.synchronize()
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier(group=group)
+    gd, gc = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(gd, stream=side):
+            recv, cnt, handle, _, _ = d()
+        with torch.cuda.graph(gc, stream=side):
+            out, _, _ = buf.low_latency_combine(y, idx, w, handle, num_sms=sms)
+    torch.cuda.synchronize()
+    td, tc = [], []
+    warm = 10
+    for i in range(warm + replays):
+        if world > 1:
+            buf.barrier(use_comm_stream=False)
+        torch.cuda._sleep(400_000)
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        gd.replay()
+        e[1].record()
+        gc.replay()
+        e[2].record()
+        if i >= warm:
+            td.append((e[0], e[1]))
+            tc.append((e[1], e[2]))
+    torch.cuda.synchronize()
+    buf.check_status()
+    td = reduce_max([a.elapsed_time(b) * 1e3 for a, b in td]).cpu().numpy()
+    tc = reduce_max([a.elapsed_time(b) * 1e3 for a, b in tc]).cpu().numpy()
+    finite = bool(torch.isfinite(out.float()).all())
+    return {'ll_tokens_per_rank': M, 'll_replays': replays, 'll_num_sms': sms,
+            'll_dispatch_p50_us': float(np.percentile(td, 50)), 'll_dispatch_p99_us': float(np.percentile(td, 99)),
+            'll_combine_p50_us': float(np.percentile(tc, 50)), 'll_combine_p99_us': float(np.percentile(tc, 99)),
+            'll_output_finite': finite,
+            'll_reference': 'no SM100 number is published; the reference quotes 77 / 114 us on H800 + CX7 RDMA'}
 
 
 if __name__ == '__main__':

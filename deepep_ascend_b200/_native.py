@@ -8,7 +8,6 @@ shapes are runtime arguments (the reference compiles each shape with nvcc at run
 import glob
 import importlib.util
 import os
-import sys
 import threading
 from typing import Optional
 
@@ -31,15 +30,7 @@ def sources():
 
 
 def extra_include_paths():
-    """CUTLASS / CuTe headers vendored in site-packages (used by the tcgen05 GEMM kernels for descriptor
-    layouts only)."""
-    paths = [_CSRC]
-    for p in sys.path:
-        cand = os.path.join(p, 'flashinfer', 'data', 'cutlass', 'include')
-        if os.path.isdir(cand):
-            paths.append(cand)
-            break
-    return paths
+    return [_CSRC]
 
 
 def shared_object() -> Optional[str]:
@@ -115,8 +106,8 @@ def load(required: bool = True):
             raise
         return None
     if required:
-        raise ImportError('deepep_ascend_b200: native extension is not built and nvcc is not available; '
-                          'run `python -c "import __graft_entry__ as g; g.build()"` on a machine with CUDA 12.9')
+        raise ImportError('deepep_ascend_b200: the native extension is not built and nvcc is not available; build it on a '
+                          'machine with CUDA 12.9 (`python setup.py build_ext --inplace`, or `deepep_ascend_b200._native.build()`)')
     return None
 
 

@@ -34,9 +34,35 @@ def _a2a(group, chunks: List[torch.Tensor]) -> List[torch.Tensor]:
     return list(recv.split(recv_counts.tolist(), dim=0))
 
 
+class CollectiveMismatch(RuntimeError):
+    """The ranks of a group did not make the same call (different arguments, or a rank that never joined)."""
+
+
 class CpuBackend:
     def __init__(self, group, rank: int, num_ranks: int):
         self.group, self.rank, self.R = group, rank, num_ranks
+        self._calls = 0
+
+    def _preflight(self, what: str, signature: tuple) -> None:
+        """Every rank publishes (call number, operation, arguments that must agree) before any payload moves; a rank
+        that disagrees, or that does not show up before the process group's time limit, turns into an error that names
+        the ranks on EVERY rank, instead of a hang or of silently mixed-up rows.  Parity: the collective preflight of
+        the reference's Python layer (deep_ep/buffers/elastic.py:555-862)."""
+        self._calls += 1
+        mine = (self._calls, what) + tuple(signature)
+        if self.R == 1:
+            return
+        everyone = [None] * self.R
+        try:
+            dist.all_gather_object(everyone, mine, group=self.group)
+        except Exception as e:
+            raise CollectiveMismatch(f'[EP rank {self.rank}] {what} number {self._calls}: not every rank joined the call '
+                                     f'before the process group gave up ({type(e).__name__}: {str(e)[:200]})') from e
+        odd = [r for r, sig in enumerate(everyone) if sig != everyone[0]]
+        if odd:
+            detail = ', '.join(f'rank {r}: {everyone[r]}' for r in ([0] + odd))
+            raise CollectiveMismatch(f'[EP rank {self.rank}] {what} number {self._calls}: ranks {odd} disagree with rank 0 '
+                                     f'about the call ({detail})')
 
     def _gather_counts(self, local: layout_ref.LocalLayout):
         mine = torch.cat([local.rank_count, local.expert_count]).to(torch.int64)
@@ -57,6 +83,8 @@ class CpuBackend:
             x_in, sf_in = per_token_cast_to_fp8(x_in)
         T, H = x_in.shape
         El = num_experts // R
+        self._preflight('dispatch', (num_experts, num_max_tokens, alignment, bool(do_expand), handle is not None, H,
+                                     str(x_in.dtype), (handle.topk_idx if handle is not None else topk_idx).shape[1]))
         if handle is not None:
             topk_idx = handle.topk_idx
         K = topk_idx.shape[1]
@@ -103,7 +131,7 @@ class CpuBackend:
             handle = EPHandle(do_expand, num_experts, alignment, num_max_tokens, 0,
                               topk_idx.clone() if do_handle_copy else topk_idx, gl.num_recv_tokens, gl.num_expanded_tokens,
                               per_expert_list, gl.psum_recv_per_rank, gl.psum_recv_per_expert, gl.recv_per_expert, meta,
-                              gl.lane_src, gl.plan, H, 0, topk_weights)
+                              gl.lane_src, gl.plan, H, 0, topk_weights, stamp=buf._stamp(T, K))
         else:
             handle.recv_src_metadata = meta
         x_out = (recv_x, recv_sf) if sf_in is not None else recv_x
@@ -113,6 +141,8 @@ class CpuBackend:
         R, me = self.R, self.rank
         T, K = handle.plan.shape
         H = x.shape[1]
+        self._preflight('combine', (handle.num_experts, handle.num_max_tokens_per_rank, bool(handle.do_expand), H, str(x.dtype),
+                                    K, topk_weights is not None, bool(weighted)))
         meta = handle.recv_src_metadata.to(torch.int64)
         rows = handle.num_rows
         # expert rank side: send every row (and its carried weights) back to the rank it came from, in row order
@@ -131,12 +161,12 @@ class CpuBackend:
         got_w = _a2a(self.group, send_w) if topk_weights is not None else None
 
         def rows_of(rank: int):
-            table = torch.zeros((int(got_row[rank].max().item()) + 1 if got_row[rank].numel() else 1, H), dtype=torch.bfloat16)
+            table = torch.zeros((int(got_row[rank].max().item()) + 1 if got_row[rank].numel() else 1, H), dtype=x.dtype)
             if got_row[rank].numel():
                 table[got_row[rank].squeeze(1)] = got_x[rank]
             return table
         mul = handle.topk_weights if weighted else None
-        out = layout_ref.combine_ref(rows_of, handle.plan, H, bias0, bias1, mul)
+        out = layout_ref.combine_ref(rows_of, handle.plan, H, bias0, bias1, mul, out_dtype=x.dtype)
         out_w = None
         if topk_weights is not None:
             out_w = torch.zeros((T, K), dtype=torch.float32)

@@ -39,12 +39,15 @@ class EmulatedWorld:
         states = []
         for r, b in enumerate(self.buffers):
             h = handles[r] if handles is not None else None
+            if h is not None:
+                b._attest(h, 'cached dispatch')
             states.append(b._prepare_dispatch(
                 xs[r], None if h is not None else topk_idxs[r], topk_weights[r], stats[r] if stats is not None else None,
-                num_experts, b.num_max_tokens_per_rank, expert_alignment, num_sms, h, True,
-                do_cpu_sync and h is None, do_expand if h is None else h.do_expand, use_tma_aligned_col_major_sf))
+                num_experts, b.num_max_tokens_per_rank, expert_alignment if h is None else h.expert_alignment, num_sms, h, True,
+                do_cpu_sync and h is None, do_expand if h is None else h.do_expand, use_tma_aligned_col_major_sf,
+                None, do_zero_padding))
         self._C.ElasticBuffer.dispatch_group(self.cores, [s.call for s in states], num_sms)
-        return [b._finish_dispatch(s, do_zero_padding) for b, s in zip(self.buffers, states)]
+        return [b._finish_dispatch(s) for b, s in zip(self.buffers, states)]
 
     def combine(self, xs: Sequence[torch.Tensor], handles: Sequence, topk_weights: Optional[Sequence] = None,
                 bias0: Optional[Sequence] = None, bias1: Optional[Sequence] = None, weighted: bool = False, num_sms: int = 0):
@@ -52,9 +55,12 @@ class EmulatedWorld:
         num_sms = min(num_sms or 8, self.max_sms_per_rank())
         calls, outs = [], []
         for r, b in enumerate(self.buffers):
-            call, out, out_w = b._prepare_combine(
+            b._attest(handles[r], 'combine')
+            call, out, out_w, staged = b._prepare_combine(
                 xs[r], handles[r], topk_weights[r] if topk_weights is not None else None,
                 bias0[r] if bias0 is not None else None, bias1[r] if bias1 is not None else None, weighted)
+            for dst, src in staged:
+                dst.copy_(src)
             calls.append(call)
             outs.append((out, out_w))
         self._C.ElasticBuffer.combine_group(self.cores, calls, num_sms)
@@ -137,23 +143,25 @@ class EmulatedWorld:
             outs.append(out)
         return outs
 
-    def engram_write(self, storages: Sequence[torch.Tensor]) -> None:
-        from ..utils.math import align
+    def engram_write(self, storages: Sequence[torch.Tensor], sfs: Optional[Sequence[torch.Tensor]] = None) -> None:
         self._C.ElasticBuffer.barrier_group(self.cores, self._C.CH_ENGRAM)
-        for b, st in zip(self.buffers, storages):
+        for r, (b, st) in enumerate(zip(self.buffers, storages)):
             st = st.contiguous()
-            N, H = st.shape
-            entry = H * st.element_size()
-            if b._engram is None:
-                b._engram = {'offset': b.reserve(align(N * entry, 1024)), 'N': N, 'H': H, 'dtype': st.dtype, 'entry': entry}
-            b.core.view(b._engram['offset'], [N, H], [H, 1], st.dtype).copy_(st)
+            e = b._engram_place(st.shape[0], st.shape[1], st.dtype)
+            e['sf'] = sfs[r] if sfs is not None else None
+            b._engram_store(e, st)
         self._C.ElasticBuffer.barrier_group(self.cores, self._C.CH_ENGRAM)
 
-    def engram_fetch(self, indices: Sequence[torch.Tensor], num_sms: int = 4):
+    def engram_fetch(self, indices: Sequence[torch.Tensor], num_sms: int = 4, use_tma_aligned_col_major_sf: bool = False):
+        """-> per-rank list of ``(fetched, fetched_sf | None)``."""
         e = self.buffers[0]._engram
         idx = [i.contiguous().to(torch.int32) for i in indices]
-        outs = [torch.empty((i.shape[0], i.shape[1] * e['H']), dtype=e['dtype'], device=i.device) for i in idx]
-        self._C.ElasticBuffer.engram_fetch_group(self.cores, [i.view(-1) for i in idx], outs, e['N'], e['entry'], e['offset'], num_sms)
+        outs = [b._engram_fetch_outputs(i, use_tma_aligned_col_major_sf) for b, i in zip(self.buffers, idx)]
+        has_sf = e['sf'] is not None
+        self._C.ElasticBuffer.engram_fetch_group(
+            self.cores, [i.view(-1) for i in idx], [o for o, _ in outs], e['N'], e['entry'], e['offset'], e['cpu'],
+            [b._engram['sf'] for b in self.buffers] if has_sf else [], [f for _, f in outs] if has_sf else [],
+            idx[0].shape[1], num_sms)
         return outs
 
     def barrier(self) -> None:

@@ -165,41 +165,80 @@ class CollectivesMixin:
         torch.cuda.current_stream().wait_stream(s)
 
     # ------------------------------------------------------------------------------------------ Engram
+    def _engram_place(self, N: int, H: int, dtype: torch.dtype) -> dict:
+        """Where this buffer keeps its Engram table: the CPU segment (``num_cpu_bytes`` at construction) when there is
+        one and the table fits it, else a region of the symmetric device buffer.  Every rank decides alike."""
+        entry = H * dtype.itemsize
+        assert entry % 16 == 0, 'an entry must be a multiple of 16 bytes'
+        if self._engram is None:
+            in_cpu = 0 < N * entry <= self.num_cpu_bytes
+            off = 0 if in_cpu else self.reserve(align(N * entry, 1024))
+            self._engram = {'offset': off, 'N': N, 'H': H, 'dtype': dtype, 'entry': entry, 'cpu': in_cpu, 'sf': None}
+        e = self._engram
+        assert (N, H, dtype) == (e['N'], e['H'], e['dtype']), 'the Engram table shape is fixed per buffer'
+        return e
+
+    def _engram_store(self, e: dict, storage: torch.Tensor) -> None:
+        if e['cpu']:
+            self.core.cpu_segment_write(e['offset'], storage)
+        else:
+            self.core.view(e['offset'], [e['N'], e['H']], [e['H'], 1], e['dtype']).copy_(storage)
+
     def engram_write(self, storage: torch.Tensor, sf: Optional[torch.Tensor] = None) -> None:
-        """Publish this rank's table ``storage [N, H]`` (bf16 or fp8); scale factors stay local."""
+        """Publish this rank's table ``storage [N, H]`` (bf16, or e4m3 with ``sf``).  ``sf [num_ranks * N, packs]`` is
+        the scale table of ALL ranks' entries (4-byte packs: fp32, or four UE8M0 bytes), replicated on every rank; it
+        stays local and is gathered with every fetch (csrc/elastic/buffer.hpp:212-242 of the reference).  The table
+        goes to the CPU segment when the buffer has one that is large enough, else into the device buffer."""
         storage = storage.contiguous()
         N, H = storage.shape
-        entry = H * storage.element_size()
-        assert entry % 16 == 0
-        if self._engram is None:
-            self._engram = {'offset': self.reserve(align(N * entry, 1024)), 'N': N, 'H': H, 'dtype': storage.dtype, 'entry': entry}
-        e = self._engram
-        assert (N, H, storage.dtype) == (e['N'], e['H'], e['dtype']), 'the Engram table shape is fixed per buffer'
+        e = self._engram_place(N, H, storage.dtype)
+        if sf is not None:
+            assert sf.dim() == 2 and sf.is_contiguous() and sf.element_size() == 4 and sf.shape[0] == N * self.num_ranks, \
+                '`sf` must be a contiguous [num_ranks * N, packs] table of 4-byte packs'
         e['sf'] = sf
         self.comm_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.comm_stream):
             self.core.barrier(self._C.CH_ENGRAM)       # nobody is still fetching the old table
-            self.core.view(e['offset'], [N, H], [H, 1], storage.dtype).copy_(storage)
+            self._engram_store(e, storage)
             self.core.barrier(self._C.CH_ENGRAM)       # every table is in place
         torch.cuda.current_stream().wait_stream(self.comm_stream)
 
+    def _engram_fetch_outputs(self, idx: torch.Tensor, col_major_sf: bool):
+        e = self._engram
+        T, n = idx.shape
+        out = torch.empty((T, n * e['H']), dtype=e['dtype'], device=idx.device)
+        fetched_sf = None
+        if e['sf'] is not None:
+            packs = e['sf'].shape[1]
+            if col_major_sf:     # strides (1, align(T, 4)): the layout a TMA-fed GEMM wants for its scale operand
+                fetched_sf = torch.empty_strided((T, n * packs), (1, align(T, 4)), dtype=e['sf'].dtype, device=idx.device)
+            else:
+                fetched_sf = torch.empty((T, n * packs), dtype=e['sf'].dtype, device=idx.device)
+        return out, fetched_sf
+
     def engram_fetch(self, indices: torch.Tensor, num_qps: int = 0, use_tma_aligned_col_major_sf: bool = False, num_sms: int = 16):
         """``indices int32 [T, n]`` of global entry ids (owner = id // N) -> hook; ``hook()`` waits and returns
-        ``(fetched [T, n * H], fetched_sf | None)``."""
+        ``(fetched [T, n * H], fetched_sf [T, n * packs] | None)``; the scales are column-major with
+        ``use_tma_aligned_col_major_sf`` (csrc/elastic/buffer.hpp:244-327).  ``num_qps`` must be 0."""
+        if num_qps != 0:
+            raise ValueError('num_qps must be 0: there are no RDMA queue pairs inside one NVLink domain')
         e = self._engram
         assert e is not None, 'call engram_write first'
         idx = indices.contiguous().to(torch.int32)
-        T, n = idx.shape
-        out = torch.empty((T, n * e['H']), dtype=e['dtype'], device=idx.device)
+        n = idx.shape[1]
         self.comm_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.comm_stream):
-            self._C.ElasticBuffer.engram_fetch_group([self.core], [idx.view(-1)], [out], e['N'], e['entry'], e['offset'], num_sms)
+            out, fetched_sf = self._engram_fetch_outputs(idx, use_tma_aligned_col_major_sf)
+            tabs = [] if fetched_sf is None else [e['sf']]
+            fsfs = [] if fetched_sf is None else [fetched_sf]
+            self._C.ElasticBuffer.engram_fetch_group([self.core], [idx.view(-1)], [out], e['N'], e['entry'], e['offset'],
+                                                     e['cpu'], tabs, fsfs, n, num_sms)
         event = torch.cuda.Event()
         event.record(self.comm_stream)
 
         def hook():
             torch.cuda.current_stream().wait_event(event)
-            return out, None
+            return out, fetched_sf
         return hook
 
 

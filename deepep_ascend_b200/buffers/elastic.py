@@ -14,6 +14,7 @@ How it differs from the reference by design:
 
 The same class runs on CPU tensors with a gloo group (``backends/cpu.py``) with identical handle semantics.
 """
+import itertools
 import math
 import os
 from typing import List, Optional, Sequence, Tuple, Union
@@ -32,6 +33,12 @@ from ..utils.semantic import value_or
 topk_idx_t = torch.int64 if int(os.environ.get('EP_NUM_TOPK_IDX_BITS', '64')) == 64 else torch.int32
 
 _comm_streams = {}
+_buffer_uids = itertools.count(1)
+
+
+class HandleError(RuntimeError):
+    """A handle was given to a buffer it does not belong to (another buffer, a destroyed or re-created one, or a
+    call whose shape differs from the dispatch that made it)."""
 
 
 def _get_comm_stream() -> 'torch.cuda.Stream':
@@ -62,7 +69,8 @@ class EPHandle:
                  num_recv_tokens_per_expert_list: Optional[list], psum_num_recv_tokens_per_scaleup_rank: torch.Tensor,
                  psum_num_recv_tokens_per_expert: torch.Tensor, num_unaligned_recv_tokens_per_expert: torch.Tensor,
                  recv_src_metadata: torch.Tensor, dst_buffer_slot_idx: torch.Tensor, plan: torch.Tensor,
-                 hidden: int, recv_slot: int, topk_weights: Optional[torch.Tensor] = None):
+                 hidden: int, recv_slot: int, topk_weights: Optional[torch.Tensor] = None,
+                 stamp: Optional[tuple] = None):
         self.do_expand = do_expand
         self.num_experts = num_experts
         self.expert_alignment = expert_alignment
@@ -81,6 +89,9 @@ class EPHandle:
         self.hidden = hidden
         self.recv_slot = recv_slot
         self.topk_weights = topk_weights
+        # (buffer uid, buffer generation, num_ranks, num_tokens, num_topk): checked by every call that takes a handle
+        # (the role of the reference's handle attestation, csrc/backends/ascend/elastic/dispatch_state.hpp:221-480)
+        self.stamp = stamp
         self.token_metadata_at_forward = None      # multi-node only
         self.channel_linked_list = None            # multi-node only
 
@@ -111,7 +122,11 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
     Arguments follow deep_ep (deep_ep/buffers/elastic.py:331-349).  ``num_bytes`` overrides the size derived
     from the MoE shape; ``enable_expand`` / ``num_experts`` / ``expert_alignment`` size the receive regions for
     the expand layout; ``extra_bytes`` reserves room behind the MoE regions for all-gather sessions, pipeline
-    FIFOs, Engram storage and the low-latency buffers.
+    FIFOs, Engram storage and the low-latency buffers.  ``num_cpu_bytes`` reserves pinned host memory, mapped into
+    this GPU's address space, behind the device buffer: Engram storage that does not fit the GPU region goes there
+    (deep_ep/buffers/elastic.py:511-516, csrc/kernels/backend/symmetric.hpp:145-186).  One NVLink domain has no NIC
+    path, so the RDMA-only arguments must keep their defaults: ``num_allocated_qps=0`` and ``sl_idx=3`` (anything else
+    raises ``ValueError`` instead of being silently dropped).
     """
 
     def __init__(self, group: Optional[dist.ProcessGroup], num_bytes: Optional[int] = None, num_cpu_bytes: int = 0,
@@ -122,12 +137,19 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
                  enable_expand: bool = False, num_experts: int = 0, expert_alignment: int = 1, num_recv_slots: int = 2,
                  extra_bytes: int = 0, zero_copy: bool = True, low_latency_shrink: bool = False,
                  _virtual: Optional[Tuple[int, int]] = None):
+        if num_allocated_qps != 0 or sl_idx != 3:
+            raise ValueError('num_allocated_qps / sl_idx configure RDMA queue pairs; a single NVLink domain has none '
+                             '(leave them at their defaults)')
+        if num_cpu_bytes < 0:
+            raise ValueError('num_cpu_bytes must not be negative')
         self.group = group
         self._virtual = _virtual
         self.low_latency_shrink = low_latency_shrink
         self._ll = None
         self._agrs = self._pp = self._engram = None
         self.profile = None
+        self._kernel_timing = None
+        self._tune = (0, 0)
         if _virtual is not None:
             self.rank_idx, self.num_ranks = _virtual
         else:
@@ -144,11 +166,14 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         self.explicitly_destroy = explicitly_destroy
         self.zero_copy = zero_copy
         self.enable_expand = enable_expand
+        self.num_cpu_bytes = num_cpu_bytes
         self.num_scaleout_ranks, self.num_scaleup_ranks = 1, self.num_ranks
         self.num_rdma_ranks, self.num_nvlink_ranks = 1, self.num_ranks
         self._destroyed = False
         self._recv_slot_counter = 0
+        self._combine_slot_counter = 0
         self._sm_cache = {}
+        self._uid = next(_buffer_uids)
 
         backend = dist.get_backend(group) if (group is not None and _virtual is None) else None
         self.is_cpu = (backend == 'gloo') or not torch.cuda.is_available()
@@ -182,16 +207,20 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         if os.environ.get('EP_BUFFER_DEBUG'):
             print(f'[EP rank {self.rank_idx}] symmetric buffer {total / 2**20:.1f} MiB '
                   f'(MoE regions {moe_bytes / 2**20:.1f} MiB, capacity {self.regions.capacity_rows} rows, '
-                  f'{num_recv_slots} receive slots)', flush=True)
+                  f'{num_recv_slots} receive slots, {num_cpu_bytes / 2**20:.1f} MiB mapped host memory)', flush=True)
         self.core = self._C.ElasticBuffer(self.rank_idx, self.num_ranks, total, float(num_gpu_timeout_secs),
-                                          float(num_cpu_timeout_secs))
+                                          float(num_cpu_timeout_secs), int(num_cpu_bytes))
         if _virtual is None:
             if self.num_ranks > 1:
                 handles = all_gather_object(group, bytes(self.core.get_local_ipc_handle()))
                 self.core.open_peers(handles)
+                if num_cpu_bytes > 0:
+                    self.core.open_cpu_peers(all_gather_object(group, self.core.get_local_cpu_segment_name()))
             torch.cuda.synchronize()
             if group is not None and self.num_ranks > 1:
                 dist.barrier(group=group)
+            if num_cpu_bytes > 0:
+                self.core.unlink_cpu_segment_name()      # every rank has mapped it; the mappings keep it alive
         self.comm_stream = _get_comm_stream()
 
     # ------------------------------------------------------------------------------------------ extra region
@@ -297,8 +326,15 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         return self._sm_cache[key]
 
     def get_theoretical_num_qps(self, num_sms: int) -> int:
-        """No RDMA queue pairs exist inside one NVLink domain; kept for API parity."""
+        """No RDMA queue pairs exist inside one NVLink domain: always 0 (pass that as ``num_qps``)."""
         return 0
+
+    def set_dispatch_tuning(self, num_warps: int = 0, num_stages: int = 0) -> None:
+        """Shape of the dispatch kernel: warps per CTA (1..12, each with its own staging ring) and, for the fused
+        FP8 cast, staging buffers per warp (2..4; more buffers keep more tokens' stores in flight per warp but
+        leave room for fewer warps).  0 selects the default (12 warps, 2 buffers)."""
+        assert 0 <= num_warps <= 12 and num_stages in (0, 2, 3, 4)
+        self._tune = (num_warps, num_stages)
 
     # ------------------------------------------------------------------------------------------ barrier
     def barrier(self, use_comm_stream: bool = True, with_cpu_sync: bool = False, sequential: bool = True) -> None:
@@ -317,6 +353,52 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
             stream.synchronize()
             self.core.check_status()
 
+    # ------------------------------------------------------------------------------------------ layout
+    def get_dispatch_layout(self, topk_idx: torch.Tensor, num_experts: int, previous_event: Optional[EventHandle] = None,
+                            async_finish: bool = False, allocate_on_comm_stream: bool = False):
+        """Routing summary of ``topk_idx [T, K]`` (``-1`` = no selection), computed by one sm_100a kernel.
+
+        Returns ``(num_tokens_per_rank int32 [ranks], num_tokens_per_rdma_rank (always None: one NVLink domain),
+        num_tokens_per_expert int32 [num_experts], is_token_in_rank bool [T, ranks], event)``, the tuple of the
+        reference's ``Buffer.get_dispatch_layout`` (deep_ep/buffers/legacy.py:293-319).  ``dispatch`` does not
+        need it (it counts inside its kernel); it is for callers that size or balance work before dispatching.
+        """
+        assert num_experts % self.num_ranks == 0
+        if self.is_cpu:
+            lay = layout_ref.dispatch_layout(topk_idx, num_experts, self.num_ranks)
+            return lay[0], None, lay[1], lay[2], EventOverlap(None)
+        if previous_event is not None and not allocate_on_comm_stream:
+            raise ValueError('`previous_event` requires `allocate_on_comm_stream=True`')
+        self._stream_prologue(previous_event, None)
+        with torch.cuda.stream(self.comm_stream):
+            idx = topk_idx.contiguous()
+            per_rank, per_expert, in_rank = self._C.get_dispatch_layout(idx, num_experts, self.num_ranks)
+        event = self._stream_epilogue(async_finish, (per_rank, per_expert, in_rank), (idx, topk_idx))
+        return per_rank, None, per_expert, in_rank, event
+
+    # ------------------------------------------------------------------------------------------ handles
+    def _stamp(self, T: int, K: int) -> tuple:
+        gen = 0 if self.is_cpu else int(self.core.generation())
+        return (self._uid, gen, self.num_ranks, T, K)
+
+    def _attest(self, handle: EPHandle, what: str) -> None:
+        """Reject a handle that this buffer did not make: another buffer's, one from before this buffer was destroyed
+        or poisoned, or one whose recorded shape does not fit.  Raised on the host, before anything is launched."""
+        stamp = getattr(handle, 'stamp', None)
+        where = f'[EP rank {self.rank_idx}] {what}'
+        if stamp is None:
+            raise HandleError(f'{where}: the handle carries no buffer stamp (it was not returned by ElasticBuffer.dispatch)')
+        uid, _gen, ranks, T, K = stamp
+        if uid != self._uid:
+            raise HandleError(f'{where}: the handle belongs to another buffer (buffer id {uid}, this buffer is {self._uid})')
+        if self._destroyed:
+            raise HandleError(f'{where}: the buffer that made this handle has been destroyed')
+        if ranks != self.num_ranks or tuple(handle.plan.shape) != (T, K) or tuple(handle.dst_buffer_slot_idx.shape) != (T, K):
+            raise HandleError(f'{where}: the handle was made for {ranks} ranks and [{T}, {K}] selections, which does not fit '
+                              f'this call ({self.num_ranks} ranks, plan {tuple(handle.plan.shape)})')
+        if not self.is_cpu and self.core.state() == 'poisoned':
+            raise HandleError(f'{where}: the buffer is poisoned by an earlier failure; handles made by it are void')
+
     # ------------------------------------------------------------------------------------------ dispatch
     def dispatch(self, x: Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]], topk_idx: Optional[torch.Tensor] = None,
                  topk_weights: Optional[torch.Tensor] = None,
@@ -333,15 +415,30 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         reference's meaning (deep_ep/buffers/elastic.py:1391-1603): non-expand layout gives one row per
         (token, destination rank) with expert ids localised to the receiver; ``do_expand`` gives one row per
         (token, local expert), grouped by expert with aligned group starts, ``recv_topk_idx`` is ``None`` and
-        ``recv_topk_weights`` is 1-D.  With ``do_cpu_sync`` (default unless a cached ``handle`` is passed) the
+        ``recv_topk_weights`` is 1-D; ``do_zero_padding`` makes the kernel zero the rows between an expert's last
+        row and its aligned end.  With ``do_cpu_sync`` (default unless a cached ``handle`` is passed) the
         tensors have the exact number of rows; otherwise they have the worst-case size and
         ``handle.psum_num_recv_tokens_per_scaleup_rank[-1]`` holds the valid row count on the device.
         With ``use_fp8_dispatch`` (or ``fused_fp8_cast=True`` for this call) and bf16 input the e4m3 cast is fused into
         the kernel; ``fused_fp8_cast=False`` sends bf16 rows even on an FP8 buffer (backward passes).
+
+        Streams (csrc/elastic/buffer.hpp:528-586 of the reference): the kernel runs on the communication stream, which
+        first waits for ``previous_event`` (this needs ``allocate_on_comm_stream=True``) or else for the work the
+        current stream has been given so far, and for ``previous_event_before_epilogue`` if given (the reference lets
+        that event gate only its second kernel; here placement is part of the one kernel, so it gates the launch).
+        Handle and output tensors are allocated with the communication stream current when
+        ``allocate_on_comm_stream``, otherwise with the caller's stream current.  With ``async_with_compute_stream``
+        the returned event must be waited for before the results are used; otherwise the current stream waits.
+        ``num_qps`` must be 0 (there are no queue pairs inside one NVLink domain).
         """
         assert not self._destroyed
+        if num_qps != 0:
+            raise ValueError('num_qps must be 0: there are no RDMA queue pairs inside one NVLink domain')
+        if previous_event is not None and not allocate_on_comm_stream:
+            raise ValueError('`previous_event` requires `allocate_on_comm_stream=True`')
         if handle is not None:
             assert topk_idx is None, '`topk_idx` comes from the cached handle'
+            self._attest(handle, 'cached dispatch')
             num_experts = handle.num_experts
             expert_alignment = handle.expert_alignment
             do_expand = handle.do_expand
@@ -361,14 +458,23 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
 
         K = (handle.topk_idx if topk_idx is None else topk_idx).shape[1]
         num_sms = self.get_theoretical_num_sms(num_experts, K) if num_sms == 0 else num_sms
-        self._stream_prologue(previous_event, allocate_on_comm_stream)
-        with torch.cuda.stream(self.comm_stream):
+        alloc_stream = self.comm_stream if allocate_on_comm_stream else torch.cuda.current_stream()
+        if allocate_on_comm_stream:
+            self._stream_prologue(previous_event, previous_event_before_epilogue)
+        with torch.cuda.stream(alloc_stream):
             st = self._prepare_dispatch(x, topk_idx, topk_weights, cumulative_local_expert_recv_stats, num_experts,
                                         num_max_tokens_per_rank, expert_alignment, num_sms, handle, do_handle_copy,
-                                        do_cpu_sync, do_expand, use_tma_aligned_col_major_sf, fused_fp8_cast)
-            self.core.dispatch(st.call, num_sms)
-            out = self._finish_dispatch(st, do_zero_padding)
-        event = self._stream_epilogue(async_with_compute_stream, out)
+                                        do_cpu_sync, do_expand, use_tma_aligned_col_major_sf, fused_fp8_cast,
+                                        do_zero_padding)
+        if not allocate_on_comm_stream:
+            # input copies made while preparing ran on the caller's stream: wait for them too
+            self._stream_prologue(previous_event, previous_event_before_epilogue)
+        with torch.cuda.stream(self.comm_stream):
+            self._timed('dispatch', lambda: self.core.dispatch(st.call, num_sms))
+            out = self._finish_dispatch(st)
+        inputs = (st.call.x, st.call.sf, st.call.topk_idx, st.call.topk_weights, st.call.stats, st.call.lane_src,
+                  st.call.plan, st.call.psum_rank, st.call.psum_expert, st.call.recv_per_expert, x, topk_idx, topk_weights)
+        event = self._stream_epilogue(async_with_compute_stream, out, inputs)
         return (*out, event)
 
     def _next_recv_slot(self) -> int:
@@ -377,7 +483,8 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         return slot
 
     def _prepare_dispatch(self, x, topk_idx, topk_weights, stats, num_experts, num_max_tokens, alignment, num_sms, handle,
-                          do_handle_copy, do_cpu_sync, do_expand, col_major_sf, fused_fp8_cast=None) -> _DispatchState:
+                          do_handle_copy, do_cpu_sync, do_expand, col_major_sf, fused_fp8_cast=None,
+                          do_zero_padding=False) -> _DispatchState:
         C = self._C
         x_in, sf_in = x if isinstance(x, tuple) else (x, None)
         T, H = x_in.shape
@@ -419,7 +526,9 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         call.num_max_tokens = num_max_tokens
         call.quantize = quantize
         call.do_expand = do_expand
+        call.do_zero_padding = bool(do_zero_padding)
         call.cached = cached
+        call.tune_warps, call.tune_stages = self._tune
         slot_idx = self._next_recv_slot()
         slot = self.regions.slot(slot_idx)
         cap = self.regions.capacity_rows
@@ -428,22 +537,20 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         G = (H + 127) // 128
         call.sf_stride_row, call.sf_stride_col = (1, cap) if col_major_sf else (G, 1)
         call.recv_capacity_rows = cap
-        side = None
-        if not do_expand and not col_major_sf and os.environ.get('EP_DISABLE_PACKED_SIDE', '0') != '1':
-            # scales, expert ids, weights and source ids of a row travel as one packed record
-            sf_bytes = G * 4 if fp8_out else 0
-            off_idx = align(sf_bytes, 8)
-            off_w = off_idx + K * idx.element_size()
+        tail = None
+        if not do_expand and not col_major_sf and (not fp8_out or (G * 4) % 16 == 0):
+            # scales travel as one bulk store per row; expert ids (already relative to the receiver), weights and
+            # source ids as one more: the tail record {ids | weights | metadata}
+            off_w = K * idx.element_size()
             off_meta = align(off_w + K * 4, 8)
-            side_bytes = align(off_meta + 8, 16)
-            assert side_bytes <= self.regions.side_bytes, 'side record larger than the buffer was sized for'
+            tail_bytes = align(off_meta + 8, 16)
+            assert tail_bytes <= self.regions.tail_bytes, 'tail record larger than the buffer was sized for'
             call.side_packed = True
-            call.side_bytes, call.side_off_idx, call.side_off_w, call.side_off_meta = side_bytes, off_idx, off_w, off_meta
-            call.off_recv_side = slot.side
-            side = (side_bytes, off_idx, off_w, off_meta)
+            call.tail_bytes, call.tail_off_w, call.tail_off_meta = tail_bytes, off_w, off_meta
+            call.off_recv_tail = slot.tail
+            tail = (tail_bytes, off_w, off_meta)
         if self.profile is not None:
             call.prof = self.profile['dispatch']
-            call.skip_side_stores = bool(int(os.environ.get('EP_PROFILE_SKIP_SIDE_STORES', '0')))
 
         st = _DispatchState()
         st.call, st.T, st.H, st.K, st.E = call, T, H, K, num_experts
@@ -454,10 +561,10 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         st.cached_handle = handle
         st.x_dtype = x_in.dtype
         st.do_handle_copy = do_handle_copy
-        st.side = side
+        st.side = tail
         return st
 
-    def _finish_dispatch(self, st: _DispatchState, do_zero_padding: bool = False):
+    def _finish_dispatch(self, st: _DispatchState):
         core, cap = self.core, self.regions.capacity_rows
         R, El = self.num_ranks, st.E // self.num_ranks
         K, H = st.K, st.H
@@ -478,15 +585,15 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         recv_x = core.view(st.slot.x, [rows, H], [H, 1], x_dtype)
         recv_sf = recv_w = None
         if st.side is not None:
-            # strided views over the packed side records
-            side_bytes, off_idx, off_w, off_meta = st.side
+            # contiguous scales; strided views over the tail records
+            tail_bytes, off_w, off_meta = st.side
             if st.fp8_out:
-                recv_sf = core.view(st.slot.side, [rows, G], [side_bytes // 4, 1], torch.float32)
+                recv_sf = core.view(st.slot.sf, [rows, G], [G, 1], torch.float32)
             isz = st.topk_idx.element_size()
-            recv_idx = core.view(st.slot.side + off_idx, [rows, K], [side_bytes // isz, 1], st.topk_idx.dtype)
+            recv_idx = core.view(st.slot.tail, [rows, K], [tail_bytes // isz, 1], st.topk_idx.dtype)
             if st.topk_weights is not None:
-                recv_w = core.view(st.slot.side + off_w, [rows, K], [side_bytes // 4, 1], torch.float32)
-            meta = core.view(st.slot.side + off_meta, [rows, 2], [side_bytes // 4, 1], torch.int32)
+                recv_w = core.view(st.slot.tail + off_w, [rows, K], [tail_bytes // 4, 1], torch.float32)
+            meta = core.view(st.slot.tail + off_meta, [rows, 2], [tail_bytes // 4, 1], torch.int32)
         else:
             if st.fp8_out:
                 strides = [1, cap] if st.col_major_sf else [G, 1]
@@ -496,9 +603,6 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
                 recv_w = core.view(st.slot.w, [rows], [1], torch.float32) if st.do_expand else \
                     core.view(st.slot.w, [rows, K], [K, 1], torch.float32)
             meta = core.view(st.slot.meta, [rows, 2], [2, 1], torch.int32)
-        if do_zero_padding and st.do_expand:
-            psum = st.call.psum_expert if st.cached_handle is None else st.cached_handle.psum_num_recv_tokens_per_expert
-            self._zero_padding(recv_x, psum, st.alignment, rows)
         if not self.zero_copy:
             recv_x = recv_x.clone()
             recv_sf = None if recv_sf is None else recv_sf.clone()
@@ -514,28 +618,19 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
             handle = EPHandle(st.do_expand, st.E, st.alignment, st.call.num_max_tokens, st.num_sms, idx_copy, num_recv,
                               num_expanded, per_expert_list, st.call.psum_rank, st.call.psum_expert,
                               st.call.recv_per_expert, meta, st.call.lane_src, st.call.plan, H, st.slot_idx,
-                              st.topk_weights)
+                              st.topk_weights, stamp=self._stamp(st.T, K))
         x_out = (recv_x, recv_sf) if st.fp8_out else recv_x
         return x_out, recv_idx, recv_w, handle
 
-    @staticmethod
-    def _zero_padding(recv_x: torch.Tensor, psum_expert: torch.Tensor, alignment: int, rows: int) -> None:
-        """Zero the alignment gap behind every expert segment of the expand layout."""
-        if alignment <= 1 or rows == 0:
-            return
-        ends = psum_expert.to(torch.int64)
-        aligned = (ends + alignment - 1) // alignment * alignment
-        r = torch.arange(rows, device=recv_x.device).unsqueeze(1)
-        pad = ((r >= ends.unsqueeze(0)) & (r < aligned.unsqueeze(0))).any(dim=1)
-        recv_x.view(torch.uint8)[pad] = 0
-
     # ------------------------------------------------------------------------------------------ combine
     def get_combine_buffer(self, handle: EPHandle, hidden: Optional[int] = None) -> torch.Tensor:
-        """bf16 ``[handle.num_rows, hidden]`` view of the combine input region.  Expert outputs written here
-        are combined without the staging copy that a plain tensor needs."""
+        """bf16 ``[handle.num_rows, hidden]`` view of the input region that the NEXT ``combine`` call of this buffer
+        reads.  Expert outputs written here are combined without the staging copy that a plain tensor needs.
+        There are two such regions, used by alternate calls (peers may still be pulling from the previous call's
+        region), so ask for the view after the previous ``combine`` has been issued."""
         assert not self.is_cpu
         H = value_or(hidden, handle.hidden)
-        return self.core.view(self.regions.combine_x, [handle.num_rows, H], [H, 1], torch.bfloat16)
+        return self.core.view(self.regions.combine_x(self._combine_slot_counter), [handle.num_rows, H], [H, 1], torch.bfloat16)
 
     def combine(self, x: torch.Tensor, handle: EPHandle, topk_weights: Optional[torch.Tensor] = None,
                 bias: Union[None, torch.Tensor, Tuple[torch.Tensor, torch.Tensor]] = None, num_sms: int = 0,
@@ -549,19 +644,34 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         bf16 (no weighting, as deep_ep/buffers/elastic.py:1616-1712); with ``weighted=True`` each row is first
         multiplied by the token's own ``topk_weights[t, k]`` (fused weighted reduce).  ``topk_weights`` given
         here are carried back to the home rank unchanged (``[rows, K]`` non-expand, ``[rows]`` expand) and
-        returned as ``combined_topk_weights [T, K]``.
-        Returns ``(combined_x, combined_topk_weights, event)``.
+        returned as ``combined_topk_weights [T, K]``.  A plain ``x`` is first copied into the buffer's input region
+        (one local pass over the rows); a tensor obtained from :meth:`get_combine_buffer` is read in place.
+        Stream arguments behave as in :meth:`dispatch`.  Returns ``(combined_x, combined_topk_weights, event)``.
         """
         assert not self._destroyed
+        if num_qps != 0:
+            raise ValueError('num_qps must be 0: there are no RDMA queue pairs inside one NVLink domain')
+        if previous_event is not None and not allocate_on_comm_stream:
+            raise ValueError('`previous_event` requires `allocate_on_comm_stream=True`')
+        self._attest(handle, 'combine')
         bias0, bias1 = (bias if isinstance(bias, (tuple, list)) else (bias, None)) if bias is not None else (None, None)
         if self.is_cpu:
             return self._cpu.combine(self, x, handle, topk_weights, bias0, bias1, weighted)
         num_sms = value_or(num_sms or None, handle.num_sms)
-        self._stream_prologue(previous_event, allocate_on_comm_stream)
+        alloc_stream = self.comm_stream if allocate_on_comm_stream else torch.cuda.current_stream()
+        if allocate_on_comm_stream:
+            self._stream_prologue(previous_event, previous_event_before_epilogue)
+        with torch.cuda.stream(alloc_stream):
+            call, out, out_w, staged = self._prepare_combine(x, handle, topk_weights, bias0, bias1, weighted)
+        if not allocate_on_comm_stream:
+            self._stream_prologue(previous_event, previous_event_before_epilogue)
         with torch.cuda.stream(self.comm_stream):
-            call, out, out_w = self._prepare_combine(x, handle, topk_weights, bias0, bias1, weighted)
-            self.core.combine(call, num_sms)
-        event = self._stream_epilogue(async_with_compute_stream, (out, out_w))
+            for dst, src in staged:      # plain tensors go through the symmetric buffer
+                dst.copy_(src)
+            self._timed('combine', lambda: self.core.combine(call, num_sms))
+        inputs = (x, topk_weights, bias0, bias1, call.bias0, call.bias1, call.mul_weights, handle.plan,
+                  handle.dst_buffer_slot_idx)
+        event = self._stream_epilogue(async_with_compute_stream, (out, out_w), inputs)
         return out, out_w, event
 
     def _prepare_combine(self, x, handle: EPHandle, topk_weights, bias0, bias1, weighted):
@@ -569,11 +679,15 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         H = x.shape[1]
         rows = handle.num_rows
         assert x.dtype == torch.bfloat16 and x.shape[0] >= rows, 'combine input must be bf16 with one row per received row'
-        staging = self.get_combine_buffer(handle, H)
+        region = self._combine_slot_counter & 1
+        self._combine_slot_counter += 1
+        off_x, off_w = self.regions.combine_x(region), self.regions.combine_w(region)
+        staging = self.core.view(off_x, [rows, H], [H, 1], torch.bfloat16)
+        staged = []
         if x.data_ptr() != staging.data_ptr():
-            staging.copy_(x[:rows])
+            staged.append((staging, x[:rows]))
         call = C.CombineCall()
-        call.off_x = self.regions.combine_x
+        call.off_x = off_x
         call.plan = handle.plan
         call.lane_src = handle.dst_buffer_slot_idx
         call.hidden = H
@@ -585,10 +699,10 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         out_w = None
         if topk_weights is not None:
             w_cols = 1 if handle.do_expand else K
-            wview = self.core.view(self.regions.combine_w, [rows, w_cols], [w_cols, 1], torch.float32)
-            wview.copy_(topk_weights[:rows].reshape(rows, w_cols))
+            wview = self.core.view(off_w, [rows, w_cols], [w_cols, 1], torch.float32)
+            staged.append((wview, topk_weights[:rows].reshape(rows, w_cols)))
             out_w = torch.empty((T, K), dtype=torch.float32, device=x.device)
-            call.off_w, call.w_cols, call.out_w = self.regions.combine_w, w_cols, out_w
+            call.off_w, call.w_cols, call.out_w = off_w, w_cols, out_w
         if weighted:
             assert handle.do_expand, 'the fused weighted reduce needs the expand layout (one row per expert hit)'
             assert handle.topk_weights is not None, 'dispatch must have been given topk_weights'
@@ -597,18 +711,26 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
             call.bias0 = bias0.contiguous()
         if bias1 is not None:
             call.bias1 = bias1.contiguous()
-        return call, out, out_w
+        return call, out, out_w, staged
 
     # ------------------------------------------------------------------------------------------ streams
-    def _stream_prologue(self, previous_event: Optional[EventHandle], allocate_on_comm_stream: bool) -> None:
-        """The communication stream waits for ``previous_event`` or for the current stream's work so far."""
+    def _stream_prologue(self, previous_event: Optional[EventHandle], before_epilogue: Optional[EventHandle]) -> None:
+        """The communication stream waits for ``previous_event`` or for the current stream's work so far, and for
+        ``before_epilogue`` (see :meth:`dispatch`)."""
         if previous_event is not None and previous_event.event is not None:
             self.comm_stream.wait_event(previous_event.event)
         else:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
+        if before_epilogue is not None and before_epilogue.event is not None:
+            self.comm_stream.wait_event(before_epilogue.event)
 
-    def _stream_epilogue(self, async_with_compute_stream: bool, tensors) -> EventOverlap:
-        """Either hand back an event on the communication stream (async) or make the current stream wait."""
+    def _stream_epilogue(self, async_with_compute_stream: bool, outputs, inputs=()) -> EventOverlap:
+        """Either hand back an event on the communication stream (async) or make the current stream wait.
+
+        In the async case the caching allocator must not hand a block to someone else while the other stream still
+        uses it: every tensor involved (inputs read by the kernel, handle tensors, outputs; the handle is walked
+        too) is recorded on both streams, or, with ``EP_AVOID_RECORD_STREAM=1``, kept alive by the returned event
+        instead (csrc/elastic/buffer.hpp:558-586, 1151-1164 of the reference)."""
         flat: List[torch.Tensor] = []
 
         def walk(o):
@@ -617,13 +739,19 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
             elif isinstance(o, (tuple, list)):
                 for i in o:
                     walk(i)
-        walk(tensors)
+            elif isinstance(o, EPHandle):
+                for v in vars(o).values():
+                    if isinstance(v, torch.Tensor):
+                        flat.append(v)
+        walk(outputs)
+        walk(inputs)
         if async_with_compute_stream:
-            cur = torch.cuda.current_stream()
-            for t in flat:
-                if t.is_cuda:
-                    t.record_stream(cur)
-                    t.record_stream(self.comm_stream)
+            if os.environ.get('EP_AVOID_RECORD_STREAM', '0') != '1':
+                cur = torch.cuda.current_stream()
+                for t in flat:
+                    if t.is_cuda:
+                        t.record_stream(cur)
+                        t.record_stream(self.comm_stream)
             return EventOverlap(EventHandle(self.comm_stream, tuple(flat)))
         torch.cuda.current_stream().wait_stream(self.comm_stream)
         return EventOverlap(None)
@@ -632,11 +760,36 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         """An event on the current stream, usable as ``previous_event``."""
         return EventHandle(torch.cuda.current_stream() if not self.is_cpu else None)
 
+    # ------------------------------------------------------------------------------------------ kernel timing
+    def enable_kernel_timing(self, enabled: bool = True) -> None:
+        """Bracket every dispatch / combine kernel with CUDA events recorded on the communication stream right
+        around the launch (what a per-kernel profiler reports), without the cross-stream hand-over on either side.
+        Read the pairs with :meth:`kernel_times_ms`."""
+        self._kernel_timing = {'dispatch': [], 'combine': []} if enabled else None
+
+    def _timed(self, name: str, launch) -> None:
+        if self._kernel_timing is None:
+            launch()
+            return
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(self.comm_stream)
+        launch()
+        e1.record(self.comm_stream)
+        self._kernel_timing[name].append((e0, e1))
+
+    def kernel_times_ms(self, name: str, clear: bool = True) -> List[float]:
+        """Device time of every ``name`` ('dispatch' or 'combine') kernel launched since timing was enabled (or since
+        the last call with ``clear``).  Synchronises the device."""
+        torch.cuda.synchronize()
+        out = [a.elapsed_time(b) for a, b in self._kernel_timing[name]]
+        if clear:
+            self._kernel_timing[name] = []
+        return out
+
     # ------------------------------------------------------------------------------------------ profiling
     def enable_profiling(self, enabled: bool = True) -> None:
-        """Make dispatch / combine record device-side phase timestamps (ns, CTA 0 of this rank); read them with
-        :meth:`phase_times`.  Dispatch: start, counted, exchanged, assigned, scattered, grid drained, peers done.
-        Combine: start, entry barrier, pulled, grid drained, exit barrier."""
+        """Make dispatch / combine record device-side phase timestamps (ns; CTA 0 of this rank, and the last CTA to
+        finish for the closing phases); read them with :meth:`phase_times`."""
         keys = ('dispatch', 'combine', 'll_dispatch', 'll_combine')
         self.profile = {k: torch.zeros(8, dtype=torch.int64, device='cuda') for k in keys} if enabled else None
 
@@ -644,8 +797,8 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         """Microseconds spent in each phase of the last dispatch and combine."""
         torch.cuda.synchronize()
         d, c = self.profile['dispatch'].tolist(), self.profile['combine'].tolist()
-        names_d = ['layout_count', 'count_exchange', 'assign_rows', 'scatter', 'grid_drain', 'peer_done', 'localise_ids']
-        names_c = ['entry_barrier', 'pull_reduce', 'grid_drain', 'exit_barrier']
+        names_d = ['layout_count', 'count_exchange', 'assign_rows', 'scatter', 'last_cta_drained', 'peers_done', 'close']
+        names_c = ['entry_barrier', 'pull_reduce', 'last_cta_done']
         out = {'dispatch': {n: (d[i + 1] - d[i]) / 1e3 for i, n in enumerate(names_d) if d[i + 1] and d[i]},
                'combine': {n: (c[i + 1] - c[i]) / 1e3 for i, n in enumerate(names_c) if c[i + 1] and c[i]}}
         # low-latency kernels: microseconds since the start of the kernel at which each point was reached (CTA 0, except

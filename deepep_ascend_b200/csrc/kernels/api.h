@@ -60,7 +60,9 @@ enum EpPhase {
     EP_PH_TEST_FLAG = 11,
     EP_PH_PP = 12,
     EP_PH_TILE_FLAG = 13,
-    EP_PH_GEMM_PIPE = 14
+    EP_PH_GEMM_PIPE = 14,
+    EP_PH_DISPATCH_ASSIGN = 15,
+    EP_PH_CTA_COUNTS = 16
 };
 
 struct RankCtx {
@@ -97,13 +99,17 @@ struct DispatchArgs {
     uint64_t off_recv_x, off_recv_sf, off_recv_idx, off_recv_w, off_recv_meta;
     int64_t sf_stride_row, sf_stride_col;   // element strides of the receiver's scale tensor
     int recv_capacity_rows;
-    uint64_t* prof;                // optional [8] phase timestamps (ns) written by CTA 0, or null
-    // packed side records (non-expand layout, row-major scales): {scales | global expert ids | weights | source id}
-    // travel as ONE extra bulk store per destination row; the receiver localises the ids after the final barrier
+    uint64_t* prof;                // optional [8] phase timestamps (ns), or null: start, counted, exchanged, assigned, CTA 0 done
+                                   //     sending | by the last CTA of the rank to finish: all stores drained, peers done, end
+    // Bulk side stores (non-expand layout, row-major scales whose row is a multiple of 16 bytes): besides the payload row
+    // every destination row gets ONE bulk store of its scales (into recv_sf) and ONE of a tail record
+    // {expert ids relative to the receiver | weights | source token, source rank * K + sending lane} built by the sender,
+    // so nothing is left for the receiver to rewrite.  Otherwise the small pieces go out as plain peer stores.
     int side_packed;
-    int side_bytes, side_off_idx, side_off_w, side_off_meta;
-    uint64_t off_recv_side;
-    int skip_side_stores;          // profiling only: leave out the per-row scale / index / weight / metadata stores
+    int tail_bytes, tail_off_w, tail_off_meta;   // tail record: ids at 0, weights, metadata; multiple of 16 bytes
+    uint64_t off_recv_tail;
+    int do_zero_padding;           // expand layout: zero the rows (and scales) between an expert's last row and its aligned end
+    int tune_warps, tune_stages;   // 0 = automatic; warps per CTA and staging buffers per warp of the fused-cast path
 };
 
 struct CombineArgs {
@@ -146,6 +152,7 @@ struct LaunchShape {
     int num_ctas;
     int num_warps;
     int smem_bytes;
+    int num_stages;
 };
 
 // Every launcher takes `n` argument structs: n == 1 is the production path (this process drives one GPU);
@@ -220,8 +227,15 @@ struct EngramFetchArgs {
     int num_fetches;
     int entries_per_rank;
     int entry_bytes;             // multiple of 16
-    uint64_t off_storage;        // storage region inside every rank's symmetric buffer
+    const uint8_t* storage[EP_MAX_RANKS];   // every rank's table as seen from this GPU: a region of the peer's symmetric
+                                 //     buffer, or the peer's CPU segment (pinned host memory mapped into this GPU)
     void* out;                   // [num_fetches, entry_bytes]
+    // scale factors of quantised tables: a table replicated on every rank, gathered locally with the fetch
+    const int32_t* sf_table;     // [num_ranks * entries_per_rank, sf_packs] 4-byte packs (fp32 or four UE8M0), or null
+    int32_t* fetched_sf;         // pack p of fetch i (token i / per_token, entry i % per_token) goes to
+    int sf_packs;                //     fetched_sf[token * sf_token_stride + (entry * sf_packs + p) * sf_pack_stride]
+    int entries_per_token;
+    int64_t sf_token_stride, sf_pack_stride;
 };
 
 // ------------------------------------------------------------------------------------------------ local reduce

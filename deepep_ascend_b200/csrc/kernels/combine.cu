@@ -3,23 +3,27 @@
 // peer mappings, no multicast) and reduces them in fp32 registers, so the reduction is fused into the gather
 // and no intermediate slab is written or re-read.
 //
-// Work item = (token, column chunk of 32 lanes x 16 B x kUnroll).  Each warp owns kSlots item slots; a slot
-// has one chunk buffer per top-k lane and one mbarrier.  While the warp reduces item n, the loads of item
-// n + kSlots - 1 are in flight.  The accumulation order is fixed (bias0 + bias1 first, then the plan entries in
-// top-k lane order), so results are bitwise reproducible.
+// Work item = (token, column chunk of 32 lanes x 16 B x kUnroll).  Items are claimed dynamically by the warps of all
+// CTAs from one counter, a whole token's chunks per claim at first and single chunks near the end, so that no warp is
+// left with a long tail.  Each warp owns a ring of chunk buffers with one mbarrier each: while it reduces one chunk,
+// the loads of the following ones are in flight.  The accumulation order is fixed (bias0 + bias1 first, then the plan
+// entries in top-k lane order), so results are bitwise reproducible.
+//
+// There is no grid-wide barrier and no exit barrier.  Entry: CTA 0 signals every peer, every CTA watches the peers'
+// signals itself (all ranks' input rows are in place once all ranks have entered the call).  Exit: the caller
+// alternates between two input regions, and a rank can only pass the entry barrier of call n + 1 after every rank has
+// entered it, i.e. has finished pulling for call n; so the region of call n is free again when call n + 1 returns.
 //
 // Parity: does the work of combine_impl + combine_reduce_epilogue_impl
 // (deep_ep/include/deep_ep/impls/combine.cuh:15-243, combine_reduce_epilogue.cuh:12-143) plus the weighted
 // reduction of the legacy low-latency combine (csrc/kernels/legacy/internode_ll.cu:1033-1136).
-#include <cstdlib>
-
 #include "common.cuh"
 
 namespace ep {
 
 namespace {
 
-constexpr int kCombineMaxWarps = 16;
+constexpr int kCombineMaxWarps = 12;
 constexpr int kCombineMaxRing = 32;              // chunk buffers (and mbarriers) per warp
 constexpr int kCombineSmemBudget = 208 * 1024;
 constexpr int kCombineQueue = 64;                // claimed-token queue per warp (producer -> consumer)
@@ -38,7 +42,7 @@ __host__ __device__ inline CombineSmemPlan combine_smem_plan(int chunk_bytes, in
     p.num_warps = num_warps;
     p.off_bar = 128;
     p.off_queue = 128 + num_warps * kCombineMaxRing * 8;
-    p.off_data = p.off_queue + num_warps * kCombineQueue * 4;
+    p.off_data = p.off_queue + num_warps * kCombineQueue * 8;   // claimed ranges: first item and length
     p.off_data = (p.off_data + 1023) / 1024 * 1024;
     int ring = (kCombineSmemBudget - p.off_data) / (num_warps * chunk_bytes);
     p.ring = ring > kCombineMaxRing ? kCombineMaxRing : ring;
@@ -46,14 +50,15 @@ __host__ __device__ inline CombineSmemPlan combine_smem_plan(int chunk_bytes, in
     return p;
 }
 
-// Cursor over the flattened sequence of (work item, source) pairs of one warp.  Lane k holds plan[t][k] of the
-// cursor's item; `pending` has one bit per source that is still to be visited, lowest lane first.
+// Cursor over the flattened sequence of (work item, source) pairs of one warp.  Items are numbered token * num_chunks +
+// chunk; a cursor walks a claimed range [item, range_end).  Lane k holds plan[t][k] of the cursor's token; `pending`
+// has one bit per source that is still to be visited, lowest lane first.
 struct PullCursor {
-    int token;           // >= num_tokens when exhausted
-    int chunk;
+    int item, range_end;   // current item and end of the claimed range (item == range_end: range used up)
+    int token;             // token whose plan is loaded, -1 for none
     int plan_k;
-    uint32_t sources;    // lanes of the token's plan that hold a row
-    uint32_t pending;    // sources of the current chunk not visited yet
+    uint32_t sources;      // lanes of the token's plan that hold a row
+    uint32_t pending;      // sources of the current chunk not visited yet
 };
 
 template <int kUnroll>
@@ -73,8 +78,10 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
     uint8_t** s_peer = reinterpret_cast<uint8_t**>(smem);
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + sp.off_bar) + warp * kCombineMaxRing;
     uint8_t* s_data = smem + sp.off_data + static_cast<size_t>(warp) * ring * kChunk;
-    int* s_queue = reinterpret_cast<int*>(smem + sp.off_queue) + warp * kCombineQueue;
-    if (blockIdx.x == 0 && tid == 0) atomicExch(&ws->dyn_counter[EP_CH_COMBINE], 0u);   // ordered before its first use by the grid barrier
+    int* s_queue = reinterpret_cast<int*>(smem + sp.off_queue) + warp * 2 * kCombineQueue;
+    int* s_qlen = s_queue + kCombineQueue;
+    // every CTA reads the entry-barrier sequence before it arrives anywhere; the last CTA to finish writes the new one
+    const uint64_t entry_seq = *reinterpret_cast<volatile uint64_t*>(&ws->comb_seq) + 1;
 
     if (tid < EP_MAX_RANKS) s_peer[tid] = tid < ctx.num_ranks ? ctx.peer_base[tid] : nullptr;
     if (lane == 0)
@@ -87,61 +94,96 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
         if (a.prof != nullptr && blockIdx.x == 0 && tid == 0) a.prof[i] = globaltimer_ns();
     };
     stamp(0);
-    // every rank's input rows must be in place before anyone pulls
+    // every rank's input rows must be in place before anyone pulls: CTA 0 tells the peers that this rank has entered
+    // the call (stream order puts its rows before the kernel), every CTA waits for all peers' words itself
     bool alive = !is_aborted(ws);
-    if (blockIdx.x == 0) alive = xgpu_barrier(ctx, ws, EP_CH_COMBINE, EP_PH_COMBINE_ENTRY) && alive;
-    alive = grid_sync(ctx, ws, EP_CH_COMBINE, EP_PH_GRID_SYNC) && alive;
+    {
+        int ok = alive ? 1 : 0;
+        if (alive && tid < ctx.num_ranks) {
+            if (blockIdx.x == 0) ptx::red_add_release_sys(&reinterpret_cast<Workspace*>(s_peer[tid])->xbar[EP_CH_COMBINE][ctx.rank], 1ull);
+            const uint64_t* mine = &ws->xbar[EP_CH_COMBINE][tid];
+            ok = bounded_wait(
+                ctx, ws, EP_PH_COMBINE_ENTRY, tid, entry_seq, [&] { return ptx::ld_acquire_sys(mine) >= entry_seq; },
+                [&] { return ptx::ld_relaxed_sys(mine); });
+        }
+        alive = __syncthreads_and(ok) != 0;
+    }
     stamp(1);
 
-    // Tokens are claimed dynamically from a counter shared by all CTAs of this rank (SMs that get a smaller share of
-    // the NVLink bandwidth claim fewer tokens, so no CTA is left with a tail).  The producer cursor claims; the
-    // claimed ids travel through a small per-warp queue to the consumer cursor, which follows in the same order.
-    uint32_t claimed = 0, started = 0;     // tokens claimed by the producer / started by the consumer
-    auto claim_token = [&]() -> int {
-        int tkn = 0;
+    // Items are claimed from a counter shared by all CTAs of this rank (SMs that get a smaller share of the NVLink
+    // bandwidth claim fewer), which is zero at entry: the last CTA of every call clears it.  The producer cursor
+    // claims; the claimed ranges travel through a small per-warp queue to the consumer cursor, which follows in the
+    // same order.
+    const int total_items = T * num_chunks;
+    const int tail_zone = 2 * static_cast<int>(gridDim.x) * num_warps * num_chunks;
+    uint32_t claimed = 0, started = 0;     // ranges claimed by the producer / started by the consumer
+    int last_base = 0;
+    auto claim_range = [&](int& amount) -> int {   // -> first item of the range; base and length also go into the queue
+        amount = last_base + tail_zone < total_items ? num_chunks : 1;
+        int base = 0;
         if (lane == 0) {
-            tkn = static_cast<int>(atomicAdd(&ws->dyn_counter[EP_CH_COMBINE], 1u));
-            s_queue[claimed % kCombineQueue] = tkn;
+            base = static_cast<int>(atomicAdd(&ws->dyn_counter[EP_CH_COMBINE], static_cast<uint32_t>(amount)));
+            s_queue[claimed % kCombineQueue] = base;
+            s_qlen[claimed % kCombineQueue] = amount;
         }
         __syncwarp();
         ++claimed;
-        return __shfl_sync(0xffffffffu, tkn, 0);
+        base = __shfl_sync(0xffffffffu, base, 0);
+        last_base = base;
+        return base;
     };
     auto load_token = [&](PullCursor& c) {
-        c.chunk = 0;
-        c.plan_k = -1;
-        c.sources = 0;
-        if (c.token < T) {
-            c.plan_k = lane < K ? a.plan[static_cast<int64_t>(c.token) * K + lane] : -1;
-            c.sources = __ballot_sync(0xffffffffu, c.plan_k >= 0);
+        // (re)load the plan of the cursor's current item if it belongs to another token
+        const int tkn = c.item < total_items ? c.item / num_chunks : -1;
+        if (tkn != c.token) {
+            c.token = tkn;
+            c.plan_k = -1;
+            c.sources = 0;
+            if (tkn >= 0) {
+                c.plan_k = lane < K ? __ldg(a.plan + static_cast<int64_t>(tkn) * K + lane) : -1;
+                c.sources = __ballot_sync(0xffffffffu, c.plan_k >= 0);
+            }
         }
         c.pending = c.sources;
     };
-    // producer: move to its next token (claims one); returns false when the queue is too full to claim right now
-    auto producer_next_token = [&](PullCursor& c) -> bool {
-        if (claimed - started >= static_cast<uint32_t>(kCombineQueue - 8)) return false;
-        c.token = c.token < T ? claim_token() : T;
+    auto set_range = [&](PullCursor& c, int base, int len) {
+        c.item = base;
+        c.range_end = min(total_items, base + len);
+        if (c.item >= c.range_end) c.item = c.range_end = total_items;   // nothing left anywhere
         load_token(c);
+    };
+    // producer: move to its next range (claims one); returns false when the queue is too full to claim right now
+    auto producer_next_range = [&](PullCursor& c) -> bool {
+        if (claimed - started >= static_cast<uint32_t>(kCombineQueue - 8)) return false;
+        if (c.item >= total_items) return true;   // exhausted: stay there
+        int len;
+        const int base = claim_range(len);
+        set_range(c, base, len);
         return true;
     };
 
     if (alive) {
-        PullCursor prod{0, 0, -1, 0, 0}, cons{0, 0, -1, 0, 0};
-        prod.token = claim_token();
-        load_token(prod);
+        PullCursor prod{0, 0, -1, -1, 0, 0}, cons{0, 0, -1, -1, 0, 0};
+        {
+            int len;
+            const int base = claim_range(len);
+            set_range(prod, base, len);
+        }
         uint32_t issued = 0, consumed = 0;   // loads issued / consumed by this warp; buffer = counter % ring
 
         // issue loads in sequence order until the ring is full or the warp's work is exhausted
         auto issue_ahead = [&]() {
-            while (issued - consumed < static_cast<uint32_t>(ring) && prod.token < T) {
+            while (issued - consumed < static_cast<uint32_t>(ring) && prod.item < total_items) {
                 if (prod.pending == 0) {
-                    if (++prod.chunk == num_chunks) {
-                        if (!producer_next_token(prod)) {
-                            prod.chunk = num_chunks - 1;   // retry the claim on the next call
+                    if (prod.item + 1 >= prod.range_end) {
+                        prod.item = prod.range_end;
+                        if (!producer_next_range(prod)) {
+                            prod.item = prod.range_end - 1;   // retry the claim on the next call
                             break;
                         }
                     } else {
-                        prod.pending = prod.sources;
+                        ++prod.item;
+                        load_token(prod);
                     }
                     continue;
                 }
@@ -149,7 +191,7 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
                 prod.pending &= prod.pending - 1;
                 const int p = __shfl_sync(0xffffffffu, prod.plan_k, k);
                 if (lane == 0) {
-                    const int c = prod.chunk;
+                    const int c = prod.item % num_chunks;
                     const int bytes = min(kChunk, row_bytes - c * kChunk);
                     const int b = issued % ring;
                     const uint8_t* src = s_peer[p >> 24] + a.off_x + static_cast<int64_t>(p & 0xffffff) * row_bytes +
@@ -161,20 +203,21 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
             }
         };
 
-        // consumer: pop the next claimed token (making the producer claim one if it has not run ahead)
-        auto consumer_next_token = [&](PullCursor& c) {
+        // consumer: pop the next claimed range (making the producer claim one if it has not run ahead)
+        auto consumer_next_range = [&](PullCursor& c) {
             if (started == claimed) {
-                // the producer has consumed all its claims too: it sits at the end of its current token
-                prod.token = prod.token < T ? claim_token() : T;
-                load_token(prod);
+                // the producer has used up all its claims too: it sits at the end of its current range
+                int len;
+                const int base = claim_range(len);
+                set_range(prod, base, len);
             }
-            c.token = s_queue[started % kCombineQueue];
+            const int base = s_queue[started % kCombineQueue], len = s_qlen[started % kCombineQueue];
             ++started;
-            load_token(c);
+            set_range(c, base, len);
         };
-        consumer_next_token(cons);
-        for (; cons.token < T && alive;) {
-            const int t = cons.token, c = cons.chunk;
+        consumer_next_range(cons);
+        for (; cons.item < total_items && alive;) {
+            const int t = cons.token, c = cons.item % num_chunks;
             const int bytes = min(kChunk, row_bytes - c * kChunk);
             const int col0 = c * kChunk;   // byte offset inside the row
             issue_ahead();
@@ -259,28 +302,25 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a) {
                     ptx::st_na_v4(out + off, raw);
                 }
             }
-            if (++cons.chunk == num_chunks) consumer_next_token(cons);
-            else cons.pending = cons.sources;
+            if (cons.item + 1 >= cons.range_end) consumer_next_range(cons);
+            else {
+                ++cons.item;
+                load_token(cons);
+            }
         }
-        // loads still in flight belong to nobody once the loop was left early: wait for them (bounded) so that
-        // no copy lands in shared memory after the CTA has exited
-        while (consumed < issued) {
-            if (!bounded_wait(ctx, ws, EP_PH_COMBINE_LOAD, -1, consumed,
-                              [&] { return ptx::mbar_try_wait(&s_bar[consumed % ring], (consumed / ring) & 1); }, [&] { return 0ull; }))
-                break;
-            ++consumed;
-        }
+        // loads still in flight belong to nobody once the loop was left early: give them time to land so that no
+        // copy arrives in shared memory after the CTA has exited
+        for (; consumed < issued; ++consumed) mbar_drain(&s_bar[consumed % ring], (consumed / ring) & 1, 1000ull * 1000 * 1000);
     }
 
     stamp(2);
-    // nobody may overwrite its input rows until every rank has finished pulling
-    const bool cta_ok = __syncthreads_and(alive ? 1 : 0) != 0;
-    alive = grid_sync(ctx, ws, EP_CH_COMBINE, EP_PH_GRID_SYNC) && cta_ok;
-    stamp(3);
-    if (blockIdx.x == 0) {
-        if (alive) xgpu_barrier(ctx, ws, EP_CH_COMBINE, EP_PH_COMBINE_EXIT);
-        stamp(4);
-        if (tid == 0) ws->epoch[EP_CH_COMBINE] += 1;
+    // the last CTA to finish closes the call: new entry-barrier sequence, claim counter back to zero
+    if (!arrive_is_last(&ws->arrive[EP_CH_COMBINE][0])) return;
+    if (tid == 0) {
+        if (a.prof != nullptr) a.prof[3] = globaltimer_ns();
+        atomicExch(&ws->dyn_counter[EP_CH_COMBINE], 0u);
+        ws->comb_seq = entry_seq;
+        ws->epoch[EP_CH_COMBINE] += 1;
     }
 }
 
@@ -293,17 +333,10 @@ __global__ void __launch_bounds__(kCombineMaxWarps * 32, 1) combine_kernel_multi
     combine_body<kUnroll>(args[blockIdx.y]);
 }
 
-inline int env_int(const char* name, int fallback) {
-    const char* v = std::getenv(name);
-    return v != nullptr && *v != 0 ? std::atoi(v) : fallback;
-}
-
-// column chunk = 512 B x unroll; EP_COMBINE_UNROLL overrides the choice when the row divides evenly
+// column chunk = 512 B x unroll: larger chunks amortise the per-chunk bookkeeping: 3584 B when the row divides evenly
+// (hidden 7168), else 2048 B
 inline int pick_unroll(const CombineArgs& a) {
     const int row_bytes = a.hidden * 2;
-    const int forced = env_int("EP_COMBINE_UNROLL", 0);
-    if ((forced == 7 || forced == 4 || forced == 2 || forced == 1) && row_bytes % (512 * forced) == 0) return forced;
-    // larger chunks amortise the per-chunk bookkeeping: 3584 B when the row divides evenly (hidden 7168), else 2048 B
     if (row_bytes % 3584 == 0) return 7;
     return row_bytes % 2048 == 0 ? 4 : (row_bytes % 1024 == 0 ? 2 : (row_bytes >= 2048 ? 4 : 1));
 }
@@ -313,9 +346,7 @@ inline int pick_unroll(const CombineArgs& a) {
 LaunchShape combine_launch_shape(const CombineArgs& a, int num_sms) {
     LaunchShape s;
     s.num_ctas = num_sms < 1 ? 1 : (num_sms > EP_MAX_CTAS ? EP_MAX_CTAS : num_sms);
-    int warps = env_int("EP_COMBINE_WARPS", 12);
-    warps = warps < 1 ? 1 : (warps > kCombineMaxWarps ? kCombineMaxWarps : warps);
-    const CombineSmemPlan p = combine_smem_plan(512 * pick_unroll(a), warps);
+    const CombineSmemPlan p = combine_smem_plan(512 * pick_unroll(a), kCombineMaxWarps);
     s.num_warps = p.num_warps;
     s.smem_bytes = p.total;
     return s;
@@ -337,8 +368,10 @@ cudaError_t launch_combine(const CombineArgs* args, int n, int num_sms, cudaStre
     if (err != cudaSuccess) return err;
     dim3 grid(shape.num_ctas, n, 1), block(shape.num_warps * 32, 1, 1);
     if (n == 1) {
+        // no CTA waits on another CTA of its own rank, so a plain launch is enough (and can share the GPU with a
+        // compute kernel that is already running)
         void* params[] = {const_cast<CombineArgs*>(&a0)};
-        return cudaLaunchCooperativeKernel(fn, grid, block, params, shape.smem_bytes, stream);
+        return cudaLaunchKernel(fn, grid, block, params, shape.smem_bytes, stream);
     }
     CombineArgs* dev = nullptr;
     err = cudaMallocAsync(reinterpret_cast<void**>(&dev), sizeof(CombineArgs) * n, stream);

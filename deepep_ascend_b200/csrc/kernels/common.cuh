@@ -42,6 +42,13 @@ struct Workspace {
     alignas(128) uint32_t cta_expert_count[EP_MAX_CTAS][EP_MAX_EXPERTS];
     alignas(128) uint32_t ll_counters[4][EP_MAX_EXPERTS];                  // low-latency slot / finish counters
     alignas(128) uint32_t arrive[EP_NUM_CHANNELS][2];                      // CTAs that finished a phase (arrive_is_last)
+    // dispatch layout phase without grid barriers: accumulators of this rank's totals (the last CTA to add reads and
+    // clears them) and per-CTA progress words holding the low 32 bits of the dispatch epoch they belong to
+    alignas(128) uint32_t tot_rank[EP_MAX_RANKS];
+    alignas(128) uint32_t tot_expert[EP_MAX_EXPERTS];
+    alignas(128) uint32_t cta_counted[EP_MAX_CTAS];                        // per-CTA counts of that epoch are in cta_*_count
+    alignas(128) uint32_t cta_assigned[EP_MAX_CTAS];                       // row numbers of the CTA's tokens are in lane_src / plan
+    alignas(128) uint64_t comb_seq;                                        // combine calls completed (entry-barrier sequence)
 };
 static_assert(sizeof(Workspace) <= EP_WORKSPACE_BYTES, "workspace region too small");
 
@@ -176,6 +183,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(const RankCtx& ctx, Workspace*
     const bool ok = bounded_wait(
         ctx, ws, phase, -1, parity, [&] { return ptx::mbar_try_wait(bar, parity); }, [&] { return 0ull; });
     return __all_sync(0xffffffffu, ok) != 0;
+}
+
+// After a failure: give a bulk load that is still in flight time to land (it must not arrive in shared memory that
+// a later CTA owns), without looking at the abort flag.  Returns once the phase completed or `limit_ns` passed.
+__device__ __forceinline__ void mbar_drain(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
+    const uint64_t t0 = globaltimer_ns();
+    while (!ptx::mbar_try_wait(bar, parity)) {
+        if (globaltimer_ns() - t0 > limit_ns) break;
+    }
 }
 
 }  // namespace ep

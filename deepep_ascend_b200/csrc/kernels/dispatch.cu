@@ -1,23 +1,25 @@
-// Expert-parallel dispatch for one NVLink domain, as ONE kernel per call:
+// Expert-parallel dispatch for one NVLink domain, as ONE kernel per call with no grid-wide barrier inside:
 //
-//   1. layout   - every CTA counts, for its slice of tokens, the rows it will send to each rank (a token
-//                 counts once per rank) and the selections of each expert;
-//   2. exchange - CTA 0 publishes this rank's totals into every peer's workspace as epoch-tagged words and
-//                 every CTA waits for all ranks' totals (this is also the entry barrier: a peer's totals
-//                 arrive only once the peer has entered the same call);
-//   3. assign   - prefix sums turn the counts into FINAL row numbers in the receivers' output tensors, in
-//                 (source rank, token) order, so the result is deterministic and needs no second pass;
-//   4. scatter  - tokens are claimed dynamically by the warps of all CTAs; per token: optional fused bf16 -> e4m3
-//                 cast with 1x128 scales (register batches straight from global memory) or a TMA bulk load,
-//                 then one bulk store per destination rank straight into that rank's recv_x through its peer
-//                 mapping, plus ONE more bulk store of a packed side record (scales, global expert ids, weights,
-//                 source token);
-//   5. finish   - drain the bulk stores, grid barrier, CTA 0 tells every peer "my rows have arrived"; every CTA waits
-//                 for all peers' words itself and then rewrites its share of the received expert ids as local ids.
+//   1. count    - every CTA counts, for its slice of tokens, the rows it will send to each rank (a token counts once
+//                 per rank) and the selections of each expert, publishes its own counts (for the CTAs above it) and
+//                 adds them to this rank's totals with atomics;
+//   2. exchange - the last CTA to add publishes the totals into every peer's workspace as epoch-tagged words; every
+//                 CTA waits for all ranks' totals itself (this is also the entry barrier: a peer's totals arrive only
+//                 once the peer has entered the same call);
+//   3. assign   - prefix sums over (lower source ranks, lower CTAs, lower warps) turn the counts into FINAL row numbers in
+//                 the receivers' output tensors, in (source rank, token) order, so the result is deterministic and needs
+//                 no second pass; a CTA then flags its slice as assigned;
+//   4. scatter  - tokens are claimed dynamically by the warps of all CTAs (a claimer waits for the flag of the CTA that
+//                 owns the token); per token: optional fused bf16 -> e4m3 cast with 1x128 scales (register batches
+//                 straight from global memory) or a TMA bulk load, then per destination rank one bulk store of the row
+//                 straight into that rank's recv_x through its peer mapping, one of the scales and one of a tail record
+//                 (expert ids already relative to the receiver, weights, source token and sending lane);
+//   5. finish   - every CTA drains its bulk stores and arrives; the last one tells every peer "my rows have arrived",
+//                 waits for the peers' words and closes the call.  All other CTAs leave as soon as they are drained.
 //
 // Parity: does the work of dispatch_impl + dispatch_copy_epilogue_impl
-// (deep_ep/include/deep_ep/impls/dispatch.cuh:17-409, dispatch_copy_epilogue.cuh:11-323) and of the fused
-// FP8 cast of the legacy low-latency kernel (csrc/kernels/legacy/internode_ll.cu:212-250).
+// (deep_ep/include/deep_ep/impls/dispatch.cuh:17-409, dispatch_copy_epilogue.cuh:11-323, zero padding :231-322) and of
+// the fused FP8 cast of the legacy low-latency kernel (csrc/kernels/legacy/internode_ll.cu:212-250).
 #include <cstdlib>
 
 #include "common.cuh"
@@ -27,30 +29,37 @@ namespace ep {
 namespace {
 
 constexpr int kDispatchMaxWarps = 12;
-constexpr int kDispatchSmemBudget = 220 * 1024;
+constexpr int kDispatchMaxStages = 4;
+constexpr int kDispatchSmemBudget = 222 * 1024;
 
 struct DispatchSmemPlan {
     int off_peer;       // uint8_t* [EP_MAX_RANKS]
     int off_tot;        // uint32 [E]   expert totals over sources
-    int off_before;     // uint32 [E]   selections from lower source ranks
+    int off_before;     // uint32 [E]   selections from lower source ranks (and lower CTAs)
     int off_start;      // uint32 [E]   first row of each expert at its rank
     int off_prefix;     // uint32 [R]   rows of lower ranks / CTAs per destination
     int off_wc_rank;    // uint32 [W][R]
-    int off_wc_expert;  // uint32 [W][E]
+    int off_wc_expert;  // uint32 [W][E] (expand layout) or [E] shared by the CTA
     int off_bar;        // uint64 [W][3]
-    int off_sf;         // float  [W][2][G]
-    int off_side;       // bytes  [W][2][side_bytes] packed side records being sent
+    int off_sf;         // float  [W][n_side][sf_floats]
+    int off_tail;       // bytes  [W][n_side][max_dst][tail_bytes] tail records being sent
     int off_stage;      // per warp: stage buffers
+    int sf_floats, max_dst, n_side;
     int in_bytes, out_bytes, n_in, n_out, warp_stage_bytes;
     int total;
 };
 
 __host__ __device__ inline int align_int(int x, int a) { return (x + a - 1) / a * a; }
 
-__host__ __device__ inline DispatchSmemPlan make_smem_plan(const DispatchArgs& a, int num_warps) {
+__host__ __device__ inline DispatchSmemPlan make_smem_plan(const DispatchArgs& a, int num_warps, int num_stages) {
     DispatchSmemPlan p;
     const int E = a.num_experts, R = a.ctx.num_ranks;
     const int G = (a.hidden + 127) / 128;
+    p.sf_floats = align_int(G, 4);
+    p.max_dst = a.num_topk < R ? a.num_topk : R;
+    // staging buffers of the small pieces follow the payload stages: a buffer is reused once the bulk stores of the
+    // token that last used it have read their sources
+    p.n_side = a.quantize ? num_stages : 2;
     int off = 0;
     p.off_peer = off;       off += EP_MAX_RANKS * 8;
     p.off_tot = off;        off += align_int(E * 4, 16);
@@ -58,20 +67,20 @@ __host__ __device__ inline DispatchSmemPlan make_smem_plan(const DispatchArgs& a
     p.off_start = off;      off += align_int(E * 4, 16);
     p.off_prefix = off;     off += EP_MAX_RANKS * 4;
     p.off_wc_rank = off;    off += align_int(num_warps * R * 4, 16);
-    p.off_wc_expert = off;  off += align_int(num_warps * E * 4, 16);
+    p.off_wc_expert = off;  off += align_int((a.do_expand ? num_warps : 1) * E * 4, 16);
     p.off_bar = off;        off += align_int(num_warps * 3 * 8, 16);   // keeps everything behind it 16-byte aligned (bulk copy sources)
-    p.off_sf = off;         off += align_int(num_warps * 2 * G * 4, 16);
-    p.off_side = off;       off += a.side_packed ? num_warps * 2 * align_int(a.side_bytes, 16) : 0;
+    p.off_sf = off;         off += num_warps * p.n_side * p.sf_floats * 4;
+    p.off_tail = off;       off += a.side_packed ? num_warps * p.n_side * p.max_dst * a.tail_bytes : 0;
     off = align_int(off, 128);
     p.off_stage = off;
     const int in_row = a.hidden * (a.x_is_fp8 ? 1 : 2);
     p.in_bytes = align_int(in_row, 128);
     if (a.quantize) {
-        // the cast reads global memory directly; two output stages (the stores of token n-1 may still be
-        // reading while token n is cast)
+        // the cast reads global memory directly; `num_stages` output stages (the stores of earlier tokens may still be
+        // reading their stages while the next token is cast)
         p.out_bytes = align_int(a.hidden, 128);
         p.n_in = 0;
-        p.n_out = 2;
+        p.n_out = num_stages;
     } else {
         // the input stage is also the store source: three stages keep one load and one store in flight
         p.out_bytes = 0;
@@ -226,6 +235,16 @@ __device__ __forceinline__ void cast_batch(const RowBatch& b, uint8_t* out, floa
     }
 }
 
+// sources of all but the `pending` most recent bulk groups of this thread have been read
+__device__ __forceinline__ void bulk_wait_read_n(int pending) {
+    switch (pending) {
+        case 1: ptx::bulk_wait_read<1>(); break;
+        case 2: ptx::bulk_wait_read<2>(); break;
+        case 3: ptx::bulk_wait_read<3>(); break;
+        default: ptx::bulk_wait_read<0>(); break;
+    }
+}
+
 template <bool kQuant>
 __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -236,7 +255,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
     const int cta = blockIdx.x, num_ctas = gridDim.x;
     const int R = ctx.num_ranks, me = ctx.rank, E = a.num_experts, El = E / R, K = a.num_topk, T = a.num_tokens;
     const int G = (a.hidden + 127) / 128;
-    const DispatchSmemPlan sp = make_smem_plan(a, num_warps);
+    const DispatchSmemPlan sp = make_smem_plan(a, num_warps, a.tune_stages);
 
     uint8_t** s_peer = reinterpret_cast<uint8_t**>(smem + sp.off_peer);
     uint32_t* s_tot = reinterpret_cast<uint32_t*>(smem + sp.off_tot);
@@ -246,12 +265,15 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
     uint32_t* s_wc_rank = reinterpret_cast<uint32_t*>(smem + sp.off_wc_rank);
     uint32_t* s_wc_expert = reinterpret_cast<uint32_t*>(smem + sp.off_wc_expert);
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + sp.off_bar) + warp * 3;
-    float* s_sf = reinterpret_cast<float*>(smem + sp.off_sf) + warp * 2 * G;
-    uint8_t* s_side = smem + sp.off_side + warp * 2 * align_int(a.side_bytes, 16);
+    float* s_sf = reinterpret_cast<float*>(smem + sp.off_sf) + warp * sp.n_side * sp.sf_floats;
+    uint8_t* s_tail = smem + sp.off_tail + warp * sp.n_side * sp.max_dst * a.tail_bytes;
     uint8_t* s_stage = smem + sp.off_stage + warp * sp.warp_stage_bytes;
+    const int expert_sets = a.do_expand ? num_warps : 1;   // private expert counters per warp only where row order needs them
 
-    const uint64_t epoch = ws->epoch[EP_CH_DISPATCH] + 1;
-    if (cta == 0 && tid == 0) atomicExch(&ws->dyn_counter[EP_CH_DISPATCH], 0u);   // ordered before its first use by a grid barrier
+    // every CTA reads the call number before it arrives anywhere; the last CTA to finish writes the new one
+    const uint64_t epoch = *reinterpret_cast<volatile uint64_t*>(&ws->epoch[EP_CH_DISPATCH]) + 1;
+    const uint32_t epoch32 = static_cast<uint32_t>(epoch);
+    const uint64_t entry_seq = *reinterpret_cast<volatile uint64_t*>(&ws->bar_seq[EP_CH_DISPATCH]) + 1;
     if (tid < EP_MAX_RANKS) s_peer[tid] = tid < R ? ctx.peer_base[tid] : nullptr;
     if (lane == 0) {
         ptx::mbar_init(&s_bar[0], 1);
@@ -260,49 +282,57 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
     }
     ptx::mbar_fence_init();
     for (int i = tid; i < num_warps * R; i += nthreads) s_wc_rank[i] = 0;
-    for (int i = tid; i < num_warps * E; i += nthreads) s_wc_expert[i] = 0;
+    for (int i = tid; i < expert_sets * E; i += nthreads) s_wc_expert[i] = 0;
     __syncthreads();
     ptx::fence_proxy_async_smem();
 
     const Slice sl = warp_slice(T, K, num_warps, warp);
+    const int own_chunk = max(1, (T + num_ctas - 1) / num_ctas);
     bool alive = !is_aborted(ws);
     auto stamp = [&](int i) {
         if (a.prof != nullptr && cta == 0 && tid == 0) a.prof[i] = globaltimer_ns();
     };
     stamp(0);
+    const bool bookkeeper = cta == num_ctas - 1;   // writes what this rank receives (handle tensors, host counters); its tokens are claimed last
+    const bool need_experts = a.do_expand || bookkeeper;
 
     if (!a.cached) {
-        // ---------------------------------------------------------------- 1. layout (counts)
-        layout_pass<false>(a, sl, s_wc_rank + warp * R, s_wc_expert + warp * E);
+        // ---------------------------------------------------------------- 1. count
+        layout_pass<false>(a, sl, s_wc_rank + warp * R, s_wc_expert + (a.do_expand ? warp * E : 0));
         __syncthreads();
         for (int i = tid; i < E + R; i += nthreads) {
             uint32_t tot = 0;
             if (i < E) {
-                for (int w = 0; w < num_warps; ++w) tot += s_wc_expert[w * E + i];
-                __stcg(&ws->cta_expert_count[cta][i], tot);
+                for (int w = 0; w < expert_sets; ++w) tot += s_wc_expert[w * E + i];
+                if (a.do_expand) __stcg(&ws->cta_expert_count[cta][i], tot);
+                if (tot) atomicAdd(&ws->tot_expert[i], tot);
             } else {
                 for (int w = 0; w < num_warps; ++w) tot += s_wc_rank[w * R + (i - E)];
                 __stcg(&ws->cta_rank_count[cta][i - E], tot);
+                if (tot) atomicAdd(&ws->tot_rank[i - E], tot);
             }
         }
-        alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && alive;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) ptx::st_release_gpu_u32(&ws->cta_counted[cta], epoch32);
+        const bool last_to_count = arrive_is_last(&ws->arrive[EP_CH_DISPATCH][0]);
         stamp(1);
 
         // ---------------------------------------------------------------- 2. exchange
-        if (alive && cta == 0) {
+        if (last_to_count && alive) {
+            // every CTA of this rank has added its counts: publish the totals to all ranks (this rank included) and
+            // clear the accumulators for the next call
             for (int i = tid; i < E + R; i += nthreads) {
-                uint32_t tot = 0;
-                for (int c = 0; c < num_ctas; ++c)
-                    tot += i < E ? __ldcg(&ws->cta_expert_count[c][i]) : __ldcg(&ws->cta_rank_count[c][i - E]);
+                uint32_t* acc = i < E ? &ws->tot_expert[i] : &ws->tot_rank[i - E];
+                const uint32_t tot = __ldcg(acc);
+                __stcg(acc, 0u);
                 const uint64_t word = tag_value(epoch, tot);
                 for (int p = 0; p < R; ++p) {
                     Workspace* pws = reinterpret_cast<Workspace*>(s_peer[p]);
-                    ptx::st_relaxed_sys(i < E ? &pws->disp_expert_count[me][i] : &pws->disp_rank_count[me][i - E],
-                                        word);
+                    ptx::st_relaxed_sys(i < E ? &pws->disp_expert_count[me][i] : &pws->disp_rank_count[me][i - E], word);
                 }
             }
         }
-        const bool need_experts = a.do_expand || cta == 0;
         int ok = alive ? 1 : 0;
         if (alive) {
             for (int i = tid; i < R * R && ok; i += nthreads) {
@@ -311,6 +341,13 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                     ctx, ws, EP_PH_COUNT_EXCHANGE, i / R, epoch,
                     [&] { return tag_matches(ptx::ld_relaxed_sys(slot), epoch); },
                     [&] { return ptx::ld_relaxed_sys(slot); });
+            }
+            // counts of the CTAs below this one
+            for (int c = tid; c < cta && ok; c += nthreads) {
+                const uint32_t* flag = &ws->cta_counted[c];
+                ok = bounded_wait(
+                    ctx, ws, EP_PH_CTA_COUNTS, c, epoch32, [&] { return ptx::ld_acquire_gpu_u32(flag) == epoch32; },
+                    [&] { return static_cast<uint64_t>(ptx::ld_relaxed_gpu_u32(flag)); });
             }
             if (need_experts) {
                 for (int i = tid; i < R * E && ok; i += nthreads) {
@@ -394,7 +431,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                         }
                     }
                 }
-                if (cta == 0) {
+                if (bookkeeper) {
                     // what this rank receives: handle tensors + host-visible counters (each word carries its own
                     // epoch tag, so the host needs no ordering between them)
                     volatile uint64_t* st = ctx.status;
@@ -419,17 +456,52 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                 }
             }
             __syncthreads();
-            layout_pass<true>(a, sl, s_wc_rank + warp * R, s_wc_expert + warp * E);
+            layout_pass<true>(a, sl, s_wc_rank + warp * R, s_wc_expert + (a.do_expand ? warp * E : 0));
         }
-        // every row number is now in global memory: from here on any warp may send any token
-        alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && alive;
+        // the row numbers of this CTA's slice are in global memory: any warp of the rank may now send those tokens
+        __threadfence();
+        __syncthreads();
+        if (tid == 0 && alive) ptx::st_release_gpu_u32(&ws->cta_assigned[cta], epoch32);
     } else {
-        // cached layout: only the entry barrier (receivers must be done with the previous contents)
-        if (cta == 0) alive = xgpu_barrier(ctx, ws, EP_CH_DISPATCH, EP_PH_XGPU_BARRIER) && alive;
-        alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && alive;
+        // cached layout: only the entry barrier (receivers must be done with the previous contents); CTA 0 signals the
+        // peers, every CTA watches the peers' arrivals itself
+        int ok = alive ? 1 : 0;
+        if (alive && tid < R) {
+            if (cta == 0) ptx::red_add_release_sys(&reinterpret_cast<Workspace*>(s_peer[tid])->xbar[EP_CH_DISPATCH][me], 1ull);
+            const uint64_t* mine = &ws->xbar[EP_CH_DISPATCH][tid];
+            ok = bounded_wait(
+                ctx, ws, EP_PH_XGPU_BARRIER, tid, entry_seq, [&] { return ptx::ld_acquire_sys(mine) >= entry_seq; },
+                [&] { return ptx::ld_relaxed_sys(mine); });
+        }
+        alive = __syncthreads_and(ok) != 0;
+    }
+    stamp(3);
+
+    // -------------------------------------------------------------------- 3b. zero padding of the expand layout
+    if (alive && a.do_expand && a.do_zero_padding && a.expert_alignment > 1) {
+        // rows between the end of a local expert's segment and its aligned end are written by nobody: zero them here
+        // (payload and scales), one expert per warp
+        const uint32_t A = a.expert_alignment;
+        const int out_row = (kQuant || a.x_is_fp8) ? a.hidden : a.hidden * 2;
+        const bool has_sf = kQuant || a.sf != nullptr;
+        uint8_t* base = s_peer[me];
+        for (int j = cta * num_warps + warp; j < El; j += num_ctas * num_warps) {
+            uint32_t end;
+            if (a.cached) end = static_cast<uint32_t>(__ldcg(a.psum_expert + j));
+            else end = s_start[me * El + j] + s_tot[me * El + j];
+            uint32_t aligned_end = (end + A - 1) / A * A;
+            if (aligned_end > static_cast<uint32_t>(a.recv_capacity_rows)) aligned_end = a.recv_capacity_rows;
+            for (uint32_t row = end; row < aligned_end; ++row) {
+                uint8_t* dst = base + a.off_recv_x + static_cast<int64_t>(row) * out_row;
+                for (int off = lane * 16; off < out_row; off += 32 * 16) ptx::st_na_v4(dst + off, make_int4(0, 0, 0, 0));
+                if (has_sf) {
+                    float* sfp = reinterpret_cast<float*>(base + a.off_recv_sf);
+                    for (int g = lane; g < G; g += 32) sfp[static_cast<int64_t>(row) * a.sf_stride_row + g * a.sf_stride_col] = 0.f;
+                }
+            }
+        }
     }
 
-    stamp(3);
     // -------------------------------------------------------------------- 4. scatter
     if (alive) {
         const int in_row = a.hidden * (a.x_is_fp8 ? 1 : 2);
@@ -440,63 +512,101 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
         uint8_t* out_stage = s_stage + sp.n_in * sp.in_bytes;
         const uint8_t* xb = reinterpret_cast<const uint8_t*>(a.x);
         const int S_in = kQuant ? 1 : sp.n_in;
+        const int S_side = sp.n_side;
         const int num_batches = ((a.hidden + 255) / 256 + kCastSteps - 1) / kCastSteps;
-        // Tokens are claimed dynamically, two at a time, from a counter shared by all CTAs of this rank: SMs that get
-        // a smaller share of the NVLink bandwidth simply claim fewer tokens, so no CTA is left with a long tail.
-        constexpr int kClaim = 2;
-        auto claim = [&]() -> int {
+        const uint32_t lt = ptx::lanemask_lt();
+        // Tokens are claimed dynamically from a counter shared by all CTAs of this rank: SMs that get a smaller share of
+        // the NVLink bandwidth simply claim fewer tokens.  Two tokens per claim, one near the end so that no warp is
+        // left with a long tail.  The counter is zero at entry: the last CTA of every call clears it.
+        const int tail_zone = 4 * num_ctas * num_warps;
+        int last_base = 0;
+        auto claim = [&](int& amount) -> int {
+            amount = last_base + tail_zone < T ? 2 : 1;
             int b = 0;
-            if (lane == 0) b = static_cast<int>(atomicAdd(&ws->dyn_counter[EP_CH_DISPATCH], static_cast<uint32_t>(kClaim)));
-            return __shfl_sync(0xffffffffu, b, 0);
+            if (lane == 0) b = static_cast<int>(atomicAdd(&ws->dyn_counter[EP_CH_DISPATCH], static_cast<uint32_t>(amount)));
+            b = __shfl_sync(0xffffffffu, b, 0);
+            last_base = b;
+            return b;
         };
-        int chunk_base = claim(), next_base = claim(), in_chunk = 0;
+        int chunk_n = 0, next_n = 0;
+        int chunk_base = claim(chunk_n), next_base = claim(next_n), in_chunk = 0;
         auto next_token = [&]() -> int {
-            if (in_chunk == kClaim) {
+            if (in_chunk == chunk_n) {
                 chunk_base = next_base;
-                next_base = chunk_base < T ? claim() : T;
+                chunk_n = next_n;
+                if (chunk_base < T) next_base = claim(next_n);
+                else next_base = T, next_n = 1;
                 in_chunk = 0;
             }
             const int t = chunk_base + in_chunk++;
             return t < T ? t : -1;
         };
+        // row numbers of tokens outside this CTA's own slice were written by another CTA: wait for its flag once
+        int known_lo = a.cached ? 0 : cta * own_chunk, known_hi = a.cached ? T : min(T, known_lo + own_chunk);
+        auto rows_assigned = [&](int t) -> bool {
+            if (t >= known_lo && t < known_hi) return true;
+            const int owner = t / own_chunk;
+            int ok = 1;
+            if (lane == 0) {
+                const uint32_t* flag = &ws->cta_assigned[owner];
+                ok = bounded_wait(
+                    ctx, ws, EP_PH_DISPATCH_ASSIGN, owner, epoch32, [&] { return ptx::ld_acquire_gpu_u32(flag) == epoch32; },
+                    [&] { return static_cast<uint64_t>(ptx::ld_relaxed_gpu_u32(flag)); });
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            __syncwarp();
+            known_lo = owner * own_chunk;
+            known_hi = min(T, known_lo + own_chunk);
+            return ok != 0;
+        };
         int t = next_token(), t_next = next_token();
+        int loads_issued = 0, loads_waited = 0;   // bulk loads of the pass-through path (token i uses stage i % S_in)
         RowBatch cur;
         if (kQuant) {
             if (t >= 0) load_batch(cur, xb + static_cast<int64_t>(t) * in_row, a.hidden, 0);
-        } else if (t >= 0 && lane == 0) {
-            ptx::mbar_arrive_expect_tx(&s_bar[0], in_row);
-            ptx::bulk_load(in_stage, xb + static_cast<int64_t>(t) * in_row, in_row, &s_bar[0]);
+        } else if (t >= 0) {
+            if (lane == 0) {
+                ptx::mbar_arrive_expect_tx(&s_bar[0], in_row);
+                ptx::bulk_load(in_stage, xb + static_cast<int64_t>(t) * in_row, in_row, &s_bar[0]);
+            }
+            loads_issued = 1;
         }
         for (int n = 0; t >= 0 && alive; ++n, t = t_next, t_next = next_token()) {
             const int st = n % S_in;
             const uint32_t parity = (n / S_in) & 1;
+            // the staging buffers about to be overwritten were last read by the stores of token n - S_side
+            bulk_wait_read_n(S_side - 1);
+            __syncwarp();
             if (!kQuant) {
                 // prefetch the next token; its stage was the source of the bulk stores of token n-2
-                ptx::bulk_wait_read<1>();
-                __syncwarp();
-                if (t_next >= 0 && lane == 0) {
-                    const int ns = (n + 1) % S_in;
-                    ptx::mbar_arrive_expect_tx(&s_bar[ns], in_row);
-                    ptx::bulk_load(in_stage + ns * sp.in_bytes, xb + static_cast<int64_t>(t_next) * in_row, in_row, &s_bar[ns]);
+                if (t_next >= 0) {
+                    if (lane == 0) {
+                        const int ns = (n + 1) % S_in;
+                        ptx::mbar_arrive_expect_tx(&s_bar[ns], in_row);
+                        ptx::bulk_load(in_stage + ns * sp.in_bytes, xb + static_cast<int64_t>(t_next) * in_row, in_row, &s_bar[ns]);
+                    }
+                    ++loads_issued;
                 }
+            }
+            if (!rows_assigned(t)) {
+                alive = false;
+                break;
             }
             int e_k = -1, plan_k = -1;
             float w_k = 0.f;
             if (lane < K) {
                 e_k = load_idx(a, t, lane);
-                plan_k = a.plan[static_cast<int64_t>(t) * K + lane];
+                plan_k = __ldcg(a.plan + static_cast<int64_t>(t) * K + lane);
                 if (a.topk_weights != nullptr) w_k = __ldg(a.topk_weights + static_cast<int64_t>(t) * K + lane);
             }
-            uint8_t* side_cur = s_side + (n & 1) * align_int(a.side_bytes, 16);
-            float* sf_cur = a.side_packed ? reinterpret_cast<float*>(side_cur) : s_sf + (n & 1) * G;
+            const int side_slot = n % S_side;
+            float* sf_cur = s_sf + side_slot * sp.sf_floats;
+            uint8_t* tail_cur = s_tail + side_slot * sp.max_dst * a.tail_bytes;
             if (!kQuant && has_sf)
                 for (int j = lane; j < G; j += 32) sf_cur[j] = __ldg(a.sf + static_cast<int64_t>(t) * G + j);
             const uint8_t* src_smem;
             if (kQuant) {
-                // the out stage about to be overwritten was read by the stores of token n-2
-                ptx::bulk_wait_read<1>();
-                __syncwarp();
-                uint8_t* o = out_stage + (n & 1) * sp.out_bytes;
+                uint8_t* o = out_stage + side_slot * sp.out_bytes;
                 const uint8_t* row = xb + static_cast<int64_t>(t) * in_row;
                 for (int b = 0; b < num_batches; ++b) {
                     RowBatch nxt;
@@ -505,74 +615,89 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                     cast_batch(cur, o, sf_cur, a.hidden, b);
                     cur = nxt;
                 }
-                ptx::fence_proxy_async_smem();
-                __syncwarp();
                 src_smem = o;
             } else {
                 alive = mbar_wait_bounded(ctx, ws, &s_bar[st], parity, EP_PH_DISPATCH_LOAD);
                 if (!alive) break;
+                ++loads_waited;
                 src_smem = in_stage + st * sp.in_bytes;
-                __syncwarp();
             }
+            const uint32_t sends = __ballot_sync(0xffffffffu, plan_k >= 0);   // lanes that own a destination row
             if (a.side_packed) {
-                // the side record is the same for every destination: scales (already in place), GLOBAL expert ids,
-                // weights and the source token id; the receiver localises the ids after the final barrier
-                if (lane < K) {
-                    if (a.idx_is_64) reinterpret_cast<long long*>(side_cur + a.side_off_idx)[lane] = e_k;
-                    else reinterpret_cast<int*>(side_cur + a.side_off_idx)[lane] = e_k;
-                    reinterpret_cast<float*>(side_cur + a.side_off_w)[lane] = w_k;
+                // one tail record per destination: expert ids relative to THAT rank's first expert (-1 for experts of
+                // other ranks), the weights, the source token and the lane that sends the row
+                int j = 0;
+                for (uint32_t m = sends; m != 0; m &= m - 1, ++j) {
+                    const int k = __ffs(m) - 1;
+                    const int d = __shfl_sync(0xffffffffu, plan_k, k) >> 24;
+                    uint8_t* rec = tail_cur + j * a.tail_bytes;
+                    if (lane < K) {
+                        const int lo = d * El;
+                        const int local = (e_k >= lo && e_k < lo + El) ? e_k - lo : -1;
+                        if (a.idx_is_64) reinterpret_cast<long long*>(rec)[lane] = local;
+                        else reinterpret_cast<int*>(rec)[lane] = local;
+                        reinterpret_cast<float*>(rec + a.tail_off_w)[lane] = w_k;
+                    }
+                    if (lane == 0) *reinterpret_cast<int2*>(rec + a.tail_off_meta) = make_int2(me * a.num_max_tokens + t, me * K + k);
                 }
-                if (lane == 0) *reinterpret_cast<int2*>(side_cur + a.side_off_meta) = make_int2(me * a.num_max_tokens + t, 0);
-                ptx::fence_proxy_async_smem();
-                __syncwarp();
             }
-            // one bulk store per destination row (two with a side record), issued by the lane that owns the plan entry
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            // bulk stores of a destination row are issued by the lane that owns the plan entry
             if (plan_k >= 0) {
                 const int d = plan_k >> 24, row = plan_k & 0xffffff;
                 if (row < a.recv_capacity_rows) {
-                    ptx::bulk_store(s_peer[d] + a.off_recv_x + static_cast<int64_t>(row) * out_row, src_smem, out_row);
-                    if (a.side_packed)
-                        ptx::bulk_store(s_peer[d] + a.off_recv_side + static_cast<int64_t>(row) * a.side_bytes, side_cur, a.side_bytes);
+                    uint8_t* base = s_peer[d];
+                    ptx::bulk_store(base + a.off_recv_x + static_cast<int64_t>(row) * out_row, src_smem, out_row);
+                    if (a.side_packed) {
+                        if (has_sf) ptx::bulk_store(base + a.off_recv_sf + static_cast<int64_t>(row) * G * 4, sf_cur, G * 4);
+                        const int j = __popc(sends & lt);
+                        ptx::bulk_store(base + a.off_recv_tail + static_cast<int64_t>(row) * a.tail_bytes, tail_cur + j * a.tail_bytes, a.tail_bytes);
+                    }
                 } else {
                     report_failure(ctx, ws, EP_ERR_BOUNDS, EP_PH_DISPATCH_LOAD, d, a.recv_capacity_rows, row);
                     plan_k = -1;
                 }
             }
             ptx::bulk_commit();
-            // small per-row pieces go out as plain peer stores
-            uint32_t sends = __ballot_sync(0xffffffffu, plan_k >= 0);
-            if (a.skip_side_stores || a.side_packed) sends = 0;
-            while (sends) {
-                const int k = __ffs(sends) - 1;
-                sends &= sends - 1;
-                const int p = __shfl_sync(0xffffffffu, plan_k, k);
-                const int d = p >> 24;
-                const int64_t row = p & 0xffffff;
-                uint8_t* base = s_peer[d];
-                if (has_sf) {
-                    float* dst = reinterpret_cast<float*>(base + a.off_recv_sf);
-                    for (int j = lane; j < G; j += 32) dst[row * a.sf_stride_row + j * a.sf_stride_col] = sf_cur[j];
-                }
-                if (a.do_expand) {
-                    const float w = __shfl_sync(0xffffffffu, w_k, k);
-                    if (lane == 0) {
-                        if (a.topk_weights != nullptr) reinterpret_cast<float*>(base + a.off_recv_w)[row] = w;
-                        reinterpret_cast<int2*>(base + a.off_recv_meta)[row] = make_int2(me * a.num_max_tokens + t, me * K + k);
+            if (!a.side_packed) {
+                // small per-row pieces go out as plain peer stores
+                uint32_t m = __ballot_sync(0xffffffffu, plan_k >= 0);
+                while (m) {
+                    const int k = __ffs(m) - 1;
+                    m &= m - 1;
+                    const int p = __shfl_sync(0xffffffffu, plan_k, k);
+                    const int d = p >> 24;
+                    const int64_t row = p & 0xffffff;
+                    uint8_t* base = s_peer[d];
+                    if (has_sf) {
+                        float* dst = reinterpret_cast<float*>(base + a.off_recv_sf);
+                        for (int j = lane; j < G; j += 32) dst[row * a.sf_stride_row + j * a.sf_stride_col] = sf_cur[j];
                     }
-                } else {
-                    if (lane < K) {
-                        const int lo = d * El;
-                        const int local = (e_k >= lo && e_k < lo + El) ? e_k - lo : -1;
-                        uint8_t* ip = base + a.off_recv_idx + (row * K + lane) * idx_bytes;
-                        if (a.idx_is_64) *reinterpret_cast<long long*>(ip) = local;
-                        else *reinterpret_cast<int*>(ip) = local;
-                        if (a.topk_weights != nullptr) reinterpret_cast<float*>(base + a.off_recv_w)[row * K + lane] = w_k;
+                    if (a.do_expand) {
+                        const float w = __shfl_sync(0xffffffffu, w_k, k);
+                        if (lane == 0) {
+                            if (a.topk_weights != nullptr) reinterpret_cast<float*>(base + a.off_recv_w)[row] = w;
+                            reinterpret_cast<int2*>(base + a.off_recv_meta)[row] = make_int2(me * a.num_max_tokens + t, me * K + k);
+                        }
+                    } else {
+                        if (lane < K) {
+                            const int lo = d * El;
+                            const int local = (e_k >= lo && e_k < lo + El) ? e_k - lo : -1;
+                            uint8_t* ip = base + a.off_recv_idx + (row * K + lane) * idx_bytes;
+                            if (a.idx_is_64) *reinterpret_cast<long long*>(ip) = local;
+                            else *reinterpret_cast<int*>(ip) = local;
+                            if (a.topk_weights != nullptr) reinterpret_cast<float*>(base + a.off_recv_w)[row * K + lane] = w_k;
+                        }
+                        if (lane == 0)
+                            reinterpret_cast<int2*>(base + a.off_recv_meta)[row] = make_int2(me * a.num_max_tokens + t, me * K + k);
                     }
-                    if (lane == 0)
-                        reinterpret_cast<int2*>(base + a.off_recv_meta)[row] = make_int2(me * a.num_max_tokens + t, me * K + k);
                 }
             }
         }
+        // left early after a failure: loads still in flight must land before this CTA gives up its shared memory
+        for (; loads_waited < loads_issued; ++loads_waited)
+            mbar_drain(&s_bar[loads_waited % S_in], (loads_waited / S_in) & 1, 1000ull * 1000 * 1000);
     }
 
     // ------------------------------------------------------------------------ 5. finish
@@ -580,19 +705,19 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
     ptx::bulk_wait<0>();
     __threadfence_system();
     stamp(4);
-    const bool cta_ok = __syncthreads_and(alive ? 1 : 0) != 0;
-    alive = grid_sync(ctx, ws, EP_CH_DISPATCH, EP_PH_GRID_SYNC) && cta_ok;
-    stamp(5);
-    // Completion: after the grid barrier every store of this rank has been drained, so CTA 0 tells every peer
-    // "all rows of my dispatch number `epoch` have arrived"; then EVERY CTA waits for all peers' words itself (no
-    // second grid barrier) before it touches received data.
-    if (cta == 0 && alive && tid < R) {
-        Workspace* pws = reinterpret_cast<Workspace*>(s_peer[tid]);
-        ptx::st_release_sys(&pws->disp_done[me], epoch);
-    }
+    // Every CTA arrives once its own stores are complete; only the last one stays: it tells every peer "all rows of my
+    // dispatch number `epoch` have arrived", waits for the same word from every peer (the kernel must not end before
+    // this rank's received rows are in place) and closes the call.
+    if (!arrive_is_last(&ws->arrive[EP_CH_DISPATCH][1])) return;
+    auto stamp_last = [&](int i) {
+        if (a.prof != nullptr && tid == 0) a.prof[i] = globaltimer_ns();
+    };
+    stamp_last(5);
+    alive = !is_aborted(ws);
     {
         int ok = alive ? 1 : 0;
         if (alive && tid < R) {
+            ptx::st_release_sys(&reinterpret_cast<Workspace*>(s_peer[tid])->disp_done[me], epoch);
             const uint64_t* word = &ws->disp_done[tid];
             ok = bounded_wait(
                 ctx, ws, EP_PH_DISPATCH_DONE, tid, epoch, [&] { return ptx::ld_acquire_sys(word) >= epoch; },
@@ -600,56 +725,13 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
         }
         alive = __syncthreads_and(ok) != 0;
     }
-    stamp(6);
-    if (a.side_packed && alive) {
-        // every row has arrived: turn the global expert ids of the received side records into ids relative to this
-        // rank's first expert (-1 for experts of other ranks) and fill in source rank * K + the lane that sent the row.
-        // One lane per (row, top-k lane), so the ids of a row are read and written as one contiguous run; four rows'
-        // worth of loads are in flight per lane before the first store.
-        const int num_recv = __ldcg(a.psum_rank + (R - 1));
-        const int lo = me * El;
-        const int grp = K <= 8 ? 8 : 16, rows_per_step = 32 / grp;
-        const int sub = lane / grp, k = lane - sub * grp;
-        const uint32_t grp_mask = (grp == 8 ? 0xffu : 0xffffu) << (sub * grp);
-        constexpr int kBatch = 4;
-        const int stride = num_ctas * num_warps * rows_per_step;
-        for (int row0 = (cta * num_warps + warp) * rows_per_step; row0 < num_recv; row0 += kBatch * stride) {
-            long long gidx[kBatch];
-            int2 meta[kBatch];
-#pragma unroll
-            for (int b = 0; b < kBatch; ++b) {
-                const int row = row0 + b * stride + sub;
-                gidx[b] = -1;
-                if (row < num_recv) {
-                    const uint8_t* rec = s_peer[me] + a.off_recv_side + static_cast<int64_t>(row) * a.side_bytes;
-                    if (k < K)
-                        gidx[b] = a.idx_is_64 ? __ldcg(reinterpret_cast<const long long*>(rec + a.side_off_idx) + k)
-                                              : static_cast<long long>(__ldcg(reinterpret_cast<const int*>(rec + a.side_off_idx) + k));
-                    if (k == 0) meta[b] = __ldcg(reinterpret_cast<const int2*>(rec + a.side_off_meta));
-                }
-            }
-#pragma unroll
-            for (int b = 0; b < kBatch; ++b) {
-                const int row = row0 + b * stride + sub;
-                const bool mine = gidx[b] >= lo && gidx[b] < lo + El;
-                const uint32_t hits = __ballot_sync(0xffffffffu, mine) & grp_mask;
-                if (row < num_recv) {
-                    uint8_t* rec = s_peer[me] + a.off_recv_side + static_cast<int64_t>(row) * a.side_bytes;
-                    if (k < K) {
-                        const long long local = mine ? gidx[b] - lo : -1;
-                        if (a.idx_is_64) reinterpret_cast<long long*>(rec + a.side_off_idx)[k] = local;
-                        else reinterpret_cast<int*>(rec + a.side_off_idx)[k] = static_cast<int>(local);
-                    }
-                    if (k == 0) {
-                        const int master = hits ? (31 - __clz(hits)) - sub * grp : 0;
-                        *reinterpret_cast<int2*>(rec + a.side_off_meta) = make_int2(meta[b].x, (meta[b].x / a.num_max_tokens) * K + master);
-                    }
-                }
-            }
-        }
+    stamp_last(6);
+    if (tid == 0) {
+        atomicExch(&ws->dyn_counter[EP_CH_DISPATCH], 0u);
+        if (a.cached) ws->bar_seq[EP_CH_DISPATCH] = entry_seq;
+        ws->epoch[EP_CH_DISPATCH] = epoch;
     }
-    stamp(7);
-    if (cta == 0 && tid == 0) ws->epoch[EP_CH_DISPATCH] = epoch;
+    stamp_last(7);
 }
 
 template <bool kQuant>
@@ -668,26 +750,33 @@ __global__ void __launch_bounds__(kDispatchMaxWarps * 32, 1) dispatch_kernel_mul
 LaunchShape dispatch_launch_shape(const DispatchArgs& a, int num_sms) {
     LaunchShape s;
     s.num_ctas = num_sms < 1 ? 1 : (num_sms > EP_MAX_CTAS ? EP_MAX_CTAS : num_sms);
-    // as many warps (each with its own staging ring) as fit in shared memory; the token-per-step layout
-    // needs at least one warp
-    const char* forced = std::getenv("EP_DISPATCH_WARPS");
-    s.num_warps = kDispatchMaxWarps;
-    if (forced != nullptr && std::atoi(forced) >= 1 && std::atoi(forced) <= kDispatchMaxWarps) s.num_warps = std::atoi(forced);
-    while (s.num_warps > 1 && make_smem_plan(a, s.num_warps).total > kDispatchSmemBudget) --s.num_warps;
-    s.smem_bytes = make_smem_plan(a, s.num_warps).total;
+    // staging buffers per warp of the fused-cast path (two unless the caller asks for more), then as many warps (each
+    // with its own staging ring) as fit in shared memory; the token-per-step layout needs at least one warp
+    s.num_stages = a.tune_stages >= 2 && a.tune_stages <= kDispatchMaxStages ? a.tune_stages : 2;
+    s.num_warps = a.tune_warps >= 1 && a.tune_warps <= kDispatchMaxWarps ? a.tune_warps : kDispatchMaxWarps;
+    while (s.num_warps > 1 && make_smem_plan(a, s.num_warps, s.num_stages).total > kDispatchSmemBudget) --s.num_warps;
+    s.smem_bytes = make_smem_plan(a, s.num_warps, s.num_stages).total;
     return s;
 }
 
-cudaError_t launch_dispatch(const DispatchArgs* args, int n, int num_sms, cudaStream_t stream) {
+cudaError_t launch_dispatch(const DispatchArgs* args_in, int n, int num_sms, cudaStream_t stream) {
+    const LaunchShape shape = dispatch_launch_shape(args_in[0], num_sms);
+    if (shape.smem_bytes > 227 * 1024 || n < 1 || n > EP_MAX_RANKS) return cudaErrorInvalidValue;
+    // the kernel derives its shared-memory plan from the resolved shape
+    DispatchArgs args[EP_MAX_RANKS];
+    for (int i = 0; i < n; ++i) {
+        args[i] = args_in[i];
+        args[i].tune_warps = shape.num_warps;
+        args[i].tune_stages = shape.num_stages;
+    }
     const DispatchArgs& a0 = args[0];
-    const LaunchShape shape = dispatch_launch_shape(a0, num_sms);
-    if (shape.smem_bytes > 227 * 1024) return cudaErrorInvalidValue;
     const void* fn;
     if (n == 1) fn = a0.quantize ? (const void*)dispatch_kernel<true> : (const void*)dispatch_kernel<false>;
     else fn = a0.quantize ? (const void*)dispatch_kernel_multi<true> : (const void*)dispatch_kernel_multi<false>;
     cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, shape.smem_bytes);
     if (err != cudaSuccess) return err;
     dim3 grid(shape.num_ctas, n, 1), block(shape.num_warps * 32, 1, 1);
+    // cooperative: the CTAs of a rank (and of all virtual ranks) wait on one another, so they must be co-resident
     if (n == 1) {
         void* params[] = {const_cast<DispatchArgs*>(&a0)};
         return cudaLaunchCooperativeKernel(fn, grid, block, params, shape.smem_bytes, stream);

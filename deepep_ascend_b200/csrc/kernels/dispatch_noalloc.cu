@@ -21,7 +21,6 @@ static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
 
 std::mutex g_mu;
 unsigned char* g_scratch_addr[kMaxDevices] = {};   // per device, filled on the first call with that device current
-uint64_t g_calls[kMaxDevices] = {};
 
 int fail(char* err, int err_len, const char* msg, cudaError_t e = cudaSuccess) {
     if (err != nullptr && err_len > 0) {
@@ -48,15 +47,21 @@ extern "C" int ep_dispatch_one_rank_noalloc(const void* x, const void* topk_idx,
         recv_src_meta == nullptr || lane_src == nullptr || plan == nullptr || psum_rank == nullptr || psum_expert == nullptr ||
         recv_per_expert == nullptr || (quantize && recv_sf == nullptr))
         return fail(err, err_len, "a required buffer is null");
-    if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || reinterpret_cast<uintptr_t>(recv_x) % 16 != 0)
-        return fail(err, err_len, "x and recv_x must be 16-byte aligned");
+    // a misaligned pointer would fault on the GPU instead of returning an error, so every alignment the kernel relies
+    // on is checked here: 16 bytes for the rows (bulk copies), 8 for 64-bit ids and the int2 metadata, 4 for the rest
+    auto misaligned = [](const void* p, uintptr_t a) { return p != nullptr && reinterpret_cast<uintptr_t>(p) % a != 0; };
+    if (misaligned(x, 16) || misaligned(recv_x, 16)) return fail(err, err_len, "x and recv_x must be 16-byte aligned");
+    if (misaligned(topk_idx, 8) || misaligned(recv_topk_idx, 8) || misaligned(recv_src_meta, 8))
+        return fail(err, err_len, "topk_idx, recv_topk_idx and recv_src_meta must be 8-byte aligned");
+    if (misaligned(topk_weights, 4) || misaligned(recv_sf, 4) || misaligned(recv_topk_weights, 4) || misaligned(lane_src, 4) ||
+        misaligned(plan, 4) || misaligned(psum_rank, 4) || misaligned(psum_expert, 4) || misaligned(recv_per_expert, 4))
+        return fail(err, err_len, "fp32 and int32 buffers must be 4-byte aligned");
 
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return fail(err, err_len, "cudaGetDevice", e);
     if (device < 0 || device >= kMaxDevices) return fail(err, err_len, "device index beyond 63");
     unsigned char* base = nullptr;
-    uint64_t call_index = 0;
     {
         std::lock_guard<std::mutex> lock(g_mu);
         if (g_scratch_addr[device] == nullptr) {
@@ -67,14 +72,24 @@ extern "C" int ep_dispatch_one_rank_noalloc(const void* x, const void* topk_idx,
             g_scratch_addr[device] = static_cast<unsigned char*>(p);
         }
         base = g_scratch_addr[device];
-        call_index = ++g_calls[device];
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // what must start at zero: the abort flag of the workspace and the status words (a failure of an earlier call
-    // must not leak into this one).  Epochs, barrier generations and tagged counters carry over by design.
-    e = cudaMemsetAsync(base + offsetof(ep::Workspace, abort_flag), 0, sizeof(uint32_t), s);
-    if (e == cudaSuccess) e = cudaMemsetAsync(base + kWorkspaceBytes, 0, 8 * sizeof(uint64_t), s);
-    if (e != cudaSuccess) return fail(err, err_len, "cudaMemsetAsync(scratch flags)", e);
+    // What must start at zero: the abort flag, the status words, and everything a call that gave up half way may have
+    // left behind (token claim counter, CTA arrival counters, count accumulators), so that a failure of an earlier call
+    // cannot leak into this one.  Epochs and epoch-tagged words carry over by design.
+    struct Span { size_t off, bytes; };
+    const Span spans[] = {
+        {offsetof(ep::Workspace, abort_flag), sizeof(uint32_t)},
+        {offsetof(ep::Workspace, dyn_counter) + EP_CH_DISPATCH * sizeof(uint32_t), sizeof(uint32_t)},
+        {offsetof(ep::Workspace, arrive) + EP_CH_DISPATCH * 2 * sizeof(uint32_t), 2 * sizeof(uint32_t)},
+        {offsetof(ep::Workspace, tot_rank), sizeof(uint32_t) * EP_MAX_RANKS},
+        {offsetof(ep::Workspace, tot_expert), sizeof(uint32_t) * EP_MAX_EXPERTS},
+        {kWorkspaceBytes, 8 * sizeof(uint64_t)},
+    };
+    for (const Span& sp : spans) {
+        e = cudaMemsetAsync(base + sp.off, 0, sp.bytes, s);
+        if (e != cudaSuccess) return fail(err, err_len, "cudaMemsetAsync(scratch flags)", e);
+    }
 
     DispatchArgs a;
     std::memset(&a, 0, sizeof(a));
@@ -109,8 +124,29 @@ extern "C" int ep_dispatch_one_rank_noalloc(const void* x, const void* topk_idx,
     a.sf_stride_row = (hidden + 127) / 128;
     a.sf_stride_col = 1;
     a.recv_capacity_rows = num_tokens > 0 ? num_tokens : 1;
-    (void)call_index;
     e = ep::launch_dispatch(&a, 1, num_sms, s);
     if (e != cudaSuccess) return fail(err, err_len, "dispatch launch", e);
+    return 0;
+}
+
+extern "C" int ep_noalloc_last_status(unsigned long long out[6], void* stream, char* err, int err_len) {
+    if (out == nullptr) return fail(err, err_len, "out is null");
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return fail(err, err_len, "cudaGetDevice", e);
+    if (device < 0 || device >= kMaxDevices) return fail(err, err_len, "device index beyond 63");
+    unsigned char* base = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        base = g_scratch_addr[device];
+    }
+    if (base == nullptr) {   // no dispatch has run on this device yet: nothing to report
+        for (int i = 0; i < 6; ++i) out[i] = 0;
+        return 0;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    e = cudaMemcpyAsync(out, base + kWorkspaceBytes, 6 * sizeof(uint64_t), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return fail(err, err_len, "reading the status words", e);
     return 0;
 }

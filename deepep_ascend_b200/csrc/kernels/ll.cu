@@ -102,6 +102,16 @@ __device__ __forceinline__ int find_segment(const uint32_t* pref, int n, uint32_
     return lo;
 }
 
+// Shrink mode: wait for a tagged word until the time limit; like every other wait it also gives up when the buffer has
+// been aborted.  Returns whether the word arrived; running out of time is not an error here (the caller masks the rank).
+__device__ __forceinline__ bool shrink_wait(const RankCtx& ctx, Workspace* ws, const uint64_t* sig, uint64_t epoch, uint64_t t0) {
+    uint32_t spins = 0;
+    while (!tag_matches(ptx::ld_acquire_sys(sig), epoch)) {
+        if ((++spins & 31u) == 0u && (is_aborted(ws) || globaltimer_ns() - t0 > ctx.timeout_ns)) return false;
+    }
+    return true;
+}
+
 __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const RankCtx& ctx = a.ctx;
@@ -218,11 +228,9 @@ __device__ __forceinline__ void ll_dispatch_body(const LLDispatchArgs& a) {
                 const uint64_t t0 = globaltimer_ns();
                 if (a.shrink) {
                     // shrink mode: a source that stays silent is masked out instead of failing the call
-                    bool got = false;
-                    while (!(got = tag_matches(ptx::ld_acquire_sys(sig), epoch)))
-                        if (globaltimer_ns() - t0 > ctx.timeout_ns) break;
-                    if (!got) atomicExch(a.mask + src, 1);
-                    else n_recv = count_low32(ptx::ld_relaxed_sys(sig));
+                    const bool got = shrink_wait(ctx, ws, sig, epoch, t0);
+                    if (!got && !is_aborted(ws)) atomicExch(a.mask + src, 1);
+                    if (got) n_recv = count_low32(ptx::ld_relaxed_sys(sig));
                 } else {
                     const int got = bounded_wait(
                         ctx, ws, EP_PH_LL_RECV_COUNT, src, epoch, [&] { return tag_matches(ptx::ld_acquire_sys(sig), epoch); },
@@ -405,10 +413,7 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
             const uint64_t* sig = &ws->ll_signal[1][tid];
             const uint64_t t0 = globaltimer_ns();
             if (a.shrink) {
-                bool got = false;
-                while (!(got = tag_matches(ptx::ld_acquire_sys(sig), epoch)))
-                    if (globaltimer_ns() - t0 > ctx.timeout_ns) break;
-                if (!got) atomicExch(a.mask + tid, 1);
+                if (!shrink_wait(ctx, ws, sig, epoch, t0) && !is_aborted(ws)) atomicExch(a.mask + tid, 1);
             } else {
                 ok = bounded_wait(
                     ctx, ws, EP_PH_LL_COMBINE_FLAG, tid, epoch, [&] { return tag_matches(ptx::ld_acquire_sys(sig), epoch); },
@@ -479,12 +484,23 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
 }
 
 __global__ void __launch_bounds__(kLLThreads, 1) ll_dispatch_kernel(const __grid_constant__ LLDispatchArgs a) { ll_dispatch_body(a); }
-__global__ void __launch_bounds__(kLLThreads, 1) ll_dispatch_kernel_multi(const LLDispatchArgs* a) { ll_dispatch_body(a[blockIdx.y]); }
+// n virtual ranks on one device: the argument structs travel as ONE kernel parameter (no allocation, no copy), which
+// keeps the launch capturable in a CUDA graph
+template <typename Args>
+struct MultiArgs {
+    Args a[EP_MAX_RANKS];
+};
+__global__ void __launch_bounds__(kLLThreads, 1) ll_dispatch_kernel_multi(const __grid_constant__ MultiArgs<LLDispatchArgs> m) { ll_dispatch_body(m.a[blockIdx.y]); }
 __global__ void __launch_bounds__(kLLThreads, 1) ll_combine_kernel(const __grid_constant__ LLCombineArgs a) { ll_combine_body(a); }
-__global__ void __launch_bounds__(kLLThreads, 1) ll_combine_kernel_multi(const LLCombineArgs* a) { ll_combine_body(a[blockIdx.y]); }
+__global__ void __launch_bounds__(kLLThreads, 1) ll_combine_kernel_multi(const __grid_constant__ MultiArgs<LLCombineArgs> m) { ll_combine_body(m.a[blockIdx.y]); }
 
 template <typename Args>
 cudaError_t launch_ll(const void* single, const void* multi, const Args* args, int n, int num_sms, int smem, cudaStream_t stream) {
+    // A launch that both sends and receives must have all its CTAs resident: the counts a CTA waits for are published by
+    // the LAST CTA of the peer to finish sending, which may be one that only starts when a waiting CTA leaves.  The
+    // halves of the hook mode have no such dependency (the send half waits for nothing, the receive half only for peers'
+    // send halves), so they are plain launches that can share the GPU with a compute kernel.
+    const bool both_phases = (args[0].phases & (EP_LL_SEND | EP_LL_RECV)) == (EP_LL_SEND | EP_LL_RECV);
     const void* fn = n == 1 ? single : multi;
     cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (err != cudaSuccess) return err;
@@ -492,18 +508,15 @@ cudaError_t launch_ll(const void* single, const void* multi, const Args* args, i
     dim3 grid(ctas, n, 1), block(kLLThreads, 1, 1);
     if (n == 1) {
         void* params[] = {const_cast<Args*>(args)};
-        return cudaLaunchCooperativeKernel(fn, grid, block, params, smem, stream);
+        if (both_phases) return cudaLaunchCooperativeKernel(fn, grid, block, params, smem, stream);
+        return cudaLaunchKernel(fn, grid, block, params, smem, stream);
     }
-    Args* dev = nullptr;
-    err = cudaMallocAsync(reinterpret_cast<void**>(&dev), sizeof(Args) * n, stream);
-    if (err != cudaSuccess) return err;
-    err = cudaMemcpyAsync(dev, args, sizeof(Args) * n, cudaMemcpyHostToDevice, stream);
-    if (err == cudaSuccess) {
-        void* params[] = {&dev};
-        err = cudaLaunchCooperativeKernel(fn, grid, block, params, smem, stream);
-    }
-    cudaFreeAsync(dev, stream);
-    return err;
+    if (n > EP_MAX_RANKS) return cudaErrorInvalidValue;
+    MultiArgs<Args> multi_args;
+    for (int i = 0; i < n; ++i) multi_args.a[i] = args[i];
+    void* params[] = {&multi_args};
+    // the virtual ranks wait on one another: all their CTAs must be resident
+    return cudaLaunchCooperativeKernel(fn, grid, block, params, smem, stream);
 }
 
 }  // namespace

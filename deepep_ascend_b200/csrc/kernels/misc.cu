@@ -128,7 +128,8 @@ __global__ void quant_kernel(const QuantArgs a) {
 }
 
 // Engram fetch: one warp per requested entry; the entry is pulled from its owner's storage (TMA bulk load through
-// the peer mapping, no multicast) into shared memory and bulk-stored into the local output row.
+// the peer mapping, or from the owner's CPU segment, no multicast) into shared memory and bulk-stored into the local
+// output row.  Parity: deep_ep/include/deep_ep/impls/engram_fetch.cuh:46-82 (payload get + local scale gather).
 __device__ __forceinline__ void engram_fetch_body(const EngramFetchArgs& a) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const RankCtx& ctx = a.ctx;
@@ -159,8 +160,14 @@ __device__ __forceinline__ void engram_fetch_body(const EngramFetchArgs& a) {
         }
         if (lane == 0) {
             ptx::mbar_arrive_expect_tx(&bars[st], a.entry_bytes);
-            ptx::bulk_load(stage + st * stage_bytes,
-                           ctx.peer_base[owner] + a.off_storage + static_cast<int64_t>(local) * a.entry_bytes, a.entry_bytes, &bars[st]);
+            ptx::bulk_load(stage + st * stage_bytes, a.storage[owner] + static_cast<int64_t>(local) * a.entry_bytes, a.entry_bytes, &bars[st]);
+        }
+        if (a.sf_table != nullptr) {
+            // the scales of the entry come from the local copy of the replicated table while the payload is in flight
+            const int token = i / a.entries_per_token, entry = i - token * a.entries_per_token;
+            for (int p = lane; p < a.sf_packs; p += 32)
+                a.fetched_sf[token * a.sf_token_stride + static_cast<int64_t>(entry * a.sf_packs + p) * a.sf_pack_stride] =
+                    __ldg(a.sf_table + static_cast<int64_t>(id) * a.sf_packs + p);
         }
         alive = mbar_wait_bounded(ctx, ws, &bars[st], (n >> 1) & 1, EP_PH_COMBINE_LOAD);
         if (!alive) break;

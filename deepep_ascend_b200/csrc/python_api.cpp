@@ -8,10 +8,6 @@
 #include "runtime/layout.hpp"
 #include "runtime/low_latency.hpp"
 
-#include <execinfo.h>
-#include <signal.h>
-#include <unistd.h>
-
 namespace py = pybind11;
 using namespace ep_host;
 
@@ -334,15 +330,6 @@ at::Tensor dequant_transpose(const at::Tensor& q, const at::Tensor& sf, const at
     return out_t;
 }
 
-// Debug aid: print the native call stack when the process receives SIGSEGV, then re-raise.
-void segv_backtrace_handler(int sig) {
-    void* frames[64];
-    const int n = backtrace(frames, 64);
-    backtrace_symbols_fd(frames, n, STDERR_FILENO);
-    signal(sig, SIG_DFL);
-    raise(sig);
-}
-
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -373,19 +360,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readonly("idx", &RecvSlot::idx)
         .def_readonly("w", &RecvSlot::w)
         .def_readonly("meta", &RecvSlot::meta)
-        .def_readonly("side", &RecvSlot::side);
+        .def_readonly("tail", &RecvSlot::tail);
     py::class_<RegionLayout>(m, "RegionLayout")
         .def_readonly("capacity_rows", &RegionLayout::capacity_rows)
         .def_readonly("x_row_bytes", &RegionLayout::x_row_bytes)
         .def_readonly("sf_cols", &RegionLayout::sf_cols)
-        .def_readonly("side_bytes", &RegionLayout::side_bytes)
+        .def_readonly("tail_bytes", &RegionLayout::tail_bytes)
         .def_readonly("num_recv_slots", &RegionLayout::num_recv_slots)
         .def("slot", [](const RegionLayout& r, int i) {
             TORCH_CHECK(i >= 0 && i < r.num_recv_slots, "slot index out of range");
             return r.slots[i];
         })
-        .def_readonly("combine_x", &RegionLayout::combine_x)
-        .def_readonly("combine_w", &RegionLayout::combine_w)
+        .def("combine_x", [](const RegionLayout& r, int i) { return r.combine_x[i & 1]; })
+        .def("combine_w", [](const RegionLayout& r, int i) { return r.combine_w[i & 1]; })
         .def_readonly("extra", &RegionLayout::extra)
         .def_readonly("moe_bytes", &RegionLayout::moe_bytes);
     m.def("plan_regions", &plan_regions);
@@ -418,13 +405,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("sf_stride_col", &DispatchCall::sf_stride_col)
         .def_readwrite("recv_capacity_rows", &DispatchCall::recv_capacity_rows)
         .def_readwrite("prof", &DispatchCall::prof)
-        .def_readwrite("skip_side_stores", &DispatchCall::skip_side_stores)
         .def_readwrite("side_packed", &DispatchCall::side_packed)
-        .def_readwrite("side_bytes", &DispatchCall::side_bytes)
-        .def_readwrite("side_off_idx", &DispatchCall::side_off_idx)
-        .def_readwrite("side_off_w", &DispatchCall::side_off_w)
-        .def_readwrite("side_off_meta", &DispatchCall::side_off_meta)
-        .def_readwrite("off_recv_side", &DispatchCall::off_recv_side);
+        .def_readwrite("tail_bytes", &DispatchCall::tail_bytes)
+        .def_readwrite("tail_off_w", &DispatchCall::tail_off_w)
+        .def_readwrite("tail_off_meta", &DispatchCall::tail_off_meta)
+        .def_readwrite("off_recv_tail", &DispatchCall::off_recv_tail)
+        .def_readwrite("do_zero_padding", &DispatchCall::do_zero_padding)
+        .def_readwrite("tune_warps", &DispatchCall::tune_warps)
+        .def_readwrite("tune_stages", &DispatchCall::tune_stages);
     py::class_<CombineCall>(m, "CombineCall")
         .def(py::init<>())
         .def_readwrite("off_x", &CombineCall::off_x)
@@ -441,8 +429,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("prof", &CombineCall::prof);
 
     py::class_<ElasticBufferCore>(m, "ElasticBuffer")
-        .def(py::init<int, int, int64_t, double, double>(), py::arg("rank"), py::arg("num_ranks"), py::arg("num_bytes"),
-             py::arg("gpu_timeout_secs") = 100.0, py::arg("cpu_timeout_secs") = 300.0)
+        .def(py::init<int, int, int64_t, double, double, int64_t>(), py::arg("rank"), py::arg("num_ranks"), py::arg("num_bytes"),
+             py::arg("gpu_timeout_secs") = 100.0, py::arg("cpu_timeout_secs") = 300.0, py::arg("num_cpu_bytes") = 0)
+        .def("num_cpu_bytes", &ElasticBufferCore::num_cpu_bytes)
+        .def("get_local_cpu_segment_name", &ElasticBufferCore::get_local_cpu_segment_name)
+        .def("open_cpu_peers", &ElasticBufferCore::open_cpu_peers)
+        .def("unlink_cpu_segment_name", &ElasticBufferCore::unlink_cpu_segment_name)
+        .def("cpu_segment_write", &ElasticBufferCore::cpu_segment_write)
         .def("get_local_ipc_handle", &ElasticBufferCore::get_local_ipc_handle)
         .def("open_peers", [](ElasticBufferCore& b, const std::vector<py::bytes>& handles) {
             std::vector<std::string> hs;
@@ -546,7 +539,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("weighted_transpose", &weighted_transpose);
     m.def("dequant_transpose", &dequant_transpose);
     m.def("gemm_error", [](int device) { return gemm_error_flag(device).item<int>(); });
-    m.def("install_segv_backtrace", [] { signal(SIGSEGV, segv_backtrace_handler); });
     m.def("get_dispatch_layout", &get_dispatch_layout);
     m.def("per_token_cast_to_fp8", &per_token_cast_to_fp8, py::arg("x"), py::arg("round_scale") = false,
           py::arg("use_ue8m0") = false);

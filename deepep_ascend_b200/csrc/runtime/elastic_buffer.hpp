@@ -43,10 +43,11 @@ struct DispatchCall {
     int64_t off_recv_x = 0, off_recv_sf = 0, off_recv_idx = 0, off_recv_w = 0, off_recv_meta = 0;
     int64_t sf_stride_row = 0, sf_stride_col = 1;
     int64_t recv_capacity_rows = 0;
-    OptTensor prof;               // int64 [8]: phase timestamps of CTA 0 (profiling)
-    bool skip_side_stores = false;
-    bool side_packed = false;
-    int64_t side_bytes = 0, side_off_idx = 0, side_off_w = 0, side_off_meta = 0, off_recv_side = 0;
+    OptTensor prof;               // int64 [8]: phase timestamps (profiling)
+    bool side_packed = false;     // scales and a tail record {ids | weights | metadata} travel as bulk stores
+    int64_t tail_bytes = 0, tail_off_w = 0, tail_off_meta = 0, off_recv_tail = 0;
+    bool do_zero_padding = false;
+    int64_t tune_warps = 0, tune_stages = 0;
 };
 
 struct CombineCall {
@@ -63,8 +64,9 @@ struct CombineCall {
 
 class ElasticBufferCore {
 public:
-    ElasticBufferCore(int rank, int num_ranks, int64_t num_bytes, double gpu_timeout_secs, double cpu_timeout_secs)
-        : mem_(std::make_unique<SymmetricMemory>(rank, num_ranks, num_bytes)),
+    ElasticBufferCore(int rank, int num_ranks, int64_t num_bytes, double gpu_timeout_secs, double cpu_timeout_secs,
+                      int64_t num_cpu_bytes = 0)
+        : mem_(std::make_unique<SymmetricMemory>(rank, num_ranks, num_bytes, num_cpu_bytes)),
           gpu_timeout_ns_(static_cast<uint64_t>(gpu_timeout_secs * 1e9)),
           cpu_timeout_secs_(cpu_timeout_secs) {}
 
@@ -239,26 +241,72 @@ public:
                    "peer cudaMemcpyAsync");
     }
 
-    // Engram: pull `indices.numel()` entries of `entry_bytes` from their owners' storage regions into `out`.
+    // ------------------------------------------------------------------ CPU segment
+    int64_t num_cpu_bytes() const { return mem_->cpu_bytes(); }
+    std::string get_local_cpu_segment_name() const { return mem_->export_cpu_name(); }
+    void open_cpu_peers(const std::vector<std::string>& names) { mem_->open_cpu_peers(names); }
+    void unlink_cpu_segment_name() { mem_->unlink_cpu_name(); }
+    // stream-ordered copy of a contiguous device tensor into this rank's CPU segment at `offset`
+    void cpu_segment_write(int64_t offset, const at::Tensor& src) {
+        TORCH_CHECK(mem_->cpu_segment_host() != nullptr, "the buffer was built without a CPU segment (num_cpu_bytes = 0)");
+        TORCH_CHECK(src.is_cuda() && src.is_contiguous(), "src must be a contiguous CUDA tensor");
+        const int64_t bytes = src.numel() * src.element_size();
+        TORCH_CHECK(offset >= 0 && offset + bytes <= mem_->cpu_bytes(), "write outside the CPU segment");
+        if (bytes == 0) return;
+        cuda_check(cudaMemcpyAsync(mem_->cpu_segment_host() + offset, src.data_ptr(), static_cast<size_t>(bytes), cudaMemcpyDefault,
+                                   at::cuda::getCurrentCUDAStream()),
+                   "cudaMemcpyAsync(device -> CPU segment)");
+    }
+
+    // Engram: pull `indices.numel()` entries of `entry_bytes` from their owners' tables into `out`.  The tables live at
+    // `off_storage` of every rank's symmetric buffer, or, with `in_cpu_segment`, at that offset of every rank's CPU
+    // segment.  `sf_table` (replicated scale packs of all entries) is gathered locally into `fetched_sf`.
     static void engram_fetch_group(const std::vector<ElasticBufferCore*>& group, const std::vector<at::Tensor>& indices,
                                    const std::vector<at::Tensor>& outs, int64_t entries_per_rank, int64_t entry_bytes,
-                                   int64_t off_storage, int num_sms) {
+                                   int64_t off_storage, bool in_cpu_segment, const std::vector<at::Tensor>& sf_tables,
+                                   const std::vector<at::Tensor>& fetched_sfs, int64_t entries_per_token, int num_sms) {
         std::vector<EngramFetchArgs> args(group.size());
+        TORCH_CHECK(sf_tables.empty() || (sf_tables.size() == group.size() && fetched_sfs.size() == group.size()),
+                    "one scale table and one output per buffer");
         for (size_t i = 0; i < group.size(); ++i) {
             group[i]->check_status();
             const at::Tensor& idx = indices[i];
             TORCH_CHECK(idx.is_cuda() && idx.is_contiguous() && idx.scalar_type() == at::kInt, "indices must be contiguous int32");
             TORCH_CHECK(outs[i].is_contiguous() && outs[i].numel() * outs[i].element_size() == idx.numel() * entry_bytes,
                         "output has the wrong size");
-            group[i]->check_region(off_storage, entries_per_rank * entry_bytes, "engram storage");
             EngramFetchArgs a{};
             a.ctx = group[i]->ctx();
+            const int R = a.ctx.num_ranks;
+            if (in_cpu_segment) {
+                TORCH_CHECK(off_storage >= 0 && off_storage % 16 == 0 && off_storage + entries_per_rank * entry_bytes <= group[i]->num_cpu_bytes(),
+                            "engram storage does not fit the CPU segment");
+                for (int r = 0; r < R; ++r) {
+                    TORCH_CHECK(group[i]->mem_->cpu_segment(r) != nullptr, "the CPU segment of rank ", r, " is not mapped");
+                    a.storage[r] = group[i]->mem_->cpu_segment(r) + off_storage;
+                }
+            } else {
+                group[i]->check_region(off_storage, entries_per_rank * entry_bytes, "engram storage");
+                for (int r = 0; r < R; ++r) a.storage[r] = a.ctx.peer_base[r] + off_storage;
+            }
             a.indices = idx.data_ptr<int32_t>();
             a.num_fetches = static_cast<int>(idx.numel());
             a.entries_per_rank = static_cast<int>(entries_per_rank);
             a.entry_bytes = static_cast<int>(entry_bytes);
-            a.off_storage = off_storage;
             a.out = outs[i].data_ptr();
+            a.entries_per_token = static_cast<int>(entries_per_token > 0 ? entries_per_token : 1);
+            if (!sf_tables.empty()) {
+                const at::Tensor& tab = sf_tables[i];
+                const at::Tensor& fsf = fetched_sfs[i];
+                TORCH_CHECK(tab.is_cuda() && tab.is_contiguous() && tab.dim() == 2 && tab.element_size() == 4 &&
+                                tab.size(0) == entries_per_rank * R, "the scale table must be contiguous [all entries, packs] of 4-byte packs");
+                TORCH_CHECK(fsf.is_cuda() && fsf.dim() == 2 && fsf.element_size() == 4 && fsf.size(0) * a.entries_per_token == idx.numel() &&
+                                fsf.size(1) == a.entries_per_token * tab.size(1), "fetched scales must be [tokens, entries per token * packs]");
+                a.sf_table = reinterpret_cast<const int32_t*>(tab.data_ptr());
+                a.fetched_sf = reinterpret_cast<int32_t*>(fsf.data_ptr());
+                a.sf_packs = static_cast<int>(tab.size(1));
+                a.sf_token_stride = fsf.stride(0);
+                a.sf_pack_stride = fsf.stride(1);
+            }
             args[i] = a;
         }
         cuda_check(ep::launch_engram_fetch(args.data(), static_cast<int>(args.size()), num_sms, at::cuda::getCurrentCUDAStream()),
@@ -363,20 +411,24 @@ private:
             TORCH_CHECK(c.prof->scalar_type() == at::kLong && c.prof->numel() >= 8 && c.prof->is_cuda(), "prof must be int64 [8] on the GPU");
             a.prof = reinterpret_cast<uint64_t*>(c.prof->data_ptr<int64_t>());
         }
-        a.skip_side_stores = c.skip_side_stores;
+        a.do_zero_padding = c.do_zero_padding;
+        TORCH_CHECK(!c.do_zero_padding || c.do_expand, "zero padding needs the expand layout");
+        a.tune_warps = static_cast<int>(c.tune_warps);
+        a.tune_stages = static_cast<int>(c.tune_stages);
         if (c.side_packed) {
-            TORCH_CHECK(!c.do_expand && c.sf_stride_col == 1, "packed side records need the non-expand layout and row-major scales");
-            TORCH_CHECK(c.side_bytes % 16 == 0 && c.side_off_idx % 8 == 0 && c.side_off_w % 4 == 0 && c.side_off_meta % 8 == 0 &&
-                            c.side_off_idx >= ((c.quantize || fp8) ? G * 4 : 0) && c.side_off_w >= c.side_off_idx + K * (a.idx_is_64 ? 8 : 4) &&
-                            c.side_off_meta >= c.side_off_w + K * 4 && c.side_bytes >= c.side_off_meta + 8,
-                        "inconsistent side record layout");
-            check_region(c.off_recv_side, cap * c.side_bytes, "recv side records");
+            const int64_t idx_bytes = K * (a.idx_is_64 ? 8 : 4);
+            TORCH_CHECK(!c.do_expand && c.sf_stride_col == 1, "bulk side stores need the non-expand layout and row-major scales");
+            TORCH_CHECK(!(c.quantize || fp8) || (c.sf_stride_row == G && (G * 4) % 16 == 0),
+                        "bulk side stores need contiguous scale rows that are a multiple of 16 bytes");
+            TORCH_CHECK(c.tail_bytes % 16 == 0 && c.tail_off_w % 4 == 0 && c.tail_off_meta % 8 == 0 && c.tail_off_w >= idx_bytes &&
+                            c.tail_off_meta >= c.tail_off_w + K * 4 && c.tail_bytes >= c.tail_off_meta + 8,
+                        "inconsistent tail record layout");
+            check_region(c.off_recv_tail, cap * c.tail_bytes, "recv tail records");
             a.side_packed = 1;
-            a.side_bytes = static_cast<int>(c.side_bytes);
-            a.side_off_idx = static_cast<int>(c.side_off_idx);
-            a.side_off_w = static_cast<int>(c.side_off_w);
-            a.side_off_meta = static_cast<int>(c.side_off_meta);
-            a.off_recv_side = c.off_recv_side;
+            a.tail_bytes = static_cast<int>(c.tail_bytes);
+            a.tail_off_w = static_cast<int>(c.tail_off_w);
+            a.tail_off_meta = static_cast<int>(c.tail_off_meta);
+            a.off_recv_tail = c.off_recv_tail;
         }
         return a;
     }

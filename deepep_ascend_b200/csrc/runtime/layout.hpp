@@ -1,10 +1,13 @@
 // Overflow-checked placement of every region inside a symmetric buffer.  All ranks compute the same offsets
 // from the same arguments, which is what lets a sender address a peer's tensors directly.
 //
-//   [ workspace | recv slot 0 | recv slot 1 | ... | combine input | extra (AG/RS, PP, Engram, LL) ]
+//   [ workspace | recv slot 0 | recv slot 1 | ... | combine input 0 | combine input 1 | extra (AG/RS, PP, Engram, LL) ]
 //
 // A recv slot holds the final output tensors of one dispatch: x rows, scales, localised expert ids, weights
-// and per-row source metadata.  Plain C++17, host-testable.
+// and per-row source metadata.  There are two combine input regions, used alternately: peers may still be pulling
+// from the one of call n while the rows of call n + 1 are written, and the entry barrier of call n + 1 (which no
+// rank passes before all ranks have finished call n) is what frees the region of call n, so combine needs no exit
+// barrier.  Plain C++17, host-testable.
 // Parity: the sizing rules of csrc/elastic/buffer.hpp:588-688 and the checked layout of the reference's NPU
 // backend (csrc/backends/ascend/elastic/layout.hpp:218-299).
 #pragma once
@@ -41,17 +44,17 @@ struct MoeShape {
 
 struct RecvSlot {
     int64_t x = 0, sf = 0, idx = 0, w = 0, meta = 0;
-    int64_t side = 0;   // packed per-row side records {scales | expert ids | weights | source metadata}
+    int64_t tail = 0;   // per-row tail records {local expert ids | weights | source metadata} of the bulk side stores
 };
 
 struct RegionLayout {
     int64_t capacity_rows = 0;     // rows a rank can receive in one dispatch
     int64_t x_row_bytes = 0;       // widest row dispatch may write (bf16 unless fp8-only)
     int64_t sf_cols = 0;
-    int64_t side_bytes = 0;        // bytes of one packed side record (multiple of 16)
+    int64_t tail_bytes = 0;        // bytes of one tail record (multiple of 16)
     int num_recv_slots = 0;
     RecvSlot slots[4];
-    int64_t combine_x = 0, combine_w = 0;
+    int64_t combine_x[2] = {0, 0}, combine_w[2] = {0, 0};
     int64_t extra = 0;             // first byte after the MoE regions
     int64_t moe_bytes = 0;         // workspace + MoE regions, aligned to EP_BUFFER_ALIGNMENT
 };
@@ -76,7 +79,7 @@ inline RegionLayout plan_regions(const MoeShape& s) {
     r.capacity_rows = recv_capacity_rows(s);
     r.x_row_bytes = s.use_fp8_dispatch ? s.hidden : checked_mul(s.hidden, 2);
     r.sf_cols = (s.hidden + 127) / 128;
-    r.side_bytes = align_up(r.sf_cols * 4 + static_cast<int64_t>(s.num_topk) * 12 + 8, 16);
+    r.tail_bytes = align_up(static_cast<int64_t>(s.num_topk) * 12 + 8, 16);
     r.num_recv_slots = s.num_recv_slots;
     const int64_t A = 1024;
     int64_t off = EP_WORKSPACE_BYTES;
@@ -86,10 +89,12 @@ inline RegionLayout plan_regions(const MoeShape& s) {
         r.slots[i].idx = off;  off = align_up(checked_add(off, checked_mul(r.capacity_rows, s.num_topk * 8)), A);
         r.slots[i].w = off;    off = align_up(checked_add(off, checked_mul(r.capacity_rows, s.num_topk * 4)), A);
         r.slots[i].meta = off; off = align_up(checked_add(off, checked_mul(r.capacity_rows, 8)), A);
-        r.slots[i].side = off; off = align_up(checked_add(off, checked_mul(r.capacity_rows, r.side_bytes)), A);
+        r.slots[i].tail = off; off = align_up(checked_add(off, checked_mul(r.capacity_rows, r.tail_bytes)), A);
     }
-    r.combine_x = off; off = align_up(checked_add(off, checked_mul(r.capacity_rows, checked_mul(s.hidden, 2))), A);
-    r.combine_w = off; off = align_up(checked_add(off, checked_mul(r.capacity_rows, s.num_topk * 4)), A);
+    for (int i = 0; i < 2; ++i) {
+        r.combine_x[i] = off; off = align_up(checked_add(off, checked_mul(r.capacity_rows, checked_mul(s.hidden, 2))), A);
+        r.combine_w[i] = off; off = align_up(checked_add(off, checked_mul(r.capacity_rows, s.num_topk * 4)), A);
+    }
     r.extra = off;
     r.moe_bytes = align_up(off, EP_BUFFER_ALIGNMENT);
     return r;

@@ -158,10 +158,11 @@ def localize_topk_idx(topk_idx: torch.Tensor, dst_rank: int, num_experts: int, n
 
 
 def combine_ref(rows_of, plan: torch.Tensor, hidden: int, bias0: Optional[torch.Tensor] = None,
-                bias1: Optional[torch.Tensor] = None, weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+                bias1: Optional[torch.Tensor] = None, weights: Optional[torch.Tensor] = None,
+                out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """fp32 reference of combine: start from ``bias0 + bias1`` (fp32), add the row of every non-negative
-    plan entry in lane order (times ``weights[t, k]`` when given), round once to bf16.
-    ``rows_of(rank) -> [rows, hidden]`` bf16 tensor of that rank's combine input."""
+    plan entry in lane order (times ``weights[t, k]`` when given), round once to ``out_dtype`` (bf16 on the GPU).
+    ``rows_of(rank) -> [rows, hidden]`` tensor of that rank's combine input."""
     T, K = plan.shape
     acc = torch.zeros(T, hidden, dtype=torch.float32)
     if bias0 is not None:
@@ -178,4 +179,4 @@ def combine_ref(rows_of, plan: torch.Tensor, hidden: int, bias0: Optional[torch.
             if weights is not None:
                 contrib = contrib * weights[m, k].float().cpu().unsqueeze(1)
             acc[m] += contrib
-    return acc.to(torch.bfloat16)
+    return acc.to(out_dtype)

@@ -82,20 +82,22 @@ static void test_layout() {
     const RegionLayout r = plan_regions(s);
     CHECK(r.capacity_rows == 8 * 8192);
     CHECK(r.x_row_bytes == 7168 && r.sf_cols == 56);
-    CHECK(r.side_bytes % 16 == 0 && r.side_bytes >= 56 * 4 + 8 * 12 + 8);
+    CHECK(r.tail_bytes % 16 == 0 && r.tail_bytes >= 8 * 12 + 8);
     // regions are ordered, aligned, disjoint and inside the buffer
     int64_t prev_end = EP_WORKSPACE_BYTES;
     for (int i = 0; i < 2; ++i) {
-        const int64_t offs[] = {r.slots[i].x, r.slots[i].sf, r.slots[i].idx, r.slots[i].w, r.slots[i].meta, r.slots[i].side};
+        const int64_t offs[] = {r.slots[i].x, r.slots[i].sf, r.slots[i].idx, r.slots[i].w, r.slots[i].meta, r.slots[i].tail};
         const int64_t sizes[] = {r.capacity_rows * r.x_row_bytes, r.capacity_rows * 56 * 4, r.capacity_rows * 64, r.capacity_rows * 32,
-                                 r.capacity_rows * 8, r.capacity_rows * r.side_bytes};
+                                 r.capacity_rows * 8, r.capacity_rows * r.tail_bytes};
         for (int k = 0; k < 6; ++k) {
             CHECK(offs[k] % 1024 == 0 && offs[k] >= prev_end);
             prev_end = offs[k] + sizes[k];
         }
     }
-    CHECK(r.combine_x >= prev_end && r.combine_w >= r.combine_x + r.capacity_rows * 7168 * 2);
-    CHECK(r.extra >= r.combine_w && r.moe_bytes >= r.extra && r.moe_bytes % EP_BUFFER_ALIGNMENT == 0);
+    // two combine input regions (alternate calls), each followed by its weight rows
+    CHECK(r.combine_x[0] >= prev_end && r.combine_w[0] >= r.combine_x[0] + r.capacity_rows * 7168 * 2);
+    CHECK(r.combine_x[1] >= r.combine_w[0] + r.capacity_rows * 8 * 4 && r.combine_w[1] >= r.combine_x[1] + r.capacity_rows * 7168 * 2);
+    CHECK(r.extra >= r.combine_w[1] + r.capacity_rows * 8 * 4 && r.moe_bytes >= r.extra && r.moe_bytes % EP_BUFFER_ALIGNMENT == 0);
     // bf16 buffers are wider, expand buffers hold more rows
     MoeShape b = s;
     b.use_fp8_dispatch = false;

@@ -53,6 +53,11 @@ def test_noalloc_dispatch_matches_elastic_buffer(quantize):
                 t.view(torch.uint8).fill_(0xEE)
             _call(lib, x, idx, w, E, quantize, outs)
             torch.cuda.synchronize()
+            # the kernel's own verdict is readable without any allocation either
+            status = (ctypes.c_ulonglong * 6)(*([7] * 6))
+            err = ctypes.create_string_buffer(256)
+            assert lib.ep_noalloc_last_status(status, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), err, 256) == 0
+            assert list(status) == [0, 0, 0, 0, 0, 0], list(status)
             ref_x, ref_idx, ref_w, handle, _ = buf.dispatch(x, idx, w, num_experts=E, num_sms=8)
             torch.cuda.synchronize()
             n = handle.num_recv_tokens
@@ -83,3 +88,9 @@ def test_noalloc_rejects_sizes_beyond_the_builtin_array():
     assert rc != 0 and b'num_experts' in err.value
     rc = lib.ep_dispatch_one_rank_noalloc(p, p, p, 4, 128, 2, 8, 0, p, p, p, p, p, p, p, p, p, p, 1000, None, err, 256)
     assert rc != 0 and b'num_sms' in err.value
+    # misaligned pointers are refused on the host (nothing is launched): 4-byte aligned ids, 2-byte aligned weights
+    p4, p2 = ctypes.c_void_p(t.data_ptr() + 4), ctypes.c_void_p(t.data_ptr() + 2)
+    rc = lib.ep_dispatch_one_rank_noalloc(p, p4, p, 4, 128, 2, 8, 0, p, p, p, p, p, p, p, p, p, p, 8, None, err, 256)
+    assert rc != 0 and b'8-byte aligned' in err.value
+    rc = lib.ep_dispatch_one_rank_noalloc(p, p, p2, 4, 128, 2, 8, 0, p, p, p, p, p, p, p, p, p, p, 8, None, err, 256)
+    assert rc != 0 and b'4-byte aligned' in err.value
