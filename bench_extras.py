@@ -102,26 +102,35 @@ def main():
         disp(64)()
         torch.cuda.synchronize()
         rows = float(st['h'].psum_num_recv_tokens_per_scaleup_rank[-1])
+        buf.enable_kernel_timing(True)
+
+        def kernel_ms(name, fn, iters=args.iters):
+            """median over steps of the per-step maximum over ranks of the kernel's own events"""
+            buf.kernel_times_ms(name)
+            timeit(fn, buf, iters=iters)
+            return float(np.median(reduce_max(buf.kernel_times_ms(name)[-iters:])))
         for sms in (24, 64):
-            t = np.median(timeit(disp(sms), buf))
-            emit(bench='dispatch', num_sms=sms, ms=float(t), gbs=rows * 7488 / t / 1e6)
+            for warps, stages in ((0, 0), (8, 3), (6, 4)):
+                buf.set_dispatch_tuning(warps, stages)
+                t = kernel_ms('dispatch', disp(sms))
+                emit(bench='dispatch', num_sms=sms, warps=warps or 12, stages=stages or 2, ms=t, gbs=rows * 7488 / t / 1e6)
+            buf.set_dispatch_tuning(0, 0)
             buf.enable_profiling(True)
-            disp(sms)()
-            buf.combine(buf.get_combine_buffer(st['h']), st['h'], num_sms=sms)
-            emit(bench='phase_times_us', num_sms=sms, **buf.phase_times())
-            os.environ['EP_PROFILE_SKIP_SIDE_STORES'] = '1'
-            t2 = np.median(timeit(disp(sms), buf))
-            os.environ['EP_PROFILE_SKIP_SIDE_STORES'] = '0'
+            for _ in range(3):
+                if world > 1:
+                    buf.barrier(use_comm_stream=False)
+                disp(sms)()
+                buf.combine(buf.get_combine_buffer(st['h']), st['h'], num_sms=sms)
+                emit(bench='phase_times_us', num_sms=sms, **buf.phase_times())
             buf.enable_profiling(False)
-            emit(bench='dispatch_without_side_stores', num_sms=sms, ms=float(t2), gbs=rows * 7488 / t2 / 1e6)
             h0 = st['h']
-            t3 = np.median(timeit(lambda: buf.dispatch(x, handle=h0, topk_weights=w, num_sms=sms), buf))
-            emit(bench='dispatch_cached_layout', num_sms=sms, ms=float(t3), gbs=rows * 7488 / t3 / 1e6)
+            t3 = kernel_ms('dispatch', lambda: buf.dispatch(x, handle=h0, topk_weights=w, num_sms=sms))
+            emit(bench='dispatch_cached_layout', num_sms=sms, ms=t3, gbs=rows * 7488 / t3 / 1e6)
             q = buf._C.per_token_cast_to_fp8(x, False, False)
-            t4 = np.median(timeit(lambda: buf.dispatch((q[0], q[1]), idx, w, num_experts=E, num_sms=sms, do_cpu_sync=False), buf))
-            emit(bench='dispatch_prequantized_fp8', num_sms=sms, ms=float(t4), gbs=rows * 7488 / t4 / 1e6)
-            t5 = np.median(timeit(lambda: buf.combine(buf.get_combine_buffer(st['h']), st['h'], num_sms=sms), buf))
-            emit(bench='combine', num_sms=sms, ms=float(t5), gbs=rows * 14368 / t5 / 1e6)
+            t4 = kernel_ms('dispatch', lambda: buf.dispatch((q[0], q[1]), idx, w, num_experts=E, num_sms=sms, do_cpu_sync=False))
+            emit(bench='dispatch_prequantized_fp8', num_sms=sms, ms=t4, gbs=rows * 7488 / t4 / 1e6)
+            t5 = kernel_ms('combine', lambda: buf.combine(buf.get_combine_buffer(st['h']), st['h'], num_sms=sms))
+            emit(bench='combine', num_sms=sms, ms=t5, gbs=rows * 14336 / t5 / 1e6)
         buf.destroy()
 
     # ------------------------------------------------------------------ NCCL all_to_all_single baseline (same bytes)

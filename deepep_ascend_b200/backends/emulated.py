@@ -86,9 +86,10 @@ class EmulatedWorld:
             outs.append(((c.packed_x, sf) if use_fp8 else c.packed_x, c.packed_count, handle))
         return outs
 
-    def low_latency_combine(self, xs, topk_idxs, topk_weights, handles, num_sms: int = 0, split_phases: bool = False):
+    def low_latency_combine(self, xs, topk_idxs, topk_weights, handles, num_sms: int = 0, split_phases: bool = False,
+                            use_logfmt: bool = False):
         num_sms = min(num_sms or 8, self.max_sms_per_rank())
-        calls = [b._ll_prepare_combine(xs[r], topk_idxs[r], topk_weights[r], handles[r], None, None, 3)
+        calls = [b._ll_prepare_combine(xs[r], topk_idxs[r], topk_weights[r], handles[r], None, None, 3, use_logfmt)
                  for r, b in enumerate(self.buffers)]
         for phases in ((1, 2) if split_phases else (3,)):
             for c in calls:

@@ -222,6 +222,9 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
             if num_cpu_bytes > 0:
                 self.core.unlink_cpu_segment_name()      # every rank has mapped it; the mappings keep it alive
         self.comm_stream = _get_comm_stream()
+        # combine launches on this stream; it is the communication stream unless a caller that overlaps dispatches of one
+        # batch with combines of another (a pipelined MoE layer) gives combine a stream of its own
+        self.combine_stream = self.comm_stream
 
     # ------------------------------------------------------------------------------------------ extra region
     def reserve(self, num_bytes: int, alignment: int = 1024) -> int:
@@ -636,7 +639,7 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
                 bias: Union[None, torch.Tensor, Tuple[torch.Tensor, torch.Tensor]] = None, num_sms: int = 0,
                 num_qps: int = 0, previous_event: Optional[EventHandle] = None,
                 previous_event_before_epilogue: Optional[EventHandle] = None, async_with_compute_stream: bool = False,
-                allocate_on_comm_stream: bool = False, weighted: bool = False):
+                allocate_on_comm_stream: bool = False, weighted: bool = False, out: Optional[torch.Tensor] = None):
         """Reduce the experts' output rows back onto the tokens' home ranks.
 
         ``x`` has one row per received row of the dispatch (``handle.num_rows``).  The result for token ``t`` is
@@ -646,7 +649,9 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         here are carried back to the home rank unchanged (``[rows, K]`` non-expand, ``[rows]`` expand) and
         returned as ``combined_topk_weights [T, K]``.  A plain ``x`` is first copied into the buffer's input region
         (one local pass over the rows); a tensor obtained from :meth:`get_combine_buffer` is read in place.
-        Stream arguments behave as in :meth:`dispatch`.  Returns ``(combined_x, combined_topk_weights, event)``.
+        Stream arguments behave as in :meth:`dispatch` (the kernel runs on ``self.combine_stream``).  ``out`` (contiguous
+        bf16 ``[T, H]``) receives the result in place of a new tensor.
+        Returns ``(combined_x, combined_topk_weights, event)``.
         """
         assert not self._destroyed
         if num_qps != 0:
@@ -658,23 +663,24 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         if self.is_cpu:
             return self._cpu.combine(self, x, handle, topk_weights, bias0, bias1, weighted)
         num_sms = value_or(num_sms or None, handle.num_sms)
-        alloc_stream = self.comm_stream if allocate_on_comm_stream else torch.cuda.current_stream()
+        stream = self.combine_stream
+        alloc_stream = stream if allocate_on_comm_stream else torch.cuda.current_stream()
         if allocate_on_comm_stream:
-            self._stream_prologue(previous_event, previous_event_before_epilogue)
+            self._stream_prologue(previous_event, previous_event_before_epilogue, stream)
         with torch.cuda.stream(alloc_stream):
-            call, out, out_w, staged = self._prepare_combine(x, handle, topk_weights, bias0, bias1, weighted)
+            call, out, out_w, staged = self._prepare_combine(x, handle, topk_weights, bias0, bias1, weighted, out)
         if not allocate_on_comm_stream:
-            self._stream_prologue(previous_event, previous_event_before_epilogue)
-        with torch.cuda.stream(self.comm_stream):
+            self._stream_prologue(previous_event, previous_event_before_epilogue, stream)
+        with torch.cuda.stream(stream):
             for dst, src in staged:      # plain tensors go through the symmetric buffer
                 dst.copy_(src)
-            self._timed('combine', lambda: self.core.combine(call, num_sms))
+            self._timed('combine', lambda: self.core.combine(call, num_sms), stream)
         inputs = (x, topk_weights, bias0, bias1, call.bias0, call.bias1, call.mul_weights, handle.plan,
                   handle.dst_buffer_slot_idx)
-        event = self._stream_epilogue(async_with_compute_stream, (out, out_w), inputs)
+        event = self._stream_epilogue(async_with_compute_stream, (out, out_w), inputs, stream)
         return out, out_w, event
 
-    def _prepare_combine(self, x, handle: EPHandle, topk_weights, bias0, bias1, weighted):
+    def _prepare_combine(self, x, handle: EPHandle, topk_weights, bias0, bias1, weighted, out=None):
         C = self._C
         H = x.shape[1]
         rows = handle.num_rows
@@ -694,7 +700,9 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         if self.profile is not None:
             call.prof = self.profile['combine']
         T, K = handle.plan.shape
-        out = torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
+        if out is None:
+            out = torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
+        assert out.shape == (T, H) and out.dtype == torch.bfloat16 and out.is_contiguous(), '`out` must be contiguous bf16 [T, H]'
         call.out = out
         out_w = None
         if topk_weights is not None:
@@ -714,17 +722,18 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         return call, out, out_w, staged
 
     # ------------------------------------------------------------------------------------------ streams
-    def _stream_prologue(self, previous_event: Optional[EventHandle], before_epilogue: Optional[EventHandle]) -> None:
+    def _stream_prologue(self, previous_event: Optional[EventHandle], before_epilogue: Optional[EventHandle], stream=None) -> None:
         """The communication stream waits for ``previous_event`` or for the current stream's work so far, and for
         ``before_epilogue`` (see :meth:`dispatch`)."""
+        stream = self.comm_stream if stream is None else stream
         if previous_event is not None and previous_event.event is not None:
-            self.comm_stream.wait_event(previous_event.event)
+            stream.wait_event(previous_event.event)
         else:
-            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            stream.wait_stream(torch.cuda.current_stream())
         if before_epilogue is not None and before_epilogue.event is not None:
-            self.comm_stream.wait_event(before_epilogue.event)
+            stream.wait_event(before_epilogue.event)
 
-    def _stream_epilogue(self, async_with_compute_stream: bool, outputs, inputs=()) -> EventOverlap:
+    def _stream_epilogue(self, async_with_compute_stream: bool, outputs, inputs=(), stream=None) -> EventOverlap:
         """Either hand back an event on the communication stream (async) or make the current stream wait.
 
         In the async case the caching allocator must not hand a block to someone else while the other stream still
@@ -745,15 +754,16 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
                         flat.append(v)
         walk(outputs)
         walk(inputs)
+        stream = self.comm_stream if stream is None else stream
         if async_with_compute_stream:
             if os.environ.get('EP_AVOID_RECORD_STREAM', '0') != '1':
                 cur = torch.cuda.current_stream()
                 for t in flat:
                     if t.is_cuda:
                         t.record_stream(cur)
-                        t.record_stream(self.comm_stream)
-            return EventOverlap(EventHandle(self.comm_stream, tuple(flat)))
-        torch.cuda.current_stream().wait_stream(self.comm_stream)
+                        t.record_stream(stream)
+            return EventOverlap(EventHandle(stream, tuple(flat)))
+        torch.cuda.current_stream().wait_stream(stream)
         return EventOverlap(None)
 
     def capture(self) -> EventHandle:
@@ -767,14 +777,15 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         Read the pairs with :meth:`kernel_times_ms`."""
         self._kernel_timing = {'dispatch': [], 'combine': []} if enabled else None
 
-    def _timed(self, name: str, launch) -> None:
+    def _timed(self, name: str, launch, stream=None) -> None:
         if self._kernel_timing is None:
             launch()
             return
+        stream = self.comm_stream if stream is None else stream
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(self.comm_stream)
+        e0.record(stream)
         launch()
-        e1.record(self.comm_stream)
+        e1.record(stream)
         self._kernel_timing[name].append((e0, e1))
 
     def kernel_times_ms(self, name: str, clear: bool = True) -> List[float]:

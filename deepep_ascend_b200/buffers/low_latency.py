@@ -128,7 +128,7 @@ class LowLatencyMixin:
         return recv_x, call.packed_count, handle, event, hook
 
     # ------------------------------------------------------------------------------------------ combine
-    def _ll_prepare_combine(self, x, topk_idx, topk_weights, handle, out, wait_stats, phases):
+    def _ll_prepare_combine(self, x, topk_idx, topk_weights, handle, out, wait_stats, phases, use_logfmt=False):
         C = self._C
         src_info, layout_range, M, H, E = handle
         K = topk_idx.shape[1]
@@ -147,6 +147,7 @@ class LowLatencyMixin:
             call.prof = self.profile['ll_combine']
         call.mask = ll['mask']
         call.shrink = self.low_latency_shrink
+        call.use_logfmt = bool(use_logfmt)
         return call
 
     def low_latency_combine(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, handle: tuple,
@@ -156,8 +157,11 @@ class LowLatencyMixin:
         """-> ``(combined_x [T, H] bf16 = sum_k topk_weights[t, k] * x_k, event, hook)``.
 
         ``x [E_local, ranks * max_tokens, H]`` bf16 holds the expert outputs in the packed order of the dispatch.
-        ``zero_copy`` is accepted for API parity: rows are read in place from ``x`` either way.  ``use_logfmt`` is
-        accepted and ignored: rows always travel as bf16 over NVLink.
+        Rows are read in place from ``x`` whether or not it came from :meth:`get_next_low_latency_combine_buffer`, so
+        ``zero_copy`` changes nothing here.  With ``use_logfmt`` the rows cross the wire as LogFMT-10: 10-bit
+        logarithmic codes with one range per 128 channels (36 % fewer bytes; ``H`` must be a multiple of 128), coded by
+        the sender and decoded inside the weighted reduction
+        (csrc/kernels/legacy/internode_ll.cu:556-712 of the reference; ``utils.math.logfmt10_roundtrip`` states the code).
         """
         C = self._C
         num_sms = self._ll_num_sms(num_sms)
@@ -166,7 +170,7 @@ class LowLatencyMixin:
             stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
             call = self._ll_prepare_combine(x, topk_idx, topk_weights, handle, out, combine_wait_recv_cost_stats,
-                                            1 if return_recv_hook else 3)
+                                            1 if return_recv_hook else 3, use_logfmt)
             C.ll_combine_group([self.core], [call], num_sms)
         event, hook = EventOverlap(None), None
         if return_recv_hook:

@@ -211,6 +211,7 @@ struct LLCombineArgs {
     int64_t* wait_stats;
     int32_t* mask;
     int shrink;
+    int use_logfmt;              // rows cross the wire as 10-bit logarithmic codes with one range per 128 channels (logfmt.cuh)
     uint64_t* prof;              // [8] phase timestamps (ns) or null: start, stores issued, stores complete, flags published
                                  //     (by the last CTA), flags received, reduced
 };
@@ -269,6 +270,9 @@ struct GemmArgs {
     const float* sfb;                 // fp8: [num_groups, ceil(N/128), ceil(K/128)] contiguous
     const int32_t* tile_group;        // [ceil(M/128)] or null (single group 0)
     int* error;                       // device int set to non-zero if a pipeline wait ran out
+    uint64_t* status;                 // status block of a communication buffer that should hear about such a failure, or null
+    int status_rank;
+    uint64_t timeout_ns;              // limit of every pipeline wait; 0 = 4 s
     // fused collectives (null / 0 when unused)
     const uint64_t* a_ready_flags;    // all-gather fused into the loads: rows of M tile t may be read once
     uint64_t a_ready_value;           //   a_ready_flags[a_flag_of_tile[t]] >= a_ready_value

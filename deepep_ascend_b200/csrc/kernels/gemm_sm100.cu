@@ -54,7 +54,7 @@ __device__ __forceinline__ void reg_dealloc() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
 }
 constexpr int kMaxAccBufs = 4;
-constexpr uint64_t kWaitLimitNs = 4ull * 1000 * 1000 * 1000;
+constexpr uint64_t kDefaultWaitLimitNs = 4ull * 1000 * 1000 * 1000;   // when the caller gives no limit
 
 struct GemmSmem {
     uint64_t full[kMaxStages], empty[kMaxStages], tmem_full[kMaxAccBufs], tmem_empty[kMaxAccBufs];
@@ -69,17 +69,37 @@ __device__ __forceinline__ uint64_t gemm_timer() {
     return t;
 }
 
+__device__ __forceinline__ uint64_t wait_limit_ns(const GemmArgs& g) { return g.timeout_ns != 0 ? g.timeout_ns : kDefaultWaitLimitNs; }
+
+// A pipeline wait ran out: stop this CTA's loops, raise the per-device flag and, when the caller gave the status block of
+// a communication buffer, record the failure there too, so that the buffer's check_status() reports it and poisons the
+// buffer like any other failed device wait.  `code`: 1 = empty stage, 2 = free accumulator, 3 = rows-ready flag,
+// 4 = full stage, 5 = finished accumulator, 7 = all-gather copy.
+__device__ __noinline__ void gemm_fail(const GemmArgs& g, GemmSmem* sm, int code) {
+    sm->failed = code;
+    if (g.error != nullptr && atomicCAS(g.error, 0, code) == 0 && g.status != nullptr) {
+        volatile uint64_t* st = g.status;
+        st[EP_STATUS_PHASE] = EP_PH_GEMM_PIPE;
+        st[EP_STATUS_PEER] = static_cast<uint64_t>(-1ll);
+        st[EP_STATUS_EXPECTED] = static_cast<uint64_t>(code);
+        st[EP_STATUS_OBSERVED] = blockIdx.x;
+        st[EP_STATUS_RANK] = static_cast<uint64_t>(g.status_rank);
+        __threadfence_system();
+        st[EP_STATUS_CODE] = EP_ERR_TIMEOUT;
+        __threadfence_system();
+    }
+}
+
 // bounded mbarrier wait; returns false (and raises the failure flags) when the limit runs out
-__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, GemmSmem* sm, int* error, int code) {
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, GemmSmem* sm, const GemmArgs& g, int code) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = gemm_timer();
     uint32_t spins = 0;
     while (!ptx::mbar_try_wait(bar, parity)) {
         if ((++spins & 63u) == 0u) {
             if (*reinterpret_cast<volatile int*>(&sm->failed)) return false;
-            if (gemm_timer() - t0 > kWaitLimitNs) {
-                sm->failed = code;
-                if (error != nullptr) atomicCAS(error, 0, code);
+            if (gemm_timer() - t0 > wait_limit_ns(g)) {
+                gemm_fail(g, sm, code);
                 return false;
             }
         }
@@ -215,9 +235,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         const uint64_t* flag = &ws->tile_flags[m_blk];
                         const uint64_t t0 = gemm_timer();
                         while (ptx::ld_acquire_sys(flag) < epoch) {
-                            if (gemm_timer() - t0 > kWaitLimitNs || *reinterpret_cast<volatile int*>(&sm->failed)) {
-                                sm->failed = 3;
-                                if (g.error != nullptr) atomicCAS(g.error, 0, 3);
+                            if (gemm_timer() - t0 > wait_limit_ns(g) || *reinterpret_cast<volatile int*>(&sm->failed)) {
+                                gemm_fail(g, sm, 3);
                                 ok = false;
                                 break;
                             }
@@ -230,9 +249,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         const uint64_t* flag = g.a_ready_flags + (g.a_flag_of_tile != nullptr ? g.a_flag_of_tile[m_blk] : m_blk);
                         const uint64_t t0 = gemm_timer();
                         while (ptx::ld_acquire_sys(flag) < g.a_ready_value) {
-                            if (gemm_timer() - t0 > kWaitLimitNs || *reinterpret_cast<volatile int*>(&sm->failed)) {
-                                sm->failed = 3;
-                                if (g.error != nullptr) atomicCAS(g.error, 0, 3);
+                            if (gemm_timer() - t0 > wait_limit_ns(g) || *reinterpret_cast<volatile int*>(&sm->failed)) {
+                                gemm_fail(g, sm, 3);
                                 ok = false;
                                 break;
                             }
@@ -240,7 +258,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         if (!ok) break;
                     }
                     for (int kb = tw.kb0; kb < tw.kb1 && ok; ++kb) {
-                        ok = wait_bar(&sm->empty[p.stage], p.phase ^ 1, sm, g.error, 1);
+                        ok = wait_bar(&sm->empty[p.stage], p.phase ^ 1, sm, g, 1);
                         if (!ok) break;
                         ptx::mbar_arrive_expect_tx(&sm->full[p.stage], kTileBytes + kTileBytesB);
                         umma::tma_load_2d(s_a + p.stage * kTileBytes, &map_a, kb * kBlockK, m_blk * kBlockM, &sm->full[p.stage]);
@@ -260,16 +278,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const TileWork tw = tile_work(g, tile, num_m, num_n, num_k, group_m, kBlockK);
                     if (tw.grp < 0 || tw.kb1 <= tw.kb0) continue;
                     if (!kFp8) {
-                        ok = wait_bar(&sm->tmem_empty[acc], acc_phase ^ 1, sm, g.error, 2);
+                        ok = wait_bar(&sm->tmem_empty[acc], acc_phase ^ 1, sm, g, 2);
                         if (!ok) break;
                         umma::fence_after_thread_sync();
                     }
                     for (int kb = tw.kb0; kb < tw.kb1 && ok; ++kb) {
                         if (kFp8) {
-                            ok = wait_bar(&sm->tmem_empty[acc], acc_phase ^ 1, sm, g.error, 2);
+                            ok = wait_bar(&sm->tmem_empty[acc], acc_phase ^ 1, sm, g, 2);
                             if (!ok) break;
                         }
-                        ok = wait_bar(&sm->full[p.stage], p.phase, sm, g.error, 4);
+                        ok = wait_bar(&sm->full[p.stage], p.phase, sm, g, 4);
                         if (!ok) break;
                         umma::fence_after_thread_sync();
                         const uint64_t desc_a = umma::make_smem_desc_sw128(s_a + p.stage * kTileBytes);
@@ -323,7 +341,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
             const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
             if (!kFp8) {
-                ok = wait_bar(&sm->tmem_full[acc], acc_phase, sm, g.error, 5);
+                ok = wait_bar(&sm->tmem_full[acc], acc_phase, sm, g, 5);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 umma::fence_after_thread_sync();
@@ -389,7 +407,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const float scale = scale_next;
                     if (kb + 1 < num_k)
                         scale_next = (row < g.M ? __ldg(g.sfa + row * g.sfa_stride_row + (kb + 1) * g.sfa_stride_kb) : 0.f) * __ldg(sfb + kb + 1);
-                    ok = wait_bar(&sm->tmem_full[acc], acc_phase, sm, g.error, 5);
+                    ok = wait_bar(&sm->tmem_full[acc], acc_phase, sm, g, 5);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     umma::fence_after_thread_sync();
@@ -494,13 +512,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         for (int item = copier; item < num_items && alive; item += g.num_copy_ctas) {
             const int src = (ctx.rank + 1 + item / tiles_per_shard) % ctx.num_ranks;
             const int m_blk = src * tiles_per_shard + item % tiles_per_shard;
-            const int my_rows = (kBlockM - warp + kCopyWarps - 1) / kCopyWarps;
-            auto row_offset = [&](int i) { return g.off_full + (static_cast<int64_t>(m_blk) * kBlockM + warp + i * kCopyWarps) * row_bytes; };
+            // this warp's rows of the tile, each moved in pieces of at most one 16 KB staging buffer
+            constexpr int kPiece = 16384;
+            const int pieces = (row_bytes + kPiece - 1) / kPiece;
+            const int my_rows = (kBlockM - warp + kCopyWarps - 1) / kCopyWarps * pieces;   // (row, piece) pairs
+            auto row_offset = [&](int i) {
+                return g.off_full + (static_cast<int64_t>(m_blk) * kBlockM + warp + (i / pieces) * kCopyWarps) * row_bytes + static_cast<int64_t>(i % pieces) * kPiece;
+            };
+            auto piece_bytes = [&](int i) { return min(kPiece, row_bytes - (i % pieces) * kPiece); };
             auto issue_load = [&](int i) {
                 const uint32_t l = n_loaded + i;
                 if (lane == 0) {
-                    ptx::mbar_arrive_expect_tx(&bars[l & 1], row_bytes);
-                    ptx::bulk_load(stage + (l & 1) * 16384, ctx.peer_base[src] + row_offset(i), row_bytes, &bars[l & 1]);
+                    ptx::mbar_arrive_expect_tx(&bars[l & 1], piece_bytes(i));
+                    ptx::bulk_load(stage + (l & 1) * kPiece, ctx.peer_base[src] + row_offset(i), piece_bytes(i), &bars[l & 1]);
                 }
             };
             ptx::bulk_wait_read<0>();
@@ -508,7 +532,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             issue_load(0);
             for (int i = 0; i < my_rows && alive; ++i) {
                 if (i + 1 < my_rows) {
-                    ptx::bulk_wait_read<0>();   // the other stage was the source of the previous row's store
+                    ptx::bulk_wait_read<0>();   // the other stage was the source of the previous piece's store
                     __syncwarp();
                     issue_load(i + 1);
                 }
@@ -518,7 +542,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     sm->failed = 7;
                     break;
                 }
-                if (lane == 0) ptx::bulk_store(ctx.peer_base[ctx.rank] + row_offset(i), stage + (l & 1) * 16384, row_bytes);
+                if (lane == 0) ptx::bulk_store(ctx.peer_base[ctx.rank] + row_offset(i), stage + (l & 1) * kPiece, piece_bytes(i));
                 ptx::bulk_commit();
             }
             n_loaded += my_rows;
@@ -628,7 +652,7 @@ cudaError_t launch_gemm(const GemmArgs& g, int num_sms, cudaStream_t stream) {
         return cudaErrorInvalidValue;
     // bf16: 128 x 256 output tiles (fewer A re-reads, longer MMAs); the block-scaled FP8 path and the reduce-scatter
     // epilogue (which stages 128-column rows) use 128 x 128 tiles
-    const int block_n = (g.fuse != EP_GEMM_FUSE_REDUCE_SCATTER && g.N >= 256 && !(g.is_fp8 && getenv("EP_GEMM_FP8_N128") != nullptr)) ? 256 : 128;
+    const int block_n = (g.fuse != EP_GEMM_FUSE_REDUCE_SCATTER && g.N >= 256) ? 256 : 128;
     CUtensorMap map_a, map_b;
     if (!make_operand_map(&map_a, g.a, g.M, g.K, g.lda, g.is_fp8, 128) ||
         !make_operand_map(&map_b, g.b, static_cast<int64_t>(g.k_group_off != nullptr ? 1 : g.num_groups) * g.N, g.K, g.ldb, g.is_fp8, block_n))
@@ -645,7 +669,7 @@ cudaError_t launch_gemm(const GemmArgs& g, int num_sms, cudaStream_t stream) {
     if (g.fuse != EP_GEMM_FUSE_NONE) {
         // the CTAs of a fused launch wait on one another (grid barrier, copier -> producer flags): cooperative launch
         const int R = g.ctx.num_ranks;
-        if (g.is_fp8 || g.M % (kBlockM * R) != 0 || g.N % 128 != 0 || g.K * 2 > 16384 || g.tile_group != nullptr) return cudaErrorInvalidValue;
+        if (g.is_fp8 || g.M % (kBlockM * R) != 0 || g.N % 128 != 0 || g.tile_group != nullptr) return cudaErrorInvalidValue;
         if (g.fuse == EP_GEMM_FUSE_ALL_GATHER && (g.num_copy_ctas < 1 || g.num_copy_ctas >= ctas)) return cudaErrorInvalidValue;
         if (g.fuse == EP_GEMM_FUSE_REDUCE_SCATTER && g.num_copy_ctas != 0) return cudaErrorInvalidValue;
         if (g.M / kBlockM >= EP_MAX_TILE_FLAGS - 1) return cudaErrorInvalidValue;

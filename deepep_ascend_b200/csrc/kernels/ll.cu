@@ -19,6 +19,7 @@
 //
 // Parity: csrc/kernels/legacy/internode_ll.cu:128-554 (dispatch) and 714-1238 (combine) of the reference.
 #include "common.cuh"
+#include "logfmt.cuh"
 
 namespace ep {
 
@@ -28,9 +29,11 @@ constexpr int kLLThreads = 512;
 constexpr int kLLWarps = kLLThreads / 32;
 constexpr int kLLCombineSmemBudget = 200 * 1024;
 
-// warps of a CTA that stage combine rows (two bf16 rows of shared memory each)
+// warps of a CTA that stage combine rows (two bf16 rows of shared memory each, plus one word per 128 channels for the
+// range headers of the LogFMT coding)
+__host__ __device__ inline int ll_combine_hdr_bytes(int hidden) { return ((hidden + 127) / 128 * 4 + 15) / 16 * 16; }
 __host__ __device__ inline int ll_combine_send_warps(int hidden) {
-    const int w = (kLLCombineSmemBudget - 1024) / (2 * hidden * 2);
+    const int w = (kLLCombineSmemBudget - 1024) / (2 * hidden * 2 + ll_combine_hdr_bytes(hidden));
     return w < 1 ? 1 : (w > kLLWarps ? kLLWarps : w);
 }
 
@@ -326,6 +329,9 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
     const int send_warps = ll_combine_send_warps(H);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * 2;
     uint8_t* stage = smem + 1024 + static_cast<size_t>(warp < send_warps ? warp : 0) * 2 * row_bytes;
+    uint32_t* hdr_scratch = reinterpret_cast<uint32_t*>(smem + 1024 + static_cast<size_t>(send_warps) * 2 * row_bytes +
+                                                        static_cast<size_t>(warp < send_warps ? warp : 0) * ll_combine_hdr_bytes(H));
+    const int wire_bytes = a.use_logfmt ? logfmt::wire_bytes(H) : row_bytes;   // what one row puts on the wire
     if (lane == 0) {
         ptx::mbar_init(&bars[0], 1);
         ptx::mbar_init(&bars[1], 1);
@@ -385,9 +391,15 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
             alive = mbar_wait_bounded(ctx, ws, &bars[st], (n_loaded >> 1) & 1, EP_PH_COMBINE_LOAD);
             ++n_loaded;
             if (!alive) break;
+            if (a.use_logfmt) {
+                // re-code the row in place: 10 bits per channel plus one range per 128 channels
+                logfmt::encode_row_in_place(stage + st * row_bytes, hdr_scratch, H);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+            }
             if (lane == 0) {
                 uint8_t* dst = s_peer[s] + a.off_slab[set] + (static_cast<int64_t>(t) * K + k) * row_bytes;
-                ptx::bulk_store(dst, stage + st * row_bytes, row_bytes);
+                ptx::bulk_store(dst, stage + st * row_bytes, wire_bytes);
             }
             ptx::bulk_commit();
             pos = next_pos;
@@ -424,7 +436,58 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
         }
         alive = __syncthreads_and(ok) != 0;
         stamp(4);
-        if (alive) {
+        if (alive && a.use_logfmt) {
+            // out[t] = sum_k w[t, k] * decode(slot[t, k]); work item = (token, 512 channels), one warp each; a lane decodes
+            // 16 channels (five words of codes) of every source row, eight lanes share a range header
+            const uint8_t* slab = s_peer[me] + a.off_slab[set];
+            const int steps = (H + logfmt::kStepChannels - 1) / logfmt::kStepChannels;
+            const int groups = H / logfmt::kGroup;
+            const int64_t items = static_cast<int64_t>(a.num_tokens) * steps;
+            for (int64_t it = static_cast<int64_t>(blockIdx.x) * kLLWarps + warp; it < items; it += static_cast<int64_t>(gridDim.x) * kLLWarps) {
+                const int t = static_cast<int>(it / steps), c = static_cast<int>(it % steps);
+                const int ch = c * logfmt::kStepChannels + lane * logfmt::kLaneChannels;
+                const bool in_row = ch < H;
+                int e_k = -1;
+                float w_k = 0.f;
+                if (lane < K) {
+                    e_k = ll_load_idx(a.topk_idx, a.idx_is_64, static_cast<int64_t>(t) * K + lane);
+                    w_k = __ldg(a.topk_weights + static_cast<int64_t>(t) * K + lane);
+                    if (e_k >= 0 && rank_masked(a.mask, e_k / El)) e_k = -1;
+                }
+                const uint32_t srcs = __ballot_sync(0xffffffffu, e_k >= 0 && e_k < E);
+                float acc[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+                for (uint32_t m = srcs; m != 0; m &= m - 1) {
+                    const int k = __ffs(m) - 1;
+                    const float w = __shfl_sync(0xffffffffu, w_k, k);
+                    if (in_row) {
+                        const uint8_t* row = slab + (static_cast<int64_t>(t) * K + k) * row_bytes;
+                        const uint32_t* codes = reinterpret_cast<const uint32_t*>(row + (ch / logfmt::kLaneChannels) * 20);
+                        uint32_t wds[5], cds[16];
+#pragma unroll
+                        for (int j = 0; j < 5; ++j) wds[j] = __ldcg(codes + j);
+                        const uint32_t hdr = __ldcg(reinterpret_cast<const uint32_t*>(row + groups * logfmt::kCodeBytesPerGroup) + ch / logfmt::kGroup);
+                        const float2 mm = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hdr));   // (amax, amin)
+                        logfmt::unpack16(wds, cds);
+                        if (mm.x > 0.f) {
+                            const logfmt::Range r = logfmt::make_range(mm.x, mm.y);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) acc[i] = fmaf(w, logfmt::decode_one(cds[i], r), acc[i]);
+                        }
+                    }
+                }
+                if (in_row) {
+                    int4 o[2];
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) h[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+                    int4* dst = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(a.out) + static_cast<int64_t>(t) * row_bytes + ch * 2);
+                    dst[0] = o[0];
+                    dst[1] = o[1];
+                }
+            }
+        } else if (alive) {
             // out[t] = sum_k w[t, k] * slot[t, k]; work item = (token, 512-byte column chunk), one warp each: every lane
             // has the 16-byte loads of all top-k rows in flight at once, so an item costs one memory round trip
             const uint8_t* slab = s_peer[me] + a.off_slab[set];
@@ -528,8 +591,9 @@ cudaError_t launch_ll_dispatch(const LLDispatchArgs* args, int n, int num_sms, c
 }
 
 cudaError_t launch_ll_combine(const LLCombineArgs* args, int n, int num_sms, cudaStream_t stream) {
-    const int smem = 1024 + ll_combine_send_warps(args[0].hidden) * 2 * args[0].hidden * 2;
+    const int smem = 1024 + ll_combine_send_warps(args[0].hidden) * (2 * args[0].hidden * 2 + ll_combine_hdr_bytes(args[0].hidden));
     if (smem > 227 * 1024) return cudaErrorInvalidValue;
+    if (args[0].use_logfmt && args[0].hidden % 128 != 0) return cudaErrorInvalidValue;
     return launch_ll<LLCombineArgs>((const void*)ll_combine_kernel, (const void*)ll_combine_kernel_multi, args, n, num_sms, smem, stream);
 }
 

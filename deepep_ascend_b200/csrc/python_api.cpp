@@ -70,7 +70,8 @@ at::Tensor& gemm_error_flag(int device) {
 // `tile_group` int32 [ceil(M/128)]: weights group of every 128-row tile (-1 = skip the tile).
 at::Tensor gemm_nt(const at::Tensor& a, const at::Tensor& b, const std::optional<at::Tensor>& sfa, const std::optional<at::Tensor>& sfb,
                    const std::optional<at::Tensor>& tile_group, const std::optional<at::Tensor>& out, int64_t num_sms,
-                   const std::optional<at::Tensor>& a_ready_flags, int64_t a_ready_value, const std::optional<at::Tensor>& a_flag_of_tile) {
+                   const std::optional<at::Tensor>& a_ready_flags, int64_t a_ready_value, const std::optional<at::Tensor>& a_flag_of_tile,
+                   ElasticBufferCore* report_to) {
     TORCH_CHECK(a.is_cuda() && a.dim() == 2 && a.stride(1) == 1, "A must be [M, K] with contiguous rows");
     TORCH_CHECK(b.is_cuda() && (b.dim() == 2 || b.dim() == 3) && b.is_contiguous(), "B must be contiguous [N, K] or [G, N, K]");
     const bool fp8 = a.scalar_type() == at::kFloat8_e4m3fn;
@@ -114,6 +115,15 @@ at::Tensor gemm_nt(const at::Tensor& a, const at::Tensor& b, const std::optional
         if (a_flag_of_tile.has_value()) g.a_flag_of_tile = a_flag_of_tile->data_ptr<int32_t>();
     }
     g.error = gemm_error_flag(a.get_device()).data_ptr<int>();
+    if (report_to != nullptr) {
+        // a pipeline wait that runs out is recorded in this buffer's status block (its limit applies too), so the
+        // buffer's check_status() raises and poisons it like any other failed device wait
+        report_to->check_status();
+        const RankCtx c0 = report_to->ctx();
+        g.status = c0.status;
+        g.status_rank = c0.rank;
+        g.timeout_ns = c0.timeout_ns;
+    }
     const int sms = num_sms > 0 ? static_cast<int>(num_sms) : at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
     cuda_check(ep::launch_gemm(g, sms, at::cuda::getCurrentCUDAStream()), "tcgen05 GEMM launch");
     return c;
@@ -141,6 +151,9 @@ at::Tensor ag_gemm(ElasticBufferCore& core, int64_t off_full, int64_t M, int64_t
     g.error = gemm_error_flag(b.get_device()).data_ptr<int>();
     g.fuse = EP_GEMM_FUSE_ALL_GATHER;
     g.ctx = core.ctx();
+    g.status = g.ctx.status;
+    g.status_rank = g.ctx.rank;
+    g.timeout_ns = g.ctx.timeout_ns;
     g.num_copy_ctas = static_cast<int>(num_copy_ctas);
     g.off_full = off_full;
     g.m_tile_offset = static_cast<int>(core.rank() * (M / 128 / core.num_ranks()));
@@ -172,6 +185,9 @@ at::Tensor gemm_rs(ElasticBufferCore& core, const at::Tensor& a, const at::Tenso
     g.error = gemm_error_flag(a.get_device()).data_ptr<int>();
     g.fuse = EP_GEMM_FUSE_REDUCE_SCATTER;
     g.ctx = core.ctx();
+    g.status = g.ctx.status;
+    g.status_rank = g.ctx.rank;
+    g.timeout_ns = g.ctx.timeout_ns;
     g.off_slots = off_slots;
     g.slot_set_bytes = slot_set_bytes;
     g.rs_out = out.data_ptr();
@@ -504,7 +520,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("wait_stats", &LLCombineCall::wait_stats)
         .def_readwrite("prof", &LLCombineCall::prof)
         .def_readwrite("mask", &LLCombineCall::mask)
-        .def_readwrite("shrink", &LLCombineCall::shrink);
+        .def_readwrite("shrink", &LLCombineCall::shrink)
+        .def_readwrite("use_logfmt", &LLCombineCall::use_logfmt);
     m.def("ll_dispatch_group", &ll_dispatch_group);
     m.def("ll_combine_group", &ll_combine_group);
     m.def("ll_message_bytes", &ll_message_bytes);
@@ -529,7 +546,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.attr("CH_ENGRAM") = static_cast<int>(EP_CH_ENGRAM);
     m.def("gemm_nt", &gemm_nt, py::arg("a"), py::arg("b"), py::arg("sfa") = py::none(), py::arg("sfb") = py::none(),
           py::arg("tile_group") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0, py::arg("a_ready_flags") = py::none(),
-          py::arg("a_ready_value") = 0, py::arg("a_flag_of_tile") = py::none());
+          py::arg("a_ready_value") = 0, py::arg("a_flag_of_tile") = py::none(), py::arg("report_to") = nullptr);
     m.def("ag_gemm", &ag_gemm);
     m.def("gemm_rs", &gemm_rs);
     m.def("swiglu_quant", &swiglu_quant, py::arg("h"), py::arg("keep_bf16") = false);

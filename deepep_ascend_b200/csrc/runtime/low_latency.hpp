@@ -26,6 +26,7 @@ struct LLCombineCall {
     int64_t off_slab0 = 0, off_slab1 = 0;
     OptTensor wait_stats, mask, prof;
     bool shrink = false;
+    bool use_logfmt = false;      // rows travel as 10-bit logarithmic codes (hidden must be a multiple of 128)
 };
 
 inline int64_t ll_message_bytes(int64_t hidden) {
@@ -139,6 +140,8 @@ inline LLCombineArgs make_ll_combine_args(ElasticBufferCore& core, const LLCombi
     a.wait_stats = c.wait_stats.has_value() ? c.wait_stats->data_ptr<int64_t>() : nullptr;
     a.mask = c.mask.has_value() ? c.mask->data_ptr<int32_t>() : nullptr;
     a.shrink = c.shrink;
+    TORCH_CHECK(!c.use_logfmt || H % 128 == 0, "LogFMT coding needs a hidden size that is a multiple of 128");
+    a.use_logfmt = c.use_logfmt;
     if (c.prof.has_value()) {
         TORCH_CHECK(c.prof->scalar_type() == at::kLong && c.prof->numel() >= 8 && c.prof->is_cuda(), "prof must be int64 [8] on the GPU");
         a.prof = reinterpret_cast<uint64_t*>(c.prof->data_ptr<int64_t>());

@@ -20,51 +20,106 @@ from ..ops import gemm as G
 
 
 class _MoEFunction(torch.autograd.Function):
+    """Forward and backward of the layer.  The token batch is cut into ``layer.num_chunks`` pieces that run as a software
+    pipeline: while the tensor cores work on the experts of chunk c, the communication stream combines chunk c - 1 and
+    dispatches chunk c + 1, each through one of the buffer's two receive slots / two combine input regions.  Every rank
+    issues its communication kernels in the same order on ONE stream (d0, d1, c0, d2, c1, ...), and the GEMMs leave the
+    communication kernels their SMs (``num_sms`` of them), so the kernels of different ranks can never wait for SMs that
+    a kernel waiting for them holds."""
+
     @staticmethod
     def forward(ctx, x, topk_weights, w13, w2, layer, topk_idx):
         buf: ElasticBuffer = layer.buffer
         E = layer.num_experts
-        (rx, rsf), _, recv_w, handle, _ = buf.dispatch(x, topk_idx, topk_weights, num_experts=E, do_expand=True,
-                                                      expert_alignment=G.BLOCK_M, fused_fp8_cast=True, num_sms=layer.num_sms)
-        rows = handle.num_rows
-        tile_group, valid_row = G.expert_tile_groups(handle.psum_num_recv_tokens_per_expert, rows)
+        T = x.shape[0]
+        C = max(1, min(layer.num_chunks, T))
+        bounds = [T * c // C for c in range(C + 1)]
+        pipelined = C > 1
+        need_grad = any(ctx.needs_input_grad)
+        keep_copy = need_grad and (pipelined or layer.copy_saved_rows)
+        comm_sms, gemm_sms = layer.sm_split(pipelined)
         q13, s13, q2, s2 = layer.fp8_weights()
-        h = G.grouped_gemm_nt(rx, q13, tile_group, sfa=rsf, sfb=s13)                       # [rows, 2I]
-        a2, sf2 = G.swiglu_quant(h)
-        y = buf.get_combine_buffer(handle)
-        G.grouped_gemm_nt(a2, q2, tile_group, out=y, sfa=sf2, sfb=s2)                      # [rows, H] in the combine region
-        out, _, _ = buf.combine(y, handle, weighted=True, num_sms=layer.num_sms)
-        ctx.layer, ctx.handle = layer, handle
-        if layer.copy_saved_rows:
-            # the received rows live in a receive slot of the buffer that later dispatches (other layers) will reuse
-            rx, rsf, recv_w = rx.clone(), rsf.clone(), recv_w.clone()
-        ctx.save_for_backward(rx, rsf, recv_w, h, tile_group, valid_row)
+        out = torch.empty((T, x.shape[1]), dtype=torch.bfloat16, device=x.device)
+        slots = buf.regions.num_recv_slots
+        start = buf.capture() if pipelined else None
+        disp, g1_done, comb_done, saved, handles = {}, [], [], [], []
+
+        def issue_dispatch(c):
+            lo, hi = bounds[c], bounds[c + 1]
+            kw = {}
+            if pipelined:
+                # the receive slot of chunk c was last read by the first GEMM (and the copies for backward) of chunk c - slots
+                kw = dict(previous_event=g1_done[c - slots] if c >= slots else start, allocate_on_comm_stream=True,
+                          async_with_compute_stream=True)
+            disp[c] = buf.dispatch(x[lo:hi], topk_idx[lo:hi], topk_weights[lo:hi], num_experts=E, do_expand=True,
+                                   expert_alignment=G.BLOCK_M, fused_fp8_cast=True, num_sms=comm_sms, **kw)
+
+        issue_dispatch(0)
+        for c in range(C):
+            lo, hi = bounds[c], bounds[c + 1]
+            (rx, rsf), _, recv_w, handle, ev = disp.pop(c)
+            ev.current_stream_wait()
+            rows = handle.num_rows
+            tile_group, valid_row = G.expert_tile_groups(handle.psum_num_recv_tokens_per_expert, rows)
+            h = G.grouped_gemm_nt(rx, q13, tile_group, sfa=rsf, sfb=s13, num_sms=gemm_sms, buffer=buf)    # [rows, 2I]
+            if keep_copy:
+                # the received rows live in a receive slot of the buffer that later dispatches will reuse
+                rx, rsf, recv_w = rx.clone(), rsf.clone(), recv_w.clone()
+            if pipelined:
+                g1_done.append(buf.capture())
+                if c + 1 < C:
+                    issue_dispatch(c + 1)      # runs while the tensor cores are busy with this chunk
+            a2, sf2 = G.swiglu_quant(h)
+            if pipelined and c >= 1:
+                # the combine input region about to be written was read by the combine of chunk c - 2, which every rank
+                # has finished once this rank's combine of chunk c - 1 has completed
+                comb_done[c - 1].current_stream_wait()
+            y = buf.get_combine_buffer(handle)
+            G.grouped_gemm_nt(a2, q2, tile_group, out=y, sfa=sf2, sfb=s2, num_sms=gemm_sms, buffer=buf)    # [rows, H] in the combine region
+            kw = dict(previous_event=buf.capture(), allocate_on_comm_stream=True, async_with_compute_stream=True) if pipelined else {}
+            _, _, cev = buf.combine(y, handle, weighted=True, num_sms=comm_sms, out=out[lo:hi], **kw)
+            comb_done.append(cev)
+            handles.append(handle)
+            saved += [rx, rsf, recv_w, h, tile_group, valid_row]
+        for cev in comb_done[-2:]:
+            cev.current_stream_wait()
+        ctx.layer, ctx.handles, ctx.bounds = layer, handles, bounds
+        ctx.save_for_backward(*saved)
         return out
 
     @staticmethod
     def backward(ctx, d_out):
-        layer, handle = ctx.layer, ctx.handle
+        layer, bounds = ctx.layer, ctx.bounds
         buf: ElasticBuffer = layer.buffer
-        rx, rsf, recv_w, h, tile_group, valid_row = ctx.saved_tensors
-        seg_off = G.segment_offsets(handle.psum_num_recv_tokens_per_expert)
-        rw = recv_w.contiguous()
-        # backward of the weighted combine: every expert row receives its token's gradient g (cached dispatch)
-        g_rows, _, _, _, _ = buf.dispatch(d_out.contiguous(), handle=handle, fused_fp8_cast=False, num_sms=layer.num_sms)
         w2_t, w13_t = layer.transposed_weights()
-        # down projection on the UNWEIGHTED gradient: d loss / d weight of a row is <g W2, activation> (= <g, y>, so the
-        # expert outputs need not be kept), and the weight is applied inside the SwiGLU backward kernel.  Padding rows of
-        # g_rows hold stale data; every consumer masks them.
-        d_act_u = G.grouped_gemm_nt(g_rows, w2_t, tile_group)                               # [rows, I]
-        dh, dh_t, act_t, d_w_rows = G.swiglu_bwd(d_act_u, h, valid_row, row_weight=rw)
-        # up projection: the gradient rows go into the combine region and travel home (backward of dispatch)
-        d_recv = buf.get_combine_buffer(handle)
-        G.grouped_gemm_nt(dh, w13_t, tile_group, out=d_recv)
-        dx, d_topk_w, _ = buf.combine(d_recv, handle, topk_weights=d_w_rows, num_sms=layer.num_sms)
-        # weight gradients: one K-grouped GEMM per weight tensor, reduction over the rows of every expert segment
-        dy_t = G.weighted_transpose(g_rows, rw, valid_row)                                  # (g * w)^T [H, rows]
-        x_t = G.dequant_transpose(rx, rsf, valid_row)
-        d_w2 = G.gemm_kgrouped(dy_t, act_t, seg_off)                                        # [El, H, I]
-        d_w13 = G.gemm_kgrouped(dh_t, x_t, seg_off)                                         # [El, 2I, H]
+        d_out = d_out.contiguous()
+        dxs, dws, d_w2, d_w13 = [], [], None, None
+        for c, handle in enumerate(ctx.handles):
+            rx, rsf, recv_w, h, tile_group, valid_row = ctx.saved_tensors[6 * c:6 * c + 6]
+            seg_off = G.segment_offsets(handle.psum_num_recv_tokens_per_expert)
+            rw = recv_w.contiguous()
+            # backward of the weighted combine: every expert row receives its token's gradient g (cached dispatch)
+            g_rows, _, _, _, _ = buf.dispatch(d_out[bounds[c]:bounds[c + 1]], handle=handle, fused_fp8_cast=False, num_sms=layer.num_sms)
+            # down projection on the UNWEIGHTED gradient: d loss / d weight of a row is <g W2, activation> (= <g, y>, so the
+            # expert outputs need not be kept), and the weight is applied inside the SwiGLU backward kernel.  Padding rows of
+            # g_rows hold stale data; every consumer masks them.
+            d_act_u = G.grouped_gemm_nt(g_rows, w2_t, tile_group, buffer=buf)                    # [rows, I]
+            dh, dh_t, act_t, d_w_rows = G.swiglu_bwd(d_act_u, h, valid_row, row_weight=rw)
+            # up projection: the gradient rows go into the combine region and travel home (backward of dispatch)
+            d_recv = buf.get_combine_buffer(handle)
+            G.grouped_gemm_nt(dh, w13_t, tile_group, out=d_recv, buffer=buf)
+            dx, d_topk_w, _ = buf.combine(d_recv, handle, topk_weights=d_w_rows, num_sms=layer.num_sms)
+            # weight gradients: one K-grouped GEMM per weight tensor, reduction over the rows of every expert segment
+            dy_t = G.weighted_transpose(g_rows, rw, valid_row)                                  # (g * w)^T [H, rows]
+            x_t = G.dequant_transpose(rx, rsf, valid_row)
+            g2 = G.gemm_kgrouped(dy_t, act_t, seg_off)                                          # [El, H, I]
+            g13 = G.gemm_kgrouped(dh_t, x_t, seg_off)                                           # [El, 2I, H]
+            d_w2 = g2 if d_w2 is None else d_w2 + g2
+            d_w13 = g13 if d_w13 is None else d_w13 + g13
+            dxs.append(dx)
+            dws.append(d_topk_w)
+        dx = dxs[0] if len(dxs) == 1 else torch.cat(dxs)
+        d_topk_w = dws[0] if len(dws) == 1 else torch.cat(dws)
         return dx, d_topk_w, d_w13, d_w2, None, None
 
 
@@ -73,25 +128,38 @@ class FusedMoE(nn.Module):
 
     ``w13 [E_local, 2 * intermediate, hidden]`` (gate rows then up rows) and ``w2 [E_local, hidden, intermediate]`` are
     bf16 master weights; the forward pass runs on e4m3 copies with 128 x 128 block scales that are refreshed
-    whenever the master weights change.  ``forward(x [T, hidden] bf16, topk_idx [T, K], topk_weights [T, K] fp32)``
+    whenever the master weights change.  ``num_chunks > 1`` cuts the batch into chunks whose dispatch / combine run under
+    the GEMMs of the neighbouring chunks (see ``_MoEFunction``).  ``forward(x [T, hidden] bf16, topk_idx [T, K], topk_weights [T, K] fp32)``
     returns ``sum_k w_k * FFN_{e_k}(x)`` as bf16 ``[T, hidden]``.
     """
 
     def __init__(self, buffer: ElasticBuffer, num_experts: int, hidden: int, intermediate: int, init_std: float = 0.02,
-                 num_sms: int = 0, device='cuda', copy_saved_rows: bool = False):
+                 num_sms: int = 0, device='cuda', copy_saved_rows: bool = True, num_chunks: int = 1):
         super().__init__()
         assert num_experts % buffer.num_ranks == 0 and hidden % 128 == 0 and intermediate % 128 == 0
         assert buffer.enable_expand, 'construct the buffer with enable_expand=True, expert_alignment=128'
         self.buffer, self.num_experts, self.hidden, self.intermediate = buffer, num_experts, hidden, intermediate
         self.num_sms = num_sms
-        # False: the backward pass reads the dispatched rows in place (valid while no other dispatch but this layer's own
-        # backward one runs on the buffer in between); True: they are copied, as needed when several layers share the buffer
+        # True (default): the dispatched rows kept for the backward pass are copied out of the receive slot, which later
+        # dispatches on the same buffer (other layers, micro-batches, gradient accumulation) overwrite.  False saves the copy
+        # and is only valid while no dispatch but this layer's own backward one runs on the buffer in between.
         self.copy_saved_rows = copy_saved_rows
+        # > 1: the batch is processed as that many pipelined chunks (communication of one chunk under the GEMMs of another)
+        self.num_chunks = num_chunks
         el = num_experts // buffer.num_ranks
         self.w13 = nn.Parameter((torch.randn(el, 2 * intermediate, hidden, device=device) * init_std).bfloat16())
         self.w2 = nn.Parameter((torch.randn(el, hidden, intermediate, device=device) * init_std).bfloat16())
         self._fp8 = None
         self._t = None
+
+    def sm_split(self, pipelined: bool):
+        """(SMs of the communication kernels, SMs of the GEMMs; 0 = all).  In the pipelined schedule the two run at the same
+        time, so the GEMMs leave the communication kernels their SMs."""
+        if not pipelined:
+            return self.num_sms, 0
+        total = torch.cuda.get_device_properties('cuda').multi_processor_count
+        comm = self.num_sms if self.num_sms else 24
+        return comm, max(1, total - comm)
 
     def _versions(self):
         return (self.w13._version, self.w2._version, self.w13.data_ptr(), self.w2.data_ptr())

@@ -12,16 +12,23 @@ from .. import _native
 BLOCK_M = 128   # rows of one output tile; expert segments of the grouped GEMM are aligned to it
 
 
-def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, num_sms: int = 0) -> torch.Tensor:
-    """``a [M, K] @ b [N, K]^T -> bf16 [M, N]`` (bf16 operands, fp32 accumulation in tensor memory)."""
-    return _native.load().gemm_nt(a, b, None, None, None, out, num_sms)
+def _core_of(buffer):
+    return None if buffer is None else buffer.core
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, num_sms: int = 0, buffer=None) -> torch.Tensor:
+    """``a [M, K] @ b [N, K]^T -> bf16 [M, N]`` (bf16 operands, fp32 accumulation in tensor memory).  With ``buffer``
+    (an ``ElasticBuffer``) a pipeline wait that runs out inside the kernel is reported through that buffer's status
+    block and time limit, so ``buffer.check_status()`` raises and poisons it like any other failed device wait."""
+    return _native.load().gemm_nt(a, b, None, None, None, out, num_sms, None, 0, None, _core_of(buffer))
 
 
 def grouped_gemm_nt(a: torch.Tensor, b: torch.Tensor, tile_group: torch.Tensor, out: Optional[torch.Tensor] = None,
-                    sfa: Optional[torch.Tensor] = None, sfb: Optional[torch.Tensor] = None, num_sms: int = 0) -> torch.Tensor:
+                    sfa: Optional[torch.Tensor] = None, sfb: Optional[torch.Tensor] = None, num_sms: int = 0, buffer=None) -> torch.Tensor:
     """Every 128-row tile ``t`` of ``a`` is multiplied by ``b[tile_group[t]]`` (``-1`` skips the tile).  bf16 operands,
-    or e4m3 operands with ``sfa [M, K/128]`` and ``sfb [G, N/128, K/128]`` fp32 block scales."""
-    return _native.load().gemm_nt(a, b, sfa, sfb, tile_group, out, num_sms)
+    or e4m3 operands with ``sfa [M, K/128]`` and ``sfb [G, N/128, K/128]`` fp32 block scales.  ``buffer``: see
+    :func:`gemm_nt`."""
+    return _native.load().gemm_nt(a, b, sfa, sfb, tile_group, out, num_sms, None, 0, None, _core_of(buffer))
 
 
 def quantize_weight_blocks(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:

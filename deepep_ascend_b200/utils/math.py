@@ -123,3 +123,24 @@ def count_bytes(*tensors) -> int:
         elif t is not None:
             total += t.numel() * t.element_size()
     return total
+
+
+def logfmt10_roundtrip(x: torch.Tensor) -> torch.Tensor:
+    """What a bf16 tensor ``[..., H]`` (H a multiple of 128) looks like after the LogFMT-10 coding of the low-latency
+    combine (``use_logfmt=True``): per group of 128 channels the magnitudes are rounded to 510 equal steps of log2
+    between the smallest non-zero and the largest magnitude of the group (at most 32 octaves), the sign is kept, zeros
+    stay zero.  Returns fp32.  The device code evaluates log2 / exp2 with the hardware approximations, so single values can
+    land on a neighbouring step; compare with a tolerance of one step."""
+    xf = x.float()
+    g = xf.reshape(*xf.shape[:-1], xf.shape[-1] // 128, 128)
+    mag = g.abs()
+    amax = mag.amax(dim=-1, keepdim=True)
+    amin = torch.where(mag > 0, mag, torch.full_like(mag, float('inf'))).amin(dim=-1, keepdim=True)
+    hi = torch.log2(amax.clamp_min(1e-38))
+    lo = torch.maximum(torch.log2(amin.clamp(1e-38, 3e38)), hi - 32.0)
+    step = (hi - lo) / 510.0
+    inv = torch.where(step > 0, 1.0 / step, torch.zeros_like(step))
+    code = torch.round(((torch.log2(mag.clamp_min(1e-38)) - lo) * inv).clamp(0, 510))
+    dec = torch.exp2(lo + code * step)
+    out = torch.where(mag > 0, torch.sign(g) * dec, torch.zeros_like(g))
+    return out.reshape(xf.shape)

@@ -87,3 +87,39 @@ def test_low_latency_roundtrip(R, T, H, E, K, mode, split):
                 torch.testing.assert_close(res[s].cpu().float(), want.bfloat16().float(), atol=3e-2, rtol=2e-2)
     finally:
         world.destroy()
+
+
+@pytest.mark.parametrize('R,T,H,E,K', [(2, 16, 256, 8, 2), (4, 33, 2048, 32, 4), (8, 32, 7168, 64, 8)])
+@pytest.mark.parametrize('split', [False, True])
+def test_low_latency_combine_logfmt(R, T, H, E, K, split):
+    """Combine with LogFMT-10 rows on the wire: the result is the weighted sum of the CODED rows (stated in plain PyTorch by
+    ``logfmt10_roundtrip``) and stays within the accuracy the reference asks of this mode (calc_diff against the exact
+    sum, tests/legacy/test_low_latency.py:178-181).  Zero rows and rows of one repeated value are coded exactly."""
+    from deepep_ascend_b200.backends.emulated import EmulatedWorld
+    from deepep_ascend_b200.buffers.elastic import ElasticBuffer
+    from deepep_ascend_b200.utils.math import calc_diff, logfmt10_roundtrip
+    M = T + 1
+    extra = ElasticBuffer.get_low_latency_size_hint(M, H, R, E, K)
+    world = EmulatedWorld(R, num_max_tokens_per_rank=M, hidden=H, num_topk=K, extra_bytes=extra, num_gpu_timeout_secs=5)
+    try:
+        for it in range(3):
+            xs, idxs, ws = _inputs(R, T, H, E, K, seed=40 + it)
+            for x in xs:
+                x[0] = 0                 # an all-zero row
+                x[1, :128] = -1.5        # a group with a single magnitude
+            outs = world.low_latency_dispatch(xs, idxs, M, E, use_fp8=False, split_phases=split)
+            res = world.low_latency_combine([o[0] for o in outs], idxs, ws, [o[2] for o in outs], split_phases=split, use_logfmt=True)
+            torch.cuda.synchronize()
+            for r in range(R):
+                world.buffers[r].check_status()
+                wsum = (ws[r].cpu() * (idxs[r].cpu() >= 0)).sum(dim=1, keepdim=True)
+                coded = logfmt10_roundtrip(xs[r].cpu()) * wsum
+                exact = xs[r].cpu().float() * wsum
+                got = res[r].cpu().float()
+                assert bool(torch.isfinite(got).all())
+                assert calc_diff(got, exact) < 2e-5, calc_diff(got, exact)
+                torch.testing.assert_close(got, coded, atol=3e-2, rtol=3e-2)
+                assert bool((got[0] == 0).all())
+                torch.testing.assert_close(got[1, :128], (-1.5 * wsum[1]).expand(128).bfloat16().float(), atol=0, rtol=1e-2)
+    finally:
+        world.destroy()

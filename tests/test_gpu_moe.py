@@ -6,9 +6,9 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize('copy_rows', [False, True])
+@pytest.mark.parametrize('copy_rows,chunks', [(False, 1), (True, 1), (True, 2), (True, 4)])
 @pytest.mark.parametrize('T,H,I,E,K', [(200, 256, 128, 4, 2), (512, 1024, 512, 8, 4)])
-def test_fused_moe_forward_backward(T, H, I, E, K, copy_rows):
+def test_fused_moe_forward_backward(T, H, I, E, K, copy_rows, chunks):
     from deepep_ascend_b200 import ElasticBuffer
     from deepep_ascend_b200.models.moe import FusedMoE, moe_reference
     from deepep_ascend_b200.utils.math import calc_diff
@@ -16,7 +16,7 @@ def test_fused_moe_forward_backward(T, H, I, E, K, copy_rows):
     buf = ElasticBuffer(None, num_max_tokens_per_rank=T, hidden=H, num_topk=K, enable_expand=True, num_experts=E,
                         expert_alignment=128)
     try:
-        layer = FusedMoE(buf, E, H, I, init_std=0.05, num_sms=16, copy_saved_rows=copy_rows)
+        layer = FusedMoE(buf, E, H, I, init_std=0.05, num_sms=16, copy_saved_rows=copy_rows, num_chunks=chunks)
         x = torch.randn(T, H, device='cuda').bfloat16().requires_grad_(True)
         scores = torch.softmax(torch.randn(T, E, device='cuda'), dim=-1)
         w, idx = scores.topk(K, dim=-1)
@@ -87,3 +87,79 @@ def test_backward_elementwise_kernels(rows, H, I):
     x_t = G.dequant_transpose(q, sf, valid)
     ref_x = torch.where(vm, per_token_cast_back(q, sf).bfloat16(), torch.zeros_like(x))
     assert torch.equal(x_t, ref_x.t().contiguous())
+
+
+def test_two_layers_share_one_buffer():
+    """Two layers on ONE buffer, both forwards before any backward (what gradient accumulation and pipeline micro-batches
+    do): the rows a layer keeps for its backward pass must survive the other layer's dispatches."""
+    from deepep_ascend_b200 import ElasticBuffer
+    from deepep_ascend_b200.models.moe import FusedMoE, moe_reference
+    from deepep_ascend_b200.utils.math import calc_diff
+    T, H, I, E, K = 256, 512, 256, 4, 2
+    torch.manual_seed(3)
+    buf = ElasticBuffer(None, num_max_tokens_per_rank=T, hidden=H, num_topk=K, enable_expand=True, num_experts=E, expert_alignment=128)
+    try:
+        layers = [FusedMoE(buf, E, H, I, init_std=0.05, num_sms=8) for _ in range(2)]
+        xs, ws, idxs, outs, gs = [], [], [], [], []
+        for layer in layers:
+            x = torch.randn(T, H, device='cuda').bfloat16().requires_grad_(True)
+            w, idx = torch.softmax(torch.randn(T, E, device='cuda'), dim=-1).topk(K, dim=-1)
+            w = w.clone().requires_grad_(True)
+            outs.append(layer(x, idx, w))
+            xs.append(x), ws.append(w), idxs.append(idx), gs.append(torch.randn(T, H, device='cuda').bfloat16())
+        for out, g in zip(outs, gs):
+            out.backward(g)
+        torch.cuda.synchronize()
+        buf.check_status()
+        for layer, x, w, idx, g in zip(layers, xs, ws, idxs, gs):
+            xr, wr = x.detach().float().requires_grad_(True), w.detach().clone().requires_grad_(True)
+            w13, w2 = layer.w13.detach().float().requires_grad_(True), layer.w2.detach().float().requires_grad_(True)
+            moe_reference(xr, idx, wr, w13, w2).backward(g.float())
+            assert calc_diff(x.grad.float(), xr.grad) < 3e-3 and calc_diff(w.grad, wr.grad) < 3e-3
+            assert calc_diff(layer.w13.grad.float(), w13.grad) < 3e-3 and calc_diff(layer.w2.grad.float(), w2.grad) < 3e-3
+    finally:
+        buf.destroy()
+
+
+@pytest.mark.parametrize('R', [2, 4])
+def test_moe_forward_on_virtual_ranks(R):
+    """The forward data flow of the layer across several ranks on one GPU (every collective of the virtual ranks is one
+    cooperative launch): expand-layout FP8 dispatch -> grouped FP8 GEMMs with SwiGLU -> fused weighted combine, against the
+    plain PyTorch layer that holds all experts."""
+    from deepep_ascend_b200.backends.emulated import EmulatedWorld
+    from deepep_ascend_b200.models.moe import moe_reference
+    from deepep_ascend_b200.ops import gemm as G
+    from deepep_ascend_b200.utils.math import calc_diff
+    T, H, I, K = 160, 512, 256, 4
+    E = 4 * R
+    El = E // R
+    torch.manual_seed(R)
+    world = EmulatedWorld(R, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=True, enable_expand=True,
+                          num_experts=E, expert_alignment=128)
+    try:
+        w13 = (torch.randn(E, 2 * I, H, device='cuda') * 0.05).bfloat16()
+        w2 = (torch.randn(E, H, I, device='cuda') * 0.05).bfloat16()
+        xs = [torch.randn(T - r, H, device='cuda').bfloat16() for r in range(R)]
+        tk = [torch.softmax(torch.randn(T - r, E, device='cuda'), dim=-1).topk(K, dim=-1) for r in range(R)]
+        ws, idxs = [t[0].contiguous() for t in tk], [t[1].contiguous() for t in tk]
+        outs = world.dispatch(xs, idxs, ws, E, num_sms=6, expert_alignment=128, do_expand=True)
+        ys, handles = [], []
+        for r, ((rx, rsf), _, recv_w, handle) in enumerate(outs):
+            q13, s13 = G.quantize_weight_blocks(w13[r * El:(r + 1) * El].float())
+            q2, s2 = G.quantize_weight_blocks(w2[r * El:(r + 1) * El].float())
+            tile_group, _ = G.expert_tile_groups(handle.psum_num_recv_tokens_per_expert, handle.num_rows)
+            h = G.grouped_gemm_nt(rx, q13, tile_group, sfa=rsf, sfb=s13, buffer=world.buffers[r])
+            a2, sf2 = G.swiglu_quant(h)
+            y = world.buffers[r].get_combine_buffer(handle)
+            G.grouped_gemm_nt(a2, q2, tile_group, out=y, sfa=sf2, sfb=s2, buffer=world.buffers[r])
+            ys.append(y)
+            handles.append(handle)
+        res = world.combine(ys, handles, weighted=True, num_sms=6)
+        torch.cuda.synchronize()
+        for r in range(R):
+            world.buffers[r].check_status()
+            ref = moe_reference(xs[r].float(), idxs[r], ws[r], w13.float(), w2.float())
+            d = calc_diff(res[r][0].float(), ref)
+            assert d < 3e-3, (r, d)
+    finally:
+        world.destroy()

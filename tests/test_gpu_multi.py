@@ -56,7 +56,51 @@ def _worker(rank: int, world: int, port: int):
             assert torch.equal(out.view(torch.int16), acc.bfloat16().view(torch.int16))
             valid = idx >= 0
             assert torch.equal(back_w[valid], w[valid])
+        # ---- back to back without any host synchronisation: ten dispatch -> combine rounds with different data in flight
+        # behind one another (receive slots and the two combine input regions are recycled while peers may still be busy
+        # with the previous round); everything is checked at the end
+        t = T - rank
+        rounds = []
+        for rnd in range(10):
+            torch.manual_seed(1000 + rnd * 10 + rank)
+            x = torch.randn(t, H, device='cuda').bfloat16()
+            w, idx = torch.softmax(torch.randn(t, E, device='cuda'), -1).topk(K, -1)
+            (rx, rsf), ridx, rw, handle, _ = buf.dispatch(x, idx, w, num_experts=E, num_sms=8, do_cpu_sync=False)
+            n = handle.psum_num_recv_tokens_per_scaleup_rank[-1:]
+            y = buf.get_combine_buffer(handle)
+            # "expert": dequantise the received row and scale it by (1 + local expert hits); rows past the valid count are unused
+            hits = (ridx >= 0).sum(dim=1, keepdim=True).float()
+            y.copy_((rx.float().view(rx.shape[0], -1, 128) * rsf.unsqueeze(-1)).view(rx.shape[0], H) * hits)
+            out, _, _ = buf.combine(y, handle, num_sms=8)
+            rounds.append((x, idx, out))
+        torch.cuda.synchronize()
+        buf.check_status()
+        from deepep_ascend_b200.utils.math import per_token_cast_back
+        for x, idx, out in rounds:
+            xq = per_token_cast_back(*per_token_cast_to_fp8(x.cpu())).cuda()
+            valid = (idx >= 0).sum(dim=1, keepdim=True).float()          # every valid selection contributes its row once
+            torch.testing.assert_close(out.float(), xq.float() * valid, atol=0.13, rtol=0.02)
         buf.barrier(with_cpu_sync=True)
+        buf.destroy()
+        # ---- expand layout with aligned, zero-padded expert segments and the fused weighted reduce
+        A = 16
+        buf = ep.ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=False, enable_expand=True,
+                               num_experts=E, expert_alignment=A, num_gpu_timeout_secs=10, num_cpu_timeout_secs=30)
+        torch.manual_seed(77 + rank)
+        x = torch.randn(T - rank, H, device='cuda').bfloat16()
+        w, idx = torch.softmax(torch.randn(T - rank, E, device='cuda'), -1).topk(K, -1)
+        rx, ridx, rw, handle, _ = buf.dispatch(x, idx, w, num_experts=E, num_sms=8, do_expand=True, expert_alignment=A, do_zero_padding=True)
+        assert ridx is None and rw.dim() == 1 and rx.shape[0] == handle.num_expanded_tokens
+        ends = handle.psum_num_recv_tokens_per_expert.long().cpu()
+        starts = torch.cat([torch.zeros(1, dtype=torch.long), (ends[:-1] + A - 1) // A * A])
+        for j in range(E // world):
+            assert handle.num_recv_tokens_per_expert_list[j] % A == 0
+            pad = rx[int(ends[j]):int((ends[j] + A - 1) // A * A)]
+            assert bool((pad == 0).all()), 'alignment padding must be zeroed by the kernel'
+            assert int(ends[j] - starts[j]) == int(handle.num_unaligned_recv_tokens_per_expert[j])
+        out, _, _ = buf.combine(rx, handle, weighted=True, num_sms=8)      # identity experts: sum_k w_k x
+        torch.testing.assert_close(out.float(), x.float() * w.sum(-1, keepdim=True), atol=3e-2, rtol=2e-2)
+        buf.check_status()
         buf.destroy()
     finally:
         dist.destroy_process_group()
@@ -80,7 +124,7 @@ def _worker_misc(rank: int, world: int, port: int):
         M, H, E, K = 64, 2048, 8 * world, 4
         extra = ep.ElasticBuffer.get_low_latency_size_hint(M, H, world, E, K) + (96 << 20)
         buf = ep.ElasticBuffer(group, num_max_tokens_per_rank=256, hidden=H, num_topk=K, extra_bytes=extra,
-                               num_gpu_timeout_secs=10, num_cpu_timeout_secs=30)
+                               num_gpu_timeout_secs=10, num_cpu_timeout_secs=30, num_cpu_bytes=1 << 20)
         # ---- all-gather / reduce-scatter session
         buf.agrs_set_config(64 << 20)
         buf.create_agrs_session()
@@ -114,13 +158,39 @@ def _worker_misc(rank: int, world: int, port: int):
             buf.pp_send(send, nxt)
         torch.cuda.synchronize()
         assert bool((recv == prv).all())
-        # ---- Engram
+        # ---- pipeline: a random schedule (same on every rank) of directions and sizes, with random GPU-side skew in
+        # front of the calls; every received tensor must hold what the neighbour sent in that step
+        import random
+        rng = random.Random(4242)
+        for step in range(12):
+            forward, n = rng.random() < 0.5, rng.choice([1, 257, 4096, 65536])
+            skew = [rng.randint(0, 3) * 200_000 for _ in range(world)]
+            dst, src = (nxt, prv) if forward else (prv, nxt)
+            send = torch.full((n,), float(rank * 100 + step), device='cuda')
+            recv = torch.empty_like(send)
+            if skew[rank]:
+                torch.cuda._sleep(skew[rank])
+            if rank % 2 == 0:
+                buf.pp_send(send, dst)
+                buf.pp_recv(recv, src)
+            else:
+                buf.pp_recv(recv, src)
+                buf.pp_send(send, dst)
+            torch.cuda.synchronize()
+            assert bool((recv == src * 100 + step).all()), (step, forward, n)
+        # ---- Engram: the tables live in the CPU segments (pinned host memory that every rank's GPU maps); scales come from
+        # a table replicated on every rank
         table = torch.full((100, 256), float(rank), device='cuda', dtype=torch.bfloat16) + torch.arange(100, device='cuda').unsqueeze(1).bfloat16()
-        buf.engram_write(table)
+        sf_table = (torch.arange(100 * world * 2, device='cuda', dtype=torch.float32) * 0.5).view(100 * world, 2)
+        buf.engram_write(table, sf_table)
+        assert buf._engram['cpu']
         idx = torch.randint(0, 100 * world, (50, 2), device='cuda', dtype=torch.int32)
-        fetched, _ = buf.engram_fetch(idx)()
-        want = (idx // 100).float().unsqueeze(-1) + (idx % 100).float().unsqueeze(-1)
-        assert torch.equal(fetched.view(50, 2, 256).float(), want.expand(50, 2, 256).bfloat16().float())
+        for col_major in (False, True):
+            fetched, fetched_sf = buf.engram_fetch(idx, use_tma_aligned_col_major_sf=col_major)()
+            want = (idx // 100).float().unsqueeze(-1) + (idx % 100).float().unsqueeze(-1)
+            assert torch.equal(fetched.view(50, 2, 256).float(), want.expand(50, 2, 256).bfloat16().float())
+            assert torch.equal(fetched_sf, sf_table[idx.long().view(-1)].view(50, 4))
+            assert fetched_sf.stride() == ((1, 52) if col_major else (4, 1))
         # ---- low latency (also in hook mode) and its use through the legacy API names
         torch.manual_seed(rank)
         xt = torch.randn(M - rank, H, device='cuda').bfloat16()
@@ -209,3 +279,63 @@ def test_multi_process_fused_tp_gemm(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f'needs {world} GPUs')
     mp.spawn(_worker_tp, args=(world, _free_port()), nprocs=world, join=True)
+
+
+def _worker_moe(rank: int, world: int, port: int):
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    try:
+        import deepep_ascend_b200 as ep
+        from deepep_ascend_b200.models.moe import FusedMoE, moe_reference
+        from deepep_ascend_b200.utils.math import calc_diff
+        group = dist.new_group(list(range(world)))
+        T, H, I, K = 384, 512, 256, 4
+        E = 4 * world
+        buf = ep.ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, enable_expand=True, num_experts=E,
+                               expert_alignment=128, num_gpu_timeout_secs=10, num_cpu_timeout_secs=30)
+        torch.manual_seed(5 + rank)
+        layer = FusedMoE(buf, E, H, I, init_std=0.05, num_sms=8)
+        # every rank needs all experts' weights for the reference
+        def gather(p):
+            parts = [torch.empty_like(p.data) for _ in range(world)]
+            dist.all_gather(parts, p.data.contiguous(), group=group)
+            return torch.cat(parts).float()
+        w13_all, w2_all = gather(layer.w13), gather(layer.w2)
+        for chunks in (1, 3):
+            layer.num_chunks = chunks
+            layer.zero_grad()
+            x = torch.randn(T - 5 * rank, H, device='cuda').bfloat16().requires_grad_(True)
+            wts, idx = torch.softmax(torch.randn(x.shape[0], E, device='cuda'), dim=-1).topk(K, dim=-1)
+            idx[::9, 1] = -1
+            wts = wts.clone().requires_grad_(True)
+            out = layer(x, idx, wts)
+            g = torch.randn_like(out)
+            out.backward(g)
+            torch.cuda.synchronize()
+            buf.check_status()
+            xr, wr = x.detach().float().requires_grad_(True), wts.detach().clone().requires_grad_(True)
+            w13r, w2r = w13_all.clone().requires_grad_(True), w2_all.clone().requires_grad_(True)
+            ref = moe_reference(xr, idx, wr, w13r, w2r)
+            ref.backward(g.float())
+            # weight gradients: every rank's tokens contribute to every expert
+            dist.all_reduce(w13r.grad, group=group)
+            dist.all_reduce(w2r.grad, group=group)
+            El = E // world
+            sl = slice(rank * El, (rank + 1) * El)
+            for name, got, want in (('out', out.float(), ref), ('dx', x.grad.float(), xr.grad), ('dw', wts.grad, wr.grad),
+                                    ('d_w2', layer.w2.grad.float(), w2r.grad[sl]), ('d_w13', layer.w13.grad.float(), w13r.grad[sl])):
+                d = calc_diff(got, want)
+                assert d < 3e-3, (chunks, name, d)
+        buf.destroy()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('world', [2, 8])
+def test_multi_process_fused_moe(world):
+    """The fused MoE layer on several GPUs, as one pass and as a three-chunk pipeline: output and all four gradients against
+    the plain PyTorch layer that holds every expert's weights."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f'needs {world} GPUs')
+    mp.spawn(_worker_moe, args=(world, _free_port()), nprocs=world, join=True)
