@@ -126,7 +126,9 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
     this GPU's address space, behind the device buffer: Engram storage that does not fit the GPU region goes there
     (deep_ep/buffers/elastic.py:511-516, csrc/kernels/backend/symmetric.hpp:145-186).  One NVLink domain has no NIC
     path, so the RDMA-only arguments must keep their defaults: ``num_allocated_qps=0`` and ``sl_idx=3`` (anything else
-    raises ``ValueError`` instead of being silently dropped).
+    raises ``ValueError`` instead of being silently dropped).  ``symmetric_memory`` selects how the buffer is allocated and
+    shared with the peers: ``'ipc'`` = ``cudaMalloc`` + ``cudaIpc`` handles, ``'vmm'`` = ``cuMemCreate`` / ``cuMemMap`` with the
+    allocation's POSIX file descriptor passed over a Unix-domain socket (csrc/kernels/backend/symmetric.hpp:22-87 of the reference).
     """
 
     def __init__(self, group: Optional[dist.ProcessGroup], num_bytes: Optional[int] = None, num_cpu_bytes: int = 0,
@@ -136,7 +138,10 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
                  num_cpu_timeout_secs: float = 300, num_gpu_timeout_secs: float = 100, explicitly_destroy: bool = False,
                  enable_expand: bool = False, num_experts: int = 0, expert_alignment: int = 1, num_recv_slots: int = 2,
                  extra_bytes: int = 0, zero_copy: bool = True, low_latency_shrink: bool = False,
-                 _virtual: Optional[Tuple[int, int]] = None):
+                 symmetric_memory: str = 'ipc', _virtual: Optional[Tuple[int, int]] = None):
+        if symmetric_memory not in ('ipc', 'vmm'):
+            raise ValueError("symmetric_memory must be 'ipc' (cudaMalloc + cudaIpc handles) or 'vmm' (CUDA virtual memory "
+                             "allocation shared as a POSIX file descriptor)")
         if num_allocated_qps != 0 or sl_idx != 3:
             raise ValueError('num_allocated_qps / sl_idx configure RDMA queue pairs; a single NVLink domain has none '
                              '(leave them at their defaults)')
@@ -208,8 +213,10 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
             print(f'[EP rank {self.rank_idx}] symmetric buffer {total / 2**20:.1f} MiB '
                   f'(MoE regions {moe_bytes / 2**20:.1f} MiB, capacity {self.regions.capacity_rows} rows, '
                   f'{num_recv_slots} receive slots, {num_cpu_bytes / 2**20:.1f} MiB mapped host memory)', flush=True)
+        extra_args = (int(num_cpu_bytes), True) if symmetric_memory == 'vmm' else ((int(num_cpu_bytes),) if num_cpu_bytes else ())
         self.core = self._C.ElasticBuffer(self.rank_idx, self.num_ranks, total, float(num_gpu_timeout_secs),
-                                          float(num_cpu_timeout_secs), int(num_cpu_bytes))
+                                          float(num_cpu_timeout_secs), *extra_args)
+        self.symmetric_memory = symmetric_memory
         if _virtual is None:
             if self.num_ranks > 1:
                 handles = all_gather_object(group, bytes(self.core.get_local_ipc_handle()))
@@ -221,6 +228,8 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
                 dist.barrier(group=group)
             if num_cpu_bytes > 0:
                 self.core.unlink_cpu_segment_name()      # every rank has mapped it; the mappings keep it alive
+            if symmetric_memory == 'vmm':
+                self.core.finish_export()                # every peer has fetched the descriptor
         self.comm_stream = _get_comm_stream()
         # combine launches on this stream; it is the communication stream unless a caller that overlaps dispatches of one
         # batch with combines of another (a pipelined MoE layer) gives combine a stream of its own

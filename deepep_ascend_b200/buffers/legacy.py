@@ -93,6 +93,27 @@ class Buffer:
     def get_comm_stream(self):
         return self._elastic.get_comm_stream() if self._elastic is not None else torch.cuda.current_stream()
 
+    def get_local_ipc_handle(self) -> bytes:
+        """What a peer process needs to map this rank's buffer (a cudaIpc handle, or the descriptor socket of a VMM
+        allocation).  The exchange itself happens when the buffer is built; this is for inspection and external set-ups
+        (deep_ep/buffers/legacy.py:74-131 of the reference)."""
+        assert self._elastic is not None and not self._elastic.is_cpu, 'the buffer is built on first use (or pass its shape to the constructor)'
+        return bytes(self._elastic.core.get_local_ipc_handle())
+
+    def get_local_buffer_tensor(self, dtype: torch.dtype = torch.uint8, offset: int = 0) -> torch.Tensor:
+        """The data area of this rank's symmetric buffer (everything behind the workspace) as a flat tensor of ``dtype``,
+        starting ``offset`` bytes in."""
+        e = self._elastic
+        assert e is not None and not e.is_cpu
+        start = e._C.get_workspace_bytes() + offset
+        n = (e.num_bytes - start) // dtype.itemsize
+        return e.core.view(start, [n], [1], dtype)
+
+    def sync(self, *args, **kwargs) -> None:
+        """Peers are mapped when the buffer is built (a collective step of the constructor), so there is nothing left to
+        synchronise; kept so that code written for the two-step set-up of the reference keeps working."""
+        return None
+
     def destroy(self) -> None:
         if self._elastic is not None:
             self._elastic.destroy()

@@ -184,9 +184,20 @@ class LowLatencyMixin:
         return call.out, event, hook
 
     def get_next_low_latency_combine_buffer(self, handle: tuple) -> torch.Tensor:
-        """A bf16 ``[E_local, ranks * max_tokens, H]`` tensor for the expert outputs of the next combine."""
+        """The bf16 ``[E_local, ranks * max_tokens, H]`` tensor that the expert outputs of the next combine should be
+        written to.  The combine kernel reads its input rows in place wherever they live, so no copy is saved or added by
+        using it; what it gives is ONE allocation with a stable address that is reused by every call (the two sets alternate
+        like the kernels' own buffer sets), which is what a captured CUDA graph needs."""
         _, _, M, H, E = handle
-        return torch.empty((E // self.num_ranks, self.num_ranks * M, H), dtype=torch.bfloat16, device='cuda')
+        ll = self._ll
+        assert ll is not None, 'a handle comes from low_latency_dispatch, which sets the low-latency regions up'
+        if 'combine_x' not in ll:
+            shape = (E // self.num_ranks, self.num_ranks * M, H)
+            ll['combine_x'] = [torch.empty(shape, dtype=torch.bfloat16, device='cuda') for _ in range(2)]
+            ll['combine_x_next'] = 0
+        buf = ll['combine_x'][ll['combine_x_next'] & 1]
+        ll['combine_x_next'] += 1
+        return buf
 
     # ------------------------------------------------------------------------------------------ shrink mode
     low_latency_shrink = False

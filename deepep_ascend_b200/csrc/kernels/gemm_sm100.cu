@@ -395,16 +395,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 // this warp promotes one half of the tile's columns for its 32 rows
                 constexpr int kCols = kBlockN / 2;
                 const int col_half = (warp - kEpiWarp0) >> 2;
-                float sum[kCols];
+                uint64_t sum2[kCols / 2];   // fp32 pairs (columns 2i, 2i + 1)
 #pragma unroll
-                for (int i = 0; i < kCols; ++i) sum[i] = 0.f;
+                for (int i = 0; i < kCols / 2; ++i) sum2[i] = 0ull;
                 const int num_kb_sf = (g.K + 127) / 128, num_nb_sf = (g.N + 127) / 128;
                 // the B scale block of this warp's columns (a half tile never straddles two 128-column blocks)
                 const int nb_sf = min((n0 + col_half * kCols) / 128, num_nb_sf - 1);
                 const float* sfb = g.sfb + (static_cast<int64_t>(grp) * num_nb_sf + nb_sf) * num_kb_sf;
                 float scale_next = (row < g.M ? __ldg(g.sfa + row * g.sfa_stride_row) : 0.f) * __ldg(sfb);
                 for (int kb = 0; kb < num_k && ok; ++kb) {
-                    const float scale = scale_next;
+                    const uint64_t scale2 = umma::pack_f32x2(__float_as_uint(scale_next), __float_as_uint(scale_next));
                     if (kb + 1 < num_k)
                         scale_next = (row < g.M ? __ldg(g.sfa + row * g.sfa_stride_row + (kb + 1) * g.sfa_stride_kb) : 0.f) * __ldg(sfb + kb + 1);
                     ok = wait_bar(&sm->tmem_full[acc], acc_phase, sm, g, 5);
@@ -422,9 +422,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            sum[i] = fmaf(scale, __uint_as_float(r0[i]), sum[i]);
-                            sum[32 + i] = fmaf(scale, __uint_as_float(r1[i]), sum[32 + i]);
+                        for (int i = 0; i < 16; ++i) {
+                            umma::fma_f32x2(sum2[i], umma::pack_f32x2(r0[2 * i], r0[2 * i + 1]), scale2);
+                            umma::fma_f32x2(sum2[16 + i], umma::pack_f32x2(r1[2 * i], r1[2 * i + 1]), scale2);
                         }
                     } else {
                         // 128 columns in two steps of two loads each (64 loaded values live at a time)
@@ -440,9 +440,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                                 if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
                             }
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                sum[c * 64 + i] = fmaf(scale, __uint_as_float(r0[i]), sum[c * 64 + i]);
-                                sum[c * 64 + 32 + i] = fmaf(scale, __uint_as_float(r1[i]), sum[c * 64 + 32 + i]);
+                            for (int i = 0; i < 16; ++i) {
+                                umma::fma_f32x2(sum2[c * 32 + i], umma::pack_f32x2(r0[2 * i], r0[2 * i + 1]), scale2);
+                                umma::fma_f32x2(sum2[c * 32 + 16 + i], umma::pack_f32x2(r1[2 * i], r1[2 * i + 1]), scale2);
                             }
                         }
                     }
@@ -459,7 +459,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             int4 out;
                             __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(sum[v * 8 + 2 * j], sum[v * 8 + 2 * j + 1]);
+                            for (int j = 0; j < 4; ++j) {
+                                float lo, hi;
+                                umma::unpack_f32x2(sum2[v * 4 + j], lo, hi);
+                                h[j] = __floats2bfloat162_rn(lo, hi);
+                            }
                             *reinterpret_cast<int4*>(cb + (static_cast<int64_t>(row) * g.ldc + col) * 2) = out;
                         }
                     }

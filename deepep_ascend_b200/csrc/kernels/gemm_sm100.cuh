@@ -91,6 +91,24 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ------------------------------------------------------------------------------------------------ packed fp32 math
+// Two fp32 lanes per instruction (fma.rn.f32x2, sm_100): acc.{lo,hi} += x.{lo,hi} * s.{lo,hi}.  The promotion of block-scaled
+// accumulators is bound by instruction issue, so halving the FMA count matters.
+__device__ __forceinline__ uint64_t pack_f32x2(uint32_t lo, uint32_t hi) {
+    uint64_t v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(lo), "r"(hi));
+    return v;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+    uint32_t a, b;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+    lo = __uint_as_float(a);
+    hi = __uint_as_float(b);
+}
+__device__ __forceinline__ void fma_f32x2(uint64_t& acc, uint64_t x, uint64_t s) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(x), "l"(s));
+}
+
 // ------------------------------------------------------------------------------------------------ TMA
 // 2-D tile load, global -> this CTA's shared memory (no multicast).  c0 = innermost coordinate (elements).
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {

@@ -445,8 +445,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("prof", &CombineCall::prof);
 
     py::class_<ElasticBufferCore>(m, "ElasticBuffer")
-        .def(py::init<int, int, int64_t, double, double, int64_t>(), py::arg("rank"), py::arg("num_ranks"), py::arg("num_bytes"),
-             py::arg("gpu_timeout_secs") = 100.0, py::arg("cpu_timeout_secs") = 300.0, py::arg("num_cpu_bytes") = 0)
+        .def(py::init<int, int, int64_t, double, double, int64_t, bool>(), py::arg("rank"), py::arg("num_ranks"), py::arg("num_bytes"),
+             py::arg("gpu_timeout_secs") = 100.0, py::arg("cpu_timeout_secs") = 300.0, py::arg("num_cpu_bytes") = 0,
+             py::arg("use_vmm") = false)
+        .def("finish_export", &ElasticBufferCore::finish_export)
+        .def("uses_vmm", &ElasticBufferCore::uses_vmm)
         .def("num_cpu_bytes", &ElasticBufferCore::num_cpu_bytes)
         .def("get_local_cpu_segment_name", &ElasticBufferCore::get_local_cpu_segment_name)
         .def("open_cpu_peers", &ElasticBufferCore::open_cpu_peers)

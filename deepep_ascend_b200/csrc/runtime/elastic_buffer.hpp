@@ -65,8 +65,8 @@ struct CombineCall {
 class ElasticBufferCore {
 public:
     ElasticBufferCore(int rank, int num_ranks, int64_t num_bytes, double gpu_timeout_secs, double cpu_timeout_secs,
-                      int64_t num_cpu_bytes = 0)
-        : mem_(std::make_unique<SymmetricMemory>(rank, num_ranks, num_bytes, num_cpu_bytes)),
+                      int64_t num_cpu_bytes = 0, bool use_vmm = false)
+        : mem_(std::make_unique<SymmetricMemory>(rank, num_ranks, num_bytes, num_cpu_bytes, use_vmm)),
           gpu_timeout_ns_(static_cast<uint64_t>(gpu_timeout_secs * 1e9)),
           cpu_timeout_secs_(cpu_timeout_secs) {}
 
@@ -75,8 +75,10 @@ public:
     }
 
     // ------------------------------------------------------------------ set-up / tear-down
-    py::bytes get_local_ipc_handle() const { return py::bytes(mem_->export_handle()); }
+    py::bytes get_local_ipc_handle() { return py::bytes(mem_->export_handle()); }
     void open_peers(const std::vector<std::string>& handles) { mem_->open_peers(handles); }
+    void finish_export() { mem_->finish_export(); }
+    bool uses_vmm() const { return mem_->uses_vmm(); }
     static void link_local(const std::vector<ElasticBufferCore*>& group) {
         std::vector<SymmetricMemory*> mems;
         for (auto* g : group) mems.push_back(g->mem_.get());

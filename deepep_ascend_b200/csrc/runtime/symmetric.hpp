@@ -3,6 +3,11 @@
 // pointers.  Two ways to build the table:
 //   * processes, one per GPU: cudaIpc handles exchanged by the caller (torch.distributed all_gather_object);
 //   * several virtual ranks inside one process on one GPU (protocol tests on a single GPU): plain pointers.
+// The local buffer is either a cudaMalloc allocation shared through cudaIpc handles, or (`use_vmm`) a CUDA virtual-memory
+// allocation (cuMemCreate + cuMemMap) exported as a POSIX file descriptor that travels to the peers over a Unix-domain
+// socket (SCM_RIGHTS) and is mapped there with cuMemImportFromShareableHandle: the scheme that also carries fabric handles
+// across NVLink-connected nodes and that lets further allocations be mapped behind the same address range
+// (csrc/kernels/backend/symmetric.hpp:22-87, csrc/utils/shared_memory.hpp:48-125 of the reference).
 // Also owns the status block: pinned host memory mapped into the device, where kernels report failed waits
 // and publish receive counts for the host.
 // Optional CPU segment ("elastic" part of the buffer): `num_cpu_bytes` of host memory per rank that every rank's GPU
@@ -12,16 +17,23 @@
 // Parity: the role of csrc/kernels/backend/symmetric.hpp:14-319, csrc/utils/shared_memory.hpp:48-125 and the
 // mapped host counters of csrc/elastic/buffer.hpp:127-142.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime_api.h>
 #include <fcntl.h>
 #include <sys/mman.h>
+#include <sys/socket.h>
+#include <sys/un.h>
 #include <unistd.h>
 
 #include <atomic>
 #include <cerrno>
+#include <chrono>
 #include <cstring>
+#include <memory>
 #include <sstream>
 #include <string>
+#include <thread>
+#include <type_traits>
 #include <vector>
 
 #include "../kernels/api.h"
@@ -36,16 +48,217 @@ inline void cuda_check(cudaError_t e, const char* what) {
         throw BufferError(os.str());
     }
 }
+// The driver's virtual-memory entry points, looked up at run time through the runtime API so that the extension does not
+// link against libcuda (it must load on machines without a driver, e.g. for the CPU backend).
+struct DriverApi {
+    CUresult (*GetAllocationGranularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) = nullptr;
+    CUresult (*Create)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
+    CUresult (*AddressReserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+    CUresult (*Map)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+    CUresult (*SetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
+    CUresult (*ExportToShareableHandle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType, unsigned long long) = nullptr;
+    CUresult (*ImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType) = nullptr;
+    CUresult (*Unmap)(CUdeviceptr, size_t) = nullptr;
+    CUresult (*AddressFree)(CUdeviceptr, size_t) = nullptr;
+    CUresult (*Release)(CUmemGenericAllocationHandle) = nullptr;
+
+    static const DriverApi& get() {
+        static const DriverApi api = [] {
+            DriverApi a;
+            auto load = [](const char* name, auto& fn) {
+                void* p = nullptr;
+                cudaDriverEntryPointQueryResult q;
+                if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || p == nullptr)
+                    throw BufferError(std::string("the CUDA driver does not provide ") + name);
+                fn = reinterpret_cast<std::remove_reference_t<decltype(fn)>>(p);
+            };
+            load("cuMemGetAllocationGranularity", a.GetAllocationGranularity);
+            load("cuMemCreate", a.Create);
+            load("cuMemAddressReserve", a.AddressReserve);
+            load("cuMemMap", a.Map);
+            load("cuMemSetAccess", a.SetAccess);
+            load("cuMemExportToShareableHandle", a.ExportToShareableHandle);
+            load("cuMemImportFromShareableHandle", a.ImportFromShareableHandle);
+            load("cuMemUnmap", a.Unmap);
+            load("cuMemAddressFree", a.AddressFree);
+            load("cuMemRelease", a.Release);
+            return a;
+        }();
+        return api;
+    }
+};
+
+inline void driver_check(CUresult r, const char* what) {
+    if (r != CUDA_SUCCESS) throw BufferError(std::string(what) + " failed with CUDA driver error " + std::to_string(static_cast<int>(r)));
+}
+
+// One CUDA virtual-memory mapping: a physical allocation (own or imported) mapped read/write for `device`.
+struct VmmMapping {
+    CUmemGenericAllocationHandle handle = 0;
+    CUdeviceptr ptr = 0;
+    size_t size = 0;
+
+    static CUmemAllocationProp props(int device) {
+        CUmemAllocationProp p{};
+        p.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+        p.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        p.location.id = device;
+        p.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+        return p;
+    }
+    static size_t granularity(int device) {
+        const CUmemAllocationProp p = props(device);
+        size_t g = 0;
+        driver_check(DriverApi::get().GetAllocationGranularity(&g, &p, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED), "cuMemGetAllocationGranularity");
+        return g;
+    }
+    void map(int device) {
+        const size_t g = granularity(device);
+        driver_check(DriverApi::get().AddressReserve(&ptr, size, g, 0, 0), "cuMemAddressReserve");
+        driver_check(DriverApi::get().Map(ptr, size, 0, handle, 0), "cuMemMap");
+        CUmemAccessDesc acc{};
+        acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        acc.location.id = device;
+        acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+        driver_check(DriverApi::get().SetAccess(ptr, size, &acc, 1), "cuMemSetAccess");
+    }
+    void create(int device, size_t bytes) {
+        const size_t g = granularity(device);
+        size = (bytes + g - 1) / g * g;
+        const CUmemAllocationProp p = props(device);
+        driver_check(DriverApi::get().Create(&handle, size, &p, 0), "cuMemCreate");
+        map(device);
+    }
+    int export_fd() const {
+        int fd = -1;
+        driver_check(DriverApi::get().ExportToShareableHandle(&fd, handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0), "cuMemExportToShareableHandle");
+        return fd;
+    }
+    void import_fd(int device, int fd, size_t bytes) {
+        const size_t g = granularity(device);
+        size = (bytes + g - 1) / g * g;
+        driver_check(DriverApi::get().ImportFromShareableHandle(&handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
+                                                    CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR),
+                     "cuMemImportFromShareableHandle");
+        map(device);
+    }
+    bool release() {
+        bool ok = true;
+        if (ptr != 0) {
+            ok = DriverApi::get().Unmap(ptr, size) == CUDA_SUCCESS && ok;
+            ok = DriverApi::get().AddressFree(ptr, size) == CUDA_SUCCESS && ok;
+            ptr = 0;
+        }
+        if (handle != 0) {
+            ok = DriverApi::get().Release(handle) == CUDA_SUCCESS && ok;
+            handle = 0;
+        }
+        return ok;
+    }
+};
+
+// Hands one file descriptor to `num_clients` peers over an abstract Unix-domain socket (SCM_RIGHTS), from a helper thread.
+class FdServer {
+public:
+    FdServer(const std::string& name, int fd, int num_clients) : name_(name) {
+        sock_ = socket(AF_UNIX, SOCK_STREAM, 0);
+        if (sock_ < 0) throw BufferError("socket(AF_UNIX) failed");
+        sockaddr_un addr{};
+        addr.sun_family = AF_UNIX;
+        std::memcpy(addr.sun_path + 1, name.data(), std::min(name.size(), sizeof(addr.sun_path) - 2));   // abstract: leading NUL
+        const socklen_t len = static_cast<socklen_t>(offsetof(sockaddr_un, sun_path) + 1 + std::min(name.size(), sizeof(addr.sun_path) - 2));
+        if (bind(sock_, reinterpret_cast<sockaddr*>(&addr), len) != 0 || listen(sock_, num_clients + 1) != 0) {
+            close(sock_);
+            throw BufferError("cannot listen on the descriptor socket " + name + ": " + std::strerror(errno));
+        }
+        timeval tv{30, 0};   // a peer that never connects must not keep the thread forever
+        setsockopt(sock_, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
+        thread_ = std::thread([this, fd, num_clients] {
+            for (int i = 0; i < num_clients; ++i) {
+                const int c = accept(sock_, nullptr, nullptr);
+                if (c < 0) break;
+                send_fd(c, fd);
+                close(c);
+            }
+        });
+    }
+    ~FdServer() { finish(); }
+    void finish() {
+        if (thread_.joinable()) thread_.join();
+        if (sock_ >= 0) close(sock_);
+        sock_ = -1;
+    }
+    static int fetch(const std::string& name) {
+        sockaddr_un addr{};
+        addr.sun_family = AF_UNIX;
+        std::memcpy(addr.sun_path + 1, name.data(), std::min(name.size(), sizeof(addr.sun_path) - 2));
+        const socklen_t len = static_cast<socklen_t>(offsetof(sockaddr_un, sun_path) + 1 + std::min(name.size(), sizeof(addr.sun_path) - 2));
+        for (int attempt = 0; attempt < 200; ++attempt) {
+            const int s = socket(AF_UNIX, SOCK_STREAM, 0);
+            if (s < 0) break;
+            if (connect(s, reinterpret_cast<sockaddr*>(&addr), len) == 0) {
+                const int fd = recv_fd(s);
+                close(s);
+                if (fd >= 0) return fd;
+            } else {
+                close(s);
+            }
+            std::this_thread::sleep_for(std::chrono::milliseconds(25));
+        }
+        throw BufferError("could not fetch the memory descriptor from " + name);
+    }
+
+private:
+    static void send_fd(int sock, int fd) {
+        char byte = 1, control[CMSG_SPACE(sizeof(int))] = {};
+        iovec io{&byte, 1};
+        msghdr msg{};
+        msg.msg_iov = &io;
+        msg.msg_iovlen = 1;
+        msg.msg_control = control;
+        msg.msg_controllen = sizeof(control);
+        cmsghdr* c = CMSG_FIRSTHDR(&msg);
+        c->cmsg_level = SOL_SOCKET;
+        c->cmsg_type = SCM_RIGHTS;
+        c->cmsg_len = CMSG_LEN(sizeof(int));
+        std::memcpy(CMSG_DATA(c), &fd, sizeof(int));
+        sendmsg(sock, &msg, 0);
+    }
+    static int recv_fd(int sock) {
+        char byte = 0, control[CMSG_SPACE(sizeof(int))] = {};
+        iovec io{&byte, 1};
+        msghdr msg{};
+        msg.msg_iov = &io;
+        msg.msg_iovlen = 1;
+        msg.msg_control = control;
+        msg.msg_controllen = sizeof(control);
+        if (recvmsg(sock, &msg, 0) <= 0) return -1;
+        cmsghdr* c = CMSG_FIRSTHDR(&msg);
+        if (c == nullptr || c->cmsg_level != SOL_SOCKET || c->cmsg_type != SCM_RIGHTS) return -1;
+        int fd = -1;
+        std::memcpy(&fd, CMSG_DATA(c), sizeof(int));
+        return fd;
+    }
+    std::string name_;
+    int sock_ = -1;
+    std::thread thread_;
+};
 
 class SymmetricMemory {
 public:
-    SymmetricMemory(int rank, int num_ranks, int64_t num_bytes, int64_t num_cpu_bytes = 0)
-        : rank_(rank), num_ranks_(num_ranks), bytes_(num_bytes), cpu_bytes_(num_cpu_bytes) {
+    SymmetricMemory(int rank, int num_ranks, int64_t num_bytes, int64_t num_cpu_bytes = 0, bool use_vmm = false)
+        : rank_(rank), num_ranks_(num_ranks), bytes_(num_bytes), cpu_bytes_(num_cpu_bytes), use_vmm_(use_vmm) {
         if (num_ranks < 1 || num_ranks > EP_MAX_RANKS || rank < 0 || rank >= num_ranks)
             throw BufferError("rank / num_ranks out of range");
         if (num_bytes < static_cast<int64_t>(EP_WORKSPACE_BYTES)) throw BufferError("buffer smaller than its workspace");
         cuda_check(cudaGetDevice(&device_), "cudaGetDevice");
-        cuda_check(cudaMalloc(&local_, static_cast<size_t>(num_bytes)), "cudaMalloc(symmetric buffer)");
+        if (use_vmm_) {
+            cuda_check(cudaFree(nullptr), "CUDA context");   // the driver calls below need the primary context
+            vmm_[rank_].create(device_, static_cast<size_t>(num_bytes));
+            local_ = reinterpret_cast<void*>(vmm_[rank_].ptr);
+        } else {
+            cuda_check(cudaMalloc(&local_, static_cast<size_t>(num_bytes)), "cudaMalloc(symmetric buffer)");
+        }
         cuda_check(cudaMemset(local_, 0, EP_WORKSPACE_BYTES), "cudaMemset(workspace)");
         void* host = nullptr;
         cuda_check(cudaHostAlloc(&host, EP_STATUS_WORDS * sizeof(uint64_t), cudaHostAllocMapped), "cudaHostAlloc(status block)");
@@ -73,7 +286,18 @@ public:
     SymmetricMemory& operator=(const SymmetricMemory&) = delete;
     ~SymmetricMemory() { release(); }
 
-    std::string export_handle() const {
+    bool uses_vmm() const { return use_vmm_; }
+
+    // What the peers need to map this buffer: a cudaIpc handle, or (VMM) the name of a socket that hands out the file
+    // descriptor of the allocation; the helper thread behind that socket serves every peer once.
+    std::string export_handle() {
+        if (use_vmm_) {
+            static std::atomic<uint64_t> serial{0};
+            const std::string name = "ep_b200_vmm_" + std::to_string(static_cast<long long>(getpid())) + "_" + std::to_string(serial.fetch_add(1));
+            export_fd_ = vmm_[rank_].export_fd();
+            fd_server_ = std::make_unique<FdServer>(name, export_fd_, num_ranks_ - 1);
+            return "vmm:" + name;
+        }
         cudaIpcMemHandle_t h;
         cuda_check(cudaIpcGetMemHandle(&h, local_), "cudaIpcGetMemHandle");
         return std::string(reinterpret_cast<const char*>(&h), sizeof(h));
@@ -82,6 +306,18 @@ public:
     // handles[i] is rank i's export_handle(); maps every peer's buffer here
     void open_peers(const std::vector<std::string>& handles) {
         if (static_cast<int>(handles.size()) != num_ranks_) throw BufferError("one handle per rank is required");
+        if (use_vmm_) {
+            for (int i = 0; i < num_ranks_; ++i) {
+                if (i == rank_) continue;
+                if (handles[i].rfind("vmm:", 0) != 0) throw BufferError("rank " + std::to_string(i) + " did not export a VMM allocation");
+                const int fd = FdServer::fetch(handles[i].substr(4));
+                vmm_[i].import_fd(device_, fd, static_cast<size_t>(bytes_));
+                close(fd);
+                peers_[i] = reinterpret_cast<uint8_t*>(vmm_[i].ptr);
+            }
+            linked_ = true;
+            return;
+        }
         for (int i = 0; i < num_ranks_; ++i) {
             if (i == rank_) continue;
             if (handles[i].size() != sizeof(cudaIpcMemHandle_t)) throw BufferError("malformed IPC handle");
@@ -144,14 +380,27 @@ public:
         return c;
     }
 
+    // the socket thread has served every peer (call after all ranks are through open_peers)
+    void finish_export() {
+        if (fd_server_) fd_server_->finish();
+        fd_server_.reset();
+        if (export_fd_ >= 0) close(export_fd_);
+        export_fd_ = -1;
+    }
+
     bool release() {
         bool ok = true;
+        finish_export();
         for (int i = 0; i < EP_MAX_RANKS; ++i)
             if (opened_[i]) {
                 ok = cudaIpcCloseMemHandle(peers_[i]) == cudaSuccess && ok;
                 opened_[i] = false;
                 peers_[i] = nullptr;
             }
+        if (use_vmm_) {
+            for (int i = 0; i < EP_MAX_RANKS; ++i) ok = vmm_[i].release() && ok;
+            local_ = nullptr;
+        }
         if (local_ != nullptr) {
             ok = cudaFree(local_) == cudaSuccess && ok;
             local_ = nullptr;
@@ -197,6 +446,10 @@ private:
     int rank_, num_ranks_, device_ = 0;
     int64_t bytes_;
     int64_t cpu_bytes_ = 0;
+    bool use_vmm_ = false;
+    VmmMapping vmm_[EP_MAX_RANKS];
+    std::unique_ptr<FdServer> fd_server_;
+    int export_fd_ = -1;
     std::string cpu_name_;
     void* cpu_host_[EP_MAX_RANKS] = {};
     uint8_t* cpu_dev_[EP_MAX_RANKS] = {};

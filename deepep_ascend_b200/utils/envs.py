@@ -76,8 +76,11 @@ def check_nvlink_connections(group: Optional[dist.ProcessGroup] = None) -> bool:
     return all(torch.cuda.can_device_access_peer(i, j) for i in range(n) for j in range(n) if i != j)
 
 
-def check_torch_deterministic() -> None:
-    assert not torch.are_deterministic_algorithms_enabled() or True
+def check_torch_deterministic() -> bool:
+    """Whether PyTorch's deterministic mode is on.  The reference uses this to force its slower sorted layout
+    (deep_ep/utils/envs.py:361-367); here the row layout is a pure function of the routing (prefix sums, no arrival-order
+    slot claims), so results are bit-reproducible in either mode and nothing has to change: the call only reports the mode."""
+    return bool(torch.are_deterministic_algorithms_enabled())
 
 
 def parse_nvlink_status(text: str) -> float:

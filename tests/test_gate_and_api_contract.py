@@ -49,7 +49,10 @@ PACKAGE_EXPORTS = ['Buffer', 'Config', 'EPHandle', 'ElasticBuffer', 'EventHandle
                    'get_physical_domain_size', 'topk_idx_t']
 BUFFER_METHODS = ['all_gather', 'barrier', 'capture', 'combine', 'destroy', 'dispatch', 'engram_fetch', 'engram_write',
                   'get_buffer_size_hint', 'get_comm_stream', 'get_theoretical_num_sms', 'low_latency_combine', 'low_latency_dispatch',
-                  'pp_recv', 'pp_send', 'pp_set_config']
+                  'pp_recv', 'pp_send', 'pp_set_config', 'get_dispatch_layout', 'get_combine_buffer', 'reduce_scatter',
+                  'create_agrs_session', 'destroy_agrs_session', 'agrs_set_config', 'agrs_get_inplace_tensor',
+                  'low_latency_update_mask_buffer', 'low_latency_query_mask_buffer', 'low_latency_clean_mask_buffer',
+                  'get_next_low_latency_combine_buffer', 'get_physical_domain_size', 'get_logical_domain_size']
 NATIVE_FUNCTIONS = ['ag_gemm', 'dequant_transpose', 'gemm_error', 'gemm_kgrouped', 'gemm_nt', 'gemm_rs', 'get_dispatch_layout',
                     'get_elastic_buffer_alignment', 'get_platform', 'get_workspace_bytes', 'moe_bwd_prep', 'per_token_cast_to_fp8',
                     'swiglu_bwd', 'swiglu_quant', 'weighted_transpose']
@@ -63,7 +66,8 @@ def test_public_surface():
     for name in BUFFER_METHODS:
         assert callable(getattr(ep.ElasticBuffer, name, None)), name
     for name in ('dispatch', 'combine', 'get_dispatch_layout', 'low_latency_dispatch', 'low_latency_combine',
-                 'clean_low_latency_buffer', 'get_next_low_latency_combine_buffer'):
+                 'clean_low_latency_buffer', 'get_next_low_latency_combine_buffer', 'sync', 'get_local_ipc_handle',
+                 'get_local_buffer_tensor', 'get_local_device_id', 'get_comm_stream', 'is_available'):
         assert callable(getattr(ep.Buffer, name, None)), name
     handle_fields = ['do_expand', 'num_experts', 'expert_alignment', 'num_max_tokens_per_rank', 'num_sms', 'topk_idx', 'num_recv_tokens',
                      'num_expanded_tokens', 'psum_num_recv_tokens_per_scaleup_rank', 'psum_num_recv_tokens_per_expert',

@@ -82,6 +82,24 @@ def _worker(rank: int, world: int, port: int):
             torch.testing.assert_close(out.float(), xq.float() * valid, atol=0.13, rtol=0.02)
         buf.barrier(with_cpu_sync=True)
         buf.destroy()
+        # ---- the same exchange over buffers allocated with CUDA virtual memory and shared as file descriptors
+        vbuf = ep.ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=True, symmetric_memory='vmm',
+                                num_gpu_timeout_secs=10, num_cpu_timeout_secs=30)
+        assert vbuf.core.uses_vmm()
+        torch.manual_seed(500 + rank)
+        x = torch.randn(T - rank, H, device='cuda').bfloat16()
+        w, idx = torch.softmax(torch.randn(T - rank, E, device='cuda'), -1).topk(K, -1)
+        (rx, rsf), ridx, rw, handle, _ = vbuf.dispatch(x, idx, w, num_experts=E, num_sms=8)
+        q, sf = per_token_cast_to_fp8(x.cpu())
+        (ox, osf), oidx, ow, osrc, _ = refs.dispatch_nccl((q.cuda(), sf.cuda()), idx, w, T, E, group)
+        assert torch.equal(rx.view(torch.uint8), ox.view(torch.uint8)) and torch.equal(rsf, osf) and torch.equal(ridx, oidx)
+        out, _, _ = vbuf.combine(per_token_cast_back(rx, rsf).bfloat16(), handle, num_sms=8)
+        hits = torch.zeros(x.shape[0], device='cuda')
+        prank, _ = layout_ref.unpack_lane(handle.plan)
+        hits = (prank >= 0).sum(dim=1, keepdim=True).float()
+        torch.testing.assert_close(out.float(), per_token_cast_back(q, sf).cuda().float() * hits, atol=0.07, rtol=0.02)
+        vbuf.check_status()
+        vbuf.destroy()
         # ---- expand layout with aligned, zero-padded expert segments and the fused weighted reduce
         A = 16
         buf = ep.ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=False, enable_expand=True,

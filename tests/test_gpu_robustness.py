@@ -371,3 +371,31 @@ def test_all_gather_in_place_and_batched_on_one_rank():
         buf.check_status()
     finally:
         buf.destroy()
+
+
+# ----------------------------------------------------------------------------------------------- VMM symmetric memory
+def test_buffers_allocated_with_cuda_virtual_memory():
+    """The symmetric buffer as a cuMemCreate / cuMemMap allocation (the kind that is shared between processes as a file
+    descriptor): dispatch and combine give the same bits as with cudaMalloc buffers, and create / destroy can be repeated."""
+    from deepep_ascend_b200.backends.emulated import EmulatedWorld
+    R, T, H, E, K = 4, 64, 512, 16, 4
+    g = torch.Generator().manual_seed(9)
+    xs = [torch.randn(T, H, generator=g).bfloat16().cuda() for _ in range(R)]
+    idxs, ws = _routing(R, T, E, K, seed=10)
+    results = {}
+    for kind in ('ipc', 'vmm', 'vmm'):
+        world = EmulatedWorld(R, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=True, symmetric_memory=kind)
+        try:
+            assert all(b.core.uses_vmm() == (kind == 'vmm') for b in world.buffers)
+            outs = world.dispatch(xs, idxs, ws, E, num_sms=4)
+            res = world.combine([(o[0][0].float() * 0.25).bfloat16() for o in outs], [o[3] for o in outs], num_sms=4)
+            torch.cuda.synchronize()
+            for b in world.buffers:
+                b.check_status()
+            h = 0
+            for r in range(R):
+                h ^= _tensor_hash(outs[r][0][0]) ^ _tensor_hash(outs[r][0][1].contiguous()) ^ _tensor_hash(res[r][0])
+            results.setdefault(kind, set()).add(h)
+        finally:
+            world.destroy()
+    assert results['ipc'] == results['vmm'] and len(results['vmm']) == 1
