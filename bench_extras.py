@@ -315,6 +315,17 @@ def main():
         flops_fwd = rows * (2 * H * 2 * I + 2 * I * H)
         emit(bench='fused_moe_layer', tokens_per_rank=Tm, hidden=H, intermediate=I, experts_per_rank=Em // world, fwd_ms=float(tf), fwd_bwd_ms=float(tfb), fwd_bwd_ms_all=[round(float(v), 3) for v in tfb_all],
              fwd_expert_tflops_per_gpu=flops_fwd / tf / 1e9, note='includes the host sync of dispatch (exact sizes)')
+        # the same layer as a pipeline of chunks: communication of one chunk under the GEMMs of its neighbours
+        with torch.no_grad():
+            for chunks, comm_sms in ((1, 64), (2, 24), (4, 24), (4, 16), (8, 24)):
+                layer.num_chunks, layer.num_sms = chunks, comm_sms
+                t = np.median(timeit(lambda: layer(x, idx, w), buf, iters=bi, warm=bw))
+                emit(bench='fused_moe_forward_pipelined', chunks=chunks, comm_sms=comm_sms, fwd_ms=float(t),
+                     fwd_expert_tflops_per_gpu=flops_fwd / t / 1e9)
+        layer.num_chunks, layer.num_sms = 4, 24
+        tfb4 = np.median(timeit(fwd_bwd, buf, iters=bi, warm=bw))
+        emit(bench='fused_moe_layer_pipelined_forward', chunks=4, comm_sms=24, fwd_bwd_ms=float(tfb4))
+        buf.check_status()
         buf.destroy()
 
     # ------------------------------------------------------------------ Zipf-skewed routing
