@@ -386,37 +386,41 @@ def low_latency_in_a_graph(buf, group, world, rank, M, H, E, K, replays, reduce_
     if world > 1:
         import torch.distributed as dist
         dist.barrier(group=group)
-    gd, gc = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    gd, gc, gl = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
         with torch.cuda.graph(gd, stream=side):
             recv, cnt, handle, _, _ = d()
         with torch.cuda.graph(gc, stream=side):
             out, _, _ = buf.low_latency_combine(y, idx, w, handle, num_sms=sms)
+        with torch.cuda.graph(gl, stream=side):      # the same combine with LogFMT-10 rows on the wire
+            out_l, _, _ = buf.low_latency_combine(y, idx, w, handle, num_sms=sms, use_logfmt=True)
     torch.cuda.synchronize()
-    td, tc = [], []
+    td, tc, tl = [], [], []
     warm = 10
     for i in range(warm + replays):
-        if world > 1:
-            buf.barrier(use_comm_stream=False)
-        torch.cuda._sleep(400_000)
-        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        e[0].record()
-        gd.replay()
-        e[1].record()
-        gc.replay()
-        e[2].record()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        for k, g in enumerate((gd, gc, gl)):
+            if world > 1:
+                buf.barrier(use_comm_stream=False)
+            torch.cuda._sleep(400_000)
+            e[2 * k].record()
+            g.replay()
+            e[2 * k + 1].record()
         if i >= warm:
             td.append((e[0], e[1]))
-            tc.append((e[1], e[2]))
+            tc.append((e[2], e[3]))
+            tl.append((e[4], e[5]))
     torch.cuda.synchronize()
     buf.check_status()
     td = reduce_max([a.elapsed_time(b) * 1e3 for a, b in td]).cpu().numpy()
     tc = reduce_max([a.elapsed_time(b) * 1e3 for a, b in tc]).cpu().numpy()
-    finite = bool(torch.isfinite(out.float()).all())
+    tl = reduce_max([a.elapsed_time(b) * 1e3 for a, b in tl]).cpu().numpy()
+    finite = bool(torch.isfinite(out.float()).all()) and bool(torch.isfinite(out_l.float()).all())
     return {'ll_tokens_per_rank': M, 'll_replays': replays, 'll_num_sms': sms,
             'll_dispatch_p50_us': float(np.percentile(td, 50)), 'll_dispatch_p99_us': float(np.percentile(td, 99)),
             'll_combine_p50_us': float(np.percentile(tc, 50)), 'll_combine_p99_us': float(np.percentile(tc, 99)),
+            'll_combine_logfmt_p50_us': float(np.percentile(tl, 50)), 'll_combine_logfmt_p99_us': float(np.percentile(tl, 99)),
             'll_output_finite': finite,
             'll_reference': 'no SM100 number is published; the reference quotes 77 / 114 us on H800 + CX7 RDMA'}
 

@@ -458,22 +458,36 @@ __device__ __forceinline__ void ll_combine_body(const LLCombineArgs& a) {
                 float acc[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-                for (uint32_t m = srcs; m != 0; m &= m - 1) {
-                    const int k = __ffs(m) - 1;
-                    const float w = __shfl_sync(0xffffffffu, w_k, k);
-                    if (in_row) {
-                        const uint8_t* row = slab + (static_cast<int64_t>(t) * K + k) * row_bytes;
-                        const uint32_t* codes = reinterpret_cast<const uint32_t*>(row + (ch / logfmt::kLaneChannels) * 20);
-                        uint32_t wds[5], cds[16];
+                // the codes of up to eight source rows are requested together, so that an item costs one memory round
+                // trip (as in the bf16 path), then decoded and accumulated in top-k lane order
+                for (int k0 = 0; k0 < K; k0 += 8) {
+                    uint32_t wds[8][5], hdr[8];
 #pragma unroll
-                        for (int j = 0; j < 5; ++j) wds[j] = __ldcg(codes + j);
-                        const uint32_t hdr = __ldcg(reinterpret_cast<const uint32_t*>(row + groups * logfmt::kCodeBytesPerGroup) + ch / logfmt::kGroup);
-                        const float2 mm = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hdr));   // (amax, amin)
-                        logfmt::unpack16(wds, cds);
-                        if (mm.x > 0.f) {
-                            const logfmt::Range r = logfmt::make_range(mm.x, mm.y);
+                    for (int j = 0; j < 8; ++j) {
+                        const int k = k0 + j;
+                        if (k < K && ((srcs >> k) & 1u) && in_row) {
+                            const uint8_t* row = slab + (static_cast<int64_t>(t) * K + k) * row_bytes;
+                            const uint32_t* codes = reinterpret_cast<const uint32_t*>(row + (ch / logfmt::kLaneChannels) * 20);
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) acc[i] = fmaf(w, logfmt::decode_one(cds[i], r), acc[i]);
+                            for (int q = 0; q < 5; ++q) wds[j][q] = __ldcg(codes + q);
+                            hdr[j] = __ldcg(reinterpret_cast<const uint32_t*>(row + groups * logfmt::kCodeBytesPerGroup) + ch / logfmt::kGroup);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int k = k0 + j;
+                        if (k < K && ((srcs >> k) & 1u)) {      // warp-uniform
+                            const float w = __shfl_sync(0xffffffffu, w_k, k);
+                            if (in_row) {
+                                const float2 mm = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hdr[j]));   // (amax, amin)
+                                if (mm.x > 0.f) {
+                                    uint32_t cds[16];
+                                    logfmt::unpack16(wds[j], cds);
+                                    const logfmt::Range r = logfmt::make_range(mm.x, mm.y);
+#pragma unroll
+                                    for (int i = 0; i < 16; ++i) acc[i] = fmaf(w, logfmt::decode_one(cds[i], r), acc[i]);
+                                }
+                            }
                         }
                     }
                 }
