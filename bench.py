@@ -210,7 +210,8 @@ def main():
             if cached and handle is not None:
                 recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x, handle=handle, topk_weights=w, num_sms=num_sms)
             else:
-                recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x, idx, w, num_experts=E, num_sms=num_sms, do_cpu_sync=False,
+                # (the plain-tensor variant wants the exact row count, so that its staging copy moves the received rows only)
+                recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x, idx, w, num_experts=E, num_sms=num_sms, do_cpu_sync=plain_combine,
                                                                    do_handle_copy=False)
             launches['n'] += 1
             if plain_combine:

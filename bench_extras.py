@@ -114,6 +114,10 @@ def main():
                 buf.set_dispatch_tuning(warps, stages)
                 t = kernel_ms('dispatch', disp(sms))
                 emit(bench='dispatch', num_sms=sms, warps=warps or 12, stages=stages or 2, ms=t, gbs=rows * 7488 / t / 1e6)
+            for aligned in (True, False):
+                buf.set_dispatch_tuning(0, 0, line_aligned_side=aligned)
+                t = kernel_ms('dispatch', disp(sms))
+                emit(bench='dispatch_side_layout', num_sms=sms, line_aligned_side=aligned, ms=t, gbs=rows * 7488 / t / 1e6)
             buf.set_dispatch_tuning(0, 0)
             buf.enable_profiling(True)
             for _ in range(3):
@@ -358,12 +362,16 @@ def main():
         M, Kt, N = 8192, 7168, 7168
         buf = ElasticBuffer(group, num_max_tokens_per_rank=16, hidden=256, num_topk=2, extra_bytes=TensorParallelGemm.size_hint(M, Kt, N),
                             num_gpu_timeout_secs=20)
-        tp = TensorParallelGemm(buf, M, Kt, N, num_copy_ctas=16)
+        tp = TensorParallelGemm(buf, M, Kt, N)
         xs = torch.randn(M // world, Kt, device='cuda').bfloat16()
         w_col = torch.randn(N // world, Kt, device='cuda').bfloat16()          # column-parallel weight
-        t = np.median(timeit(lambda: tp.ag_gemm(xs, w_col), buf, iters=10))
-        emit(bench='ag_gemm_fused', M=M, K=Kt, N_local=N // world, ms=float(t), tflops_per_gpu=2 * M * Kt * (N // world) / t / 1e9,
-             nvlink_gbs_in=(world - 1) / world * M * Kt * 2 / t / 1e6)
+        auto_copiers = tp._copiers(N // world)
+        for copiers in sorted({16, 32, 48, auto_copiers}):
+            tp.num_copy_ctas = copiers
+            t = np.median(timeit(lambda: tp.ag_gemm(xs, w_col), buf, iters=10))
+            emit(bench='ag_gemm_fused', M=M, K=Kt, N_local=N // world, copier_ctas=copiers, default=copiers == auto_copiers, ms=float(t),
+                 tflops_per_gpu=2 * M * Kt * (N // world) / t / 1e9, nvlink_gbs_in=(world - 1) / world * M * Kt * 2 / t / 1e6)
+        tp.num_copy_ctas = 0
         xk = torch.randn(M, Kt // world, device='cuda').bfloat16()             # row-parallel: K is sharded
         w_row = torch.randn(N, Kt // world, device='cuda').bfloat16()
         t = np.median(timeit(lambda: tp.gemm_rs(xk, w_row), buf, iters=10))

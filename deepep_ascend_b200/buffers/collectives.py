@@ -3,8 +3,8 @@ pipeline-parallel send / recv, context-parallel KV gather and Engram remote fetc
 
 * AG / RS sessions (parity: csrc/elastic/buffer.hpp:379-526, deep_ep/buffers/elastic.py:1154-1251; reduce-scatter
   has no counterpart in the reference, whose README lists it as on-going): data moves with peer
-  ``cudaMemcpyAsync`` on the copy engines, one per peer; completion is a 32-thread signal kernel over NVLink, so
-  no SM is busy while the bytes move.
+  ``cudaMemcpyAsync`` on the copy engines, one per peer; completion is a 32-thread signal kernel over NVLink (bounded
+  wait), or, with ``use_stream_memops``, stream memory operations, so no SM is busy while the bytes move.
 * PP (parity: csrc/elastic/buffer.hpp:329-377): ring-neighbour send / recv on NCCL point-to-point, on a side
   stream so that it overlaps with compute.
 * Engram (parity: csrc/elastic/buffer.hpp:212-327): every rank publishes a table of fixed-size entries in its
@@ -27,13 +27,26 @@ class CollectivesMixin:
     _engram = None
 
     # ------------------------------------------------------------------------------------------ AG / RS sessions
-    def agrs_set_config(self, num_max_session_bytes: int, num_max_agrs_per_session: int = 32) -> None:
+    def agrs_set_config(self, num_max_session_bytes: int, num_max_agrs_per_session: int = 32,
+                        use_stream_memops: bool = False) -> None:
         """Reserve the gather region: ``num_max_session_bytes`` is the sum over the tensors of one session of
-        ``align(num_ranks * tensor_bytes, 32)``."""
+        ``align(num_ranks * tensor_bytes, 32)``.
+
+        ``use_stream_memops``: signal completion with stream memory operations (a 64-bit write into every peer's buffer
+        and a wait on the local words, queued on the stream by the driver) instead of the 32-thread signal kernel, so
+        that a whole all-gather uses no SM at all, as the reference does (csrc/kernels/backend/cuda_driver.cu:12-52).
+        Unlike the kernel, such a wait has no time limit: a peer that never arrives stalls the stream.  Off by default."""
         assert num_max_agrs_per_session <= 32
         assert self._agrs is None or not self._agrs['open'], 'destroy the open session first'
         self._agrs = {'offset': self.reserve(align(num_max_session_bytes, 1024)), 'bytes': num_max_session_bytes,
-                      'cursor': 0, 'open': False, 'count': 0, 'max': num_max_agrs_per_session, 'inplace': {}}
+                      'cursor': 0, 'open': False, 'count': 0, 'max': num_max_agrs_per_session, 'inplace': {},
+                      'memops': bool(use_stream_memops) and self._virtual is None}
+
+    def _agrs_signal(self) -> None:
+        """All ranks' copies queued so far have landed everywhere (on the current stream)."""
+        if self._agrs.get('memops') and self.core.signal_and_wait_memops(self._C.CH_AGRS):
+            return
+        self.core.barrier(self._C.CH_AGRS)
 
     def create_agrs_session(self) -> None:
         assert self._agrs is not None, 'call agrs_set_config first'
@@ -45,7 +58,7 @@ class CollectivesMixin:
         assert self._agrs is not None and self._agrs['open']
         self.comm_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.comm_stream):
-            self.core.barrier(self._C.CH_AGRS)
+            self._agrs_signal()
         torch.cuda.current_stream().wait_stream(self.comm_stream)
         self._agrs['open'] = False
 
@@ -92,7 +105,7 @@ class CollectivesMixin:
                     self.core.peer_copy(peer, off + self.rank_idx * nbytes, t)
                 shape = [self.num_ranks] + list(t.shape)
                 outs.append(self.core.view(off, shape, list(_contiguous_strides(shape)), t.dtype))
-            self.core.barrier(self._C.CH_AGRS)
+            self._agrs_signal()
         event = torch.cuda.Event()
         event.record(self.comm_stream)
 
@@ -113,7 +126,7 @@ class CollectivesMixin:
             for step in range(self.num_ranks):
                 peer = (self.rank_idx + step) % self.num_ranks
                 self.core.peer_copy(peer, off + self.rank_idx * nbytes, tensor[peer])
-            self.core.barrier(self._C.CH_AGRS)
+            self._agrs_signal()
             slots_shape = [self.num_ranks] + shape
             slots = self.core.view(off, slots_shape, list(_contiguous_strides(slots_shape)), tensor.dtype)
             out = torch.empty(shape, dtype=tensor.dtype, device=tensor.device)

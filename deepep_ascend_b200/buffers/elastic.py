@@ -155,6 +155,7 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         self.profile = None
         self._kernel_timing = None
         self._tune = (0, 0)
+        self._side_aligned = False
         if _virtual is not None:
             self.rank_idx, self.num_ranks = _virtual
         else:
@@ -341,12 +342,16 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         """No RDMA queue pairs exist inside one NVLink domain: always 0 (pass that as ``num_qps``)."""
         return 0
 
-    def set_dispatch_tuning(self, num_warps: int = 0, num_stages: int = 0) -> None:
+    def set_dispatch_tuning(self, num_warps: int = 0, num_stages: int = 0, line_aligned_side: Optional[bool] = None) -> None:
         """Shape of the dispatch kernel: warps per CTA (1..12, each with its own staging ring) and, for the fused
         FP8 cast, staging buffers per warp (2..4; more buffers keep more tokens' stores in flight per warp but
-        leave room for fewer warps).  0 selects the default (12 warps, 2 buffers)."""
+        leave room for fewer warps).  0 selects the default (12 warps, 2 buffers).  ``line_aligned_side``: place every
+        row's scales and tail record on 128-byte boundaries at the receiver (``recv_sf`` and ``recv_topk_idx`` /
+        ``recv_topk_weights`` become row-strided views), so that each of these small stores is whole lines on the wire."""
         assert 0 <= num_warps <= 12 and num_stages in (0, 2, 3, 4)
         self._tune = (num_warps, num_stages)
+        if line_aligned_side is not None:
+            self._side_aligned = bool(line_aligned_side)
 
     # ------------------------------------------------------------------------------------------ barrier
     def barrier(self, use_comm_stream: bool = True, with_cpu_sync: bool = False, sequential: bool = True) -> None:
@@ -556,11 +561,15 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
             off_w = K * idx.element_size()
             off_meta = align(off_w + K * 4, 8)
             tail_bytes = align(off_meta + 8, 16)
-            assert tail_bytes <= self.regions.tail_bytes, 'tail record larger than the buffer was sized for'
+            tail_pitch = align(tail_bytes, 128) if self._side_aligned else tail_bytes
+            sf_pitch = align(G * 4, 128) // 4 if self._side_aligned else G
+            assert tail_pitch <= self.regions.tail_bytes and sf_pitch * 4 <= self.regions.sf_row_bytes, \
+                'side records larger than the buffer was sized for'
             call.side_packed = True
-            call.tail_bytes, call.tail_off_w, call.tail_off_meta = tail_bytes, off_w, off_meta
+            call.tail_bytes, call.tail_off_w, call.tail_off_meta, call.tail_pitch = tail_bytes, off_w, off_meta, tail_pitch
+            call.sf_stride_row = sf_pitch
             call.off_recv_tail = slot.tail
-            tail = (tail_bytes, off_w, off_meta)
+            tail = (tail_pitch, off_w, off_meta, sf_pitch)
         if self.profile is not None:
             call.prof = self.profile['dispatch']
 
@@ -598,9 +607,9 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         recv_sf = recv_w = None
         if st.side is not None:
             # contiguous scales; strided views over the tail records
-            tail_bytes, off_w, off_meta = st.side
+            tail_bytes, off_w, off_meta, sf_pitch = st.side      # tail_bytes: distance of two rows' records
             if st.fp8_out:
-                recv_sf = core.view(st.slot.sf, [rows, G], [G, 1], torch.float32)
+                recv_sf = core.view(st.slot.sf, [rows, G], [sf_pitch, 1], torch.float32)
             isz = st.topk_idx.element_size()
             recv_idx = core.view(st.slot.tail, [rows, K], [tail_bytes // isz, 1], st.topk_idx.dtype)
             if st.topk_weights is not None:

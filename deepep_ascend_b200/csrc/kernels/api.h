@@ -12,6 +12,10 @@
 #define EP_MAX_TILE_FLAGS 16384
 #define EP_WORKSPACE_BYTES (4u << 20)
 #define EP_BUFFER_ALIGNMENT (2u << 20)
+// The last 4 KB of the workspace hold flag words that the HOST addresses directly (stream memory operations written into
+// the peers' buffers and waited for in the local one): uint64 [EP_NUM_CHANNELS][EP_MAX_RANKS], [channel][source rank].
+#define EP_WS_HOST_FLAGS_BYTES 4096u
+#define EP_WS_HOST_FLAGS_OFFSET (EP_WORKSPACE_BYTES - EP_WS_HOST_FLAGS_BYTES)
 
 // One independent sequence of collective calls per channel (own epoch, own barrier counters), so that e.g.
 // a low-latency step on one stream never aliases an all-gather session on another.
@@ -107,6 +111,7 @@ struct DispatchArgs {
     // so nothing is left for the receiver to rewrite.  Otherwise the small pieces go out as plain peer stores.
     int side_packed;
     int tail_bytes, tail_off_w, tail_off_meta;   // tail record: ids at 0, weights, metadata; multiple of 16 bytes
+    int tail_pitch;                              // distance of two rows' tail records at the receiver (>= tail_bytes, multiple of 16)
     uint64_t off_recv_tail;
     int do_zero_padding;           // expand layout: zero the rows (and scales) between an expert's last row and its aligned end
     int tune_warps, tune_stages;   // 0 = automatic; warps per CTA and staging buffers per warp of the fused-cast path

@@ -50,7 +50,8 @@ struct Workspace {
     alignas(128) uint32_t cta_assigned[EP_MAX_CTAS];                       // row numbers of the CTA's tokens are in lane_src / plan
     alignas(128) uint64_t comb_seq;                                        // combine calls completed (entry-barrier sequence)
 };
-static_assert(sizeof(Workspace) <= EP_WORKSPACE_BYTES, "workspace region too small");
+static_assert(sizeof(Workspace) <= EP_WS_HOST_FLAGS_OFFSET, "workspace region too small");
+static_assert(EP_NUM_CHANNELS * EP_MAX_RANKS * sizeof(uint64_t) <= EP_WS_HOST_FLAGS_BYTES, "host flag area too small");
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;

@@ -650,9 +650,9 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                     uint8_t* base = s_peer[d];
                     ptx::bulk_store(base + a.off_recv_x + static_cast<int64_t>(row) * out_row, src_smem, out_row);
                     if (a.side_packed) {
-                        if (has_sf) ptx::bulk_store(base + a.off_recv_sf + static_cast<int64_t>(row) * G * 4, sf_cur, G * 4);
+                        if (has_sf) ptx::bulk_store(base + a.off_recv_sf + static_cast<int64_t>(row) * a.sf_stride_row * 4, sf_cur, G * 4);
                         const int j = __popc(sends & lt);
-                        ptx::bulk_store(base + a.off_recv_tail + static_cast<int64_t>(row) * a.tail_bytes, tail_cur + j * a.tail_bytes, a.tail_bytes);
+                        ptx::bulk_store(base + a.off_recv_tail + static_cast<int64_t>(row) * a.tail_pitch, tail_cur + j * a.tail_bytes, a.tail_bytes);
                     }
                 } else {
                     report_failure(ctx, ws, EP_ERR_BOUNDS, EP_PH_DISPATCH_LOAD, d, a.recv_capacity_rows, row);

@@ -382,6 +382,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readonly("x_row_bytes", &RegionLayout::x_row_bytes)
         .def_readonly("sf_cols", &RegionLayout::sf_cols)
         .def_readonly("tail_bytes", &RegionLayout::tail_bytes)
+        .def_readonly("sf_row_bytes", &RegionLayout::sf_row_bytes)
         .def_readonly("num_recv_slots", &RegionLayout::num_recv_slots)
         .def("slot", [](const RegionLayout& r, int i) {
             TORCH_CHECK(i >= 0 && i < r.num_recv_slots, "slot index out of range");
@@ -426,6 +427,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("tail_off_w", &DispatchCall::tail_off_w)
         .def_readwrite("tail_off_meta", &DispatchCall::tail_off_meta)
         .def_readwrite("off_recv_tail", &DispatchCall::off_recv_tail)
+        .def_readwrite("tail_pitch", &DispatchCall::tail_pitch)
         .def_readwrite("do_zero_padding", &DispatchCall::do_zero_padding)
         .def_readwrite("tune_warps", &DispatchCall::tune_warps)
         .def_readwrite("tune_stages", &DispatchCall::tune_stages);
@@ -477,6 +479,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("combine", &ElasticBufferCore::combine)
         .def("barrier", &ElasticBufferCore::barrier, py::arg("channel") = static_cast<int>(EP_CH_BARRIER))
         .def("peer_copy", &ElasticBufferCore::peer_copy)
+        .def("signal_and_wait_memops", &ElasticBufferCore::signal_and_wait_memops)
         .def_static("engram_fetch_group", &ElasticBufferCore::engram_fetch_group)
         .def("wait_flag_test", &ElasticBufferCore::wait_flag_test)
         .def_static("dispatch_group", &ElasticBufferCore::dispatch_group)

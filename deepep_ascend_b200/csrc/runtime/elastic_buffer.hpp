@@ -46,6 +46,7 @@ struct DispatchCall {
     OptTensor prof;               // int64 [8]: phase timestamps (profiling)
     bool side_packed = false;     // scales and a tail record {ids | weights | metadata} travel as bulk stores
     int64_t tail_bytes = 0, tail_off_w = 0, tail_off_meta = 0, off_recv_tail = 0;
+    int64_t tail_pitch = 0;       // 0 = tail_bytes
     bool do_zero_padding = false;
     int64_t tune_warps = 0, tune_stages = 0;
 };
@@ -219,6 +220,36 @@ public:
         for (auto& s : scopes) s->commit();
     }
 
+    // Cross-GPU completion signal without any SM: after everything queued so far on the current stream (e.g. the peer copies
+    // of an all-gather), write this rank's next sequence number into every peer's host-flag word for `channel` and make the
+    // stream wait until every peer's word in the LOCAL buffer has reached the same number (stream memory operations, what
+    // the reference does with cuStreamBatchMemOp, csrc/kernels/backend/cuda_driver.cu:12-52).  Returns false when the driver
+    // refuses the operations, in which case nothing was queued and the caller uses the signal kernel instead.
+    bool signal_and_wait_memops(int channel) {
+        TORCH_CHECK(channel >= 0 && channel < EP_NUM_CHANNELS, "bad channel");
+        check_status();
+        const RankCtx c = ctx();
+        const DriverApi& api = DriverApi::get();
+        CUstream stream = at::cuda::getCurrentCUDAStream().stream();
+        const uint64_t seq = memop_seq_[channel] + 1;
+        const size_t word = EP_WS_HOST_FLAGS_OFFSET + (static_cast<size_t>(channel) * EP_MAX_RANKS) * sizeof(uint64_t);
+        for (int step = 0; step < c.num_ranks; ++step) {
+            const int p = (c.rank + step) % c.num_ranks;
+            const CUdeviceptr dst = reinterpret_cast<CUdeviceptr>(c.peer_base[p]) + word + c.rank * sizeof(uint64_t);
+            const CUresult r = api.StreamWriteValue64(stream, dst, seq, CU_STREAM_WRITE_VALUE_DEFAULT);
+            if (r != CUDA_SUCCESS) {
+                TORCH_CHECK(step == 0, "stream memory operation failed half way (driver error ", static_cast<int>(r), ")");
+                return false;
+            }
+        }
+        for (int p = 0; p < c.num_ranks; ++p) {
+            const CUdeviceptr src = reinterpret_cast<CUdeviceptr>(c.peer_base[c.rank]) + word + p * sizeof(uint64_t);
+            driver_check(api.StreamWaitValue64(stream, src, seq, CU_STREAM_WAIT_VALUE_GEQ), "cuStreamWaitValue64");
+        }
+        memop_seq_[channel] = seq;
+        return true;
+    }
+
     // Launches a kernel that waits (bounded by the GPU timeout) for a flag nothing sets; used to test that a
     // failed wait ends in a status record and a poisoned buffer instead of a trap or a hang.
     static void wait_flag_test_group(const std::vector<ElasticBufferCore*>& group, int64_t expected) {
@@ -377,7 +408,7 @@ private:
         const int64_t cap = c.recv_capacity_rows;
         TORCH_CHECK(cap > 0 && cap < (1 << 24), "bad receive capacity");
         check_region(c.off_recv_x, cap * out_row, "recv_x");
-        if (c.quantize || fp8) check_region(c.off_recv_sf, cap * G * 4, "recv_sf");
+        if (c.quantize || fp8) check_region(c.off_recv_sf, cap * (c.sf_stride_col == 1 ? c.sf_stride_row : G) * 4, "recv_sf");
         if (!c.do_expand) check_region(c.off_recv_idx, cap * K * 8, "recv_topk_idx");
         check_region(c.off_recv_w, cap * (c.do_expand ? 1 : K) * 4, "recv_topk_weights");
         check_region(c.off_recv_meta, cap * 8, "recv_src_metadata");
@@ -420,13 +451,16 @@ private:
         if (c.side_packed) {
             const int64_t idx_bytes = K * (a.idx_is_64 ? 8 : 4);
             TORCH_CHECK(!c.do_expand && c.sf_stride_col == 1, "bulk side stores need the non-expand layout and row-major scales");
-            TORCH_CHECK(!(c.quantize || fp8) || (c.sf_stride_row == G && (G * 4) % 16 == 0),
-                        "bulk side stores need contiguous scale rows that are a multiple of 16 bytes");
+            TORCH_CHECK(!(c.quantize || fp8) || (c.sf_stride_row >= G && c.sf_stride_row % 4 == 0 && (G * 4) % 16 == 0),
+                        "bulk side stores need scale rows that start on 16-byte boundaries and are a multiple of 16 bytes long");
             TORCH_CHECK(c.tail_bytes % 16 == 0 && c.tail_off_w % 4 == 0 && c.tail_off_meta % 8 == 0 && c.tail_off_w >= idx_bytes &&
                             c.tail_off_meta >= c.tail_off_w + K * 4 && c.tail_bytes >= c.tail_off_meta + 8,
                         "inconsistent tail record layout");
-            check_region(c.off_recv_tail, cap * c.tail_bytes, "recv tail records");
+            const int64_t pitch = c.tail_pitch > 0 ? c.tail_pitch : c.tail_bytes;
+            TORCH_CHECK(pitch >= c.tail_bytes && pitch % 16 == 0, "bad tail record pitch");
+            check_region(c.off_recv_tail, cap * pitch, "recv tail records");
             a.side_packed = 1;
+            a.tail_pitch = static_cast<int>(pitch);
             a.tail_bytes = static_cast<int>(c.tail_bytes);
             a.tail_off_w = static_cast<int>(c.tail_off_w);
             a.tail_off_meta = static_cast<int>(c.tail_off_meta);
@@ -484,6 +518,7 @@ private:
     uint64_t gpu_timeout_ns_;
     double cpu_timeout_secs_;
     uint64_t dispatch_epoch_ = 0;
+    uint64_t memop_seq_[EP_NUM_CHANNELS] = {};
 };
 
 }  // namespace ep_host

@@ -51,7 +51,8 @@ struct RegionLayout {
     int64_t capacity_rows = 0;     // rows a rank can receive in one dispatch
     int64_t x_row_bytes = 0;       // widest row dispatch may write (bf16 unless fp8-only)
     int64_t sf_cols = 0;
-    int64_t tail_bytes = 0;        // bytes of one tail record (multiple of 16)
+    int64_t tail_bytes = 0;        // bytes reserved per tail record (multiple of 128)
+    int64_t sf_row_bytes = 0;      // bytes reserved per scale row (multiple of 128)
     int num_recv_slots = 0;
     RecvSlot slots[4];
     int64_t combine_x[2] = {0, 0}, combine_w[2] = {0, 0};
@@ -79,13 +80,15 @@ inline RegionLayout plan_regions(const MoeShape& s) {
     r.capacity_rows = recv_capacity_rows(s);
     r.x_row_bytes = s.use_fp8_dispatch ? s.hidden : checked_mul(s.hidden, 2);
     r.sf_cols = (s.hidden + 127) / 128;
-    r.tail_bytes = align_up(static_cast<int64_t>(s.num_topk) * 12 + 8, 16);
+    // room for the line-aligned variant of the side stores: scale rows and tail records padded to 128-byte multiples
+    r.tail_bytes = align_up(static_cast<int64_t>(s.num_topk) * 12 + 8, 128);
+    r.sf_row_bytes = align_up(r.sf_cols * 4, 128);
     r.num_recv_slots = s.num_recv_slots;
     const int64_t A = 1024;
     int64_t off = EP_WORKSPACE_BYTES;
     for (int i = 0; i < s.num_recv_slots; ++i) {
         r.slots[i].x = off;    off = align_up(checked_add(off, checked_mul(r.capacity_rows, r.x_row_bytes)), A);
-        r.slots[i].sf = off;   off = align_up(checked_add(off, checked_mul(r.capacity_rows, r.sf_cols * 4)), A);
+        r.slots[i].sf = off;   off = align_up(checked_add(off, checked_mul(r.capacity_rows, r.sf_row_bytes)), A);
         r.slots[i].idx = off;  off = align_up(checked_add(off, checked_mul(r.capacity_rows, s.num_topk * 8)), A);
         r.slots[i].w = off;    off = align_up(checked_add(off, checked_mul(r.capacity_rows, s.num_topk * 4)), A);
         r.slots[i].meta = off; off = align_up(checked_add(off, checked_mul(r.capacity_rows, 8)), A);

@@ -61,6 +61,8 @@ struct DriverApi {
     CUresult (*Unmap)(CUdeviceptr, size_t) = nullptr;
     CUresult (*AddressFree)(CUdeviceptr, size_t) = nullptr;
     CUresult (*Release)(CUmemGenericAllocationHandle) = nullptr;
+    CUresult (*StreamWriteValue64)(CUstream, CUdeviceptr, cuuint64_t, unsigned int) = nullptr;
+    CUresult (*StreamWaitValue64)(CUstream, CUdeviceptr, cuuint64_t, unsigned int) = nullptr;
 
     static const DriverApi& get() {
         static const DriverApi api = [] {
@@ -82,6 +84,8 @@ struct DriverApi {
             load("cuMemUnmap", a.Unmap);
             load("cuMemAddressFree", a.AddressFree);
             load("cuMemRelease", a.Release);
+            load("cuStreamWriteValue64", a.StreamWriteValue64);
+            load("cuStreamWaitValue64", a.StreamWaitValue64);
             return a;
         }();
         return api;

@@ -12,11 +12,14 @@ import math
 
 from ..utils.math import align
 
-# Per-SM throughput of the fused kernels, GB/s (bulk loads from HBM / bulk stores + pulls over NVLink).
-# Defaults; `bench.py --sweep-sms` re-measures them.  Measured at EP8 (8192 tokens, hidden 7168, top-8 of 256): dispatch 614 GB/s
-# with 24 SMs against 645 GB/s with 64, combine 721 against 728: both kernels are NVLink-bound from about 24 SMs on, which is what
-# 40 GB/s of NVLink writes per SM (plus the 25 % headroom below) predicts.
-SM_READ_GBS = 200.0
+# Per-SM throughput of THIS library's fused kernels on B200, GB/s, from the SM sweeps of `bench.py --sweep-sms` /
+# `--min-sms` (8192 tokens, hidden 7168, top-8 of 256):
+#   * write side = dispatch with the fused bf16 -> e4m3 cast: 24 SMs deliver 600 GB/s of received rows at EP4 (SM-bound: 64 SMs
+#     reach 720) and 614 GB/s at EP8 (95 % of the 64-SM rate), i.e. 25 GB/s of rows per SM while the cast is the limit and about
+#     40 GB/s of NVLink stores per SM once the link is; 40 is what reproduces "24 SMs are within 5 % of the link" at EP8;
+#   * read side = the pull of combine: 24 SMs deliver 800 GB/s at EP4 (96 % of the 64-SM rate), at least 33 GB/s per SM with
+#     the fp32 reduction included.  (The reference's 200 / 50 GB/s are constants of its own copy kernels on H800.)
+SM_READ_GBS = 35.0
 SM_WRITE_GBS = 40.0
 NVLINK_GBS = 770.0     # measured peer-copy bandwidth per direction on this pool's B200s
 

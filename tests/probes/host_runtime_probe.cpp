@@ -82,12 +82,12 @@ static void test_layout() {
     const RegionLayout r = plan_regions(s);
     CHECK(r.capacity_rows == 8 * 8192);
     CHECK(r.x_row_bytes == 7168 && r.sf_cols == 56);
-    CHECK(r.tail_bytes % 16 == 0 && r.tail_bytes >= 8 * 12 + 8);
+    CHECK(r.tail_bytes % 128 == 0 && r.tail_bytes >= 8 * 12 + 8 && r.sf_row_bytes % 128 == 0 && r.sf_row_bytes >= 56 * 4);
     // regions are ordered, aligned, disjoint and inside the buffer
     int64_t prev_end = EP_WORKSPACE_BYTES;
     for (int i = 0; i < 2; ++i) {
         const int64_t offs[] = {r.slots[i].x, r.slots[i].sf, r.slots[i].idx, r.slots[i].w, r.slots[i].meta, r.slots[i].tail};
-        const int64_t sizes[] = {r.capacity_rows * r.x_row_bytes, r.capacity_rows * 56 * 4, r.capacity_rows * 64, r.capacity_rows * 32,
+        const int64_t sizes[] = {r.capacity_rows * r.x_row_bytes, r.capacity_rows * r.sf_row_bytes, r.capacity_rows * 64, r.capacity_rows * 32,
                                  r.capacity_rows * 8, r.capacity_rows * r.tail_bytes};
         for (int k = 0; k < 6; ++k) {
             CHECK(offs[k] % 1024 == 0 && offs[k] >= prev_end);

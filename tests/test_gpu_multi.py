@@ -163,6 +163,21 @@ def _worker_misc(rank: int, world: int, port: int):
             acc += gathered[s][rank].float()
         assert torch.equal(out, acc.bfloat16())
         buf.destroy_agrs_session()
+        # ---- the same session with completion signalled by stream memory operations (no SM at all)
+        if buf.core.signal_and_wait_memops(buf._C.CH_AGRS):      # the driver accepts them on this machine
+            buf._agrs['memops'] = True
+            for it in range(3):
+                buf.create_agrs_session()
+                xs_ = torch.full((257, 16), float(10 * it + rank), device='cuda', dtype=torch.bfloat16)
+                gathered, wait = buf.all_gather(xs_)
+                wait()
+                for r in range(world):
+                    assert bool((gathered[r] == 10 * it + r).all()), (it, r)
+                out, wait = buf.reduce_scatter(rs_in)
+                wait()
+                assert torch.equal(out, acc.bfloat16())
+                buf.destroy_agrs_session()
+            buf._agrs['memops'] = False
         # ---- pipeline send / recv around the ring
         buf.pp_set_config(1 << 20, 4)
         nxt, prv = (rank + 1) % world, (rank - 1) % world
