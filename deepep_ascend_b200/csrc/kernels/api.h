@@ -342,7 +342,18 @@ struct MoeBwdArgs {
     float* row_dot;
 };
 
+// Bookkeeping of the expand layout for a grouped GEMM (see expert_segments_kernel).  The start of a segment is a tile
+// boundary (alignment % 128 == 0), so a tile belongs to one segment and holds a token iff its first row does.
+struct ExpertSegmentsArgs {
+    const int32_t* psum_ends;     // [num_groups] inclusive ends of the segments' token rows
+    int num_groups, num_rows, alignment;
+    int32_t* tile_group;          // [ceil(num_rows / 128)] or null
+    uint8_t* valid_row;           // [num_rows] or null
+    int32_t* seg_off;             // [num_groups + 1] or null
+};
+
 namespace ep {
+cudaError_t launch_expert_segments(const ExpertSegmentsArgs& args, cudaStream_t stream);
 cudaError_t launch_swiglu_quant(const SwigluQuantArgs& args, cudaStream_t stream);
 cudaError_t launch_moe_bwd(const MoeBwdArgs& args, cudaStream_t stream);
 int moe_bwd_prep_col_blocks(int cols);   // PREP writes row_dot as [col_blocks, rows] partial sums

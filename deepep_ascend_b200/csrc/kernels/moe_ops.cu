@@ -262,6 +262,33 @@ __global__ void __launch_bounds__(kTileThreads) moe_bwd_dequant_t_kernel(const M
     flush_transposed(tile, a.out_t, a.rows, col0, row0);
 }
 
+
+// Expand-layout bookkeeping of a grouped GEMM in one launch: from the inclusive segment ends (segment e starts at
+// align(end[e - 1], alignment) and holds end[e] - start rows) -> the weights group of every 128-row tile (-1: no token
+// in the tile), one validity byte per row (0: alignment padding) and the aligned segment boundaries [G + 1].
+constexpr int kSegThreads = 256;
+__global__ void __launch_bounds__(kSegThreads) expert_segments_kernel(const ExpertSegmentsArgs a) {
+    extern __shared__ int s_seg[];                    // aligned ends [G]
+    for (int e = threadIdx.x; e < a.num_groups; e += kSegThreads)
+        s_seg[e] = (__ldg(a.psum_ends + e) + a.alignment - 1) / a.alignment * a.alignment;
+    __syncthreads();
+    if (blockIdx.x == 0 && a.seg_off != nullptr) {
+        for (int e = threadIdx.x; e <= a.num_groups; e += kSegThreads) a.seg_off[e] = e == 0 ? 0 : s_seg[e - 1];
+    }
+    const int padded_rows = (a.num_rows + 127) / 128 * 128;
+    for (int row = blockIdx.x * kSegThreads + threadIdx.x; row < padded_rows; row += gridDim.x * kSegThreads) {
+        // first segment whose aligned end lies beyond the row
+        int lo = 0, hi = a.num_groups;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (s_seg[mid] > row) hi = mid;
+            else lo = mid + 1;
+        }
+        const bool in_segment = lo < a.num_groups && row < __ldg(a.psum_ends + lo);
+        if (row < a.num_rows && a.valid_row != nullptr) a.valid_row[row] = in_segment ? 1 : 0;
+        if ((row & 127) == 0 && a.tile_group != nullptr) a.tile_group[row >> 7] = in_segment ? lo : -1;
+    }
+}
 }  // namespace
 
 int moe_bwd_prep_col_blocks(int cols) { return (cols + kPrepCols - 1) / kPrepCols; }
@@ -273,6 +300,13 @@ cudaError_t launch_moe_bwd(const MoeBwdArgs& a, cudaStream_t stream) {
     else if (a.op == EP_MOE_BWD_SWIGLU) moe_bwd_swiglu_kernel<<<dim3(a.rows / kTile, a.cols / kTile), kTileThreads, 0, stream>>>(a);
     else if (a.op == EP_MOE_BWD_DEQUANT_T) moe_bwd_dequant_t_kernel<<<dim3(a.rows / kTile, a.cols / kTile), kTileThreads, 0, stream>>>(a);
     else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_expert_segments(const ExpertSegmentsArgs& a, cudaStream_t stream) {
+    if (a.num_groups < 1 || a.num_groups > 8192 || a.alignment < 128 || a.alignment % 128 != 0 || a.num_rows < 0) return cudaErrorInvalidValue;
+    const int blocks = max(1, min(1024, (a.num_rows + kSegThreads - 1) / kSegThreads));
+    expert_segments_kernel<<<blocks, kSegThreads, a.num_groups * sizeof(int), stream>>>(a);
     return cudaGetLastError();
 }
 

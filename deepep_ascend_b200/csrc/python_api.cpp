@@ -221,6 +221,27 @@ std::vector<at::Tensor> swiglu_quant(const at::Tensor& h, bool keep_bf16) {
     return {q, sf};
 }
 
+// Expand-layout bookkeeping in one launch -> (tile_group int32 [ceil(rows / 128)], valid_row bool [rows], seg_off int32 [G + 1]).
+std::vector<at::Tensor> expert_segments(const at::Tensor& psum_ends, int64_t num_rows, int64_t alignment) {
+    TORCH_CHECK(psum_ends.is_cuda() && psum_ends.is_contiguous() && psum_ends.scalar_type() == at::kInt && psum_ends.dim() == 1,
+                "psum_ends must be a contiguous int32 vector on the device");
+    TORCH_CHECK(num_rows >= 0 && num_rows < (int64_t(1) << 31) && alignment >= 128 && alignment % 128 == 0, "bad num_rows / alignment");
+    const auto i32 = psum_ends.options();
+    at::Tensor tile_group = at::empty({(num_rows + 127) / 128}, i32);
+    at::Tensor valid = at::empty({num_rows}, i32.dtype(at::kBool));
+    at::Tensor seg_off = at::empty({psum_ends.numel() + 1}, i32);
+    ExpertSegmentsArgs a{};
+    a.psum_ends = psum_ends.data_ptr<int32_t>();
+    a.num_groups = static_cast<int>(psum_ends.numel());
+    a.num_rows = static_cast<int>(num_rows);
+    a.alignment = static_cast<int>(alignment);
+    a.tile_group = tile_group.data_ptr<int32_t>();
+    a.valid_row = reinterpret_cast<uint8_t*>(valid.data_ptr());
+    a.seg_off = seg_off.data_ptr<int32_t>();
+    cuda_check(ep::launch_expert_segments(a, at::cuda::getCurrentCUDAStream()), "expert_segments launch");
+    return {tile_group, valid, seg_off};
+}
+
 // Weight gradients of a grouped layer: out[e] = a_t[:, k0:k1] @ b_t[:, k0:k1]^T with (k0, k1) = k_off[e], k_off[e + 1]
 // (a_t [M, K_total], b_t [N, K_total] bf16, K = rows of the expert segment; k_off int32 [G + 1], multiples of 64).
 at::Tensor gemm_kgrouped(const at::Tensor& a_t, const at::Tensor& b_t, const at::Tensor& k_off, int64_t num_sms) {
@@ -555,6 +576,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("a_ready_value") = 0, py::arg("a_flag_of_tile") = py::none(), py::arg("report_to") = nullptr);
     m.def("ag_gemm", &ag_gemm);
     m.def("gemm_rs", &gemm_rs);
+    m.def("expert_segments", &expert_segments, py::arg("psum_ends"), py::arg("num_rows"), py::arg("alignment") = 128);
     m.def("swiglu_quant", &swiglu_quant, py::arg("h"), py::arg("keep_bf16") = false);
     m.def("gemm_kgrouped", &gemm_kgrouped, py::arg("a_t"), py::arg("b_t"), py::arg("k_off"), py::arg("num_sms") = 0);
     m.def("moe_bwd_prep", &moe_bwd_prep);

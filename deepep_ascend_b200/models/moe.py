@@ -60,7 +60,7 @@ class _MoEFunction(torch.autograd.Function):
             (rx, rsf), _, recv_w, handle, ev = disp.pop(c)
             ev.current_stream_wait()
             rows = handle.num_rows
-            tile_group, valid_row = G.expert_tile_groups(handle.psum_num_recv_tokens_per_expert, rows)
+            tile_group, valid_row, seg_off = G.expert_segments(handle.psum_num_recv_tokens_per_expert, rows)
             h = G.grouped_gemm_nt(rx, q13, tile_group, sfa=rsf, sfb=s13, num_sms=gemm_sms, buffer=buf)    # [rows, 2I]
             if keep_copy:
                 # the received rows live in a receive slot of the buffer that later dispatches will reuse
@@ -80,7 +80,7 @@ class _MoEFunction(torch.autograd.Function):
             _, _, cev = buf.combine(y, handle, weighted=True, num_sms=comm_sms, out=out[lo:hi], **kw)
             comb_done.append(cev)
             handles.append(handle)
-            saved += [rx, rsf, recv_w, h, tile_group, valid_row]
+            saved += [rx, rsf, recv_w, h, tile_group, valid_row, seg_off]
         for cev in comb_done[-2:]:
             cev.current_stream_wait()
         ctx.layer, ctx.handles, ctx.bounds = layer, handles, bounds
@@ -95,8 +95,7 @@ class _MoEFunction(torch.autograd.Function):
         d_out = d_out.contiguous()
         dxs, dws, d_w2, d_w13 = [], [], None, None
         for c, handle in enumerate(ctx.handles):
-            rx, rsf, recv_w, h, tile_group, valid_row = ctx.saved_tensors[6 * c:6 * c + 6]
-            seg_off = G.segment_offsets(handle.psum_num_recv_tokens_per_expert)
+            rx, rsf, recv_w, h, tile_group, valid_row, seg_off = ctx.saved_tensors[7 * c:7 * c + 7]
             rw = recv_w.contiguous()
             # backward of the weighted combine: every expert row receives its token's gradient g (cached dispatch)
             g_rows, _, _, _, _ = buf.dispatch(d_out[bounds[c]:bounds[c + 1]], handle=handle, fused_fp8_cast=False, num_sms=layer.num_sms)

@@ -44,11 +44,25 @@ def quantize_weight_blocks(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]
     return q, (amax / 448.0).contiguous()
 
 
-def expert_tile_groups(psum_expert_ends: torch.Tensor, num_rows: int, alignment: int = BLOCK_M) -> Tuple[torch.Tensor, torch.Tensor]:
+def expert_segments(psum_expert_ends: torch.Tensor, num_rows: int, alignment: int = BLOCK_M) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """From the expand-layout segment ends of ``EPHandle.psum_num_recv_tokens_per_expert`` (segment ``i`` starts at
     ``align(end[i-1], alignment)``) -> (``tile_group int32 [ceil(num_rows / 128)]`` with -1 for tiles that hold no
-    token, ``valid_row bool [num_rows]``).  Stays on the device: no host synchronisation."""
+    token, ``valid_row bool [num_rows]``, ``seg_off int32 [G + 1]`` aligned segment boundaries).  One kernel launch, no host
+    synchronisation (CPU tensors take the plain PyTorch statement below)."""
     assert alignment % BLOCK_M == 0, 'expert segments must start on a tile boundary'
+    if not psum_expert_ends.is_cuda:
+        return expert_segments_ref(psum_expert_ends, num_rows, alignment)
+    ends = psum_expert_ends if psum_expert_ends.dtype == torch.int32 else psum_expert_ends.to(torch.int32)
+    return tuple(_native.load().expert_segments(ends.contiguous(), num_rows, alignment))
+
+
+def expert_tile_groups(psum_expert_ends: torch.Tensor, num_rows: int, alignment: int = BLOCK_M) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(tile_group, valid_row)`` of ``expert_segments``."""
+    return expert_segments(psum_expert_ends, num_rows, alignment)[:2]
+
+
+def expert_segments_ref(psum_expert_ends: torch.Tensor, num_rows: int, alignment: int = BLOCK_M):
+    """The same three tensors stated with plain PyTorch operations (what the kernel is tested against)."""
     ends = psum_expert_ends.to(torch.int64)
     aligned_ends = (ends + alignment - 1) // alignment * alignment
     starts = torch.cat([torch.zeros(1, dtype=torch.int64, device=ends.device), aligned_ends[:-1]])
@@ -61,7 +75,8 @@ def expert_tile_groups(psum_expert_ends: torch.Tensor, num_rows: int, alignment:
     rows = torch.arange(num_rows, device=ends.device, dtype=torch.int64)
     rgrp = torch.searchsorted(aligned_ends, rows, right=True).clamp_max(ends.numel() - 1)
     valid_row = (rows >= starts[rgrp]) & (rows < ends[rgrp])
-    return tile_group.contiguous(), valid_row
+    seg_off = torch.cat([torch.zeros(1, dtype=torch.int64, device=ends.device), aligned_ends]).to(torch.int32)
+    return tile_group.contiguous(), valid_row, seg_off.contiguous()
 
 
 def swiglu_quant(h: torch.Tensor, keep_bf16: bool = False):
@@ -80,9 +95,7 @@ def gemm_kgrouped(a_t: torch.Tensor, b_t: torch.Tensor, k_off: torch.Tensor, num
 def segment_offsets(psum_expert_ends: torch.Tensor, alignment: int = BLOCK_M) -> torch.Tensor:
     """Expand-layout segment boundaries as ``int32 [G + 1]``: segment ``e`` covers rows ``[off[e], off[e + 1])``
     including its alignment padding.  Stays on the device."""
-    ends = psum_expert_ends.to(torch.int64)
-    aligned = (ends + alignment - 1) // alignment * alignment
-    return torch.cat([torch.zeros(1, dtype=torch.int64, device=ends.device), aligned]).to(torch.int32).contiguous()
+    return expert_segments(psum_expert_ends, 0, alignment)[2]
 
 
 def moe_bwd_prep(g_rows: torch.Tensor, y: torch.Tensor, w: torch.Tensor, valid_row: torch.Tensor):

@@ -163,3 +163,25 @@ def test_moe_forward_on_virtual_ranks(R):
             assert d < 3e-3, (r, d)
     finally:
         world.destroy()
+
+
+def test_expert_segments_kernel_matches_its_pytorch_statement():
+    """Tile groups, row validity and segment boundaries of the expand layout: the one-launch kernel against plain PyTorch."""
+    from deepep_ascend_b200.ops import gemm as G
+    torch.manual_seed(11)
+    for trial in range(30):
+        num_experts = int(torch.randint(1, 70, (1,)))
+        alignment = 128 * int(torch.randint(1, 3, (1,)))
+        counts = torch.randint(0, 700, (num_experts,))
+        counts[torch.rand(num_experts) < 0.3] = 0
+        ends, start = [], 0
+        for c in counts.tolist():
+            ends.append(start + c)
+            start = (start + c + alignment - 1) // alignment * alignment
+        rows = start + (64 if trial % 3 == 0 else 0)        # also a row count that is not a multiple of the tile
+        ends_t = torch.tensor(ends, dtype=torch.int32, device='cuda')
+        got = G.expert_segments(ends_t, rows, alignment)
+        want = G.expert_segments_ref(ends_t, rows, alignment)
+        for g, w in zip(got, want):
+            assert g.dtype == w.dtype and torch.equal(g, w)
+        assert torch.equal(G.segment_offsets(ends_t, alignment), want[2])
