@@ -202,10 +202,13 @@ def main():
                 launches['n'] = 0
                 buf.kernel_times_ms('dispatch'), buf.kernel_times_ms('combine')
             flush_l2_cache()
-            gpu_barrier()
             # keep the GPU busy for ~1 ms so that the host has enqueued the timed kernel before it can start: the
-            # interval then holds device time only, not launch latency
+            # interval then holds device time only, not launch latency.  The cross-GPU barrier comes AFTER the spin (the
+            # spin counts SM cycles, and two GPUs whose clocks differ by 1 % leave a 1 ms spin 10 us apart), so that all
+            # ranks enter the timed kernel together, as the reference's timing does (bench_kineto with
+            # barrier_comm_profiling, tests/elastic/test_ep.py:453-455).
             torch.cuda._sleep(SLEEP_CYCLES)
+            gpu_barrier()
             # no host sync inside the timed kernels: outputs get their worst-case size and the host runs ahead
             if cached and handle is not None:
                 recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x, handle=handle, topk_weights=w, num_sms=num_sms)
@@ -223,8 +226,8 @@ def main():
                 if i < 2:
                     y.normal_()              # both input regions get defined contents
             flush_l2_cache()
-            gpu_barrier()
             torch.cuda._sleep(SLEEP_CYCLES)
+            gpu_barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             out, _, _ = buf.combine(y, handle, num_sms=combine_sms or num_sms)
@@ -402,9 +405,9 @@ def low_latency_in_a_graph(buf, group, world, rank, M, H, E, K, replays, reduce_
     for i in range(warm + replays):
         e = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
         for k, g in enumerate((gd, gc, gl)):
+            torch.cuda._sleep(400_000)
             if world > 1:
                 buf.barrier(use_comm_stream=False)
-            torch.cuda._sleep(400_000)
             e[2 * k].record()
             g.replay()
             e[2 * k + 1].record()

@@ -62,9 +62,9 @@ def main():
         for i in range(warm + iters):
             if flush:
                 flush_l2_cache()
+            torch.cuda._sleep(SLEEP)        # the host runs ahead; the barrier after it lines the ranks up (the spin counts SM cycles)
             if buf is not None and world > 1:
                 buf.barrier(use_comm_stream=False)
-            torch.cuda._sleep(SLEEP)
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             fn()
@@ -200,9 +200,9 @@ def main():
             torch.cuda.synchronize()
             td, tc = [], []
             for i in range(5 + 100):
+                torch.cuda._sleep(1_000_000)
                 if world > 1:
                     buf.barrier(use_comm_stream=False)
-                torch.cuda._sleep(1_000_000)
                 e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
                 e[0].record()
                 gd.replay()

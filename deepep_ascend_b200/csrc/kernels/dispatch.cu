@@ -185,6 +185,8 @@ __device__ __forceinline__ uint32_t count_of(uint64_t word) { return static_cast
 // converted, and the unrolled conversions of a batch are independent of one another, so neither the memory
 // latency nor the shuffle / reciprocal latency chains of one 128-channel group are exposed.
 // q = x * (448 / max(amax, 1e-4)) rounded to nearest even, scale = max(amax, 1e-4) / 448.
+// The correctly rounded division amax / 448 costs ~20 instructions that only two lanes of a step would use, so the steps
+// leave the clamped amax in the staging row and scales_from_amax divides all groups of the row at once, one group per lane.
 constexpr int kCastSteps = 7;
 
 struct RowBatch {
@@ -198,6 +200,11 @@ __device__ __forceinline__ void load_batch(RowBatch& b, const uint8_t* row, int 
         const int elem = ((batch * kCastSteps + i) * 32 + lane) * 8;
         b.v[i] = elem < H ? ptx::ld_nc_v4(row + elem * 2) : make_int4(0, 0, 0, 0);
     }
+}
+
+__device__ __forceinline__ void scales_from_amax(float* sf, int num_groups) {
+    __syncwarp();
+    for (int g = ptx::lane_id(); g < num_groups; g += 32) sf[g] = __fdiv_rn(sf[g], 448.f);
 }
 
 __device__ __forceinline__ void cast_batch(const RowBatch& b, uint8_t* out, float* sf, int H, int batch) {
@@ -230,7 +237,7 @@ __device__ __forceinline__ void cast_batch(const RowBatch& b, uint8_t* out, floa
                 packed[j] = lo | (hi << 16);
             }
             *reinterpret_cast<uint2*>(out + elem) = make_uint2(packed[0], packed[1]);
-            if ((lane & 15) == 0) sf[elem / 128] = __fdiv_rn(amax, 448.f);
+            if ((lane & 15) == 0) sf[elem / 128] = amax;      // divided by 448 once per row, see scales_from_amax
         }
     }
 }
@@ -615,6 +622,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a) {
                     cast_batch(cur, o, sf_cur, a.hidden, b);
                     cur = nxt;
                 }
+                scales_from_amax(sf_cur, G);
                 src_smem = o;
             } else {
                 alive = mbar_wait_bounded(ctx, ws, &s_bar[st], parity, EP_PH_DISPATCH_LOAD);
