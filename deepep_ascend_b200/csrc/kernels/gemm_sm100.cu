@@ -16,6 +16,7 @@
 // Every pipeline wait is bounded; on expiry the kernel raises `*error`, leaves its loops and frees its TMEM.
 #include <cuda.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <mutex>
 
@@ -174,7 +175,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     constexpr int kEpiWarps = kFp8 ? 8 : 4;
     constexpr bool kWide = kFp8 && kBlockN == 256;   // register re-allocation between warpgroups
     constexpr int kEpiWarp0 = kWide ? 4 : 2;         // first epilogue warp
-    constexpr int kTmemColumns = kAccBufs * kBlockN;
+    constexpr int kTmemColumns = kAccBufs * kBlockN <= 256 ? 256 : 512;   // allocations are powers of two
+    static_assert(kBlockN % 32 == 0 && kBlockN >= 32 && kBlockN <= 256 && kAccBufs * kBlockN <= 512, "tile width");
     uint8_t* s_a = smem;
     uint8_t* s_b = smem + kStages * kTileBytes;
     GemmSmem* sm = reinterpret_cast<GemmSmem*>(smem + kStages * (kTileBytes + kTileBytesB));
@@ -654,15 +656,29 @@ cudaError_t launch_gemm(const GemmArgs& g, int num_sms, cudaStream_t stream) {
     if ((g.lda * elem) % 16 != 0 || (g.ldb * elem) % 16 != 0 || g.ldc % 8 != 0 || g.N % 8 != 0) return cudaErrorInvalidValue;
     if (reinterpret_cast<uintptr_t>(g.a) % 16 != 0 || reinterpret_cast<uintptr_t>(g.b) % 16 != 0 || reinterpret_cast<uintptr_t>(g.c) % 16 != 0)
         return cudaErrorInvalidValue;
-    // bf16: 128 x 256 output tiles (fewer A re-reads, longer MMAs); the block-scaled FP8 path and the reduce-scatter
-    // epilogue (which stages 128-column rows) use 128 x 128 tiles
-    const int block_n = (g.fuse != EP_GEMM_FUSE_REDUCE_SCATTER && g.N >= 256) ? 256 : 128;
+    // 128 x 256 output tiles (fewer A re-reads, longer MMAs); the reduce-scatter epilogue (which stages 128-column rows)
+    // and narrow outputs use 128 x 128 tiles.  The bf16 kernel also has 128 x 224 tiles and takes them when they need less
+    // tensor-core time: fewer idle CTAs in the last wave (8192 x 7168: 1792 tiles of 256 columns are 12.1 waves of 148
+    // CTAs, paid as 13; 2048 tiles of 224 columns are 13.8 waves of 7/8 the length), or no half-empty last column tile
+    // (N = 896 = 4 x 224).
+    int block_n = (g.fuse != EP_GEMM_FUSE_REDUCE_SCATTER && g.N >= 256) ? 256 : 128;
+    if (block_n == 256 && !g.is_fp8) {
+        const int64_t num_m_tiles = (g.M + kBlockM - 1) / kBlockM, groups = g.k_group_off != nullptr ? g.num_groups : 1;
+        const int64_t workers = std::max(1, (num_sms < 1 ? 1 : num_sms) - (g.fuse == EP_GEMM_FUSE_ALL_GATHER ? g.num_copy_ctas : 0));
+        auto cost = [&](int bn) {
+            const int64_t tiles = num_m_tiles * ((g.N + bn - 1) / bn) * groups;
+            return (tiles + workers - 1) / workers * (bn + 16);     // waves x (columns + per-tile overhead)
+        };
+        if (cost(224) < cost(256)) block_n = 224;
+    }
     CUtensorMap map_a, map_b;
     if (!make_operand_map(&map_a, g.a, g.M, g.K, g.lda, g.is_fp8, 128) ||
         !make_operand_map(&map_b, g.b, static_cast<int64_t>(g.k_group_off != nullptr ? 1 : g.num_groups) * g.N, g.K, g.ldb, g.is_fp8, block_n))
         return cudaErrorInvalidValue;
     const void* fn = g.is_fp8 ? (block_n == 256 ? (const void*)gemm_kernel<true, 256> : (const void*)gemm_kernel<true, 128>)
-                              : (block_n == 256 ? (const void*)gemm_kernel<false, 256> : (const void*)gemm_kernel<false, 128>);
+                              : (block_n == 256   ? (const void*)gemm_kernel<false, 256>
+                                 : block_n == 224 ? (const void*)gemm_kernel<false, 224>
+                                                  : (const void*)gemm_kernel<false, 128>);
     const int kGemmSmemBytes = gemm_smem_bytes(block_n, g.is_fp8 != 0);
     cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
     if (err != cudaSuccess) return err;

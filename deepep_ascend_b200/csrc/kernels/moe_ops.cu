@@ -10,7 +10,24 @@ namespace ep {
 
 namespace {
 
-// one warp per row; each step covers 256 channels (two 128-channel scale groups)
+// one warp per row; each step covers 256 channels (two 128-channel scale groups).  The loads of two steps are issued
+// before the arithmetic of the first, the sigmoid uses the fast reciprocal (the activation is rounded to bf16 right
+// after), and the correctly rounded amax / 448 of a group is computed once per 16 steps by the lane that kept that amax
+// (all lanes divide at once) instead of by two lanes in every step.
+struct SwigluStep {
+    int4 gate, up;
+};
+__device__ __forceinline__ SwigluStep swiglu_load(const uint8_t* gate, const uint8_t* up, int elem, int I) {
+    SwigluStep s;
+    if (elem < I) {
+        s.gate = ptx::ld_nc_v4(gate + elem * 2);
+        s.up = ptx::ld_nc_v4(up + elem * 2);
+    } else {
+        s.gate = s.up = make_int4(0, 0, 0, 0);
+    }
+    return s;
+}
+
 __global__ void swiglu_quant_kernel(const SwigluQuantArgs a) {
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -19,30 +36,35 @@ __global__ void swiglu_quant_kernel(const SwigluQuantArgs a) {
     const uint8_t* gate = reinterpret_cast<const uint8_t*>(a.h) + static_cast<int64_t>(row) * a.ldh * 2;
     const uint8_t* up = gate + static_cast<int64_t>(I) * 2;
     uint8_t* q = reinterpret_cast<uint8_t*>(a.q) + static_cast<int64_t>(row) * I;
-    const int iters = (I + 255) / 256;
+    float* sf_row = a.sf + static_cast<int64_t>(row) * a.sf_stride_row;
+    const int iters = (I + 255) / 256, num_groups = (I + 127) / 128;
+    float kept = 0.f;                 // amax of the group this lane will divide: step (lane & 15) of the current 16, half lane >> 4
+    auto flush_scales = [&](int first_step) {
+        const int group = (first_step + (lane & 15)) * 2 + (lane >> 4);
+        if (group < num_groups && first_step + (lane & 15) < iters) sf_row[group * a.sf_stride_col] = __fdiv_rn(kept, 448.f);
+    };
+    SwigluStep cur = swiglu_load(gate, up, lane * 8, I);
     for (int i = 0; i < iters; ++i) {
         const int elem = (i * 32 + lane) * 8;
         const bool in_range = elem < I;
+        const SwigluStep nxt = swiglu_load(gate, up, i + 1 < iters ? elem + 256 : I, I);
         float v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = 0.f;
-        if (in_range) {
-            const int4 graw = ptx::ld_nc_v4(gate + elem * 2), uraw = ptx::ld_nc_v4(up + elem * 2);
-            const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&graw);
-            const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+        {
+            const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&cur.gate);
+            const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&cur.up);
             int4 act_raw;
             __nv_bfloat162* ah = reinterpret_cast<__nv_bfloat162*>(&act_raw);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float2 gf = __bfloat1622float2(gh[j]), uf = __bfloat1622float2(uh[j]);
-                const float a0 = gf.x / (1.f + __expf(-gf.x)) * uf.x, a1 = gf.y / (1.f + __expf(-gf.y)) * uf.y;
+                const float a0 = __fdividef(gf.x, 1.f + __expf(-gf.x)) * uf.x, a1 = __fdividef(gf.y, 1.f + __expf(-gf.y)) * uf.y;
                 // the activation is rounded to bf16 first so that the FP8 cast sees the same values as a bf16 pipeline
                 ah[j] = __floats2bfloat162_rn(a0, a1);
                 const float2 r = __bfloat1622float2(ah[j]);
                 v[2 * j] = r.x;
                 v[2 * j + 1] = r.y;
             }
-            if (a.act_bf16 != nullptr)
+            if (in_range && a.act_bf16 != nullptr)
                 *reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(a.act_bf16) + (static_cast<int64_t>(row) * I + elem) * 2) = act_raw;
         }
         float amax = 0.f;
@@ -50,6 +72,7 @@ __global__ void swiglu_quant_kernel(const SwigluQuantArgs a) {
         for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
         amax = fmaxf(ptx::warp_max_16(amax), 1e-4f);
         const float scale = __fmul_rn(448.f, __frcp_rn(amax));
+        if ((lane & 15) == (i & 15)) kept = amax;
         if (in_range) {
             uint32_t packed[2];
 #pragma unroll
@@ -59,9 +82,11 @@ __global__ void swiglu_quant_kernel(const SwigluQuantArgs a) {
                 packed[j] = lo | (hi << 16);
             }
             *reinterpret_cast<uint2*>(q + elem) = make_uint2(packed[0], packed[1]);
-            if ((lane & 15) == 0) a.sf[static_cast<int64_t>(row) * a.sf_stride_row + (elem / 128) * a.sf_stride_col] = __fdiv_rn(amax, 448.f);
         }
+        if ((i & 15) == 15) flush_scales(i - 15);
+        cur = nxt;
     }
+    if ((iters & 15) != 0) flush_scales(iters & ~15);
 }
 
 // ---------------------------------------------------------------------------------------------- backward pass

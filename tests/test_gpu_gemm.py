@@ -10,8 +10,10 @@ def _C():
     return _native.load()
 
 
-@pytest.mark.parametrize('M,N,K', [(128, 128, 64), (128, 128, 256), (256, 384, 512), (1000, 520, 1096), (4096, 2048, 7168)])
+@pytest.mark.parametrize('M,N,K', [(128, 128, 64), (128, 128, 256), (256, 384, 512), (1000, 520, 1096), (4096, 2048, 7168),
+                                   (1024, 896, 1024), (2048, 7168, 512)])
 def test_bf16_gemm(M, N, K):
+    """Shapes that take each of the three tile widths (128, 224 and 256 columns; the launcher picks by tile count)."""
     C = _C()
     g = torch.Generator(device='cuda').manual_seed(M + N)
     a = torch.randn(M, K, device='cuda', generator=g).bfloat16()

@@ -185,3 +185,29 @@ def test_expert_segments_kernel_matches_its_pytorch_statement():
         for g, w in zip(got, want):
             assert g.dtype == w.dtype and torch.equal(g, w)
         assert torch.equal(G.segment_offsets(ends_t, alignment), want[2])
+
+
+@pytest.mark.parametrize('rows,I', [(5, 128), (77, 384), (300, 2048), (40, 4352)])
+def test_swiglu_quant_kernel(rows, I):
+    """SwiGLU fused with the 1 x 128 e4m3 cast against plain PyTorch (I = 4352 takes more than 16 steps per row, I = 384
+    ends in a half step)."""
+    from deepep_ascend_b200.ops import gemm as G
+    from deepep_ascend_b200.utils.math import calc_diff, per_token_cast_back
+    torch.manual_seed(rows + I)
+    h = (torch.randn(rows, 2 * I, device='cuda') * 2).bfloat16()
+    h[0, :I] = -60.0                      # sigmoid underflows: the activation is 0 and the scale is clamped
+    q, sf, act = G.swiglu_quant(h, keep_bf16=True)
+    gate, up = h[:, :I].float(), h[:, I:].float()
+    ref = (torch.nn.functional.silu(gate) * up)
+    assert act.dtype == torch.bfloat16 and q.dtype == torch.float8_e4m3fn and sf.shape == (rows, I // 128)
+    torch.testing.assert_close(act.float(), ref.bfloat16().float(), rtol=1.6e-2, atol=1e-6)
+    # the scales are exactly amax / 448 of the bf16 activation the kernel produced, and the codes are its cast
+    # (stated on the CPU: CUDA PyTorch turns a division by a constant into a multiplication by its reciprocal)
+    act_c = act.float().cpu().view(rows, I // 128, 128)
+    amax = act_c.abs().amax(dim=2).clamp(1e-4)
+    assert torch.equal(sf.cpu(), amax / 448.0)
+    want_q = (act_c * (448.0 / amax).unsqueeze(2)).view(rows, I).to(torch.float8_e4m3fn)
+    assert torch.equal(q.cpu().view(torch.uint8), want_q.view(torch.uint8))
+    assert calc_diff(per_token_cast_back(q, sf), ref) < 1e-3
+    q2, sf2 = G.swiglu_quant(h)
+    assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8)) and torch.equal(sf2, sf)
