@@ -319,6 +319,11 @@ def main():
         flops_fwd = rows * (2 * H * 2 * I + 2 * I * H)
         emit(bench='fused_moe_layer', tokens_per_rank=Tm, hidden=H, intermediate=I, experts_per_rank=Em // world, fwd_ms=float(tf), fwd_bwd_ms=float(tfb), fwd_bwd_ms_all=[round(float(v), 3) for v in tfb_all],
              fwd_expert_tflops_per_gpu=flops_fwd / tf / 1e9, note='includes the host sync of dispatch (exact sizes)')
+        # the same layer with the data-gradient GEMMs (and the dispatch of the output gradient) in e4m3
+        layer.fp8_backward = True
+        tfb8 = np.median(timeit(fwd_bwd, buf, iters=bi, warm=bw))
+        layer.fp8_backward = False
+        emit(bench='fused_moe_layer_fp8_backward', fwd_bwd_ms=float(tfb8), note='dgrad GEMMs and gradient dispatch in e4m3; weight gradients bf16')
         # the same layer as a pipeline of chunks: communication of one chunk under the GEMMs of its neighbours
         with torch.no_grad():
             for chunks, comm_sms in ((1, 64), (2, 24), (4, 24), (4, 16), (8, 24)):

@@ -91,25 +91,40 @@ class _MoEFunction(torch.autograd.Function):
     def backward(ctx, d_out):
         layer, bounds = ctx.layer, ctx.bounds
         buf: ElasticBuffer = layer.buffer
-        w2_t, w13_t = layer.transposed_weights()
+        w2_t, w13_t = (None, None) if layer.fp8_backward else layer.transposed_weights()
         d_out = d_out.contiguous()
         dxs, dws, d_w2, d_w13 = [], [], None, None
         for c, handle in enumerate(ctx.handles):
             rx, rsf, recv_w, h, tile_group, valid_row, seg_off = ctx.saved_tensors[7 * c:7 * c + 7]
             rw = recv_w.contiguous()
-            # backward of the weighted combine: every expert row receives its token's gradient g (cached dispatch)
-            g_rows, _, _, _, _ = buf.dispatch(d_out[bounds[c]:bounds[c + 1]], handle=handle, fused_fp8_cast=False, num_sms=layer.num_sms)
-            # down projection on the UNWEIGHTED gradient: d loss / d weight of a row is <g W2, activation> (= <g, y>, so the
-            # expert outputs need not be kept), and the weight is applied inside the SwiGLU backward kernel.  Padding rows of
-            # g_rows hold stale data; every consumer masks them.
-            d_act_u = G.grouped_gemm_nt(g_rows, w2_t, tile_group, buffer=buf)                    # [rows, I]
-            dh, dh_t, act_t, d_w_rows = G.swiglu_bwd(d_act_u, h, valid_row, row_weight=rw)
-            # up projection: the gradient rows go into the combine region and travel home (backward of dispatch)
-            d_recv = buf.get_combine_buffer(handle)
-            G.grouped_gemm_nt(dh, w13_t, tile_group, out=d_recv, buffer=buf)
-            dx, d_topk_w, _ = buf.combine(d_recv, handle, topk_weights=d_w_rows, num_sms=layer.num_sms)
+            if layer.fp8_backward:
+                # Data gradients on the e4m3 tensor cores, as the forward GEMMs: the gradient rows are cast (1 x 128 scales)
+                # inside the dispatch kernel, the weights are the forward e4m3 weights transposed (128 x 128 blocks stay
+                # 128 x 128 blocks), and the SwiGLU gradient is cast once more before the up projection.
+                q2_t, s2_t, q13_t, s13_t = layer.fp8_transposed_weights()
+                (g_q, g_sf), _, _, _, _ = buf.dispatch(d_out[bounds[c]:bounds[c + 1]], handle=handle, fused_fp8_cast=True, num_sms=layer.num_sms)
+                d_act_u = G.grouped_gemm_nt(g_q, q2_t, tile_group, sfa=g_sf, sfb=s2_t, buffer=buf)             # [rows, I]
+                dh, dh_t, act_t, d_w_rows = G.swiglu_bwd(d_act_u, h, valid_row, row_weight=rw)
+                dh_q, dh_sf = G.per_token_cast_to_fp8(dh)
+                d_recv = buf.get_combine_buffer(handle)
+                G.grouped_gemm_nt(dh_q, q13_t, tile_group, out=d_recv, sfa=dh_sf, sfb=s13_t, buffer=buf)
+                dx, d_topk_w, _ = buf.combine(d_recv, handle, topk_weights=d_w_rows, num_sms=layer.num_sms)
+                # (g * w)^T for the weight gradient: the routing weight rides on the scales of the dequantisation
+                dy_t = G.dequant_transpose(g_q, g_sf * rw.unsqueeze(1), valid_row)
+            else:
+                # backward of the weighted combine: every expert row receives its token's gradient g (cached dispatch)
+                g_rows, _, _, _, _ = buf.dispatch(d_out[bounds[c]:bounds[c + 1]], handle=handle, fused_fp8_cast=False, num_sms=layer.num_sms)
+                # down projection on the UNWEIGHTED gradient: d loss / d weight of a row is <g W2, activation> (= <g, y>, so the
+                # expert outputs need not be kept), and the weight is applied inside the SwiGLU backward kernel.  Padding rows of
+                # g_rows hold stale data; every consumer masks them.
+                d_act_u = G.grouped_gemm_nt(g_rows, w2_t, tile_group, buffer=buf)                    # [rows, I]
+                dh, dh_t, act_t, d_w_rows = G.swiglu_bwd(d_act_u, h, valid_row, row_weight=rw)
+                # up projection: the gradient rows go into the combine region and travel home (backward of dispatch)
+                d_recv = buf.get_combine_buffer(handle)
+                G.grouped_gemm_nt(dh, w13_t, tile_group, out=d_recv, buffer=buf)
+                dx, d_topk_w, _ = buf.combine(d_recv, handle, topk_weights=d_w_rows, num_sms=layer.num_sms)
+                dy_t = G.weighted_transpose(g_rows, rw, valid_row)                                  # (g * w)^T [H, rows]
             # weight gradients: one K-grouped GEMM per weight tensor, reduction over the rows of every expert segment
-            dy_t = G.weighted_transpose(g_rows, rw, valid_row)                                  # (g * w)^T [H, rows]
             x_t = G.dequant_transpose(rx, rsf, valid_row)
             g2 = G.gemm_kgrouped(dy_t, act_t, seg_off)                                          # [El, H, I]
             g13 = G.gemm_kgrouped(dh_t, x_t, seg_off)                                           # [El, 2I, H]
@@ -133,7 +148,7 @@ class FusedMoE(nn.Module):
     """
 
     def __init__(self, buffer: ElasticBuffer, num_experts: int, hidden: int, intermediate: int, init_std: float = 0.02,
-                 num_sms: int = 0, device='cuda', copy_saved_rows: bool = True, num_chunks: int = 1):
+                 num_sms: int = 0, device='cuda', copy_saved_rows: bool = True, num_chunks: int = 1, fp8_backward: bool = False):
         super().__init__()
         assert num_experts % buffer.num_ranks == 0 and hidden % 128 == 0 and intermediate % 128 == 0
         assert buffer.enable_expand, 'construct the buffer with enable_expand=True, expert_alignment=128'
@@ -145,10 +160,14 @@ class FusedMoE(nn.Module):
         self.copy_saved_rows = copy_saved_rows
         # > 1: the batch is processed as that many pipelined chunks (communication of one chunk under the GEMMs of another)
         self.num_chunks = num_chunks
+        # True: the data-gradient GEMMs (and the dispatch of the output gradient) run in e4m3 with block scales like the forward
+        # pass; the weight gradients stay in bf16.  False: the whole backward pass is bf16.
+        self.fp8_backward = fp8_backward
         el = num_experts // buffer.num_ranks
         self.w13 = nn.Parameter((torch.randn(el, 2 * intermediate, hidden, device=device) * init_std).bfloat16())
         self.w2 = nn.Parameter((torch.randn(el, hidden, intermediate, device=device) * init_std).bfloat16())
         self._fp8 = None
+        self._fp8_t = None
         self._t = None
 
     def sm_split(self, pipelined: bool):
@@ -169,6 +188,16 @@ class FusedMoE(nn.Module):
             q2, s2 = G.quantize_weight_blocks(self.w2.detach().float())
             self._fp8 = (self._versions(), (q13, s13, q2, s2))
         return self._fp8[1]
+
+    def fp8_transposed_weights(self):
+        """``(w2^T e4m3 [El, I, H], its scales, w13^T e4m3 [El, H, 2I], its scales)``: the forward e4m3 weights transposed (a
+        128 x 128 scale block of W is a 128 x 128 scale block of W^T, so nothing is quantised again)."""
+        if self._fp8_t is None or self._fp8_t[0] != self._versions():
+            q13, s13, q2, s2 = self.fp8_weights()
+            t = lambda w: w.transpose(1, 2).contiguous()    # noqa: E731
+            self._fp8_t = (self._versions(), (t(q2.view(torch.uint8)).view(torch.float8_e4m3fn), t(s2),
+                                              t(q13.view(torch.uint8)).view(torch.float8_e4m3fn), t(s13)))
+        return self._fp8_t[1]
 
     def transposed_weights(self):
         if self._t is None or self._t[0] != self._versions():

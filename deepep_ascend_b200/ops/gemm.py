@@ -79,6 +79,12 @@ def expert_segments_ref(psum_expert_ends: torch.Tensor, num_rows: int, alignment
     return tile_group.contiguous(), valid_row, seg_off.contiguous()
 
 
+def per_token_cast_to_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 ``[rows, H]`` -> (e4m3 ``[rows, H]``, fp32 scales ``[rows, ceil(H / 128)]``), one kernel."""
+    q, sf = _native.load().per_token_cast_to_fp8(x.contiguous())
+    return q, sf
+
+
 def swiglu_quant(h: torch.Tensor, keep_bf16: bool = False):
     """``h [rows, 2I]`` bf16 (gate | up) -> ``(e4m3 [rows, I], scales [rows, I/128][, bf16 activation])``."""
     return _native.load().swiglu_quant(h, keep_bf16)
