@@ -278,10 +278,15 @@ def main():
         extra.update({f'dispatch_gbs_{args.min_sms}sms': gbs(td, disp_row_bytes), f'combine_gbs_{args.min_sms}sms': gbs(tc, comb_row_bytes),
                       f'dispatch_ms_{args.min_sms}sms': td, f'combine_ms_{args.min_sms}sms': tc})
     if not args.no_variants:
-        (_, tc), _, _ = run(args.num_sms, args.combine_sms, short, 3, plain_combine=True)
-        extra.update({'combine_gbs_plain_tensor': gbs(tc, comb_row_bytes), 'combine_ms_plain_tensor': tc})
-        (td, _), _, _ = run(args.num_sms, args.combine_sms, short, 3, cached=True)
-        extra.update({'dispatch_gbs_cached_layout': gbs(td, disp_row_bytes), 'dispatch_ms_cached_layout': td})
+        # This interval spans two operations that the host enqueues one after the other (staging copy, kernel), so a host
+        # stall between the two lands in it (seen: one step of ten taking 8 - 27 ms on some runs); the median over steps
+        # is the figure, the mean is given beside it.
+        (_, tc), (_, tc_med), _ = run(args.num_sms, args.combine_sms, short, 3, plain_combine=True)
+        extra.update({'combine_gbs_plain_tensor': gbs(tc_med, comb_row_bytes), 'combine_ms_plain_tensor': tc_med,
+                      'combine_ms_plain_tensor_mean': tc})
+        (td, _), (td_med, _), _ = run(args.num_sms, args.combine_sms, short, 3, cached=True)
+        extra.update({'dispatch_gbs_cached_layout': gbs(td, disp_row_bytes), 'dispatch_ms_cached_layout': td,
+                      'dispatch_ms_cached_layout_median': td_med})
 
     sweep = {}
     for sms in [int(v) for v in args.sweep_sms.split(',') if v]:
