@@ -137,6 +137,7 @@ def main():
     import torch
     import torch.distributed as dist
     from deepep_ascend_b200 import ElasticBuffer
+    from deepep_ascend_b200.ops.gemm import per_token_cast_to_fp8
     from deepep_ascend_b200.utils.testing import flush_l2_cache
 
     world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -186,7 +187,7 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
         return t
 
-    def run(num_sms, combine_sms, steps, warmup, plain_combine=False, cached=False):
+    def run(num_sms, combine_sms, steps, warmup, plain_combine=False, cached=False, prequantized=False):
         """-> (mean, median) ms of the dispatch kernel and of the combine step, max over ranks per step.
         Kernel times are CUDA events recorded on the communication stream right around each kernel (the library's
         kernel timing).  With `plain_combine` the combine input is an ordinary tensor, and the interval (events on the
@@ -194,6 +195,9 @@ def main():
         handle = None
         outer = []
         y_plain = None
+        # `prequantized`: the e4m3 rows and their 1 x 128 scales are made before the timed kernel (what the reference's
+        # benchmark feeds its dispatch, tests/elastic/test_ep.py:286); otherwise the cast is part of the timed kernel
+        x_in = per_token_cast_to_fp8(x) if prequantized else x
         buf.kernel_times_ms('dispatch'), buf.kernel_times_ms('combine')
         for i in range(warmup + steps):
             if i == warmup:
@@ -211,10 +215,10 @@ def main():
             gpu_barrier()
             # no host sync inside the timed kernels: outputs get their worst-case size and the host runs ahead
             if cached and handle is not None:
-                recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x, handle=handle, topk_weights=w, num_sms=num_sms)
+                recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x_in, handle=handle, topk_weights=w, num_sms=num_sms)
             else:
                 # (the plain-tensor variant wants the exact row count, so that its staging copy moves the received rows only)
-                recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x, idx, w, num_experts=E, num_sms=num_sms, do_cpu_sync=plain_combine,
+                recv_x, recv_idx, recv_w, handle, _ = buf.dispatch(x_in, idx, w, num_experts=E, num_sms=num_sms, do_cpu_sync=plain_combine,
                                                                    do_handle_copy=False)
             launches['n'] += 1
             if plain_combine:
@@ -287,6 +291,13 @@ def main():
         (td, _), (td_med, _), _ = run(args.num_sms, args.combine_sms, short, 3, cached=True)
         extra.update({'dispatch_gbs_cached_layout': gbs(td, disp_row_bytes), 'dispatch_ms_cached_layout': td,
                       'dispatch_ms_cached_layout_median': td_med})
+        # the reference's own benchmark configuration: rows quantised before the call
+        (td, _), _, _ = run(args.num_sms, args.combine_sms, short, 3, prequantized=True)
+        extra.update({'dispatch_gbs_prequantized_input': gbs(td, disp_row_bytes), 'dispatch_ms_prequantized_input': td})
+        if args.min_sms > 0:
+            (td, _), _, _ = run(args.min_sms, args.min_sms, short, 3, prequantized=True)
+            extra.update({f'dispatch_gbs_prequantized_input_{args.min_sms}sms': gbs(td, disp_row_bytes),
+                          f'dispatch_ms_prequantized_input_{args.min_sms}sms': td})
 
     sweep = {}
     for sms in [int(v) for v in args.sweep_sms.split(',') if v]:
