@@ -31,6 +31,7 @@ def main():
     p.add_argument('--gpus', type=int, default=1)
     p.add_argument('--what', default='all')
     p.add_argument('--iters', type=int, default=20)
+    p.add_argument('--phase-sms', default='24,64', help='SM counts of the dispatch / combine phase breakdown and tuning sweep')
     p.add_argument('--moe-tokens', type=int, default=4096, help='tokens per rank of the fused MoE benchmark')
     p.add_argument('--moe-experts', type=int, default=0, help='experts of the fused MoE benchmark (default 256, or 32 on one GPU)')
     args = p.parse_args()
@@ -109,8 +110,8 @@ def main():
             buf.kernel_times_ms(name)
             timeit(fn, buf, iters=iters)
             return float(np.median(reduce_max(buf.kernel_times_ms(name)[-iters:])))
-        for sms in (24, 64):
-            for warps, stages in ((0, 0), (8, 3), (6, 4)):
+        for sms in [int(v) for v in args.phase_sms.split(',') if v]:
+            for warps, stages in ((0, 0), (8, 3), (6, 4), (8, 2), (10, 2)):
                 buf.set_dispatch_tuning(warps, stages)
                 t = kernel_ms('dispatch', disp(sms))
                 emit(bench='dispatch', num_sms=sms, warps=warps or 12, stages=stages or 2, ms=t, gbs=rows * 7488 / t / 1e6)
@@ -281,6 +282,24 @@ def main():
         emit(bench='fused_moe_forward_breakdown_ms', rows=hd.num_rows, dispatch_expand_fp8=float(t_disp), gemm1_fp8=float(t_g1),
              swiglu_cast=float(t_sw), gemm2_fp8=float(t_g2), combine_weighted=float(t_comb),
              gemm1_tflops=2 * hd.num_rows * H * 2 * I / t_g1 / 1e9, gemm2_tflops=2 * hd.num_rows * H * I / t_g2 / 1e9)
+        # the pieces that replace the expand-layout dispatch / combine when the expansion happens on the expert rank
+        def d_loc():
+            st['l'] = buf.dispatch(x.detach(), idx, w.detach(), num_experts=Em, do_expand=False, expert_alignment=G.BLOCK_M,
+                                   fused_fp8_cast=True, num_sms=64)
+        d_loc()
+        t_dl = np.median(timeit(d_loc, buf, iters=bi, warm=bw))
+        (rx_r, rsf_r), ridx, rw_r, hl, _ = st['l']
+        rows_l = sum(hl.num_recv_tokens_per_expert_list)
+        t_plan = np.median(timeit(lambda: G.local_expand_plan(ridx, hl.psum_num_recv_tokens_per_expert), None, iters=bi, warm=bw))
+        pos, seg_end = G.local_expand_plan(ridx, hl.psum_num_recv_tokens_per_expert)
+        t_copy = np.median(timeit(lambda: G.local_expand_copy(pos, rx_r, rows_l, sf=rsf_r, w=rw_r), None, iters=bi, warm=bw))
+        w_e = G.local_expand_copy(pos, rx_r, rows_l, sf=rsf_r, w=rw_r)[2]
+        y_exp = torch.randn(rows_l, H, device='cuda').bfloat16()
+        t_red = np.median(timeit(lambda: G.local_reduce(pos, y_exp, w=w_e, out=buf.get_combine_buffer(hl)), None, iters=bi, warm=bw))
+        t_cl = np.median(timeit(lambda: buf.combine(buf.get_combine_buffer(hl), hl, num_sms=64), buf, iters=bi, warm=bw))
+        emit(bench='fused_moe_local_expand_breakdown_ms', received_rows=hl.num_rows, expert_rows=rows_l, dispatch_fp8=float(t_dl),
+             plan=float(t_plan), expand_copy=float(t_copy), local_reduce=float(t_red), combine=float(t_cl))
+        del y_exp, w_e
         # backward pieces, timed one by one on this rank's rows
         g_rows = torch.randn(hd.num_rows, H, device='cuda').bfloat16()
         rwc = rw.contiguous()
@@ -319,6 +338,12 @@ def main():
         flops_fwd = rows * (2 * H * 2 * I + 2 * I * H)
         emit(bench='fused_moe_layer', tokens_per_rank=Tm, hidden=H, intermediate=I, experts_per_rank=Em // world, fwd_ms=float(tf), fwd_bwd_ms=float(tfb), fwd_bwd_ms_all=[round(float(v), 3) for v in tfb_all],
              fwd_expert_tflops_per_gpu=flops_fwd / tf / 1e9, note='includes the host sync of dispatch (exact sizes)')
+        # the same layer with the buffer's expand layout: one row per (token, expert) over NVLink instead of one per (token, rank)
+        layer.local_expand = False
+        tf_x = np.median(timeit(fwd, buf, iters=bi, warm=bw))
+        tfb_x = np.median(timeit(fwd_bwd, buf, iters=bi, warm=bw))
+        layer.local_expand = True
+        emit(bench='fused_moe_layer_expand_over_nvlink', fwd_ms=float(tf_x), fwd_bwd_ms=float(tfb_x))
         # the same layer with the data-gradient GEMMs (and the dispatch of the output gradient) in e4m3
         layer.fp8_backward = True
         tfb8 = np.median(timeit(fwd_bwd, buf, iters=bi, warm=bw))

@@ -352,7 +352,52 @@ struct ExpertSegmentsArgs {
     int32_t* seg_off;             // [num_groups + 1] or null
 };
 
+// Local expansion of a (token, rank) layout into the (token, expert) layout of a grouped GEMM, and its inverse.  A
+// non-expand dispatch delivers every token once per rank together with the ids of the local experts it selected
+// (recv_idx [rows, K], -1 elsewhere).  PLAN numbers the (row, k) pairs of every local expert in row order inside that
+// expert's 128-aligned segment; COPY writes each received row to its expert rows; REDUCE adds the expert rows of a received
+// row (optionally weighted) back into one row.  What crosses NVLink is then one row per (token, rank) instead of one per
+// (token, expert).
+struct LocalExpandPlanArgs {
+    const void* recv_idx;             // [rows, K] int64 / int32, row pitch idx_pitch elements
+    int idx_is_64;
+    int64_t idx_pitch;
+    int num_rows, num_topk, num_local_experts;
+    const int32_t* seg_end_aligned;   // [El] inclusive prefix sums of the 128-aligned expert counts (segment e starts at [e - 1])
+    int32_t* pos;                     // [rows, K] expert row of (row, k); the caller fills it with -1 first
+    int32_t* seg_end;                 // [El] out: end of the token rows of every segment (start + count)
+    int num_ctas;                     // CTAs of the two launches (8 warps each)
+    int32_t* warp_counts;             // scratch [num_ctas * 8, El]
+    int32_t* cta_counts;              // scratch [num_ctas, El]
+};
+struct LocalExpandCopyArgs {
+    const int32_t* pos;               // [rows, K]
+    int num_rows, num_topk;
+    const void* src;                  // [rows] rows of row_bytes (multiple of 16), pitch src_pitch bytes
+    int64_t src_pitch;
+    int row_bytes;
+    void* dst;                        // [expert rows, row_bytes] contiguous
+    const float* sf_src;              // optional scales [rows, sf_cols], element strides sf_stride_row / sf_stride_col
+    int64_t sf_stride_row, sf_stride_col;
+    int sf_cols;
+    float* sf_dst;                    // [expert rows, sf_cols] contiguous
+    const float* w_src;               // optional weights [rows, K], row pitch w_pitch elements
+    int64_t w_pitch;
+    float* w_dst;                     // [expert rows]
+};
+struct LocalReduceArgs {
+    const int32_t* pos;               // [rows, K]
+    int num_rows, num_topk;
+    const void* src;                  // [expert rows, cols] bf16 contiguous
+    int cols;                         // multiple of 8
+    const float* w;                   // optional weight of every expert row [expert rows]; null: plain sum
+    void* dst;                        // [rows, cols] bf16 contiguous; rows without an expert row get zeros
+};
+
 namespace ep {
+cudaError_t launch_local_expand_plan(const LocalExpandPlanArgs& args, cudaStream_t stream);
+cudaError_t launch_local_expand_copy(const LocalExpandCopyArgs& args, cudaStream_t stream);
+cudaError_t launch_local_reduce(const LocalReduceArgs& args, cudaStream_t stream);
 cudaError_t launch_expert_segments(const ExpertSegmentsArgs& args, cudaStream_t stream);
 cudaError_t launch_swiglu_quant(const SwigluQuantArgs& args, cudaStream_t stream);
 cudaError_t launch_moe_bwd(const MoeBwdArgs& args, cudaStream_t stream);

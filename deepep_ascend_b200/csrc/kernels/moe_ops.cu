@@ -314,6 +314,193 @@ __global__ void __launch_bounds__(kSegThreads) expert_segments_kernel(const Expe
         if ((row & 127) == 0 && a.tile_group != nullptr) a.tile_group[row >> 7] = in_segment ? lo : -1;
     }
 }
+
+// ------------------------------------------------------------------------------------------------ local expansion
+// PLAN, two launches that each read the ids once.  The (row, k) pairs are cut into one contiguous share per warp
+// (kPlanWarps warps per CTA).  COUNT: every warp counts its pairs per expert.  ASSIGN: a warp's first number for expert e
+// is the segment start plus the counts of all warps before it, and inside its share the warp numbers the pairs in
+// order (match_any groups the lanes of a step by expert), so the rows of an expert segment are ordered by received
+// row: the same result on every run.
+constexpr int kPlanWarps = 8;
+__device__ __forceinline__ int plan_id(const LocalExpandPlanArgs& a, int i, int total) {   // rows * K < 2^31
+    if (i >= total) return -1;
+    const int row = i / a.num_topk;
+    const int64_t at = static_cast<int64_t>(row) * a.idx_pitch + (i - row * a.num_topk);
+    const long long id = a.idx_is_64 ? __ldg(reinterpret_cast<const long long*>(a.recv_idx) + at)
+                                     : static_cast<long long>(__ldg(reinterpret_cast<const int*>(a.recv_idx) + at));
+    return id >= 0 && id < a.num_local_experts ? static_cast<int>(id) : -1;
+}
+// share of warp `w` of the grid: multiples of 32 pairs
+__device__ __forceinline__ void plan_share(const LocalExpandPlanArgs& a, int w, int num_warps, int& lo, int& hi) {
+    const int total = a.num_rows * a.num_topk;
+    const int share = ((total + num_warps * 32 - 1) / (num_warps * 32)) * 32;
+    lo = min(w * share, total);
+    hi = min(lo + share, total);
+}
+__global__ void __launch_bounds__(kPlanWarps * 32) local_expand_count_kernel(const LocalExpandPlanArgs a) {
+    extern __shared__ int s_plan[];                    // [kPlanWarps][El]
+    const int El = a.num_local_experts, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int* mine = s_plan + warp * El;
+    for (int e = lane; e < El; e += 32) mine[e] = 0;
+    __syncwarp();
+    int lo, hi;
+    plan_share(a, blockIdx.x * kPlanWarps + warp, gridDim.x * kPlanWarps, lo, hi);
+    constexpr int kBatch = 4;
+    for (int first = lo; first < hi; first += 32 * kBatch) {
+        int id[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) id[j] = plan_id(a, first + j * 32 + lane, hi);
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j)
+            if (id[j] >= 0) atomicAdd(mine + id[j], 1);
+    }
+    __syncthreads();
+    // per-warp counts and, for the prefix over CTAs, their sum
+    int* out = a.warp_counts + static_cast<int64_t>(blockIdx.x * kPlanWarps + warp) * El;
+    for (int e = lane; e < El; e += 32) out[e] = mine[e];
+    for (int e = threadIdx.x; e < El; e += kPlanWarps * 32) {
+        int sum = 0;
+        for (int w = 0; w < kPlanWarps; ++w) sum += s_plan[w * El + e];
+        a.cta_counts[static_cast<int64_t>(blockIdx.x) * El + e] = sum;
+    }
+}
+__global__ void __launch_bounds__(kPlanWarps * 32) local_expand_assign_kernel(const LocalExpandPlanArgs a) {
+    extern __shared__ int s_plan[];                    // [kPlanWarps][El] next number of every expert for each warp
+    const int El = a.num_local_experts, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int me = blockIdx.x * kPlanWarps + warp, num_warps = gridDim.x * kPlanWarps;
+    int* next = s_plan + warp * El;
+    for (int e = lane; e < El; e += 32) {
+        int before = e == 0 ? 0 : __ldg(a.seg_end_aligned + e - 1), all = before;
+        for (int b = 0; b < static_cast<int>(gridDim.x); ++b) {
+            const int c = __ldg(a.cta_counts + static_cast<int64_t>(b) * El + e);
+            before += b < static_cast<int>(blockIdx.x) ? c : 0;
+            all += c;
+        }
+        for (int w = 0; w < warp; ++w) before += __ldg(a.warp_counts + static_cast<int64_t>(blockIdx.x * kPlanWarps + w) * El + e);
+        next[e] = before;
+        if (me == 0) a.seg_end[e] = all;
+    }
+    __syncwarp();
+    int lo, hi;
+    plan_share(a, me, num_warps, lo, hi);
+    constexpr int kBatch = 4;
+    for (int first = lo; first < hi; first += 32 * kBatch) {
+        int id[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) id[j] = plan_id(a, first + j * 32 + lane, hi);
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            // lanes with the same expert: the lowest takes the numbers for all of them
+            const uint32_t peers = __match_any_sync(0xffffffffu, id[j]);
+            if (id[j] >= 0) {
+                const int leader = __ffs(peers) - 1;
+                int base = 0;
+                if (lane == leader) {
+                    base = next[id[j]];
+                    next[id[j]] = base + __popc(peers);
+                }
+                base = __shfl_sync(peers, base, leader);
+                a.pos[first + j * 32 + lane] = base + __popc(peers & ptx::lanemask_lt());
+            }
+            __syncwarp();
+        }
+    }
+}
+
+// COPY: one warp per received row; every 512-byte piece is read once and written to each expert row of the row.
+constexpr int kExpandWarps = 8, kMaxExpandTopk = 32;
+__global__ void __launch_bounds__(kExpandWarps * 32) local_expand_copy_kernel(const LocalExpandCopyArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kExpandWarps + (threadIdx.x >> 5);
+    if (row >= a.num_rows) return;
+    const int my_pos = lane < a.num_topk ? __ldg(a.pos + static_cast<int64_t>(row) * a.num_topk + lane) : -1;
+    uint32_t dests = __ballot_sync(0xffffffffu, my_pos >= 0);
+    if (dests == 0) return;
+    if (a.w_src != nullptr && my_pos >= 0) a.w_dst[my_pos] = __ldg(a.w_src + static_cast<int64_t>(row) * a.w_pitch + lane);
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(a.src) + static_cast<int64_t>(row) * a.src_pitch;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(a.dst);
+    const int pieces = a.row_bytes / 16;
+    for (int p0 = 0; p0 < pieces; p0 += 128) {
+        int4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int p = p0 + j * 32 + lane;
+            v[j] = p < pieces ? ptx::ld_nc_v4(src + p * 16) : make_int4(0, 0, 0, 0);
+        }
+        for (uint32_t m = dests; m != 0; m &= m - 1) {
+            const int64_t to = __shfl_sync(0xffffffffu, my_pos, __ffs(m) - 1);
+            uint8_t* out = dst + to * a.row_bytes;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int p = p0 + j * 32 + lane;
+                if (p < pieces) *reinterpret_cast<int4*>(out + p * 16) = v[j];
+            }
+        }
+    }
+    if (a.sf_src != nullptr) {
+        for (int c = lane; c < a.sf_cols; c += 32) {
+            const float f = __ldg(a.sf_src + static_cast<int64_t>(row) * a.sf_stride_row + c * a.sf_stride_col);
+            for (uint32_t m = dests; m != 0; m &= m - 1) {
+                const int64_t to = __shfl_sync(0xffffffffu, my_pos, __ffs(m) - 1);
+                a.sf_dst[to * a.sf_cols + c] = f;
+            }
+        }
+    }
+}
+
+// REDUCE: one warp per received row; fp32 sum of its expert rows (in top-k order), optionally weighted, rounded once to bf16.
+__global__ void __launch_bounds__(kExpandWarps * 32) local_reduce_kernel(const LocalReduceArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kExpandWarps + (threadIdx.x >> 5);
+    if (row >= a.num_rows) return;
+    const int my_pos = lane < a.num_topk ? __ldg(a.pos + static_cast<int64_t>(row) * a.num_topk + lane) : -1;
+    const float my_w = (a.w != nullptr && my_pos >= 0) ? __ldg(a.w + my_pos) : 1.f;
+    const uint32_t srcs = __ballot_sync(0xffffffffu, my_pos >= 0);
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(a.src);
+    uint8_t* out = reinterpret_cast<uint8_t*>(a.dst) + static_cast<int64_t>(row) * a.cols * 2;
+    const int pieces = a.cols / 8;            // 16-byte pieces of 8 bf16
+    constexpr int kPer = 4;                   // pieces per lane and step: the loads of a step are issued together
+    for (int p0 = 0; p0 < pieces; p0 += 32 * kPer) {
+        float acc[kPer][8];
+#pragma unroll
+        for (int j = 0; j < kPer; ++j)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+        for (uint32_t m = srcs; m != 0; m &= m - 1) {
+            const int k = __ffs(m) - 1;
+            const int64_t from = __shfl_sync(0xffffffffu, my_pos, k);
+            const float w = __shfl_sync(0xffffffffu, my_w, k);
+            const uint8_t* in = src + from * a.cols * 2;
+            int4 v[kPer];
+#pragma unroll
+            for (int j = 0; j < kPer; ++j) {
+                const int p = p0 + j * 32 + lane;
+                v[j] = p < pieces ? ptx::ld_nc_v4(in + p * 16) : make_int4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int j = 0; j < kPer; ++j) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(h[i]);
+                    acc[j][2 * i] = fmaf(w, f.x, acc[j][2 * i]);
+                    acc[j][2 * i + 1] = fmaf(w, f.y, acc[j][2 * i + 1]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+            const int p = p0 + j * 32 + lane;
+            if (p < pieces) {
+                int4 o;
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(acc[j][2 * i], acc[j][2 * i + 1]);
+                *reinterpret_cast<int4*>(out + p * 16) = o;
+            }
+        }
+    }
+}
 }  // namespace
 
 int moe_bwd_prep_col_blocks(int cols) { return (cols + kPrepCols - 1) / kPrepCols; }
@@ -325,6 +512,33 @@ cudaError_t launch_moe_bwd(const MoeBwdArgs& a, cudaStream_t stream) {
     else if (a.op == EP_MOE_BWD_SWIGLU) moe_bwd_swiglu_kernel<<<dim3(a.rows / kTile, a.cols / kTile), kTileThreads, 0, stream>>>(a);
     else if (a.op == EP_MOE_BWD_DEQUANT_T) moe_bwd_dequant_t_kernel<<<dim3(a.rows / kTile, a.cols / kTile), kTileThreads, 0, stream>>>(a);
     else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_local_expand_plan(const LocalExpandPlanArgs& a, cudaStream_t stream) {
+    if (a.num_local_experts < 1 || a.num_topk < 1 || a.num_topk > kMaxExpandTopk || a.num_rows < 0) return cudaErrorInvalidValue;
+    if (a.num_ctas < 1 || a.num_local_experts > 1024 || a.warp_counts == nullptr || a.cta_counts == nullptr) return cudaErrorInvalidValue;
+    const size_t smem = static_cast<size_t>(kPlanWarps) * a.num_local_experts * sizeof(int);
+    local_expand_count_kernel<<<a.num_ctas, kPlanWarps * 32, smem, stream>>>(a);
+    local_expand_assign_kernel<<<a.num_ctas, kPlanWarps * 32, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_local_expand_copy(const LocalExpandCopyArgs& a, cudaStream_t stream) {
+    if (a.num_rows == 0) return cudaSuccess;
+    if (a.num_topk < 1 || a.num_topk > kMaxExpandTopk || a.row_bytes % 16 != 0 || a.src_pitch % 16 != 0 ||
+        reinterpret_cast<uintptr_t>(a.src) % 16 != 0 || reinterpret_cast<uintptr_t>(a.dst) % 16 != 0)
+        return cudaErrorInvalidValue;
+    local_expand_copy_kernel<<<(a.num_rows + kExpandWarps - 1) / kExpandWarps, kExpandWarps * 32, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_local_reduce(const LocalReduceArgs& a, cudaStream_t stream) {
+    if (a.num_rows == 0) return cudaSuccess;
+    if (a.num_topk < 1 || a.num_topk > kMaxExpandTopk || a.cols % 8 != 0 || reinterpret_cast<uintptr_t>(a.src) % 16 != 0 ||
+        reinterpret_cast<uintptr_t>(a.dst) % 16 != 0)
+        return cudaErrorInvalidValue;
+    local_reduce_kernel<<<(a.num_rows + kExpandWarps - 1) / kExpandWarps, kExpandWarps * 32, 0, stream>>>(a);
     return cudaGetLastError();
 }
 

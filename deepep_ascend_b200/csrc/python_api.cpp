@@ -242,6 +242,102 @@ std::vector<at::Tensor> expert_segments(const at::Tensor& psum_ends, int64_t num
     return {tile_group, valid, seg_off};
 }
 
+// Numbers the (row, k) pairs of a non-expand dispatch inside their experts' 128-aligned segments
+// -> (pos int32 [rows, K] (-1: no local expert), seg_end int32 [El]: end of the token rows of every segment).
+std::vector<at::Tensor> local_expand_plan(const at::Tensor& recv_idx, const at::Tensor& seg_end_aligned) {
+    TORCH_CHECK(recv_idx.is_cuda() && recv_idx.dim() == 2 && recv_idx.stride(1) == 1 &&
+                    (recv_idx.scalar_type() == at::kLong || recv_idx.scalar_type() == at::kInt),
+                "recv_idx must be int64 / int32 [rows, K] with contiguous rows");
+    TORCH_CHECK(seg_end_aligned.is_cuda() && seg_end_aligned.is_contiguous() && seg_end_aligned.scalar_type() == at::kInt && seg_end_aligned.dim() == 1,
+                "seg_end_aligned must be a contiguous int32 vector");
+    const int64_t rows = recv_idx.size(0), K = recv_idx.size(1), El = seg_end_aligned.numel();
+    TORCH_CHECK(rows * K < (int64_t(1) << 31), "too many (row, k) pairs");
+    const auto i32 = seg_end_aligned.options();
+    at::Tensor pos = at::full({rows, K}, -1, i32);
+    at::Tensor seg_end = at::empty({El}, i32);
+    LocalExpandPlanArgs a{};
+    a.recv_idx = recv_idx.data_ptr();
+    a.idx_is_64 = recv_idx.scalar_type() == at::kLong;
+    a.idx_pitch = recv_idx.stride(0);
+    a.num_rows = static_cast<int>(rows);
+    a.num_topk = static_cast<int>(K);
+    a.num_local_experts = static_cast<int>(El);
+    a.seg_end_aligned = seg_end_aligned.data_ptr<int32_t>();
+    a.pos = pos.data_ptr<int32_t>();
+    a.seg_end = seg_end.data_ptr<int32_t>();
+    // one CTA per ~4096 pairs, at most one per SM: every warp sums the counts of all warps before it
+    a.num_ctas = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(148, (rows * K + 4095) / 4096)));
+    at::Tensor scratch = at::empty({a.num_ctas * 9, El}, i32);
+    a.warp_counts = scratch.data_ptr<int32_t>();
+    a.cta_counts = a.warp_counts + static_cast<int64_t>(a.num_ctas) * 8 * El;
+    cuda_check(ep::launch_local_expand_plan(a, at::cuda::getCurrentCUDAStream()), "local_expand_plan launch");
+    return {pos, seg_end};
+}
+
+// Copies every received row (and its scales / weights) to its expert rows -> (rows_out [num_out, width], sf_out or none, w_out or none).
+std::vector<at::Tensor> local_expand_copy(const at::Tensor& pos, const at::Tensor& x, int64_t num_out, const std::optional<at::Tensor>& sf,
+                                          const std::optional<at::Tensor>& w) {
+    TORCH_CHECK(pos.is_cuda() && pos.is_contiguous() && pos.scalar_type() == at::kInt && pos.dim() == 2, "pos must be contiguous int32 [rows, K]");
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && x.size(0) == pos.size(0), "x must be [rows, width] with contiguous rows");
+    const int64_t row_bytes = x.size(1) * x.element_size();
+    at::Tensor out = at::empty({num_out, x.size(1)}, x.options());
+    LocalExpandCopyArgs a{};
+    a.pos = pos.data_ptr<int32_t>();
+    a.num_rows = static_cast<int>(pos.size(0));
+    a.num_topk = static_cast<int>(pos.size(1));
+    a.src = x.data_ptr();
+    a.src_pitch = x.stride(0) * x.element_size();
+    a.row_bytes = static_cast<int>(row_bytes);
+    a.dst = out.data_ptr();
+    at::Tensor sf_out, w_out;
+    if (sf.has_value()) {
+        TORCH_CHECK(sf->is_cuda() && sf->dim() == 2 && sf->scalar_type() == at::kFloat && sf->size(0) == x.size(0), "sf must be fp32 [rows, groups]");
+        sf_out = at::empty({num_out, sf->size(1)}, sf->options());
+        a.sf_src = sf->data_ptr<float>();
+        a.sf_stride_row = sf->stride(0);
+        a.sf_stride_col = sf->stride(1);
+        a.sf_cols = static_cast<int>(sf->size(1));
+        a.sf_dst = sf_out.data_ptr<float>();
+    }
+    if (w.has_value()) {
+        TORCH_CHECK(w->is_cuda() && w->dim() == 2 && w->scalar_type() == at::kFloat && w->stride(1) == 1 && w->size(0) == x.size(0) &&
+                        w->size(1) == pos.size(1), "w must be fp32 [rows, K] with contiguous rows");
+        w_out = at::zeros({num_out}, w->options());
+        a.w_src = w->data_ptr<float>();
+        a.w_pitch = w->stride(0);
+        a.w_dst = w_out.data_ptr<float>();
+    }
+    cuda_check(ep::launch_local_expand_copy(a, at::cuda::getCurrentCUDAStream()), "local_expand_copy launch");
+    std::vector<at::Tensor> res{out};
+    if (sf.has_value()) res.push_back(sf_out);
+    if (w.has_value()) res.push_back(w_out);
+    return res;
+}
+
+// out[row] = sum_k (w[pos[row, k]] *) y[pos[row, k]] in fp32, rounded once to bf16; `out` may be given (e.g. a combine input region).
+at::Tensor local_reduce(const at::Tensor& pos, const at::Tensor& y, const std::optional<at::Tensor>& w, const std::optional<at::Tensor>& out) {
+    TORCH_CHECK(pos.is_cuda() && pos.is_contiguous() && pos.scalar_type() == at::kInt && pos.dim() == 2, "pos must be contiguous int32 [rows, K]");
+    TORCH_CHECK(y.is_cuda() && y.is_contiguous() && y.dim() == 2 && y.scalar_type() == at::kBFloat16 && y.size(1) % 8 == 0,
+                "y must be contiguous bf16 [expert rows, cols] with cols a multiple of 8");
+    at::Tensor res = out.has_value() ? *out : at::empty({pos.size(0), y.size(1)}, y.options());
+    TORCH_CHECK(res.is_cuda() && res.is_contiguous() && res.scalar_type() == at::kBFloat16 && res.size(0) == pos.size(0) && res.size(1) == y.size(1),
+                "out must be contiguous bf16 [rows, cols]");
+    LocalReduceArgs a{};
+    a.pos = pos.data_ptr<int32_t>();
+    a.num_rows = static_cast<int>(pos.size(0));
+    a.num_topk = static_cast<int>(pos.size(1));
+    a.src = y.data_ptr();
+    a.cols = static_cast<int>(y.size(1));
+    if (w.has_value()) {
+        TORCH_CHECK(w->is_cuda() && w->is_contiguous() && w->dim() == 1 && w->scalar_type() == at::kFloat && w->size(0) == y.size(0),
+                    "w must be contiguous fp32 [expert rows]");
+        a.w = w->data_ptr<float>();
+    }
+    a.dst = res.data_ptr();
+    cuda_check(ep::launch_local_reduce(a, at::cuda::getCurrentCUDAStream()), "local_reduce launch");
+    return res;
+}
+
 // Weight gradients of a grouped layer: out[e] = a_t[:, k0:k1] @ b_t[:, k0:k1]^T with (k0, k1) = k_off[e], k_off[e + 1]
 // (a_t [M, K_total], b_t [N, K_total] bf16, K = rows of the expert segment; k_off int32 [G + 1], multiples of 64).
 at::Tensor gemm_kgrouped(const at::Tensor& a_t, const at::Tensor& b_t, const at::Tensor& k_off, int64_t num_sms) {
@@ -576,6 +672,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("a_ready_value") = 0, py::arg("a_flag_of_tile") = py::none(), py::arg("report_to") = nullptr);
     m.def("ag_gemm", &ag_gemm);
     m.def("gemm_rs", &gemm_rs);
+    m.def("local_expand_plan", &local_expand_plan, py::arg("recv_idx"), py::arg("seg_end_aligned"));
+    m.def("local_expand_copy", &local_expand_copy, py::arg("pos"), py::arg("x"), py::arg("num_out"), py::arg("sf") = py::none(),
+          py::arg("w") = py::none());
+    m.def("local_reduce", &local_reduce, py::arg("pos"), py::arg("y"), py::arg("w") = py::none(), py::arg("out") = py::none());
     m.def("expert_segments", &expert_segments, py::arg("psum_ends"), py::arg("num_rows"), py::arg("alignment") = 128);
     m.def("swiglu_quant", &swiglu_quant, py::arg("h"), py::arg("keep_bf16") = false);
     m.def("gemm_kgrouped", &gemm_kgrouped, py::arg("a_t"), py::arg("b_t"), py::arg("k_off"), py::arg("num_sms") = 0);

@@ -43,6 +43,8 @@ class _MoEFunction(torch.autograd.Function):
         slots = buf.regions.num_recv_slots
         start = buf.capture() if pipelined else None
         disp, g1_done, comb_done, saved, handles = {}, [], [], [], []
+        local = layer.local_expand
+        no_pos = torch.empty(0, dtype=torch.int32, device=x.device)
 
         def issue_dispatch(c):
             lo, hi = bounds[c], bounds[c + 1]
@@ -51,18 +53,26 @@ class _MoEFunction(torch.autograd.Function):
                 # the receive slot of chunk c was last read by the first GEMM (and the copies for backward) of chunk c - slots
                 kw = dict(previous_event=g1_done[c - slots] if c >= slots else start, allocate_on_comm_stream=True,
                           async_with_compute_stream=True)
-            disp[c] = buf.dispatch(x[lo:hi], topk_idx[lo:hi], topk_weights[lo:hi], num_experts=E, do_expand=True,
+            disp[c] = buf.dispatch(x[lo:hi], topk_idx[lo:hi], topk_weights[lo:hi], num_experts=E, do_expand=not local,
                                    expert_alignment=G.BLOCK_M, fused_fp8_cast=True, num_sms=comm_sms, **kw)
 
         issue_dispatch(0)
         for c in range(C):
             lo, hi = bounds[c], bounds[c + 1]
-            (rx, rsf), _, recv_w, handle, ev = disp.pop(c)
+            (rx, rsf), recv_idx, recv_w, handle, ev = disp.pop(c)
             ev.current_stream_wait()
-            rows = handle.num_rows
-            tile_group, valid_row, seg_off = G.expert_segments(handle.psum_num_recv_tokens_per_expert, rows)
+            if local:
+                # One row per (token, rank) came over NVLink; every local expert the token selected gets its copy here, in the
+                # expert's 128-aligned segment (rows in received order).  The copies are private to this call.
+                rows = sum(handle.num_recv_tokens_per_expert_list)
+                pos, seg_end = G.local_expand_plan(recv_idx, handle.psum_num_recv_tokens_per_expert)
+                rx, rsf, recv_w = G.local_expand_copy(pos, rx, rows, sf=rsf, w=recv_w)
+                tile_group, valid_row, seg_off = G.expert_segments(seg_end, rows)
+            else:
+                rows, pos = handle.num_rows, no_pos
+                tile_group, valid_row, seg_off = G.expert_segments(handle.psum_num_recv_tokens_per_expert, rows)
             h = G.grouped_gemm_nt(rx, q13, tile_group, sfa=rsf, sfb=s13, num_sms=gemm_sms, buffer=buf)    # [rows, 2I]
-            if keep_copy:
+            if keep_copy and not local:
                 # the received rows live in a receive slot of the buffer that later dispatches will reuse
                 rx, rsf, recv_w = rx.clone(), rsf.clone(), recv_w.clone()
             if pipelined:
@@ -74,13 +84,18 @@ class _MoEFunction(torch.autograd.Function):
                 # the combine input region about to be written was read by the combine of chunk c - 2, which every rank
                 # has finished once this rank's combine of chunk c - 1 has completed
                 comb_done[c - 1].current_stream_wait()
-            y = buf.get_combine_buffer(handle)
-            G.grouped_gemm_nt(a2, q2, tile_group, out=y, sfa=sf2, sfb=s2, num_sms=gemm_sms, buffer=buf)    # [rows, H] in the combine region
+            if local:
+                # the weighted sum over a token's local experts happens here, so one row per (token, rank) travels home
+                y_exp = G.grouped_gemm_nt(a2, q2, tile_group, sfa=sf2, sfb=s2, num_sms=gemm_sms, buffer=buf)      # [rows, H]
+                y = G.local_reduce(pos, y_exp, w=recv_w, out=buf.get_combine_buffer(handle))
+            else:
+                y = buf.get_combine_buffer(handle)
+                G.grouped_gemm_nt(a2, q2, tile_group, out=y, sfa=sf2, sfb=s2, num_sms=gemm_sms, buffer=buf)    # [rows, H] in the combine region
             kw = dict(previous_event=buf.capture(), allocate_on_comm_stream=True, async_with_compute_stream=True) if pipelined else {}
-            _, _, cev = buf.combine(y, handle, weighted=True, num_sms=comm_sms, out=out[lo:hi], **kw)
+            _, _, cev = buf.combine(y, handle, weighted=not local, num_sms=comm_sms, out=out[lo:hi], **kw)
             comb_done.append(cev)
             handles.append(handle)
-            saved += [rx, rsf, recv_w, h, tile_group, valid_row, seg_off]
+            saved += [rx, rsf, recv_w, h, tile_group, valid_row, seg_off, pos]
         for cev in comb_done[-2:]:
             cev.current_stream_wait()
         ctx.layer, ctx.handles, ctx.bounds = layer, handles, bounds
@@ -95,34 +110,47 @@ class _MoEFunction(torch.autograd.Function):
         d_out = d_out.contiguous()
         dxs, dws, d_w2, d_w13 = [], [], None, None
         for c, handle in enumerate(ctx.handles):
-            rx, rsf, recv_w, h, tile_group, valid_row, seg_off = ctx.saved_tensors[7 * c:7 * c + 7]
+            rx, rsf, recv_w, h, tile_group, valid_row, seg_off, pos = ctx.saved_tensors[8 * c:8 * c + 8]
             rw = recv_w.contiguous()
+            local, rows = layer.local_expand, h.shape[0]
+
+            def send_home(d_rows_exp, d_w_rows):
+                """Backward of dispatch: the gradient rows (and the gradient of every routing weight) travel to the tokens' ranks."""
+                if not local:
+                    return buf.combine(d_rows_exp, handle, topk_weights=d_w_rows, num_sms=layer.num_sms)[:2]
+                d_recv = G.local_reduce(pos, d_rows_exp, out=buf.get_combine_buffer(handle))
+                d_w = torch.where(pos >= 0, d_w_rows[pos.clamp(min=0).long()], torch.zeros((), device=pos.device))
+                return buf.combine(d_recv, handle, topk_weights=d_w, num_sms=layer.num_sms)[:2]
             if layer.fp8_backward:
                 # Data gradients on the e4m3 tensor cores, as the forward GEMMs: the gradient rows are cast (1 x 128 scales)
                 # inside the dispatch kernel, the weights are the forward e4m3 weights transposed (128 x 128 blocks stay
                 # 128 x 128 blocks), and the SwiGLU gradient is cast once more before the up projection.
                 q2_t, s2_t, q13_t, s13_t = layer.fp8_transposed_weights()
                 (g_q, g_sf), _, _, _, _ = buf.dispatch(d_out[bounds[c]:bounds[c + 1]], handle=handle, fused_fp8_cast=True, num_sms=layer.num_sms)
+                if local:
+                    g_q, g_sf = G.local_expand_copy(pos, g_q, rows, sf=g_sf)
                 d_act_u = G.grouped_gemm_nt(g_q, q2_t, tile_group, sfa=g_sf, sfb=s2_t, buffer=buf)             # [rows, I]
                 dh, dh_t, act_t, d_w_rows = G.swiglu_bwd(d_act_u, h, valid_row, row_weight=rw)
                 dh_q, dh_sf = G.per_token_cast_to_fp8(dh)
-                d_recv = buf.get_combine_buffer(handle)
-                G.grouped_gemm_nt(dh_q, q13_t, tile_group, out=d_recv, sfa=dh_sf, sfb=s13_t, buffer=buf)
-                dx, d_topk_w, _ = buf.combine(d_recv, handle, topk_weights=d_w_rows, num_sms=layer.num_sms)
+                d_recv = None if local else buf.get_combine_buffer(handle)
+                d_recv = G.grouped_gemm_nt(dh_q, q13_t, tile_group, out=d_recv, sfa=dh_sf, sfb=s13_t, buffer=buf)
+                dx, d_topk_w = send_home(d_recv, d_w_rows)
                 # (g * w)^T for the weight gradient: the routing weight rides on the scales of the dequantisation
                 dy_t = G.dequant_transpose(g_q, g_sf * rw.unsqueeze(1), valid_row)
             else:
                 # backward of the weighted combine: every expert row receives its token's gradient g (cached dispatch)
                 g_rows, _, _, _, _ = buf.dispatch(d_out[bounds[c]:bounds[c + 1]], handle=handle, fused_fp8_cast=False, num_sms=layer.num_sms)
+                if local:
+                    g_rows = G.local_expand_copy(pos, g_rows, rows)[0]
                 # down projection on the UNWEIGHTED gradient: d loss / d weight of a row is <g W2, activation> (= <g, y>, so the
                 # expert outputs need not be kept), and the weight is applied inside the SwiGLU backward kernel.  Padding rows of
                 # g_rows hold stale data; every consumer masks them.
                 d_act_u = G.grouped_gemm_nt(g_rows, w2_t, tile_group, buffer=buf)                    # [rows, I]
                 dh, dh_t, act_t, d_w_rows = G.swiglu_bwd(d_act_u, h, valid_row, row_weight=rw)
                 # up projection: the gradient rows go into the combine region and travel home (backward of dispatch)
-                d_recv = buf.get_combine_buffer(handle)
-                G.grouped_gemm_nt(dh, w13_t, tile_group, out=d_recv, buffer=buf)
-                dx, d_topk_w, _ = buf.combine(d_recv, handle, topk_weights=d_w_rows, num_sms=layer.num_sms)
+                d_recv = None if local else buf.get_combine_buffer(handle)
+                d_recv = G.grouped_gemm_nt(dh, w13_t, tile_group, out=d_recv, buffer=buf)
+                dx, d_topk_w = send_home(d_recv, d_w_rows)
                 dy_t = G.weighted_transpose(g_rows, rw, valid_row)                                  # (g * w)^T [H, rows]
             # weight gradients: one K-grouped GEMM per weight tensor, reduction over the rows of every expert segment
             x_t = G.dequant_transpose(rx, rsf, valid_row)
@@ -148,7 +176,8 @@ class FusedMoE(nn.Module):
     """
 
     def __init__(self, buffer: ElasticBuffer, num_experts: int, hidden: int, intermediate: int, init_std: float = 0.02,
-                 num_sms: int = 0, device='cuda', copy_saved_rows: bool = True, num_chunks: int = 1, fp8_backward: bool = False):
+                 num_sms: int = 0, device='cuda', copy_saved_rows: bool = True, num_chunks: int = 1, fp8_backward: bool = False,
+                 local_expand: bool = True):
         super().__init__()
         assert num_experts % buffer.num_ranks == 0 and hidden % 128 == 0 and intermediate % 128 == 0
         assert buffer.enable_expand, 'construct the buffer with enable_expand=True, expert_alignment=128'
@@ -163,6 +192,10 @@ class FusedMoE(nn.Module):
         # True: the data-gradient GEMMs (and the dispatch of the output gradient) run in e4m3 with block scales like the forward
         # pass; the weight gradients stay in bf16.  False: the whole backward pass is bf16.
         self.fp8_backward = fp8_backward
+        # True: dispatch and combine move one row per (token, rank); the copies for the token's local experts and the weighted sum
+        # over them are made on the expert rank (``ops.gemm.local_expand_*`` / ``local_reduce``).  False: the buffer's expand layout
+        # moves one row per (token, expert) over NVLink.  With top-8 of 256 experts on 8 ranks that is 8 rows per token instead of 5.25.
+        self.local_expand = local_expand
         el = num_experts // buffer.num_ranks
         self.w13 = nn.Parameter((torch.randn(el, 2 * intermediate, hidden, device=device) * init_std).bfloat16())
         self.w2 = nn.Parameter((torch.randn(el, hidden, intermediate, device=device) * init_std).bfloat16())

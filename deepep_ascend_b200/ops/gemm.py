@@ -79,6 +79,29 @@ def expert_segments_ref(psum_expert_ends: torch.Tensor, num_rows: int, alignment
     return tile_group.contiguous(), valid_row, seg_off.contiguous()
 
 
+def local_expand_plan(recv_idx: torch.Tensor, psum_aligned: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """For the output of a NON-expand dispatch made with ``expert_alignment=128``: ``recv_idx [rows, K]`` (local expert ids,
+    -1 elsewhere) and ``EPHandle.psum_num_recv_tokens_per_expert`` (inclusive sums of the aligned counts) ->
+    (``pos int32 [rows, K]``: the row of pair (row, k) in the per-expert (expand) layout, -1 if none; ``seg_end int32 [El]``:
+    end of the token rows of every expert segment, the input of ``expert_segments``).  Rows of a segment are in received
+    order, the same on every run."""
+    pos, seg_end = _native.load().local_expand_plan(recv_idx, psum_aligned.contiguous())
+    return pos, seg_end
+
+
+def local_expand_copy(pos: torch.Tensor, x: torch.Tensor, num_out: int, sf: Optional[torch.Tensor] = None,
+                      w: Optional[torch.Tensor] = None):
+    """Writes every received row of ``x`` (and its scales ``sf [rows, G]`` / weights ``w [rows, K]``) to its expert rows ->
+    ``[x_out [num_out, width], sf_out, w_out [num_out]]`` (only those asked for).  Alignment rows of the output are not written."""
+    return _native.load().local_expand_copy(pos, x, num_out, sf, w)
+
+
+def local_reduce(pos: torch.Tensor, y: torch.Tensor, w: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[row] = sum_k w[pos[row, k]] * y[pos[row, k]]`` (``w``: one weight per expert row; plain sum without it) in fp32,
+    rounded once to bf16."""
+    return _native.load().local_reduce(pos, y, w, out)
+
+
 def per_token_cast_to_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 ``[rows, H]`` -> (e4m3 ``[rows, H]``, fp32 scales ``[rows, ceil(H / 128)]``), one kernel."""
     q, sf = _native.load().per_token_cast_to_fp8(x.contiguous())

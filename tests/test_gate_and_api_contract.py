@@ -54,7 +54,8 @@ BUFFER_METHODS = ['all_gather', 'barrier', 'capture', 'combine', 'destroy', 'dis
                   'low_latency_update_mask_buffer', 'low_latency_query_mask_buffer', 'low_latency_clean_mask_buffer',
                   'get_next_low_latency_combine_buffer', 'get_physical_domain_size', 'get_logical_domain_size']
 NATIVE_FUNCTIONS = ['ag_gemm', 'dequant_transpose', 'expert_segments', 'gemm_error', 'gemm_kgrouped', 'gemm_nt', 'gemm_rs', 'get_dispatch_layout',
-                    'get_elastic_buffer_alignment', 'get_platform', 'get_workspace_bytes', 'moe_bwd_prep', 'per_token_cast_to_fp8',
+                    'get_elastic_buffer_alignment', 'get_platform', 'get_workspace_bytes', 'local_expand_copy', 'local_expand_plan',
+                    'local_reduce', 'moe_bwd_prep', 'per_token_cast_to_fp8',
                     'swiglu_bwd', 'swiglu_quant', 'weighted_transpose']
 NATIVE_CLASSES = ['CombineCall', 'DispatchCall', 'ElasticBuffer', 'RecvSlot', 'LLCombineCall', 'LLDispatchCall', 'MoeShape', 'RegionLayout']
 

@@ -6,9 +6,10 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize('copy_rows,chunks', [(False, 1), (True, 1), (True, 2), (True, 4)])
+@pytest.mark.parametrize('copy_rows,chunks,local_expand', [(False, 1, True), (True, 1, True), (True, 2, True), (True, 4, True),
+                                                          (False, 1, False), (True, 1, False), (True, 2, False)])
 @pytest.mark.parametrize('T,H,I,E,K', [(200, 256, 128, 4, 2), (512, 1024, 512, 8, 4)])
-def test_fused_moe_forward_backward(T, H, I, E, K, copy_rows, chunks):
+def test_fused_moe_forward_backward(T, H, I, E, K, copy_rows, chunks, local_expand):
     from deepep_ascend_b200 import ElasticBuffer
     from deepep_ascend_b200.models.moe import FusedMoE, moe_reference
     from deepep_ascend_b200.utils.math import calc_diff
@@ -16,7 +17,7 @@ def test_fused_moe_forward_backward(T, H, I, E, K, copy_rows, chunks):
     buf = ElasticBuffer(None, num_max_tokens_per_rank=T, hidden=H, num_topk=K, enable_expand=True, num_experts=E,
                         expert_alignment=128)
     try:
-        layer = FusedMoE(buf, E, H, I, init_std=0.05, num_sms=16, copy_saved_rows=copy_rows, num_chunks=chunks)
+        layer = FusedMoE(buf, E, H, I, init_std=0.05, num_sms=16, copy_saved_rows=copy_rows, num_chunks=chunks, local_expand=local_expand)
         x = torch.randn(T, H, device='cuda').bfloat16().requires_grad_(True)
         scores = torch.softmax(torch.randn(T, E, device='cuda'), dim=-1)
         w, idx = scores.topk(K, dim=-1)
@@ -246,3 +247,57 @@ def test_swiglu_quant_kernel(rows, I):
     assert calc_diff(per_token_cast_back(q, sf), ref) < 1e-3
     q2, sf2 = G.swiglu_quant(h)
     assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8)) and torch.equal(sf2, sf)
+
+
+@pytest.mark.parametrize('rows,K,El,H,idx_dtype', [(37, 2, 4, 256, torch.int64), (900, 8, 32, 1024, torch.int64), (513, 4, 7, 7168, torch.int32)])
+def test_local_expand_and_reduce_kernels(rows, K, El, H, idx_dtype):
+    """The (token, rank) -> (token, expert) expansion on the expert rank and its inverse, against plain PyTorch: positions
+    ordered by received row inside 128-aligned expert segments, row / scale / weight copies, weighted and plain reductions."""
+    from deepep_ascend_b200.ops import gemm as G
+    g = torch.Generator().manual_seed(rows + K)
+    # every row picks up to K distinct local experts; the other lanes (experts of other ranks) are -1
+    idx = torch.full((rows, K), -1, dtype=torch.int64)
+    for r in range(rows):
+        n = int(torch.randint(0, min(K, El) + 1, (1,), generator=g))
+        lanes = torch.randperm(K, generator=g)[:n]
+        idx[r, lanes] = torch.randperm(El, generator=g)[:n]
+    counts = torch.stack([(idx == e).sum() for e in range(El)])
+    aligned = (counts + 127) // 128 * 128
+    psum = aligned.cumsum(0).to(torch.int32)
+    starts = psum - aligned.to(torch.int32)
+    total = int(psum[-1])
+    want_pos = torch.full((rows, K), -1, dtype=torch.int32)
+    for e in range(El):
+        rr, kk = torch.nonzero(idx == e, as_tuple=True)          # row-major order = received order
+        want_pos[rr, kk] = starts[e] + torch.arange(len(rr), dtype=torch.int32)
+    # the index tensor as dispatch returns it: rows with a pitch (a view into wider records)
+    wide = torch.full((rows, K + 3), 77, dtype=idx_dtype, device='cuda')
+    wide[:, :K] = idx.to(idx_dtype).cuda()
+    pos, seg_end = G.local_expand_plan(wide[:, :K], psum.cuda())
+    assert torch.equal(pos.cpu(), want_pos)
+    assert torch.equal(seg_end.cpu(), (starts + counts.to(torch.int32)))
+
+    x = torch.randn(rows, H, generator=g).bfloat16().cuda()
+    sf = torch.rand(rows, H // 128, generator=g).cuda()
+    w = torch.rand(rows, K, generator=g).cuda()
+    x_e, sf_e, w_e = G.local_expand_copy(pos, x, total, sf=sf, w=w)
+    valid = pos >= 0
+    src_row = torch.nonzero(valid, as_tuple=True)[0]
+    at = pos[valid].long()
+    assert torch.equal(x_e[at], x[src_row]) and torch.equal(sf_e[at], sf[src_row]) and torch.equal(w_e[at], w[valid])
+    q = x.view(torch.uint8)[:, :H].contiguous().view(torch.float8_e4m3fn)       # a one-byte element type takes the same path
+    assert torch.equal(G.local_expand_copy(pos, q, total)[0][at].view(torch.uint8), q[src_row].view(torch.uint8))
+
+    y = torch.zeros(total, H, dtype=torch.bfloat16, device='cuda')
+    y[at] = torch.randn(len(at), H, device='cuda').bfloat16()
+    for weights in (None, w_e):
+        got = G.local_reduce(pos, y, w=weights)
+        want = torch.zeros(rows, H, device='cuda')
+        for k in range(K):
+            m = valid[:, k]
+            rowsel = y[pos[m, k].long()].float()
+            want[m] += rowsel if weights is None else rowsel * weights[pos[m, k].long()].unsqueeze(1)
+        torch.testing.assert_close(got.float(), want.bfloat16().float(), rtol=1.6e-2, atol=1e-3)
+        assert bool((got[~valid.any(dim=1)] == 0).all())
+    out = torch.empty(rows, H, dtype=torch.bfloat16, device='cuda')
+    assert G.local_reduce(pos, y, w=w_e, out=out).data_ptr() == out.data_ptr()

@@ -335,8 +335,8 @@ def _worker_moe(rank: int, world: int, port: int):
             dist.all_gather(parts, p.data.contiguous(), group=group)
             return torch.cat(parts).float()
         w13_all, w2_all = gather(layer.w13), gather(layer.w2)
-        for chunks in (1, 3):
-            layer.num_chunks = chunks
+        for chunks, local_expand in ((1, True), (3, True), (1, False)):
+            layer.num_chunks, layer.local_expand = chunks, local_expand
             layer.zero_grad()
             x = torch.randn(T - 5 * rank, H, device='cuda').bfloat16().requires_grad_(True)
             wts, idx = torch.softmax(torch.randn(x.shape[0], E, device='cuda'), dim=-1).topk(K, dim=-1)
@@ -359,7 +359,7 @@ def _worker_moe(rank: int, world: int, port: int):
             for name, got, want in (('out', out.float(), ref), ('dx', x.grad.float(), xr.grad), ('dw', wts.grad, wr.grad),
                                     ('d_w2', layer.w2.grad.float(), w2r.grad[sl]), ('d_w13', layer.w13.grad.float(), w13r.grad[sl])):
                 d = calc_diff(got, want)
-                assert d < 3e-3, (chunks, name, d)
+                assert d < 3e-3, (chunks, local_expand, name, d)
         buf.destroy()
     finally:
         dist.destroy_process_group()
