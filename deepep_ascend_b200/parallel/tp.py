@@ -41,12 +41,12 @@ class TensorParallelGemm:
         return self.buffer.core.view(self.off_full + self.buffer.rank_idx * rows * self.K * 2, [rows, self.K], [self.K, 1], torch.bfloat16)
 
     def _copiers(self, n_local: int) -> int:
-        """CTAs that pull the remote shards (the rest run the tensor cores): 4 per rank unless the caller says otherwise.
+        """CTAs that pull the remote shards (the rest run the tensor cores): 4 per rank and at least 16 unless the caller says otherwise.
         Measured at M 8192, K 7168: on 4 GPUs (N_local 1792, gather and GEMM take about as long) 16 copiers 0.253 ms, 32: 0.278 ms,
         48: 0.351 ms (NCCL all-gather + cuBLAS: 0.345 ms); on 8 GPUs (N_local 896, the gather of 103 MB is twice as long as the
         GEMM) 16 copiers 0.290 ms, 32: 0.243 ms, 48: 0.290 ms (NCCL + cuBLAS: 0.281 ms).  More copiers than that pull more slowly
         (the loads of all CTAs queue in front of the same links) and take SMs from the GEMM."""
-        n = self.num_copy_ctas if self.num_copy_ctas > 0 else 4 * self.R
+        n = self.num_copy_ctas if self.num_copy_ctas > 0 else max(16, 4 * self.R)
         return max(1, min(n, self.num_sms - 1))
 
     def ag_gemm(self, x_shard: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
