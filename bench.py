@@ -163,6 +163,9 @@ def main():
     buf = ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=True,
                         prefer_overlap_with_compute=False, num_gpu_timeout_secs=20, num_cpu_timeout_secs=60,
                         extra_bytes=ll_extra + (1 << 20))
+    # scale rows and tail records on 128-byte lines at the receiver: 1 % faster at EP8 (691 vs 686 GB/s on 64 SMs, 673 vs 667 on
+    # 24); recv_sf / recv_topk_idx / recv_topk_weights are then strided views
+    buf.set_dispatch_tuning(0, 0, line_aligned_side=True)
     buf.enable_kernel_timing(True)
 
     # synthetic routed tokens: x ~ N(0,1) bf16, top-8 of N(0,1) logits with softmax weights; pinned host copies
@@ -368,7 +371,8 @@ def main():
                        'tokens_per_rank': T, 'hidden': H, 'num_experts': E, 'num_topk': K, 'parallelism': f'ep{world}',
                        'num_sms_dispatch': args.num_sms, 'num_sms_combine': args.combine_sms or args.num_sms,
                        'l2': 'flushed (256 MB write) before every timed kernel',
-                       'timing': 'CUDA events on the launching (communication) stream right around each kernel, behind a cross-GPU barrier and a ~1 ms GPU spin (hides launch latency and rank skew), max over ranks per step, mean over steps',
+                       'dispatch_side_records': '128-byte aligned at the receiver (set_dispatch_tuning(line_aligned_side=True))',
+                       'timing': 'CUDA events on the launching (communication) stream right around each kernel, behind a ~1 ms GPU spin (hides launch latency) and a cross-GPU barrier (lines the ranks up), max over ranks per step, mean over steps',
                        'bytes': f'dispatch {disp_row_bytes} B per received row (e4m3 row + scales + ids + weights), combine {comb_row_bytes} B (bf16 row)',
                        'baseline': f'{ref_per_gpu:.1f} GB/s per GPU = published 726 (dispatch) / 740 (combine) GB/s at EP8, 64 SMs'},
             'dispatch_ms': t_disp, 'combine_ms': t_comb, 'dispatch_ms_median': t_disp_med, 'combine_ms_median': t_comb_med, 'dispatch_gbs_per_gpu': disp_gbs, 'combine_gbs_per_gpu': comb_gbs,

@@ -48,6 +48,18 @@ def _check_dispatch(outs, expect, fp8, do_expand):
 @pytest.mark.parametrize('mode', ['bf16', 'fp8_in', 'quant'])
 @pytest.mark.parametrize('do_expand', [False, True])
 def test_dispatch_combine(R, T, H, E, K, mode, do_expand):
+    _run_dispatch_combine(R, T, H, E, K, mode, do_expand)
+
+
+@pytest.mark.parametrize('R,T,H,E,K', [(4, 200, 1024, 32, 4), (8, 96, 7168, 256, 8), (8, 77, 2048, 64, 6)])
+@pytest.mark.parametrize('mode', ['bf16', 'fp8_in', 'quant'])
+def test_dispatch_combine_line_aligned_side_records(R, T, H, E, K, mode):
+    """The same checks with ``set_dispatch_tuning(line_aligned_side=True)``: scale rows and tail records sit on 128-byte lines
+    at the receiver, so ``recv_sf`` / ``recv_topk_idx`` / ``recv_topk_weights`` are strided views with the same contents."""
+    _run_dispatch_combine(R, T, H, E, K, mode, False, aligned=True)
+
+
+def _run_dispatch_combine(R, T, H, E, K, mode, do_expand, aligned=False):
     from deepep_ascend_b200.backends.emulated import EmulatedWorld
     from deepep_ascend_b200.utils import refs
     from deepep_ascend_b200.utils.math import per_token_cast_to_fp8
@@ -55,6 +67,9 @@ def test_dispatch_combine(R, T, H, E, K, mode, do_expand):
     world = EmulatedWorld(R, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=(mode != 'bf16'),
                           enable_expand=do_expand, num_experts=E, expert_alignment=A)
     try:
+        if aligned:
+            for b in world.buffers:
+                b.set_dispatch_tuning(0, 0, line_aligned_side=True)
         xs, idxs, ws = _make_inputs(R, T, H, E, K, seed=R + K)
         fp8 = mode != 'bf16'
         if fp8:
