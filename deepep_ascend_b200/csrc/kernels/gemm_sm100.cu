@@ -38,7 +38,10 @@ __host__ __device__ constexpr int num_stages(int block_n, bool fp8) { return blo
 __host__ __device__ constexpr int gemm_smem_bytes(int block_n, bool fp8) {
     return num_stages(block_n, fp8) * stage_bytes(block_n) + 1024 + (block_n == 128 && !fp8 ? kEpiStageBytes : 0);
 }
-constexpr int kCopyWarps = 5;
+constexpr int kMaxCopyWarps = 6;
+// copy warps of a copier CTA (all-gather fusion): each owns two 16 KB staging buffers in the shared memory that the tensor-core
+// CTAs use for their operand stages: 160 KB with 128-column tiles (five warps), at least 192 KB with wider tiles (all six warps)
+__host__ __device__ constexpr int copy_warps(int block_n) { return block_n == 128 ? 5 : 6; }
 constexpr int kGemmThreads = 192;        // bf16: TMA warp, MMA warp, 4 epilogue warps
 constexpr int kGemmThreadsFp8 = 320;     // e4m3, 128-column tiles: TMA warp, MMA warp, 8 epilogue warps
 constexpr int kGemmThreadsFp8Wide = 384; // e4m3, 256-column tiles: one producer warpgroup (TMA, MMA, two idle warps) that gives its
@@ -59,7 +62,7 @@ constexpr uint64_t kDefaultWaitLimitNs = 4ull * 1000 * 1000 * 1000;   // when th
 
 struct GemmSmem {
     uint64_t full[kMaxStages], empty[kMaxStages], tmem_full[kMaxAccBufs], tmem_empty[kMaxAccBufs];
-    uint64_t copy_bar[kCopyWarps][2];
+    uint64_t copy_bar[kMaxCopyWarps][2];
     uint32_t tmem_base;
     int failed;
 };
@@ -473,6 +476,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
         }
     }
+    constexpr int kCopyWarps = copy_warps(kBlockN);
+    static_assert(kFp8 || kCopyWarps * 2 * 16384 <= num_stages(kBlockN, false) * stage_bytes(kBlockN), "copy staging must fit in front of the barriers");
     if (!kFp8 && g.fuse == EP_GEMM_FUSE_ALL_GATHER && is_copier && warp < kCopyWarps) {
         // ------------------------------------------------------------------ all-gather fused into this kernel
         // Copier CTAs pull the remote shards of A, one 128-row tile at a time, from the owners' symmetric buffers
