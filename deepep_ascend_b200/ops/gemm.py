@@ -85,8 +85,31 @@ def local_expand_plan(recv_idx: torch.Tensor, psum_aligned: torch.Tensor) -> Tup
     (``pos int32 [rows, K]``: the row of pair (row, k) in the per-expert (expand) layout, -1 if none; ``seg_end int32 [El]``:
     end of the token rows of every expert segment, the input of ``expert_segments``).  Rows of a segment are in received
     order, the same on every run."""
+    if not recv_idx.is_cuda:
+        return local_expand_plan_ref(recv_idx, psum_aligned)
     pos, seg_end = _native.load().local_expand_plan(recv_idx, psum_aligned.contiguous())
     return pos, seg_end
+
+
+def local_expand_plan_ref(recv_idx: torch.Tensor, psum_aligned: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The same two tensors stated with plain PyTorch operations (any device; what the kernels are tested against)."""
+    El = psum_aligned.numel()
+    ends = psum_aligned.to(torch.int64)
+    idx = recv_idx.to(torch.int64)
+    valid = (idx >= 0) & (idx < El)
+    flat_e = torch.where(valid, idx, torch.full_like(idx, El)).reshape(-1)
+    # stable sort by expert keeps the received (row-major) order inside every expert
+    order = torch.sort(flat_e, stable=True).indices
+    counts = torch.bincount(flat_e, minlength=El + 1)[:El]
+    aligned = torch.cat([ends[:1], ends[1:] - ends[:-1]])
+    starts = ends - aligned
+    first = torch.cumsum(counts, 0) - counts                      # position of every expert's first pair in `order`
+    sorted_e = flat_e[order]
+    keep = sorted_e < El
+    rank_in_e = torch.arange(order.numel(), device=idx.device) - first[sorted_e.clamp(max=El - 1)]
+    pos = torch.full((idx.numel(),), -1, dtype=torch.int64, device=idx.device)
+    pos[order[keep]] = (starts[sorted_e[keep]] + rank_in_e[keep])
+    return pos.reshape(idx.shape).to(torch.int32), (starts + counts).to(torch.int32)
 
 
 def local_expand_copy(pos: torch.Tensor, x: torch.Tensor, num_out: int, sf: Optional[torch.Tensor] = None,

@@ -119,3 +119,33 @@ def test_expert_tile_groups_and_segment_offsets():
         assert off[-1].item() == s
         assert torch.equal(tile_group[:rows // 128], exp_group), (counts, tile_group, exp_group)
         assert torch.equal(valid, exp_valid)
+
+
+def test_local_expand_plan_statement():
+    """Numbering of the (row, k) pairs of a non-expand dispatch inside their experts' 128-aligned segments: the PyTorch
+    statement (which the kernels are checked against on a GPU) against brute-force loops."""
+    import torch
+    from deepep_ascend_b200.ops import gemm as G
+    g = torch.Generator().manual_seed(9)
+    for rows, K, El in ((1, 1, 1), (50, 2, 3), (333, 8, 16), (64, 4, 5)):
+        idx = torch.full((rows, K), -1, dtype=torch.int64)
+        for r in range(rows):
+            n = int(torch.randint(0, min(K, El) + 1, (1,), generator=g))
+            idx[r, torch.randperm(K, generator=g)[:n]] = torch.randperm(El, generator=g)[:n]
+        counts = [int((idx == e).sum()) for e in range(El)]
+        starts, psum, s0 = [], [], 0
+        for c in counts:
+            starts.append(s0)
+            s0 += (c + 127) // 128 * 128
+            psum.append(s0)
+        want = torch.full((rows, K), -1, dtype=torch.int32)
+        nxt = list(starts)
+        for r in range(rows):
+            for k in range(K):
+                e = int(idx[r, k])
+                if e >= 0:
+                    want[r, k] = nxt[e]
+                    nxt[e] += 1
+        pos, seg_end = G.local_expand_plan(idx, torch.tensor(psum, dtype=torch.int32))
+        assert torch.equal(pos, want)
+        assert seg_end.tolist() == [s + c for s, c in zip(starts, counts)]
