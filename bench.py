@@ -381,6 +381,14 @@ def main():
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': timed_launches,
         }
         line.update(extra)
+        if at_ref_size:
+            # ratios against the published EP8 rows: with the input quantised beforehand (the reference benchmark's input), and on
+            # the reference's "min #SM" count (published 643 / 675 GB/s)
+            if 'dispatch_gbs_prequantized_input' in extra:
+                line['dispatch_prequantized_vs_ref'] = extra['dispatch_gbs_prequantized_input'] / REF_DISPATCH_GBS
+            if args.min_sms == 24:
+                line['dispatch_24sms_vs_ref'] = extra['dispatch_gbs_24sms'] / 643.0
+                line['combine_24sms_vs_ref'] = extra['combine_gbs_24sms'] / 675.0
         if ll is not None:
             line.update(ll)
         if sweep:
