@@ -56,7 +56,39 @@ def build(verbose: bool = False):
             build_directory=_EXT_DIR, verbose=verbose, with_cuda=True)
         with open(os.path.join(_EXT_DIR, 'sources.sha256'), 'w') as fh:
             fh.write(_source_digest())
+        _capture_persistent_envs()
     return _module
+
+
+# Settings that must be the same when the package runs as when it was built: they are captured at build time and applied
+# at import unless the process sets them itself (the reference writes them into deep_ep/envs.py, setup.py:31,91-110, and
+# re-applies them in deep_ep/__init__.py:13-20).  EP_NUM_TOPK_IDX_BITS selects the dtype of ``topk_idx_t``.
+PERSISTENT_ENVS = ('EP_NUM_TOPK_IDX_BITS',)
+_PERSISTENT_FILE = 'persistent_envs.json'
+
+
+def _capture_persistent_envs() -> None:
+    import json
+    found = {k: os.environ[k] for k in PERSISTENT_ENVS if k in os.environ}
+    with open(os.path.join(_EXT_DIR, _PERSISTENT_FILE), 'w') as fh:
+        json.dump(found, fh)
+
+
+def apply_persistent_envs(directory: Optional[str] = None) -> dict:
+    """Set every captured variable that the process has not set itself; returns what was captured."""
+    import json
+    path = os.path.join(directory or _EXT_DIR, _PERSISTENT_FILE)
+    if not os.path.exists(path):
+        return {}
+    try:
+        with open(path) as fh:
+            found = json.load(fh)
+    except (OSError, ValueError):
+        return {}
+    for k, v in found.items():
+        if k in PERSISTENT_ENVS:
+            os.environ.setdefault(k, str(v))
+    return found
 
 
 def _source_digest() -> str:

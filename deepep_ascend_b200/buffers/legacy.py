@@ -90,6 +90,10 @@ class Buffer:
     def get_local_device_id(self) -> int:
         return torch.cuda.current_device()
 
+    def get_local_nvshmem_unique_id(self) -> bytes:
+        """There is no NVSHMEM in this build (one NVLink domain, peers mapped directly): an empty id."""
+        return b''
+
     def get_comm_stream(self):
         return self._elastic.get_comm_stream() if self._elastic is not None else torch.cuda.current_stream()
 
@@ -199,6 +203,20 @@ class Buffer:
     internode_combine = combine
 
     # ------------------------------------------------------------------------------------------ low-latency mode
+    # The reference's native Buffer has one entry point per transport (csrc/legacy/buffer.hpp intranode_* / internode_*); inside
+    # one NVLink domain they are the same kernels, so the four names lead to the two methods above.
+    def intranode_dispatch(self, *args, **kwargs):
+        return self.dispatch(*args, **kwargs)
+
+    def intranode_combine(self, *args, **kwargs):
+        return self.combine(*args, **kwargs)
+
+    def internode_dispatch(self, *args, **kwargs):
+        return self.dispatch(*args, **kwargs)
+
+    def internode_combine(self, *args, **kwargs):
+        return self.combine(*args, **kwargs)
+
     def _ll_buffer(self, tokens: int, hidden: int, num_topk: int) -> ElasticBuffer:
         if self._elastic is None:
             self._elastic = ElasticBuffer(self.group, num_max_tokens_per_rank=max(tokens, self._shape[0]), hidden=hidden,

@@ -89,3 +89,46 @@ def test_native_module_surface():
         assert isinstance(getattr(C, name, None), type), name
     assert C.MAX_RANKS == 8 and C.MAX_TOPK == 16 and C.MAX_EXPERTS == 1024
     assert C.get_workspace_bytes() == 4 << 20
+
+
+def test_native_surface_names_of_the_reference():
+    """Every name of the reference's native-module contract (tests/platform/api_contract.py:1-42) resolves on the ``_C``
+    facade, on the buffer classes and on the event handle; the JIT and NCCL-communicator hooks are inert."""
+    from deepep_ascend_b200 import _C
+    for name in ('get_platform', 'topk_idx_t', 'EventHandle', 'ElasticBuffer', 'calculate_elastic_buffer_size', 'is_sm90_compiled',
+                 'init_jit', 'Config', 'Buffer', 'get_low_latency_rdma_size_hint', 'create_cpu_handle', 'get_elastic_buffer_alignment',
+                 'get_local_nccl_unique_id', 'create_nccl_comm', 'destroy_nccl_comm', 'get_physical_domain_size',
+                 'get_logical_domain_size'):
+        assert getattr(_C, name, None) is not None, name
+    assert _C.is_sm90_compiled() is False and _C.init_jit('/nowhere', '/usr/local/cuda') is None
+    assert _C.destroy_nccl_comm(_C.create_nccl_comm(_C.get_local_nccl_unique_id(), 0, 1)) is None
+    assert isinstance(_C.create_cpu_handle(1 << 20), bytes)
+    for name in ('destroy', 'get_comm_stream', 'get_physical_domain_size', 'get_logical_domain_size', 'barrier', 'dispatch', 'combine',
+                 'engram_write', 'engram_fetch', 'pp_set_config', 'pp_send', 'pp_recv', 'create_agrs_session', 'destroy_agrs_session',
+                 'agrs_set_config', 'agrs_get_inplace_tensor', 'all_gather'):
+        import deepep_ascend_b200 as ep
+        assert callable(getattr(ep.ElasticBuffer, name, None)), name
+    for name in ('is_available', 'get_num_rdma_ranks', 'get_rdma_rank', 'get_root_rdma_rank', 'get_local_device_id', 'get_local_ipc_handle',
+                 'get_local_nvshmem_unique_id', 'get_local_buffer_tensor', 'get_comm_stream', 'sync', 'destroy', 'get_dispatch_layout',
+                 'intranode_dispatch', 'intranode_combine', 'internode_dispatch', 'internode_combine', 'clean_low_latency_buffer',
+                 'low_latency_dispatch', 'low_latency_combine', 'low_latency_update_mask_buffer', 'low_latency_query_mask_buffer',
+                 'low_latency_clean_mask_buffer', 'get_next_low_latency_combine_buffer'):
+        assert callable(getattr(_C.Buffer, name, None)), name
+    assert callable(_C.Config.get_nvl_buffer_size_hint) and callable(_C.Config.get_rdma_buffer_size_hint)
+    assert callable(_C.EventHandle.current_stream_wait)
+
+
+def test_persistent_envs_are_captured_and_applied(tmp_path, monkeypatch):
+    """Variables fixed at build time come back at import unless the process sets them itself."""
+    import json
+    import os
+    from deepep_ascend_b200 import _native
+    (tmp_path / 'persistent_envs.json').write_text(json.dumps({'EP_NUM_TOPK_IDX_BITS': '32', 'SOMETHING_ELSE': '1'}))
+    monkeypatch.delenv('EP_NUM_TOPK_IDX_BITS', raising=False)
+    monkeypatch.delenv('SOMETHING_ELSE', raising=False)
+    assert _native.apply_persistent_envs(str(tmp_path))['EP_NUM_TOPK_IDX_BITS'] == '32'
+    assert os.environ['EP_NUM_TOPK_IDX_BITS'] == '32' and 'SOMETHING_ELSE' not in os.environ      # only the listed names
+    monkeypatch.setenv('EP_NUM_TOPK_IDX_BITS', '64')
+    _native.apply_persistent_envs(str(tmp_path))
+    assert os.environ['EP_NUM_TOPK_IDX_BITS'] == '64'                                              # the process wins
+    assert _native.apply_persistent_envs(str(tmp_path / 'missing')) == {}
