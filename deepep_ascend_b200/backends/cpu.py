@@ -3,7 +3,7 @@ process group.  It computes the same deterministic layout as the CUDA kernels (`
 rows with ``all_to_all_single``, so handles, counts and results are interchangeable with the GPU path.
 Parity: the oracle of deep_ep/utils/refs.py:10-243 promoted to a backend.
 """
-from typing import List, Optional
+from typing import List
 
 import torch
 import torch.distributed as dist

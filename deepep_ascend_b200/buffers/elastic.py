@@ -17,7 +17,7 @@ The same class runs on CPU tensors with a gloo group (``backends/cpu.py``) with 
 import itertools
 import math
 import os
-from typing import List, Optional, Sequence, Tuple, Union
+from typing import List, Optional, Tuple, Union
 
 import torch
 import torch.distributed as dist

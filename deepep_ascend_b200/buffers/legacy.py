@@ -5,13 +5,12 @@ csrc/legacy/config.hpp:24-188) on top of the same runtime and kernels as ``Elast
 for the host-sync-free path) and the low-latency calls keep their signatures and return shapes.  There is no
 RDMA path: one NVSwitch box is one NVLink domain, so the "internode" arguments are accepted and ignored.
 """
-from typing import Callable, List, Optional, Tuple, Union
+from typing import Optional, Tuple, Union
 
 import torch
 import torch.distributed as dist
 
 from ..utils.event import EventHandle, EventOverlap
-from ..utils.math import align
 from .elastic import ElasticBuffer, EPHandle
 
 

@@ -7,7 +7,7 @@ synchronisation and of protocol state on the host, so they can be captured in a 
 ``return_recv_hook=True`` splits a call into a send launch and a receive launch so that no SM is held while the
 data is in flight.
 """
-from typing import Callable, Optional, Tuple
+from typing import Optional
 
 import torch
 

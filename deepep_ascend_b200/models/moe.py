@@ -10,8 +10,6 @@ and its backward pass, in which the gradients travel the same routes in reverse 
 cached dispatch, the backward of dispatch is a combine).  The reference library stops at dispatch / combine and
 leaves the layer to the caller (its README shows this data flow for DeepSeek-V3 style training, README.md:227-273).
 """
-from typing import Optional, Tuple
-
 import torch
 import torch.nn as nn
 

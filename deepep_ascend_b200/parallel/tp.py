@@ -8,7 +8,6 @@ GEMM and only a copy-engine all-gather).
 * ``gemm_rs``: ``reduce_scatter(x @ w^T)``.  The GEMM epilogue bulk-stores every row of the partial result straight
   into the owner rank's slot for this source; after a cross-GPU barrier the same kernel sums the R slots in fp32.
 """
-from typing import Optional
 
 import torch
 

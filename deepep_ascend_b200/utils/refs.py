@@ -6,7 +6,7 @@
   (``all_to_all_single``), used as the correctness reference and timing baseline of multi-process runs
   (parity: deep_ep/utils/refs.py:10-243).
 """
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence
 
 import torch
 import torch.distributed as dist
