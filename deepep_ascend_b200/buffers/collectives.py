@@ -36,6 +36,8 @@ class CollectivesMixin:
         and a wait on the local words, queued on the stream by the driver) instead of the 32-thread signal kernel, so
         that a whole all-gather uses no SM at all, as the reference does (csrc/kernels/backend/cuda_driver.cu:12-52).
         Unlike the kernel, such a wait has no time limit: a peer that never arrives stalls the stream.  Off by default."""
+        if self.is_cpu:
+            return self._cpu_coll.agrs_set_config(num_max_session_bytes, num_max_agrs_per_session, use_stream_memops)
         assert num_max_agrs_per_session <= 32
         assert self._agrs is None or not self._agrs['open'], 'destroy the open session first'
         self._agrs = {'offset': self.reserve(align(num_max_session_bytes, 1024)), 'bytes': num_max_session_bytes,
@@ -49,12 +51,16 @@ class CollectivesMixin:
         self.core.barrier(self._C.CH_AGRS)
 
     def create_agrs_session(self) -> None:
+        if self.is_cpu:
+            return self._cpu_coll.create_agrs_session()
         assert self._agrs is not None, 'call agrs_set_config first'
         assert not self._agrs['open'], 'one session at a time'
         self._agrs.update(open=True, cursor=0, count=0, inplace={})
 
     def destroy_agrs_session(self) -> None:
         """All ranks must be done reading the gathered tensors before the region is recycled."""
+        if self.is_cpu:
+            return self._cpu_coll.destroy_agrs_session()
         assert self._agrs is not None and self._agrs['open']
         self.comm_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.comm_stream):
@@ -77,6 +83,8 @@ class CollectivesMixin:
     def agrs_get_inplace_tensor(self, shape: Sequence[int], dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
         """This rank's slice inside the next gather slot: a producer that writes its result here saves the
         local copy of ``all_gather``."""
+        if self.is_cpu:
+            return self._cpu_coll.agrs_get_inplace_tensor(shape, dtype)
         off, nbytes = self._agrs_alloc(shape, dtype)
         t = self.core.view(off + self.rank_idx * nbytes, list(shape), list(_contiguous_strides(shape)), dtype)
         self._agrs['inplace'][t.data_ptr()] = (off, nbytes)
@@ -85,6 +93,8 @@ class CollectivesMixin:
     def all_gather(self, tensors: Union[torch.Tensor, Sequence[torch.Tensor]]) -> Tuple[Union[torch.Tensor, List[torch.Tensor]], Callable]:
         """Gather ``t`` (or each tensor of a list) from all ranks -> ``([num_ranks, *shape] view(s), wait)``.
         ``wait()`` makes the current stream wait for the gathered data."""
+        if self.is_cpu:
+            return self._cpu_coll.all_gather(tensors)
         single = isinstance(tensors, torch.Tensor)
         ts = [tensors] if single else list(tensors)
         self.comm_stream.wait_stream(torch.cuda.current_stream())
@@ -117,6 +127,8 @@ class CollectivesMixin:
         """``tensor [num_ranks, *shape]`` (bf16 or fp32): rank ``r`` receives ``sum over ranks of tensor[r]``
         accumulated in fp32 in rank order.  Slices travel on the copy engines; the sum is one local kernel.
         -> ``(out [*shape], wait)``."""
+        if self.is_cpu:
+            return self._cpu_coll.reduce_scatter(tensor)
         assert tensor.shape[0] == self.num_ranks and tensor.dtype in (torch.bfloat16, torch.float32)
         tensor = tensor.contiguous()
         shape = list(tensor.shape[1:])
@@ -147,6 +159,8 @@ class CollectivesMixin:
     # ------------------------------------------------------------------------------------------ pipeline parallel
     def pp_set_config(self, num_max_tensor_bytes: int, num_max_inflight_tensors: int) -> None:
         """Ring neighbours and the side stream for pipeline send / recv."""
+        if self.is_cpu:
+            return self._cpu_coll.pp_set_config(num_max_tensor_bytes, num_max_inflight_tensors)
         self._pp = {'prev': (self.rank_idx - 1) % self.num_ranks, 'next': (self.rank_idx + 1) % self.num_ranks,
                     'max_bytes': num_max_tensor_bytes, 'inflight': num_max_inflight_tensors,
                     'stream': torch.cuda.Stream(), 'pending': []}
@@ -160,6 +174,8 @@ class CollectivesMixin:
 
     def pp_send(self, t: torch.Tensor, dst_rank_idx: int) -> None:
         """Send ``t`` to a ring neighbour; ordered after the current stream's work, executed on the side stream."""
+        if self.is_cpu:
+            return self._cpu_coll.pp_send(t, dst_rank_idx)
         self._pp_check(t, dst_rank_idx)
         s = self._pp['stream']
         s.wait_stream(torch.cuda.current_stream())
@@ -169,6 +185,8 @@ class CollectivesMixin:
 
     def pp_recv(self, t: torch.Tensor, src_rank_idx: int) -> None:
         """Receive into ``t`` from a ring neighbour; the current stream waits for the data."""
+        if self.is_cpu:
+            return self._cpu_coll.pp_recv(t, src_rank_idx)
         self._pp_check(t, src_rank_idx)
         s = self._pp['stream']
         s.wait_stream(torch.cuda.current_stream())
@@ -202,6 +220,8 @@ class CollectivesMixin:
         the scale table of ALL ranks' entries (4-byte packs: fp32, or four UE8M0 bytes), replicated on every rank; it
         stays local and is gathered with every fetch (csrc/elastic/buffer.hpp:212-242 of the reference).  The table
         goes to the CPU segment when the buffer has one that is large enough, else into the device buffer."""
+        if self.is_cpu:
+            return self._cpu_coll.engram_write(storage, sf)
         storage = storage.contiguous()
         N, H = storage.shape
         e = self._engram_place(N, H, storage.dtype)
@@ -235,6 +255,8 @@ class CollectivesMixin:
         ``use_tma_aligned_col_major_sf`` (csrc/elastic/buffer.hpp:244-327).  ``num_qps`` must be 0."""
         if num_qps != 0:
             raise ValueError('num_qps must be 0: there are no RDMA queue pairs inside one NVLink domain')
+        if self.is_cpu:
+            return self._cpu_coll.engram_fetch(indices, use_tma_aligned_col_major_sf)
         e = self._engram
         assert e is not None, 'call engram_write first'
         idx = indices.contiguous().to(torch.int32)

@@ -186,6 +186,9 @@ class ElasticBuffer(LowLatencyMixin, CollectivesMixin):
         if self.is_cpu:
             from ..backends.cpu import CpuBackend
             self._cpu = CpuBackend(group, self.rank_idx, self.num_ranks)
+            from ..backends.cpu_collectives import CpuCollectives
+            self._cpu_coll = CpuCollectives(group, self.rank_idx, self.num_ranks)
+            self.low_latency_shrink = low_latency_shrink
             self.core = None
             self.regions = None
             return

@@ -103,8 +103,11 @@ class LowLatencyMixin:
         last two dims, ``recv_count [E_local]``; only the first ``recv_count[e]`` rows of expert ``e`` are valid.
         ``handle = (src_info, layout_range, max_tokens, hidden, num_experts)``.
         """
-        C = self._C
         M, E = num_max_dispatch_tokens_per_rank, num_experts
+        if self.is_cpu:
+            return self._cpu_coll.low_latency_dispatch(x, topk_idx, M, E, cumulative_local_expert_recv_stats, use_fp8, round_scale,
+                                                       use_ue8m0)
+        C = self._C
         num_sms = self._ll_num_sms(num_sms)
         stream = torch.cuda.current_stream() if return_recv_hook else self.comm_stream
         if not return_recv_hook:
@@ -163,6 +166,8 @@ class LowLatencyMixin:
         the sender and decoded inside the weighted reduction
         (csrc/kernels/legacy/internode_ll.cu:556-712 of the reference; ``utils.math.logfmt10_roundtrip`` states the code).
         """
+        if self.is_cpu:
+            return self._cpu_coll.low_latency_combine(x, topk_idx, topk_weights, handle, use_logfmt, out)
         C = self._C
         num_sms = self._ll_num_sms(num_sms)
         stream = torch.cuda.current_stream() if return_recv_hook else self.comm_stream
@@ -188,6 +193,8 @@ class LowLatencyMixin:
         written to.  The combine kernel reads its input rows in place wherever they live, so no copy is saved or added by
         using it; what it gives is ONE allocation with a stable address that is reused by every call (the two sets alternate
         like the kernels' own buffer sets), which is what a captured CUDA graph needs."""
+        if self.is_cpu:
+            return self._cpu_coll.get_next_low_latency_combine_buffer(handle)
         _, _, M, H, E = handle
         ll = self._ll
         assert ll is not None, 'a handle comes from low_latency_dispatch, which sets the low-latency regions up'
@@ -204,10 +211,18 @@ class LowLatencyMixin:
 
     def low_latency_update_mask_buffer(self, rank_to_mask: int, mask: bool = False) -> None:
         """Mark a rank as failed (``mask=True``) or healthy; masked ranks are skipped by both kernels."""
+        if self.is_cpu:
+            self._cpu_coll.mask()[rank_to_mask] = 1 if mask else 0
+            return
         assert self._ll is not None, 'run a low-latency call (or _ll_setup) first'
         self._ll['mask'][rank_to_mask] = 1 if mask else 0
 
     def low_latency_query_mask_buffer(self, mask_status: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.is_cpu:
+            if mask_status is None:
+                return self._cpu_coll.mask().clone()
+            mask_status.copy_(self._cpu_coll.mask())
+            return mask_status
         assert self._ll is not None
         if mask_status is None:
             return self._ll['mask'].clone()
@@ -215,6 +230,9 @@ class LowLatencyMixin:
         return mask_status
 
     def low_latency_clean_mask_buffer(self) -> None:
+        if self.is_cpu:
+            self._cpu_coll.mask().zero_()
+            return
         if self._ll is not None:
             self._ll['mask'].zero_()
 
