@@ -178,7 +178,8 @@ class FusedMoE(nn.Module):
                  local_expand: bool = True):
         super().__init__()
         assert num_experts % buffer.num_ranks == 0 and hidden % 128 == 0 and intermediate % 128 == 0
-        assert buffer.enable_expand, 'construct the buffer with enable_expand=True, expert_alignment=128'
+        assert buffer.enable_expand or local_expand, \
+            'without local_expand the layer uses the expand layout: construct the buffer with enable_expand=True, expert_alignment=128'
         self.buffer, self.num_experts, self.hidden, self.intermediate = buffer, num_experts, hidden, intermediate
         self.num_sms = num_sms
         # True (default): the dispatched rows kept for the backward pass are copied out of the receive slot, which later
