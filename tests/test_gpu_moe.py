@@ -301,3 +301,34 @@ def test_local_expand_and_reduce_kernels(rows, K, El, H, idx_dtype):
         assert bool((got[~valid.any(dim=1)] == 0).all())
     out = torch.empty(rows, H, dtype=torch.bfloat16, device='cuda')
     assert G.local_reduce(pos, y, w=w_e, out=out).data_ptr() == out.data_ptr()
+
+
+def test_fused_moe_on_a_buffer_without_expand_regions():
+    """With ``local_expand`` (the default) the layer only uses the (token, rank) layout of the buffer, so a buffer built without
+    ``enable_expand`` serves it; without ``local_expand`` the constructor asks for the expand-capable buffer."""
+    from deepep_ascend_b200 import ElasticBuffer
+    from deepep_ascend_b200.models.moe import FusedMoE, moe_reference
+    from deepep_ascend_b200.utils.math import calc_diff
+    T, H, I, E, K = 300, 512, 256, 8, 4
+    torch.manual_seed(21)
+    buf = ElasticBuffer(None, num_max_tokens_per_rank=T, hidden=H, num_topk=K)      # rows sized for the bf16 gradients of the backward pass
+    try:
+        with pytest.raises(AssertionError, match='enable_expand'):
+            FusedMoE(buf, E, H, I, local_expand=False)
+        layer = FusedMoE(buf, E, H, I, init_std=0.05, num_sms=16)
+        x = torch.randn(T, H, device='cuda').bfloat16().requires_grad_(True)
+        w, idx = torch.softmax(torch.randn(T, E, device='cuda'), dim=-1).topk(K, dim=-1)
+        w = w.clone().requires_grad_(True)
+        out = layer(x, idx, w)
+        g = torch.randn_like(out)
+        out.backward(g)
+        torch.cuda.synchronize()
+        buf.check_status()
+        xr, wr = x.detach().float().requires_grad_(True), w.detach().clone().requires_grad_(True)
+        w13, w2 = layer.w13.detach().float().requires_grad_(True), layer.w2.detach().float().requires_grad_(True)
+        ref = moe_reference(xr, idx, wr, w13, w2)
+        ref.backward(g.float())
+        assert calc_diff(out.float(), ref) < 3e-3 and calc_diff(x.grad.float(), xr.grad) < 3e-3
+        assert calc_diff(layer.w13.grad.float(), w13.grad) < 3e-3 and calc_diff(w.grad, wr.grad) < 3e-3
+    finally:
+        buf.destroy()
