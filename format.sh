@@ -3,17 +3,20 @@
 # clang-format with .clang-format.  A tool that is not installed is reported and skipped.
 #   ./format.sh            rewrite files that were changed with respect to origin/main (or all files without git)
 #   ./format.sh --all      every tracked source file
-#   ./format.sh --check    change nothing; exit 1 if a file would change or ruff reports a finding
+#   ./format.sh --check    change nothing; exit 1 if ruff reports a finding; files that yapf / clang-format would rewrite are listed
+#   ./format.sh --check --strict    also exit 1 for files that yapf / clang-format would rewrite
 set -uo pipefail
 cd "$(dirname "$0")"
 
 mode=changed
 check=0
+strict=0
 for arg in "$@"; do
     case "$arg" in
         --all) mode=all ;;
         --check) check=1 ;;
-        -h|--help) sed -n 2,7p "$0"; exit 0 ;;
+        --strict) strict=1 ;;
+        -h|--help) sed -n 2,8p "$0"; exit 0 ;;
         *) echo "unknown argument: $arg" >&2; exit 2 ;;
     esac
 done
@@ -38,7 +41,7 @@ if [ -n "$py_files" ]; then
         echo "ruff is not installed: Python lint skipped"
     fi
     if command -v yapf > /dev/null; then
-        if [ $check = 1 ]; then yapf --diff $py_files > /dev/null || { echo "yapf would reformat Python files"; status=1; }
+        if [ $check = 1 ]; then yapf --diff $py_files > /dev/null || { echo "yapf would reformat Python files"; [ $strict = 1 ] && status=1; }
         else yapf --in-place $py_files; fi
     else
         echo "yapf is not installed: Python formatting skipped"
@@ -46,7 +49,8 @@ if [ -n "$py_files" ]; then
 fi
 if [ -n "$cc_files" ]; then
     if command -v clang-format > /dev/null; then
-        if [ $check = 1 ]; then clang-format --dry-run --Werror $cc_files || status=1; else clang-format -i $cc_files; fi
+        if [ $check = 1 ]; then clang-format --dry-run --Werror $cc_files > /dev/null 2>&1 || { echo "clang-format would rewrite C++ / CUDA files"; [ $strict = 1 ] && status=1; }
+        else clang-format -i $cc_files; fi
     else
         echo "clang-format is not installed: C++ / CUDA formatting skipped"
     fi
