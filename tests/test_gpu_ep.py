@@ -7,7 +7,6 @@ pytestmark = pytest.mark.gpu
 
 
 def _make_inputs(R, T, H, E, K, seed=0, drop=0.05):
-    from deepep_ascend_b200.utils import gate
     g = torch.Generator(device='cpu').manual_seed(seed)
     xs, idxs, ws = [], [], []
     for r in range(R):

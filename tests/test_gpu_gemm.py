@@ -40,7 +40,7 @@ def _quant_b(b):
 
 @pytest.mark.parametrize('M,N,K,G', [(128, 128, 128, 1), (256, 256, 512, 1), (512, 384, 1024, 4), (1024, 2048, 7168, 8)])
 def test_fp8_blockscaled_grouped_gemm(M, N, K, G):
-    from deepep_ascend_b200.utils.math import per_token_cast_back, per_token_cast_to_fp8
+    from deepep_ascend_b200.utils.math import per_token_cast_back
     C = _C()
     g = torch.Generator(device='cuda').manual_seed(K + G)
     a = torch.randn(M, K, device='cuda', generator=g).bfloat16()

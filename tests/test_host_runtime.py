@@ -3,7 +3,6 @@ compiler and runs it: no GPU, no torch."""
 import os
 import shutil
 import subprocess
-import sys
 
 import pytest
 
