@@ -197,10 +197,6 @@ class Buffer:
         return self._elastic.combine(x, ep_handle, topk_weights=topk_weights, bias=bias, num_sms=num_sms, previous_event=prev,
                                      async_with_compute_stream=async_finish)
 
-    # the reference splits these by transport; one NVLink domain has a single path
-    internode_dispatch = dispatch
-    internode_combine = combine
-
     # ------------------------------------------------------------------------------------------ low-latency mode
     # The reference's native Buffer has one entry point per transport (csrc/legacy/buffer.hpp intranode_* / internode_*); inside
     # one NVLink domain they are the same kernels, so the four names lead to the two methods above.

@@ -163,3 +163,43 @@ def _worker_low_latency(rank, world, port, mode):
 @pytest.mark.parametrize('mode', ['bf16', 'fp8', 'ue8m0'])
 def test_gloo_low_latency_roundtrip(mode):
     mp.spawn(_worker_low_latency, args=(2, _free_port(), mode), nprocs=2, join=True)
+
+
+def _worker_legacy(rank, world, port):
+    ep, group = _setup(rank, world, port)
+    try:
+        T, H, E, K = 24, 128, 8, 2
+        g = torch.Generator().manual_seed(7 + rank)
+        x = torch.randn(T, H, generator=g).bfloat16()
+        w, idx = torch.softmax(torch.randn(T, E, generator=g), dim=-1).topk(K, dim=-1)
+        buf = ep.Buffer(group, num_nvl_bytes=1 << 20, num_rdma_bytes=0)
+        per_rank, per_rdma, per_expert, in_rank, _ = buf.get_dispatch_layout(idx, E)
+        assert per_rdma is None and per_rank.tolist() == [int(((idx // (E // world)) == r).any(dim=1).sum()) for r in range(world)]
+        recv_x, recv_idx, recv_w, per_expert_list, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_tokens_per_rank=per_rank,
+                                                                            is_token_in_rank=in_rank, num_tokens_per_expert=per_expert)
+        assert sum(per_expert_list) == int((recv_idx >= 0).sum()) and recv_x.shape[0] == recv_idx.shape[0]
+        # identity experts: every received row goes back once per rank, so a token comes home as (ranks it visited) * x
+        out, out_w, _ = buf.intranode_combine(recv_x, handle, topk_weights=recv_w)
+        visits = in_rank.sum(dim=1, keepdim=True).float()
+        torch.testing.assert_close(out.float(), (x.float() * visits).bfloat16().float(), atol=2e-2, rtol=2e-2)
+        assert torch.equal(out_w, w)
+        # the cached form takes the handle tuple
+        again = buf.dispatch(x, handle=handle)[0]
+        assert torch.equal(again, recv_x)
+        # low-latency pair through the same object
+        M = 32
+        recv, count, ll_handle, _, _ = buf.low_latency_dispatch(x, idx, M, E, use_fp8=False)
+        y = buf.get_next_low_latency_combine_buffer(ll_handle)
+        y.copy_(recv)
+        res, _, _ = buf.low_latency_combine(y, idx, w, ll_handle)
+        torch.testing.assert_close(res.float(), (x.float() * w.sum(dim=1, keepdim=True)).bfloat16().float(), atol=3e-2, rtol=3e-2)
+        assert buf.is_available() and buf.get_num_rdma_ranks() == 1 and buf.get_local_nvshmem_unique_id() == b''
+        buf.destroy()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gloo_legacy_buffer():
+    """The legacy ``Buffer`` surface on two gloo ranks: layout, dispatch / combine with the handle tuple, cached dispatch,
+    the transport-named aliases and the low-latency pair."""
+    mp.spawn(_worker_legacy, args=(2, _free_port()), nprocs=2, join=True)
